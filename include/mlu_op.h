@@ -1,0 +1,279 @@
+/*
+ * mlu_op.h -- C API of the B200 (sm_100a) build of the sparse-convolution
+ * forward path of mlu-ops.
+ *
+ * This header declares the subset of the reference's public header that the
+ * path needs, with identical names, argument lists, enum values and status
+ * conventions, so that code written against the reference recompiles
+ * unchanged.  The only type that differs is the queue: a cnrtQueue_t here is a
+ * cudaStream_t (see the stand-in header cnrt.h next to this file).
+ *
+ * Every declaration cites the reference declaration it replaces as
+ * mlu_op.h:<line> (the reference's single public header) and the reference
+ * implementation as <file>:<line> inside the reference tree.
+ *
+ * All pointers named *_desc and handle are host objects of this library.
+ * All data pointers (indices, features, filters, workspace, outputs) are
+ * device pointers, except indice_num[] of the two convolution functions,
+ * which is a host array (reference mlu_op.h:10357-10358).
+ */
+#ifndef MLUOP_B200_MLU_OP_H_
+#define MLUOP_B200_MLU_OP_H_
+
+#define MLUOP_MAJOR 1       /* reference mlu_op.h:30 */
+#define MLUOP_MINOR 11      /* reference mlu_op.h:31 */
+#define MLUOP_PATCHLEVEL 1  /* reference mlu_op.h:32 */
+#define MLUOP_VERSION (MLUOP_MAJOR * 1000 + MLUOP_MINOR * 100 + MLUOP_PATCHLEVEL)
+#define MLUOP_DIM_MAX 8     /* reference mlu_op.h:39 */
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "cn_api.h" /* stand-in: CNdev */
+#include "cnrt.h"   /* stand-in: cnrtQueue_t = cudaStream_t */
+
+#ifndef MLUOP_WIN_API
+#define MLUOP_WIN_API
+#endif
+
+#if defined(__cplusplus)
+extern "C" {
+#endif
+
+/* reference mlu_op.h:63-94 */
+typedef enum {
+  MLUOP_STATUS_SUCCESS = 0,
+  MLUOP_STATUS_NOT_INITIALIZED = 1,
+  MLUOP_STATUS_ALLOC_FAILED = 2,
+  MLUOP_STATUS_BAD_PARAM = 3,
+  MLUOP_STATUS_INTERNAL_ERROR = 4,
+  MLUOP_STATUS_ARCH_MISMATCH = 5,
+  MLUOP_STATUS_EXECUTION_FAILED = 6,
+  MLUOP_STATUS_NOT_SUPPORTED = 7,
+  MLUOP_STATUS_NUMERICAL_OVERFLOW = 8,
+} mluOpStatus_t;
+
+/* reference mlu_op.h:115-140 */
+typedef enum {
+  MLUOP_LAYOUT_NCHW = 0,
+  MLUOP_LAYOUT_NHWC = 1,
+  MLUOP_LAYOUT_HWCN = 2,
+  MLUOP_LAYOUT_NDHWC = 3,
+  MLUOP_LAYOUT_ARRAY = 4,
+  MLUOP_LAYOUT_NCDHW = 5,
+  MLUOP_LAYOUT_TNC = 6,
+  MLUOP_LAYOUT_NTC = 7,
+  MLUOP_LAYOUT_NC = 8,
+  MLUOP_LAYOUT_NLC = 9,
+  MLUOP_LAYOUT_NCL = 10,
+} mluOpTensorLayout_t;
+
+/* reference mlu_op.h:169-189 */
+typedef enum {
+  MLUOP_DTYPE_INVALID = 0,
+  MLUOP_DTYPE_HALF = 1,
+  MLUOP_DTYPE_FLOAT = 2,
+  MLUOP_DTYPE_DOUBLE = 14,
+  MLUOP_DTYPE_INT8 = 3,
+  MLUOP_DTYPE_INT16 = 4,
+  MLUOP_DTYPE_INT31 = 5,
+  MLUOP_DTYPE_INT32 = 6,
+  MLUOP_DTYPE_INT64 = 9,
+  MLUOP_DTYPE_UINT8 = 7,
+  MLUOP_DTYPE_UINT16 = 13,
+  MLUOP_DTYPE_UINT32 = 11,
+  MLUOP_DTYPE_UINT64 = 12,
+  MLUOP_DTYPE_BOOL = 8,
+  MLUOP_DTYPE_COMPLEX_HALF = 15,
+  MLUOP_DTYPE_COMPLEX_FLOAT = 16,
+  MLUOP_DTYPE_BFLOAT16 = 17,
+} mluOpDataType_t;
+
+/* reference mlu_op.h:214-220 */
+typedef enum {
+  MLUOP_ATOMICS_NOT_ALLOWED = 1,
+  MLUOP_ATOMICS_ALLOWED = 2,
+} mluOpAtomicsMode_t;
+
+/* reference mlu_op.h:404, :889, :1161 */
+typedef struct mluOpContext *mluOpHandle_t;
+typedef struct mluOpTensorStruct *mluOpTensorDescriptor_t;
+typedef struct mluOpSparseConvolutionStruct *mluOpSparseConvolutionDescriptor_t;
+
+/* ---------------------------------------------------------------- handle */
+
+/* reference mlu_op.h:456, core/context.cpp:158.  Binds the handle to the
+ * current CUDA device; the queue starts as the NULL (default) stream.
+ * MLUOP_STATUS_NOT_INITIALIZED when no CUDA device can be used. */
+mluOpStatus_t MLUOP_WIN_API mluOpCreate(mluOpHandle_t *handle);
+
+/* reference mlu_op.h:530, core/context.cpp:354 */
+mluOpStatus_t MLUOP_WIN_API mluOpDestroy(mluOpHandle_t handle);
+
+/* reference mlu_op.h:571, core/context.cpp:362.  queue may be NULL. */
+mluOpStatus_t MLUOP_WIN_API mluOpSetQueue(mluOpHandle_t handle, cnrtQueue_t queue);
+
+/* reference mlu_op.h:608, core/context.cpp:372 */
+mluOpStatus_t MLUOP_WIN_API mluOpGetQueue(mluOpHandle_t handle, cnrtQueue_t *queue);
+
+/* reference core/context.cpp:382 (mluOpGetDevice) */
+mluOpStatus_t MLUOP_WIN_API mluOpGetDevice(mluOpHandle_t handle, CNdev *device);
+
+/* reference mlu_op.h:646, core/type.cpp:53 */
+const char *MLUOP_WIN_API mluOpGetErrorString(mluOpStatus_t status);
+
+/* reference mlu_op.h:682, core/type.h:55 */
+mluOpStatus_t MLUOP_WIN_API mluOpGetSizeOfDataType(mluOpDataType_t data_type, size_t *size);
+
+/* reference mlu_op.h:722, core/context.cpp:462 */
+void MLUOP_WIN_API mluOpGetLibVersion(int *major, int *minor, int *patch);
+
+/* reference mlu_op.h:837 / :874, core/context.cpp.  The default mode,
+ * MLUOP_ATOMICS_NOT_ALLOWED, is the only one this path uses: every kernel on
+ * it is deterministic. */
+mluOpStatus_t MLUOP_WIN_API mluOpSetAtomicsMode(mluOpHandle_t handle, mluOpAtomicsMode_t atomics_mode);
+mluOpStatus_t MLUOP_WIN_API mluOpGetAtomicsMode(mluOpHandle_t handle, mluOpAtomicsMode_t *atomics_mode);
+
+/* ---------------------------------------------------- tensor descriptors */
+
+/* reference mlu_op.h:1233, core/tensor.cpp:560 */
+mluOpStatus_t MLUOP_WIN_API mluOpCreateTensorDescriptor(mluOpTensorDescriptor_t *desc);
+
+/* reference mlu_op.h:1406, core/tensor.cpp:602.  Contiguous strides are derived. */
+mluOpStatus_t MLUOP_WIN_API mluOpSetTensorDescriptor(mluOpTensorDescriptor_t desc,
+                                                     mluOpTensorLayout_t layout,
+                                                     mluOpDataType_t dtype, int dimNb,
+                                                     const int dimSize[]);
+
+/* reference mlu_op.h:1511, core/tensor.cpp:609 */
+mluOpStatus_t MLUOP_WIN_API mluOpSetTensorDescriptor_v2(mluOpTensorDescriptor_t desc,
+                                                        mluOpTensorLayout_t layout,
+                                                        mluOpDataType_t dtype, int dimNb,
+                                                        const int64_t dimSize[]);
+
+/* reference mlu_op.h:1815, core/tensor.cpp:680.  Explicit strides (elements). */
+mluOpStatus_t MLUOP_WIN_API mluOpSetTensorDescriptorEx(mluOpTensorDescriptor_t desc,
+                                                       mluOpTensorLayout_t layout,
+                                                       mluOpDataType_t dtype, int dimNb,
+                                                       const int dimSize[],
+                                                       const int dimStride[]);
+
+/* reference mlu_op.h:1874, core/tensor.cpp:688 */
+mluOpStatus_t MLUOP_WIN_API mluOpSetTensorDescriptorEx_v2(mluOpTensorDescriptor_t desc,
+                                                          mluOpTensorLayout_t layout,
+                                                          mluOpDataType_t dtype, int dimNb,
+                                                          const int64_t dimSize[],
+                                                          const int64_t dimStride[]);
+
+/* reference mlu_op.h:1761, core/tensor.cpp:675 */
+mluOpStatus_t MLUOP_WIN_API mluOpResetTensorDescriptor(mluOpTensorDescriptor_t desc);
+
+/* reference mlu_op.h:2173, core/tensor.cpp:751 */
+mluOpStatus_t MLUOP_WIN_API mluOpGetTensorDescriptor(const mluOpTensorDescriptor_t desc,
+                                                     mluOpTensorLayout_t *layout,
+                                                     mluOpDataType_t *dtype, int *dimNb,
+                                                     int dimSize[]);
+
+/* reference mlu_op.h:2221, core/tensor.cpp:758 */
+mluOpStatus_t MLUOP_WIN_API mluOpGetTensorDescriptor_v2(const mluOpTensorDescriptor_t desc,
+                                                        mluOpTensorLayout_t *layout,
+                                                        mluOpDataType_t *dtype, int *dimNb,
+                                                        int64_t dimSize[]);
+
+/* reference mlu_op.h:2274, core/tensor.cpp:736 */
+mluOpStatus_t MLUOP_WIN_API mluOpGetTensorDescriptorEx(const mluOpTensorDescriptor_t desc,
+                                                       mluOpTensorLayout_t *layout,
+                                                       mluOpDataType_t *dtype, int *dimNb,
+                                                       int dimSize[], int dimStride[]);
+
+/* reference mlu_op.h:2377, core/tensor.cpp:854 */
+uint64_t MLUOP_WIN_API mluOpGetTensorElementNum(const mluOpTensorDescriptor_t desc);
+
+/* reference mlu_op.h:2573, core/tensor.cpp:817 */
+mluOpStatus_t MLUOP_WIN_API mluOpDestroyTensorDescriptor(mluOpTensorDescriptor_t desc);
+
+/* ------------------------------------------- sparse-convolution descriptor */
+
+/* reference mlu_op.h:1272, get_indice_pairs_structs.cpp:31.
+ * NULL argument -> MLUOP_STATUS_NOT_INITIALIZED. */
+mluOpStatus_t MLUOP_WIN_API
+mluOpCreateSparseConvolutionDescriptor(mluOpSparseConvolutionDescriptor_t *desc);
+
+/* reference mlu_op.h:1311, get_indice_pairs_structs.cpp:125.
+ * NULL argument -> MLUOP_STATUS_EXECUTION_FAILED. */
+mluOpStatus_t MLUOP_WIN_API
+mluOpDestroySparseConvolutionDescriptor(mluOpSparseConvolutionDescriptor_t desc);
+
+/* reference mlu_op.h:1607, get_indice_pairs_structs.cpp:47.  dimNb must be 5,
+ * batch > 0, transpose == 0, inverse == 0, pad >= 0, everything else >= 1.
+ * The three-element arrays are in (D, H, W) order. */
+mluOpStatus_t MLUOP_WIN_API mluOpSetSparseConvolutionDescriptor(
+    mluOpSparseConvolutionDescriptor_t desc, int dimNb, int batch, const int pad[],
+    const int stride[], const int dilation[], const int input_space[],
+    const int filter_space[], const int output_space[], const int sub_m,
+    const int transpose, const int inverse);
+
+/* reference mlu_op.h:1654, get_indice_pairs_structs.cpp:111.  The value is
+ * written by mluOpGetIndicePairs: the number of active output voxels in
+ * default mode; in submanifold mode this library stores the number of input
+ * voxels (the reference leaves the field untouched in that mode). */
+mluOpStatus_t MLUOP_WIN_API
+mluOpGetSparseConvolutionNumActOut(mluOpSparseConvolutionDescriptor_t desc, int *num_act_out);
+
+/* ------------------------------------------------------------ the hot path */
+
+/* reference mlu_op.h:8674, get_indice_pairs.cpp:251.  Bytes of device scratch
+ * mluOpGetIndicePairs needs for these descriptors. */
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndicePairsWorkspaceSize(
+    mluOpHandle_t handle, mluOpSparseConvolutionDescriptor_t sparse_conv_desc,
+    const mluOpTensorDescriptor_t indices_desc,
+    const mluOpTensorDescriptor_t indice_pairs_desc,
+    const mluOpTensorDescriptor_t out_indices_desc,
+    const mluOpTensorDescriptor_t indice_num_desc, size_t *workspace_size);
+
+/* reference mlu_op.h:8598, get_indice_pairs.cpp:237 ->
+ * normal_get_indice_pairs.cpp:831.  Rulebook generation:
+ *   indices       [L,4]  int32 rows (b, z, y, x)
+ *   indice_pairs  [K,2,L] int32: row [k,0,:] input ids ascending, row [k,1,:]
+ *                 the matching output ids, -1 from position indice_num[k] on
+ *   out_indices   [rows,4] int32: coordinates of the active outputs in
+ *                 ascending linear order (default mode) or a copy of indices
+ *                 (sub_m); rows past the active count are set to -1
+ *   indice_num    [K] int32 (device)
+ * Work is enqueued on the handle's queue.  In default mode the call blocks
+ * once to read the number of active outputs into the descriptor. */
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndicePairs(
+    mluOpHandle_t handle, mluOpSparseConvolutionDescriptor_t sparse_conv_desc,
+    const mluOpTensorDescriptor_t indices_desc, const void *indices, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t indice_pairs_desc,
+    void *indice_pairs, const mluOpTensorDescriptor_t out_indices_desc, void *out_indices,
+    const mluOpTensorDescriptor_t indice_num_desc, void *indice_num);
+
+/* reference mlu_op.h:10322, indice_convolution_forward.cpp:581 */
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionForwardWorkspaceSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc,
+    const mluOpTensorDescriptor_t filters_desc,
+    const mluOpTensorDescriptor_t indice_pairs_desc,
+    const mluOpTensorDescriptor_t features_out_desc, const int64_t indice_num[],
+    const int64_t num_act_out, const int64_t inverse, const int64_t sub_m,
+    size_t *workspace_size);
+
+/* reference mlu_op.h:10434, indice_convolution_forward.cpp:621.
+ *   features_out[r,:] = sum_k sum_{(j,r) in pairs_k} features[j,:] * W_k
+ * features [L,Ci], filters 5-D (NDHWC [Co,kd,kh,kw,Ci], NCDHW [Co,Ci,kd,kh,kw]
+ * or ARRAY [kd,kh,kw,Ci,Co]), features_out [num_act_out,Co]; half or float,
+ * all three the same; accumulation is in float, kernel offset ascending.
+ * Output rows without a pair are zero.  Asynchronous on the handle's queue. */
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForward(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc,
+    const void *features, const mluOpTensorDescriptor_t filters_desc, const void *filters,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *indice_pairs,
+    const int64_t indice_num[], const int64_t num_act_out, const int64_t inverse,
+    const int64_t sub_m, void *workspace, const size_t workspace_size,
+    const mluOpTensorDescriptor_t features_out_desc, void *features_out);
+
+#if defined(__cplusplus)
+}
+#endif
+
+#endif /* MLUOP_B200_MLU_OP_H_ */

@@ -1,0 +1,297 @@
+"""Python harness over the C ABI of libmluops_b200.so.
+
+The product is the shared library (include/mlu_op.h); this package only loads
+it with ctypes and wraps the calls so that tests, the benchmark and the
+backbone driver can pass torch CUDA tensors.  Function and argument names
+follow the reference's C API.  There is no CPU fallback: if the library has not
+been built, loading raises.
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libmluops_b200.so")
+
+# mluOpStatus_t
+STATUS_SUCCESS = 0
+STATUS_NOT_INITIALIZED = 1
+STATUS_ALLOC_FAILED = 2
+STATUS_BAD_PARAM = 3
+STATUS_INTERNAL_ERROR = 4
+STATUS_ARCH_MISMATCH = 5
+STATUS_EXECUTION_FAILED = 6
+STATUS_NOT_SUPPORTED = 7
+STATUS_NUMERICAL_OVERFLOW = 8
+
+# mluOpTensorLayout_t
+LAYOUT_NCHW, LAYOUT_NHWC, LAYOUT_HWCN, LAYOUT_NDHWC, LAYOUT_ARRAY, LAYOUT_NCDHW = 0, 1, 2, 3, 4, 5
+# mluOpDataType_t
+DTYPE_INVALID, DTYPE_HALF, DTYPE_FLOAT, DTYPE_INT16, DTYPE_INT32, DTYPE_INT64 = 0, 1, 2, 4, 6, 9
+
+_vp = ctypes.c_void_p
+_int = ctypes.c_int
+_i64 = ctypes.c_int64
+_szt = ctypes.c_size_t
+_intp = ctypes.POINTER(ctypes.c_int)
+_i64p = ctypes.POINTER(ctypes.c_int64)
+
+# name -> (restype, argtypes); exactly the entry points include/mlu_op.h declares
+SIGNATURES = {
+    "mluOpCreate": (_int, [ctypes.POINTER(_vp)]),
+    "mluOpDestroy": (_int, [_vp]),
+    "mluOpSetQueue": (_int, [_vp, _vp]),
+    "mluOpGetQueue": (_int, [_vp, ctypes.POINTER(_vp)]),
+    "mluOpGetDevice": (_int, [_vp, _intp]),
+    "mluOpGetErrorString": (ctypes.c_char_p, [_int]),
+    "mluOpGetSizeOfDataType": (_int, [_int, ctypes.POINTER(_szt)]),
+    "mluOpGetLibVersion": (None, [_intp, _intp, _intp]),
+    "mluOpSetAtomicsMode": (_int, [_vp, _int]),
+    "mluOpGetAtomicsMode": (_int, [_vp, _intp]),
+    "mluOpCreateTensorDescriptor": (_int, [ctypes.POINTER(_vp)]),
+    "mluOpSetTensorDescriptor": (_int, [_vp, _int, _int, _int, _intp]),
+    "mluOpSetTensorDescriptor_v2": (_int, [_vp, _int, _int, _int, _i64p]),
+    "mluOpSetTensorDescriptorEx": (_int, [_vp, _int, _int, _int, _intp, _intp]),
+    "mluOpSetTensorDescriptorEx_v2": (_int, [_vp, _int, _int, _int, _i64p, _i64p]),
+    "mluOpResetTensorDescriptor": (_int, [_vp]),
+    "mluOpGetTensorDescriptor": (_int, [_vp, _intp, _intp, _intp, _intp]),
+    "mluOpGetTensorDescriptor_v2": (_int, [_vp, _intp, _intp, _intp, _i64p]),
+    "mluOpGetTensorDescriptorEx": (_int, [_vp, _intp, _intp, _intp, _intp, _intp]),
+    "mluOpGetTensorElementNum": (ctypes.c_uint64, [_vp]),
+    "mluOpDestroyTensorDescriptor": (_int, [_vp]),
+    "mluOpCreateSparseConvolutionDescriptor": (_int, [ctypes.POINTER(_vp)]),
+    "mluOpDestroySparseConvolutionDescriptor": (_int, [_vp]),
+    "mluOpSetSparseConvolutionDescriptor": (_int, [_vp, _int, _int, _intp, _intp, _intp, _intp, _intp, _intp,
+                                                  _int, _int, _int]),
+    "mluOpGetSparseConvolutionNumActOut": (_int, [_vp, _intp]),
+    "mluOpGetIndicePairsWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_szt)]),
+    "mluOpGetIndicePairs": (_int, [_vp, _vp, _vp, _vp, _vp, _szt, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mluOpGetIndiceConvolutionForwardWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64, _i64,
+                                                            ctypes.POINTER(_szt)]),
+    "mluOpIndiceConvolutionForward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64, _i64, _vp,
+                                            _szt, _vp, _vp]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded C-ABI library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise RuntimeError(
+                "libmluops_b200.so is missing (%s); build it with `python mlu-ops_b200/build.py`. "
+                "There is no fallback path." % LIB_PATH)
+        _lib = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(_lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+    return _lib
+
+
+class MluOpError(RuntimeError):
+    def __init__(self, call, status):
+        self.status = status
+        name = lib().mluOpGetErrorString(status).decode()
+        super().__init__("%s returned %s (%d)" % (call, name, status))
+
+
+def check(call, status):
+    if status != STATUS_SUCCESS:
+        raise MluOpError(call, status)
+
+
+def int_array(values):
+    return (ctypes.c_int * len(values))(*[int(v) for v in values])
+
+
+def i64_array(values):
+    return (ctypes.c_int64 * len(values))(*[int(v) for v in values])
+
+
+class Handle:
+    """mluOpHandle_t bound to a CUDA stream (raw cudaStream_t integer, 0 = default)."""
+
+    def __init__(self, stream=0):
+        self.ptr = _vp()
+        check("mluOpCreate", lib().mluOpCreate(ctypes.byref(self.ptr)))
+        self.set_queue(stream)
+
+    def set_queue(self, stream):
+        check("mluOpSetQueue", lib().mluOpSetQueue(self.ptr, _vp(stream)))
+
+    def destroy(self):
+        if self.ptr:
+            check("mluOpDestroy", lib().mluOpDestroy(self.ptr))
+            self.ptr = _vp()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class TensorDesc:
+    """mluOpTensorDescriptor_t with contiguous strides."""
+
+    def __init__(self, layout, dtype, dims):
+        self.ptr = _vp()
+        check("mluOpCreateTensorDescriptor", lib().mluOpCreateTensorDescriptor(ctypes.byref(self.ptr)))
+        check("mluOpSetTensorDescriptor_v2",
+              lib().mluOpSetTensorDescriptor_v2(self.ptr, layout, dtype, len(dims), i64_array(dims)))
+        self.dims = tuple(int(d) for d in dims)
+
+    def destroy(self):
+        if self.ptr:
+            lib().mluOpDestroyTensorDescriptor(self.ptr)
+            self.ptr = _vp()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class SparseConvDesc:
+    """mluOpSparseConvolutionDescriptor_t; the three-element lists are (D, H, W)."""
+
+    def __init__(self, batch, pad, stride, dilation, input_space, filter_space, output_space, sub_m):
+        self.ptr = _vp()
+        check("mluOpCreateSparseConvolutionDescriptor",
+              lib().mluOpCreateSparseConvolutionDescriptor(ctypes.byref(self.ptr)))
+        check("mluOpSetSparseConvolutionDescriptor",
+              lib().mluOpSetSparseConvolutionDescriptor(
+                  self.ptr, 5, int(batch), int_array(pad), int_array(stride), int_array(dilation),
+                  int_array(input_space), int_array(filter_space), int_array(output_space), int(bool(sub_m)),
+                  0, 0))
+        self.batch = int(batch)
+        self.pad, self.stride, self.dilation = list(pad), list(stride), list(dilation)
+        self.input_space, self.filter_space = list(input_space), list(filter_space)
+        self.output_space, self.sub_m = list(output_space), int(bool(sub_m))
+
+    @property
+    def kernel_volume(self):
+        return self.filter_space[0] * self.filter_space[1] * self.filter_space[2]
+
+    def num_act_out(self):
+        n = ctypes.c_int(0)
+        check("mluOpGetSparseConvolutionNumActOut",
+              lib().mluOpGetSparseConvolutionNumActOut(self.ptr, ctypes.byref(n)))
+        return n.value
+
+    def destroy(self):
+        if self.ptr:
+            lib().mluOpDestroySparseConvolutionDescriptor(self.ptr)
+            self.ptr = _vp()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+def output_space(input_space, pad, stride, dilation, filter_space):
+    """o = (i + 2p - d(k-1) - 1)/s + 1 per dim: the size callers pass as output_space."""
+    return [(i + 2 * p - d * (k - 1) - 1) // s + 1
+            for i, p, s, d, k in zip(input_space, pad, stride, dilation, filter_space)]
+
+
+def _ptr(t):
+    return _vp(t.data_ptr() if t is not None else 0)
+
+
+def get_indice_pairs_workspace_size(handle, conv, indices_desc, pairs_desc, out_indices_desc, num_desc):
+    size = _szt(0)
+    check("mluOpGetIndicePairsWorkspaceSize",
+          lib().mluOpGetIndicePairsWorkspaceSize(handle.ptr, conv.ptr, indices_desc.ptr, pairs_desc.ptr,
+                                                 out_indices_desc.ptr, num_desc.ptr, ctypes.byref(size)))
+    return size.value
+
+
+def get_indice_pairs(handle, conv, indices, out_rows=None, workspace=None):
+    """Rulebook of one layer through mluOpGetIndicePairs.
+
+    indices: int32 CUDA tensor [L,4].  Returns (indice_pairs [K,2,L], out_indices
+    [out_rows,4], indice_num [K] (device), num_act_out (host int)).
+    """
+    import torch
+    L = indices.shape[0]
+    K = conv.kernel_volume
+    if out_rows is None:
+        cells = conv.batch * conv.output_space[0] * conv.output_space[1] * conv.output_space[2]
+        out_rows = L if conv.sub_m else min(K * L, cells)
+    dev = indices.device
+    pairs = torch.empty((K, 2, L), dtype=torch.int32, device=dev)
+    out_indices = torch.empty((out_rows, 4), dtype=torch.int32, device=dev)
+    num = torch.empty((K,), dtype=torch.int32, device=dev)
+    d_in = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (L, 4))
+    d_pairs = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K, 2, L))
+    d_out = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (out_rows, 4))
+    d_num = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K,))
+    ws_size = get_indice_pairs_workspace_size(handle, conv, d_in, d_pairs, d_out, d_num)
+    if workspace is None or workspace.numel() < ws_size:
+        workspace = torch.empty((max(ws_size, 1),), dtype=torch.uint8, device=dev)
+    check("mluOpGetIndicePairs",
+          lib().mluOpGetIndicePairs(handle.ptr, conv.ptr, d_in.ptr, _ptr(indices), _ptr(workspace), ws_size,
+                                    d_pairs.ptr, _ptr(pairs), d_out.ptr, _ptr(out_indices), d_num.ptr,
+                                    _ptr(num)))
+    n_out = conv.num_act_out()
+    for d in (d_in, d_pairs, d_out, d_num):
+        d.destroy()
+    return pairs, out_indices, num, n_out
+
+
+FILTER_LAYOUTS = {"ARRAY": LAYOUT_ARRAY, "NDHWC": LAYOUT_NDHWC, "NCDHW": LAYOUT_NCDHW}
+
+
+def filter_dims(layout, filter_space, ci, co):
+    kd, kh, kw = filter_space
+    if layout == "ARRAY":
+        return (kd, kh, kw, ci, co)
+    if layout == "NDHWC":
+        return (co, kd, kh, kw, ci)
+    if layout == "NCDHW":
+        return (co, ci, kd, kh, kw)
+    raise ValueError(layout)
+
+
+def indice_convolution_forward(handle, features, filters, filter_layout, filter_space, indice_pairs,
+                               indice_num_host, num_act_out, sub_m, workspace=None, out=None):
+    """features_out [num_act_out, Co] through mluOpIndiceConvolutionForward.
+
+    features [L,Ci] and filters (5-D, in `filter_layout`) are CUDA tensors of the
+    same dtype (float16 or float32); indice_num_host is a sequence of K ints.
+    """
+    import torch
+    L, ci = features.shape
+    dims = tuple(filters.shape)
+    co = dims[4] if filter_layout == "ARRAY" else dims[0]
+    K = indice_pairs.shape[0]
+    dt = DTYPE_HALF if features.dtype == torch.float16 else DTYPE_FLOAT
+    dev = features.device
+    if out is None:
+        out = torch.empty((num_act_out, co), dtype=features.dtype, device=dev)
+    d_f = TensorDesc(LAYOUT_ARRAY, dt, (L, ci))
+    d_w = TensorDesc(FILTER_LAYOUTS[filter_layout], dt, dims)
+    d_p = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K, 2, L))
+    d_o = TensorDesc(LAYOUT_ARRAY, dt, (num_act_out, co))
+    num = i64_array(indice_num_host)
+    size = _szt(0)
+    check("mluOpGetIndiceConvolutionForwardWorkspaceSize",
+          lib().mluOpGetIndiceConvolutionForwardWorkspaceSize(handle.ptr, d_f.ptr, d_w.ptr, d_p.ptr, d_o.ptr,
+                                                              num, num_act_out, 0, int(bool(sub_m)),
+                                                              ctypes.byref(size)))
+    if workspace is None or workspace.numel() < size.value:
+        workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+    check("mluOpIndiceConvolutionForward",
+          lib().mluOpIndiceConvolutionForward(handle.ptr, d_f.ptr, _ptr(features), d_w.ptr, _ptr(filters),
+                                              d_p.ptr, _ptr(indice_pairs), num, num_act_out, 0,
+                                              int(bool(sub_m)), _ptr(workspace), size.value, d_o.ptr,
+                                              _ptr(out)))
+    for d in (d_f, d_w, d_p, d_o):
+        d.destroy()
+    return out

@@ -1,0 +1,212 @@
+// mluOpIndiceConvolutionForward / mluOpGetIndiceConvolutionForwardWorkspaceSize:
+// argument checks and dispatch (reference
+// kernels/sparse_conv/indice_convolution_forward/indice_convolution_forward.cpp:
+// foolProof :37-169, workspace query :581-619, compute entry :621-686).
+//
+// The order of the checks, and which status each one returns, follows the
+// reference.  One limit differs: the reference refuses more than 1,000,000
+// input rows (get_indice_pairs_structs.h:36); here the bound is only that
+// every tensor has fewer than 2^31 elements.
+#include <cuda_runtime_api.h>
+
+#include <string>
+
+#include "core/context.h"
+#include "core/logging.h"
+#include "core/tensor.h"
+#include "kernels/sparse_conv/indice_convolution_kernels.h"
+
+using mluop::sparse_conv::ConvProblem;
+using mluop::sparse_conv::ConvWorkspacePlan;
+
+namespace {
+
+struct FilterShape {
+  int64_t ci = 0, co = 0, num_filter = 0;
+  int layout = 0;
+};
+
+FilterShape readFilterShape(const mluOpTensorDescriptor_t filters_desc) {
+  FilterShape s;
+  if (filters_desc->getLayout() == MLUOP_LAYOUT_ARRAY) {
+    s.ci = filters_desc->getDimIndex(3);
+    s.co = filters_desc->getDimIndex(4);
+    s.num_filter = filters_desc->getDimIndex(0) * filters_desc->getDimIndex(1) * filters_desc->getDimIndex(2);
+    s.layout = mluop::sparse_conv::kFilterArray;
+  } else {
+    s.ci = mluOpGetTensordimC(filters_desc);
+    s.co = mluOpGetTensordimN(filters_desc);
+    s.num_filter =
+        mluOpGetTensordimD(filters_desc) * mluOpGetTensordimH(filters_desc) * mluOpGetTensordimW(filters_desc);
+    s.layout = filters_desc->getLayout() == MLUOP_LAYOUT_NDHWC ? mluop::sparse_conv::kFilterNDHWC
+                                                               : mluop::sparse_conv::kFilterNCDHW;
+  }
+  return s;
+}
+
+mluOpStatus_t foolProof(const std::string &api, mluOpHandle_t handle,
+                        const mluOpTensorDescriptor_t features_desc,
+                        const mluOpTensorDescriptor_t filters_desc,
+                        const mluOpTensorDescriptor_t indice_pairs_desc, const int64_t indice_num[],
+                        const int64_t num_act_out, const int64_t inverse, const int64_t sub_m,
+                        const mluOpTensorDescriptor_t features_out_desc) {
+  PARAM_CHECK(api, handle != nullptr);
+  PARAM_CHECK(api, features_desc != nullptr);
+  PARAM_CHECK(api, filters_desc != nullptr);
+  PARAM_CHECK(api, indice_pairs_desc != nullptr);
+  PARAM_CHECK(api, indice_num != nullptr);
+  PARAM_CHECK(api, features_out_desc != nullptr);
+
+  if (handle->arch < MLUOP_MLU370) {
+    LOG(ERROR) << api << " needs a compute-capability 10.x device; this handle's device is not one.";
+    return MLUOP_STATUS_ARCH_MISMATCH;
+  }
+
+  PARAM_CHECK(api, features_desc->getDtype() == MLUOP_DTYPE_FLOAT ||
+                       features_desc->getDtype() == MLUOP_DTYPE_HALF);
+  PARAM_CHECK(api, filters_desc->getDtype() == MLUOP_DTYPE_FLOAT ||
+                       filters_desc->getDtype() == MLUOP_DTYPE_HALF);
+  PARAM_CHECK(api, indice_pairs_desc->getDtype() == MLUOP_DTYPE_INT32);
+  PARAM_CHECK(api, features_out_desc->getDtype() == MLUOP_DTYPE_FLOAT ||
+                       features_out_desc->getDtype() == MLUOP_DTYPE_HALF);
+  PARAM_CHECK(api, features_desc->getDtype() == features_out_desc->getDtype() &&
+                       features_desc->getDtype() == filters_desc->getDtype());
+
+  PARAM_CHECK(api, sub_m == 0 || sub_m == 1);
+  PARAM_CHECK(api, inverse == 0 || inverse == 1);
+  if (inverse != 0) {
+    LOG(ERROR) << api << " inverse is: " << inverse << ", which is not supported now.";
+    return MLUOP_STATUS_NOT_SUPPORTED;
+  }
+
+  if (filters_desc->getLayout() != MLUOP_LAYOUT_NDHWC && filters_desc->getLayout() != MLUOP_LAYOUT_NCDHW &&
+      filters_desc->getLayout() != MLUOP_LAYOUT_ARRAY) {
+    LOG(ERROR) << api << " The layout of filters is: "
+               << mluop::getNameOfTensorLayout(filters_desc->getLayout()) << ", which is not supported now.";
+    return MLUOP_STATUS_NOT_SUPPORTED;
+  }
+
+  PARAM_CHECK(api, features_desc->getDim() == 2);
+  PARAM_CHECK(api, indice_pairs_desc->getDim() == 3);
+  PARAM_CHECK(api, features_out_desc->getDim() == 2);
+  if (filters_desc->getDim() != 5) {
+    LOG(ERROR) << api << " The filters dimension number only support 5 currently, but filters dimension "
+               << "number is :" << filters_desc->getDim() << ".";
+    return MLUOP_STATUS_NOT_SUPPORTED;
+  }
+
+  STRIDE_TENSOR_CHECK(api + ":", features_desc, "features_desc must be contiguous");
+  STRIDE_TENSOR_CHECK(api + ":", filters_desc, "filters_desc must be contiguous");
+  STRIDE_TENSOR_CHECK(api + ":", indice_pairs_desc, "indice_pairs_desc must be contiguous");
+  STRIDE_TENSOR_CHECK(api + ":", features_out_desc, "features_out_desc must be contiguous");
+
+  if (mluOpGetTensorElementNum(features_desc) >= LARGE_TENSOR_NUM ||
+      mluOpGetTensorElementNum(filters_desc) >= LARGE_TENSOR_NUM ||
+      mluOpGetTensorElementNum(indice_pairs_desc) >= LARGE_TENSOR_NUM ||
+      mluOpGetTensorElementNum(features_out_desc) >= LARGE_TENSOR_NUM) {
+    LOG(ERROR) << api << " Max tensor number overflow. Tensors must have fewer than 2^31 elements.";
+    return MLUOP_STATUS_NOT_SUPPORTED;
+  }
+
+  const FilterShape fs = readFilterShape(filters_desc);
+
+  PARAM_CHECK(api, features_desc->getDimIndex(0) == indice_pairs_desc->getDimIndex(2));
+  PARAM_CHECK(api, features_desc->getDimIndex(1) == fs.ci);
+  PARAM_CHECK(api, indice_pairs_desc->getDimIndex(0) == fs.num_filter);
+  PARAM_CHECK(api, indice_pairs_desc->getDimIndex(1) == 2);
+  PARAM_CHECK(api, features_out_desc->getDimIndex(0) == num_act_out);
+  PARAM_CHECK(api, features_out_desc->getDimIndex(1) == fs.co);
+
+  for (int64_t i = 0; i < fs.num_filter; ++i) {
+    const std::string where = "i: " + std::to_string(i) + ".";
+    PARAM_CHECK_V2(api, indice_num[i] >= 0 && indice_num[i] <= features_desc->getDimIndex(0), << where);
+  }
+  return MLUOP_STATUS_SUCCESS;
+}
+
+bool anyZeroElement(const mluOpTensorDescriptor_t a, const mluOpTensorDescriptor_t b,
+                    const mluOpTensorDescriptor_t c, const mluOpTensorDescriptor_t d) {
+  return mluOpGetTensorElementNum(a) == 0 || mluOpGetTensorElementNum(b) == 0 ||
+         mluOpGetTensorElementNum(c) == 0 || mluOpGetTensorElementNum(d) == 0;
+}
+
+ConvProblem makeProblem(const mluOpTensorDescriptor_t features_desc,
+                        const mluOpTensorDescriptor_t filters_desc, int64_t num_act_out) {
+  const FilterShape fs = readFilterShape(filters_desc);
+  ConvProblem p{};
+  p.L = features_desc->getDimIndex(0);
+  p.n_out = num_act_out;
+  p.K = (int32_t)fs.num_filter;
+  p.ci = (int32_t)fs.ci;
+  p.co = (int32_t)fs.co;
+  p.is_half = features_desc->getDtype() == MLUOP_DTYPE_HALF;
+  p.filter_layout = fs.layout;
+  return p;
+}
+
+}  // namespace
+
+extern "C" {
+
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionForwardWorkspaceSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc,
+    const mluOpTensorDescriptor_t filters_desc, const mluOpTensorDescriptor_t indice_pairs_desc,
+    const mluOpTensorDescriptor_t features_out_desc, const int64_t indice_num[], const int64_t num_act_out,
+    const int64_t inverse, const int64_t sub_m, size_t *size) {
+  const std::string api = "[mluOpGetIndiceConvolutionForwardWorkspaceSize]";
+  mluOpStatus_t st = foolProof(api, handle, features_desc, filters_desc, indice_pairs_desc, indice_num,
+                               num_act_out, inverse, sub_m, features_out_desc);
+  if (st != MLUOP_STATUS_SUCCESS) return st;
+  if (anyZeroElement(features_desc, indice_pairs_desc, filters_desc, features_out_desc)) {
+    VLOG(5) << api << " Skip zero element tensor.";
+    return MLUOP_STATUS_SUCCESS;
+  }
+  PARAM_CHECK(api, size != nullptr);
+  const ConvProblem p = makeProblem(features_desc, filters_desc, num_act_out);
+  *size = mluop::sparse_conv::planConvWorkspace(p).total;
+  return MLUOP_STATUS_SUCCESS;
+}
+
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForward(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc, const void *features,
+    const mluOpTensorDescriptor_t filters_desc, const void *filters,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *indice_pairs, const int64_t indice_num[],
+    const int64_t num_act_out, const int64_t inverse, const int64_t sub_m, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t features_out_desc, void *features_out) {
+  const std::string api = "[mluOpIndiceConvolutionForward]";
+  mluOpStatus_t st = foolProof(api, handle, features_desc, filters_desc, indice_pairs_desc, indice_num,
+                               num_act_out, inverse, sub_m, features_out_desc);
+  if (st != MLUOP_STATUS_SUCCESS) return st;
+  if (anyZeroElement(filters_desc, features_desc, indice_pairs_desc, features_out_desc)) {
+    VLOG(5) << api << " Skip zero element tensor.";
+    return MLUOP_STATUS_SUCCESS;
+  }
+  PARAM_CHECK(api, features != nullptr);
+  PARAM_CHECK(api, filters != nullptr);
+  PARAM_CHECK(api, indice_pairs != nullptr);
+  PARAM_CHECK(api, features_out != nullptr);
+  if (workspace_size > 0) {
+    PARAM_CHECK(api, workspace != nullptr);
+  }
+  const ConvProblem p = makeProblem(features_desc, filters_desc, num_act_out);
+  const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p);
+  if (workspace_size < plan.total || workspace == nullptr) {
+    LOG(ERROR) << api << " workspace of " << workspace_size << " bytes is smaller than the " << plan.total
+               << " bytes mluOpGetIndiceConvolutionForwardWorkspaceSize reports.";
+    return MLUOP_STATUS_BAD_PARAM;
+  }
+  if (handle->host_only) {
+    LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionForward(
+      p, plan, features, filters, static_cast<const int32_t *>(indice_pairs), indice_num, workspace,
+      features_out, handle->sm_count, handle->queue);
+  if (err != cudaSuccess) {
+    LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  return MLUOP_STATUS_SUCCESS;
+}
+
+}  // extern "C"

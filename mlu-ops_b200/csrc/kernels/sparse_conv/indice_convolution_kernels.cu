@@ -1,0 +1,462 @@
+// Sparse convolution forward kernels for sm_100a.
+//
+//   features_out[r,:] = sum_k sum_{(j,r) in pairs_k} features[j,:] * W_k
+//
+// (reference kernels/sparse_conv/indice_convolution_forward/
+// indice_convolution_forward.cpp:171-571: per kernel offset a gather, a matmul,
+// a scatter into a zeroed [N_out,Co] buffer and an add over the whole output.)
+//
+// Here the computation is output-stationary.  The pair lists are first turned
+// into a neighbour table nbr[k][r] = input row feeding output row r at offset
+// k (-1 if none; a rulebook holds at most one pair per (k, r)).  A thread block
+// then owns a tile of output rows, walks the kernel offsets in ascending
+// order, gathers the live input rows of the tile into shared memory, multiplies
+// by W_k and keeps the running sum in registers in fp32.  Every output row is
+// written exactly once, already summed, in a fixed order: the scatter of the
+// reference becomes a deterministic in-order reduction with no atomics and no
+// per-offset pass over the output.
+//
+// Kernels:
+//   repackFilterKernel      any layout -> T[K][Co][Ci]
+//   buildNeighbourKernel    pair lists -> nbr table
+//   convMmaF16Kernel        half, Ci and Co in {16,32,64,128}: cp.async row
+//                           gather into padded shared tiles, ldmatrix +
+//                           mma.sync m16n8k16 with fp32 accumulators, multi-stage
+//                           pipeline over the live offsets of the tile
+//   convGenericKernel       float, and half with other channel counts: fp32 FMA
+#include "kernels/sparse_conv/indice_convolution_kernels.h"
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+namespace mluop {
+namespace sparse_conv {
+
+namespace {
+
+inline size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+constexpr int kMaxCountsByValue = 128;
+struct PairCounts {
+  int32_t n[kMaxCountsByValue];
+};
+
+// ------------------------------------------------------------ preparation
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+repackFilterKernel(const T *__restrict__ src, T *__restrict__ dst, int K, int ci, int co, int layout) {
+  const int64_t total = (int64_t)K * ci * co;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % ci);
+    const int o = (int)((i / ci) % co);
+    const int k = (int)(i / ((int64_t)ci * co));
+    int64_t s;
+    if (layout == kFilterArray) {
+      s = ((int64_t)k * ci + c) * co + o;  // [K][Ci][Co]
+    } else if (layout == kFilterNDHWC) {
+      s = ((int64_t)o * K + k) * ci + c;  // [Co][K][Ci]
+    } else {
+      s = ((int64_t)o * ci + c) * K + k;  // [Co][Ci][K]
+    }
+    dst[i] = src[s];
+  }
+}
+
+template <bool BY_VALUE>
+__global__ void __launch_bounds__(256)
+buildNeighbourKernel(const int32_t *__restrict__ pairs, int64_t L, int64_t n_out, int64_t n_pad,
+                     PairCounts counts, const int32_t *__restrict__ counts_dev,
+                     int32_t *__restrict__ nbr) {
+  const int k = blockIdx.y;
+  const int64_t pk = BY_VALUE ? counts.n[k] : counts_dev[k];
+  const int32_t *in_row = pairs + (size_t)k * 2 * L;
+  const int32_t *out_row = in_row + L;
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < pk;
+       p += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t src = in_row[p], dst = out_row[p];
+    if (src >= 0 && src < L && dst >= 0 && dst < n_out) nbr[(size_t)k * n_pad + dst] = src;
+  }
+}
+
+// ------------------------------------------------------------ generic FMA
+
+__device__ __forceinline__ float toFloat(float v) { return v; }
+__device__ __forceinline__ float toFloat(__half v) { return __half2float(v); }
+__device__ __forceinline__ void fromFloat(float v, float *dst) { *dst = v; }
+__device__ __forceinline__ void fromFloat(float v, __half *dst) { *dst = __float2half_rn(v); }
+
+constexpr int kGenRows = 32;      // output rows per block
+constexpr int kGenLanes = 8;      // threads per row
+constexpr int kGenCols = 128;     // output channels per block (blockIdx.y walks the rest)
+constexpr int kGenCiChunk = 64;   // input channels staged per step
+
+// Thread (row, lane) owns output channels lane, lane+8, ... of its row.
+template <typename T>
+__global__ void __launch_bounds__(kGenRows *kGenLanes)
+convGenericKernel(const T *__restrict__ features, const T *__restrict__ filter_kcoci,
+                  const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, int ci, int co,
+                  T *__restrict__ out) {
+  __shared__ float w_s[kGenCiChunk][kGenCols + 1];
+  const int row_in_block = threadIdx.x / kGenLanes;
+  const int lane = threadIdx.x % kGenLanes;
+  const int64_t r = (int64_t)blockIdx.x * kGenRows + row_in_block;
+  const int col0 = blockIdx.y * kGenCols;
+  const int ncols = min(kGenCols, co - col0);
+  float acc[kGenCols / kGenLanes];
+#pragma unroll
+  for (int i = 0; i < kGenCols / kGenLanes; ++i) acc[i] = 0.f;
+
+  for (int k = 0; k < K; ++k) {
+    const int idx = (r < n_out) ? nbr[(size_t)k * n_pad + r] : -1;
+    if (!__syncthreads_or(idx >= 0)) continue;
+    const T *wk = filter_kcoci + ((size_t)k * co + col0) * ci;
+    for (int c0 = 0; c0 < ci; c0 += kGenCiChunk) {
+      const int nc = min(kGenCiChunk, ci - c0);
+      __syncthreads();
+      for (int e = threadIdx.x; e < nc * ncols; e += blockDim.x) {
+        const int c = e % nc, n = e / nc;
+        w_s[c][n] = toFloat(wk[(size_t)n * ci + c0 + c]);
+      }
+      __syncthreads();
+      if (idx >= 0) {
+        const T *f = features + (size_t)idx * ci + c0;
+        for (int c = 0; c < nc; ++c) {
+          const float a = toFloat(f[c]);
+#pragma unroll
+          for (int i = 0; i < kGenCols / kGenLanes; ++i) {
+            const int n = lane + i * kGenLanes;
+            if (n < ncols) acc[i] = fmaf(a, w_s[c][n], acc[i]);
+          }
+        }
+      }
+    }
+  }
+  if (r < n_out) {
+#pragma unroll
+    for (int i = 0; i < kGenCols / kGenLanes; ++i) {
+      const int n = lane + i * kGenLanes;
+      if (n < ncols) fromFloat(acc[i], out + (size_t)r * co + col0 + n);
+    }
+  }
+}
+
+// ------------------------------------------------------------ tensor cores
+
+constexpr int kMmaMaxOffsets = 32;  // kernel volumes up to 32 keep the tile's table in shared memory
+
+__device__ __forceinline__ void cpAsync16(void *smem, const void *gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0: nothing is read, 16 zero bytes are written
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cpAsyncWait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrixX4(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3,
+                                           const void *smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(s));
+}
+__device__ __forceinline__ void mmaF16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int CI, int CO, int STAGES>
+struct MmaConfig {
+  static constexpr int kThreads = 256;
+  static constexpr int kWarpsN = (CO >= 32) ? 2 : 1;
+  static constexpr int kWarpsM = 8 / kWarpsN;
+  static constexpr int kWarpRows = kConvTileRows / kWarpsM;  // 32 or 16
+  static constexpr int kMI = kWarpRows / 16;
+  static constexpr int kWarpCols = CO / kWarpsN;
+  static constexpr int kNI = kWarpCols / 8;
+  static constexpr int kRowHalfs = CI + 8;  // 16-byte pad: conflict-free ldmatrix
+  static constexpr int kAStage = kConvTileRows * kRowHalfs;
+  static constexpr int kBStage = CO * kRowHalfs;
+  static constexpr size_t kSmemBytes =
+      (size_t)STAGES * (kAStage + kBStage) * sizeof(__half) + (size_t)kMmaMaxOffsets * kConvTileRows * 4 +
+      kMmaMaxOffsets * 8;
+};
+
+template <int CI, int CO, int STAGES>
+__global__ void __launch_bounds__(256)
+convMmaF16Kernel(const __half *__restrict__ features, const __half *__restrict__ filter_kcoci,
+                 const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K,
+                 __half *__restrict__ out) {
+  using Cfg = MmaConfig<CI, CO, STAGES>;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __half *a_s = reinterpret_cast<__half *>(smem_raw);
+  __half *b_s = a_s + STAGES * Cfg::kAStage;
+  int32_t *nbr_s = reinterpret_cast<int32_t *>(b_s + STAGES * Cfg::kBStage);  // [K][128]
+  int32_t *klist_s = nbr_s + kMmaMaxOffsets * kConvTileRows;                 // live offsets
+  int32_t *kmask_s = klist_s + kMmaMaxOffsets;                               // 16-row group masks
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t r0 = (int64_t)blockIdx.x * kConvTileRows;
+
+  // Neighbour ids of the tile for every offset (the table is padded, so the
+  // whole tile can be read), then which 16-row groups are live per offset.
+  for (int e = tid; e < K * kConvTileRows; e += Cfg::kThreads) {
+    const int k = e / kConvTileRows, r = e % kConvTileRows;
+    nbr_s[e] = nbr[(size_t)k * n_pad + r0 + r];
+  }
+  __syncthreads();
+  for (int k = warp; k < K; k += 8) {
+    const int4 v = reinterpret_cast<const int4 *>(nbr_s + k * kConvTileRows)[lane];
+    const unsigned any = __ballot_sync(0xffffffffu, (v.x & v.y & v.z & v.w) >= 0);
+    if (lane == 0) {
+      unsigned groups = 0;
+      for (int g = 0; g < 8; ++g)
+        if ((any >> (4 * g)) & 0xFu) groups |= 1u << g;
+      kmask_s[k] = (int)groups;
+    }
+  }
+  __syncthreads();
+  __shared__ int n_live_s;
+  if (tid == 0) {
+    int n = 0;
+    for (int k = 0; k < K; ++k)
+      if (kmask_s[k]) klist_s[n++] = k;
+    n_live_s = n;
+  }
+  __syncthreads();
+  const int n_live = n_live_s;
+
+  auto load_stage = [&](int stage, int k) {
+    __half *a_dst = a_s + stage * Cfg::kAStage;
+    __half *b_dst = b_s + stage * Cfg::kBStage;
+    constexpr int kChunks = CI / 8;
+    const int32_t *ids = nbr_s + k * kConvTileRows;
+    for (int e = tid; e < kConvTileRows * kChunks; e += Cfg::kThreads) {
+      const int r = e / kChunks, c = e % kChunks;
+      const int idx = ids[r];
+      const __half *src = features + (idx >= 0 ? (size_t)idx * CI + c * 8 : 0);
+      cpAsync16(a_dst + r * Cfg::kRowHalfs + c * 8, src, idx >= 0);
+    }
+    const __half *wk = filter_kcoci + (size_t)k * CO * CI;
+    for (int e = tid; e < CO * kChunks; e += Cfg::kThreads) {
+      const int n = e / kChunks, c = e % kChunks;
+      cpAsync16(b_dst + n * Cfg::kRowHalfs + c * 8, wk + (size_t)n * CI + c * 8, true);
+    }
+  };
+
+  float acc[Cfg::kMI][Cfg::kNI][4];
+#pragma unroll
+  for (int mi = 0; mi < Cfg::kMI; ++mi)
+#pragma unroll
+    for (int ni = 0; ni < Cfg::kNI; ++ni)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[mi][ni][q] = 0.f;
+
+  const int warp_m = warp / Cfg::kWarpsN, warp_n = warp % Cfg::kWarpsN;
+  const int row_base = warp_m * Cfg::kWarpRows;
+  const int col_base = warp_n * Cfg::kWarpCols;
+
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < n_live) load_stage(s, klist_s[s]);
+    cpAsyncCommit();
+  }
+
+  for (int it = 0; it < n_live; ++it) {
+    cpAsyncWait<STAGES - 2>();
+    __syncthreads();
+    const int nxt = it + STAGES - 1;
+    if (nxt < n_live) load_stage(nxt % STAGES, klist_s[nxt]);
+    cpAsyncCommit();
+
+    const int k = klist_s[it];
+    const unsigned groups = (unsigned)kmask_s[k];
+    // 16-row groups of this warp: bits row_base/16 ... (+kMI)
+    const unsigned mine = (groups >> (row_base / 16)) & ((1u << Cfg::kMI) - 1u);
+    if (mine == 0) continue;
+    const __half *a_src = a_s + (it % STAGES) * Cfg::kAStage;
+    const __half *b_src = b_s + (it % STAGES) * Cfg::kBStage;
+#pragma unroll
+    for (int kk = 0; kk < CI / 16; ++kk) {
+      unsigned a[Cfg::kMI][4];
+#pragma unroll
+      for (int mi = 0; mi < Cfg::kMI; ++mi) {
+        if ((mine >> mi) & 1u) {
+          const int row = row_base + mi * 16 + (lane & 15);
+          const int col = kk * 16 + (lane >> 4) * 8;
+          ldmatrixX4(a[mi][0], a[mi][1], a[mi][2], a[mi][3], a_src + row * Cfg::kRowHalfs + col);
+        }
+      }
+#pragma unroll
+      for (int np = 0; np < Cfg::kNI / 2; ++np) {
+        unsigned b[4];
+        const int n = col_base + np * 16 + (lane >> 4) * 8 + (lane & 7);
+        const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+        ldmatrixX4(b[0], b[1], b[2], b[3], b_src + n * Cfg::kRowHalfs + col);
+#pragma unroll
+        for (int mi = 0; mi < Cfg::kMI; ++mi) {
+          if ((mine >> mi) & 1u) {
+            mmaF16(acc[mi][np * 2], a[mi], b[0], b[1]);
+            mmaF16(acc[mi][np * 2 + 1], a[mi], b[2], b[3]);
+          }
+        }
+      }
+    }
+  }
+  cpAsyncWait<0>();
+
+  // Fragment layout of m16n8: rows lane/4 and lane/4+8, columns 2*(lane%4)+{0,1}.
+#pragma unroll
+  for (int mi = 0; mi < Cfg::kMI; ++mi) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int64_t r = r0 + row_base + mi * 16 + (lane >> 2) + half * 8;
+      if (r >= n_out) continue;
+      __half *dst = out + (size_t)r * CO + col_base + (lane & 3) * 2;
+#pragma unroll
+      for (int ni = 0; ni < Cfg::kNI; ++ni) {
+        const __half2 v = __floats2half2_rn(acc[mi][ni][half * 2], acc[mi][ni][half * 2 + 1]);
+        *reinterpret_cast<__half2 *>(dst + ni * 8) = v;
+      }
+    }
+  }
+}
+
+template <int CI, int CO, int STAGES>
+cudaError_t launchMma(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
+                      const __half *filter, const int32_t *nbr, __half *out, cudaStream_t stream) {
+  using Cfg = MmaConfig<CI, CO, STAGES>;
+  auto kernel = convMmaF16Kernel<CI, CO, STAGES>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)Cfg::kSmemBytes);
+  if (err != cudaSuccess) return err;
+  const unsigned blocks = (unsigned)(plan.n_pad / kConvTileRows);
+  kernel<<<blocks, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K,
+                                                             out);
+  return cudaGetLastError();
+}
+
+template <int CI>
+cudaError_t dispatchMmaCo(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
+                          const __half *filter, const int32_t *nbr, __half *out, cudaStream_t stream) {
+  constexpr int kStages = (CI >= 128) ? 3 : 4;
+  switch (p.co) {
+    case 16: return launchMma<CI, 16, kStages>(p, plan, features, filter, nbr, out, stream);
+    case 32: return launchMma<CI, 32, kStages>(p, plan, features, filter, nbr, out, stream);
+    case 64: return launchMma<CI, 64, kStages>(p, plan, features, filter, nbr, out, stream);
+    case 128: return launchMma<CI, 128, kStages>(p, plan, features, filter, nbr, out, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+bool mmaEligible(const ConvProblem &p, const void *features, const void *out) {
+  auto pow2_16_128 = [](int c) { return c == 16 || c == 32 || c == 64 || c == 128; };
+  return p.is_half && p.K <= kMmaMaxOffsets && pow2_16_128(p.ci) && pow2_16_128(p.co) &&
+         (reinterpret_cast<size_t>(features) % 16 == 0) && (reinterpret_cast<size_t>(out) % 4 == 0);
+}
+
+}  // namespace
+
+ConvWorkspacePlan planConvWorkspace(const ConvProblem &p) {
+  ConvWorkspacePlan plan{};
+  const size_t elem = p.is_half ? 2 : 4;
+  plan.n_pad = (p.n_out + kConvTileRows - 1) / kConvTileRows * kConvTileRows;
+  size_t off = 0;
+  plan.filter = off;
+  off = alignUp(off + (size_t)p.K * p.ci * p.co * elem, 256);
+  plan.neighbour = off;
+  off = alignUp(off + (size_t)p.K * plan.n_pad * sizeof(int32_t), 256);
+  plan.counts = off;
+  off = alignUp(off + (size_t)p.K * sizeof(int32_t), 256);
+  plan.total = off + 256;
+  return plan;
+}
+
+cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorkspacePlan &plan,
+                                           const void *features, const void *filters,
+                                           const int32_t *indice_pairs, const int64_t *indice_num,
+                                           void *workspace, void *features_out, int sm_count,
+                                           cudaStream_t stream) {
+  char *base = reinterpret_cast<char *>(alignUp(reinterpret_cast<size_t>(workspace), 256));
+  void *filter_packed = base + plan.filter;
+  int32_t *nbr = reinterpret_cast<int32_t *>(base + plan.neighbour);
+  int32_t *counts_dev = reinterpret_cast<int32_t *>(base + plan.counts);
+  cudaError_t err;
+
+  // 1. filter -> [K][Co][Ci]
+  {
+    const int64_t total = (int64_t)p.K * p.ci * p.co;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+    if (p.is_half) {
+      repackFilterKernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half *>(filters),
+                                                             static_cast<__half *>(filter_packed), p.K,
+                                                             p.ci, p.co, p.filter_layout);
+    } else {
+      repackFilterKernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float *>(filters),
+                                                            static_cast<float *>(filter_packed), p.K,
+                                                            p.ci, p.co, p.filter_layout);
+    }
+  }
+
+  // 2. neighbour table
+  if ((err = cudaMemsetAsync(nbr, 0xFF, (size_t)p.K * plan.n_pad * sizeof(int32_t), stream)) != cudaSuccess)
+    return err;
+  int64_t max_pairs = 0;
+  for (int k = 0; k < p.K; ++k) max_pairs = indice_num[k] > max_pairs ? indice_num[k] : max_pairs;
+  if (max_pairs > 0) {
+    int64_t bx = (max_pairs + 255) / 256;
+    const int64_t cap = (int64_t)sm_count * 32;
+    if (bx > cap) bx = cap;
+    const dim3 grid((unsigned)bx, (unsigned)p.K);
+    if (p.K <= kMaxCountsByValue) {
+      PairCounts counts{};
+      for (int k = 0; k < p.K; ++k) counts.n[k] = (int32_t)indice_num[k];
+      buildNeighbourKernel<true><<<grid, 256, 0, stream>>>(indice_pairs, p.L, p.n_out, plan.n_pad, counts,
+                                                           nullptr, nbr);
+    } else {
+      // Large kernel volumes: counts travel through device memory.  The copy
+      // from pageable host memory is staged by the runtime before it returns.
+      int32_t *tmp = new int32_t[p.K];
+      for (int k = 0; k < p.K; ++k) tmp[k] = (int32_t)indice_num[k];
+      err = cudaMemcpyAsync(counts_dev, tmp, (size_t)p.K * sizeof(int32_t), cudaMemcpyHostToDevice, stream);
+      delete[] tmp;
+      if (err != cudaSuccess) return err;
+      buildNeighbourKernel<false><<<grid, 256, 0, stream>>>(indice_pairs, p.L, p.n_out, plan.n_pad,
+                                                            PairCounts{}, counts_dev, nbr);
+    }
+  }
+  if ((err = cudaGetLastError()) != cudaSuccess) return err;
+
+  // 3. convolution
+  if (mmaEligible(p, features, features_out)) {
+    const __half *f = static_cast<const __half *>(features);
+    const __half *w = static_cast<const __half *>(filter_packed);
+    __half *o = static_cast<__half *>(features_out);
+    switch (p.ci) {
+      case 16: return dispatchMmaCo<16>(p, plan, f, w, nbr, o, stream);
+      case 32: return dispatchMmaCo<32>(p, plan, f, w, nbr, o, stream);
+      case 64: return dispatchMmaCo<64>(p, plan, f, w, nbr, o, stream);
+      default: return dispatchMmaCo<128>(p, plan, f, w, nbr, o, stream);
+    }
+  }
+  const dim3 grid((unsigned)((p.n_out + kGenRows - 1) / kGenRows), (unsigned)((p.co + kGenCols - 1) / kGenCols));
+  if (p.is_half) {
+    convGenericKernel<__half><<<grid, kGenRows * kGenLanes, 0, stream>>>(
+        static_cast<const __half *>(features), static_cast<const __half *>(filter_packed), nbr, p.n_out,
+        plan.n_pad, p.K, p.ci, p.co, static_cast<__half *>(features_out));
+  } else {
+    convGenericKernel<float><<<grid, kGenRows * kGenLanes, 0, stream>>>(
+        static_cast<const float *>(features), static_cast<const float *>(filter_packed), nbr, p.n_out,
+        plan.n_pad, p.K, p.ci, p.co, static_cast<float *>(features_out));
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace sparse_conv
+}  // namespace mluop

@@ -1,0 +1,50 @@
+// Device side of the sparse convolution forward: workspace plan and launch
+// sequence.  Argument checks live in indice_convolution_forward.cpp.
+#ifndef MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_KERNELS_H_
+#define MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_KERNELS_H_
+
+#include <cuda_runtime_api.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace mluop {
+namespace sparse_conv {
+
+// Output rows owned by one thread block of the tensor-core kernel; the
+// neighbour table is padded to a multiple of it.
+constexpr int kConvTileRows = 128;
+
+enum FilterLayout { kFilterArray = 0, kFilterNDHWC = 1, kFilterNCDHW = 2 };
+
+struct ConvProblem {
+  int64_t L;        // input rows
+  int64_t n_out;    // output rows
+  int32_t K;        // kernel volume
+  int32_t ci, co;
+  int32_t is_half;  // 1: half, 0: float
+  int32_t filter_layout;
+};
+
+struct ConvWorkspacePlan {
+  size_t filter;     // T[K][Co][Ci]: filter repacked so that Ci is contiguous
+  size_t neighbour;  // int32[K][n_pad]: input row feeding (k, output row), -1 if none
+  size_t counts;     // int32[K]: pair counts, only used when K is too large for kernel arguments
+  size_t total;
+  int64_t n_pad;
+};
+
+ConvWorkspacePlan planConvWorkspace(const ConvProblem &p);
+
+// Enqueues filter repack, neighbour-table build and the convolution kernel.
+// indice_num is the caller's host array.
+cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorkspacePlan &plan,
+                                           const void *features, const void *filters,
+                                           const int32_t *indice_pairs, const int64_t *indice_num,
+                                           void *workspace, void *features_out, int sm_count,
+                                           cudaStream_t stream);
+
+}  // namespace sparse_conv
+}  // namespace mluop
+
+#endif  // MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_KERNELS_H_

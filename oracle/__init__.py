@@ -1,0 +1,188 @@
+"""ctypes access to the CPU oracle (and, when built, the reference's own CPU code).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, the smoke check and the
+CPU-baseline leg of bench.py.  The shipped library never touches this package.
+
+  oracle.lib()      -> the plain-C restatement (oracle/sparse_conv_oracle.c)
+  oracle.ref_lib()  -> the reference's function bodies compiled by
+                       oracle/build_ref.py, or None when that library is absent
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SRC = os.path.join(HERE, "sparse_conv_oracle.c")
+LIB = os.path.join(HERE, "_build", "libmluops_oracle.so")
+REF_LIB = os.path.join(HERE, "_ref", "libmluops_ref_cpu.so")
+
+_i32p = ctypes.POINTER(ctypes.c_int32)
+_i64p = ctypes.POINTER(ctypes.c_int64)
+_f32p = ctypes.POINTER(ctypes.c_float)
+_u16p = ctypes.POINTER(ctypes.c_uint16)
+_f64p = ctypes.POINTER(ctypes.c_double)
+
+FILTER_LAYOUT = {"ARRAY": 0, "NDHWC": 1, "NCDHW": 2}
+
+
+def build(force=False):
+    """Compile the C oracle with gcc (a second or two)."""
+    if force or not os.path.isfile(LIB) or os.path.getmtime(LIB) < os.path.getmtime(SRC):
+        os.makedirs(os.path.dirname(LIB), exist_ok=True)
+        subprocess.check_call(["gcc", "-O2", "-std=c11", "-fPIC", "-shared", "-o", LIB, SRC, "-lm"])
+    return LIB
+
+
+_lib = None
+_ref = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(LIB)
+        _lib.mluops_oracle_float_to_half_bits.restype = ctypes.c_uint16
+        _lib.mluops_oracle_float_to_half_bits.argtypes = [ctypes.c_float]
+        _lib.mluops_oracle_half_bits_to_float.restype = ctypes.c_float
+        _lib.mluops_oracle_half_bits_to_float.argtypes = [ctypes.c_uint16]
+    return _lib
+
+
+def ref_lib():
+    global _ref
+    if _ref is None and os.path.isfile(REF_LIB):
+        _ref = ctypes.CDLL(REF_LIB)
+        _ref.mluops_ref_float_to_half_bits.restype = ctypes.c_uint16
+        _ref.mluops_ref_float_to_half_bits.argtypes = [ctypes.c_float]
+    return _ref
+
+
+def _p(a, t):
+    return a.ctypes.data_as(t)
+
+
+def _i32x3(v):
+    a = np.ascontiguousarray(np.asarray(v, dtype=np.int32))
+    assert a.shape == (3,)
+    return a
+
+
+def kernel_volume(filter_space):
+    return int(np.prod(filter_space))
+
+
+def get_indice_pairs(indices, batch, pad, stride, dilation, filter_space, out_space, sub_m,
+                     out_rows=None, sentinel_quirk=False, use_ref=False):
+    """Rulebook of one sparse convolution.
+
+    Returns (indice_pairs [K,2,L], out_indices [out_rows,4], indice_num [K], num_act_out).
+    With use_ref the reference's own compiled code runs (num_act_out is then
+    derived from out_indices, since that code does not return it).
+    """
+    indices = np.ascontiguousarray(indices, dtype=np.int32)
+    L = indices.shape[0]
+    K = kernel_volume(filter_space)
+    if out_rows is None:
+        out_rows = L if sub_m else min(K * L, int(batch) * int(np.prod(out_space)))
+        out_rows = max(out_rows, 1)
+    pairs = np.empty((K, 2, L), dtype=np.int32)
+    out_indices = np.empty((out_rows, 4), dtype=np.int32)
+    num = np.empty((K,), dtype=np.int32)
+    pad, stride, dilation = _i32x3(pad), _i32x3(stride), _i32x3(dilation)
+    fs, osp = _i32x3(filter_space), _i32x3(out_space)
+    if use_ref:
+        r = ref_lib()
+        assert r is not None, "oracle/_ref is not built"
+        rc = r.mluops_ref_get_indice_pairs(
+            _p(indices, _i32p), ctypes.c_int32(L), ctypes.c_int32(batch), _p(pad, _i32p),
+            _p(stride, _i32p), _p(dilation, _i32p), _p(fs, _i32p), _p(osp, _i32p),
+            ctypes.c_int32(int(sub_m)), _p(pairs, _i32p), _p(out_indices, _i32p),
+            ctypes.c_int64(out_rows), _p(num, _i32p))
+        assert rc == 0
+        n_out = L if sub_m else int((out_indices[:, 0] >= 0).sum())
+        return pairs, out_indices, num, n_out
+    n_out = ctypes.c_int32(0)
+    rc = lib().mluops_oracle_get_indice_pairs(
+        _p(indices, _i32p), ctypes.c_int32(L), ctypes.c_int32(batch), _p(pad, _i32p),
+        _p(stride, _i32p), _p(dilation, _i32p), _p(fs, _i32p), _p(osp, _i32p),
+        ctypes.c_int32(int(sub_m)), _p(pairs, _i32p), _p(out_indices, _i32p),
+        ctypes.c_int64(out_rows), _p(num, _i32p), ctypes.byref(n_out),
+        ctypes.c_int32(int(sentinel_quirk)))
+    assert rc == 0, "oracle allocation failed"
+    return pairs, out_indices, num, int(n_out.value)
+
+
+def indice_convolution_forward(features, filters, filter_layout, filter_space, indice_pairs,
+                               indice_num, num_act_out, co, use_ref=False, fast=False):
+    """features_out [num_act_out, co] float32, accumulated in the reference order.
+
+    features/filters are float32 arrays holding the values the device sees (for
+    a half device dtype: already rounded through half).  `fast` drops the
+    product-rounding barrier (timed baseline only; filters must be ARRAY layout).
+    """
+    features = np.ascontiguousarray(features, dtype=np.float32)
+    filters = np.ascontiguousarray(filters, dtype=np.float32)
+    pairs = np.ascontiguousarray(indice_pairs, dtype=np.int32)
+    num = np.ascontiguousarray(indice_num, dtype=np.int64)
+    L, ci = features.shape
+    K = kernel_volume(filter_space)
+    out = np.empty((num_act_out, co), dtype=np.float32)
+    code = FILTER_LAYOUT[filter_layout]
+    if use_ref:
+        r = ref_lib()
+        assert r is not None, "oracle/_ref is not built"
+        kdhw = _i32x3(filter_space)
+        rc = r.mluops_ref_indice_convolution_forward(
+            _p(features, _f32p), _p(filters, _f32p), ctypes.c_int32(code), _p(kdhw, _i32p),
+            _p(pairs, _i32p), _p(num, _i64p), ctypes.c_int64(L), ctypes.c_int64(ci),
+            ctypes.c_int64(co), ctypes.c_int64(num_act_out), _p(out, _f32p))
+    elif fast:
+        assert code == 0
+        rc = lib().mluops_oracle_indice_convolution_forward_fast(
+            _p(features, _f32p), _p(filters, _f32p), _p(pairs, _i32p), _p(num, _i64p),
+            ctypes.c_int64(L), ctypes.c_int64(ci), ctypes.c_int64(co), ctypes.c_int64(K),
+            ctypes.c_int64(num_act_out), _p(out, _f32p))
+    else:
+        rc = lib().mluops_oracle_indice_convolution_forward(
+            _p(features, _f32p), _p(filters, _f32p), ctypes.c_int32(code), _p(pairs, _i32p),
+            _p(num, _i64p), ctypes.c_int64(L), ctypes.c_int64(ci), ctypes.c_int64(co),
+            ctypes.c_int64(K), ctypes.c_int64(num_act_out), _p(out, _f32p))
+    assert rc == 0
+    return out
+
+
+def round_through_half(x):
+    """float32 -> half (reference rounding) -> float32."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    lib().mluops_oracle_round_through_half(_p(x, _f32p), _p(out, _f32p), ctypes.c_int64(x.size))
+    return out
+
+
+def float_to_half_bits(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().mluops_oracle_float_to_half_array(_p(x, _f32p), _p(out, _u16p), ctypes.c_int64(x.size))
+    return out
+
+
+def half_bits_to_float(h):
+    h = np.ascontiguousarray(h, dtype=np.uint16)
+    out = np.empty(h.shape, dtype=np.float32)
+    lib().mluops_oracle_half_to_float_array(_p(h, _u16p), _p(out, _f32p), ctypes.c_int64(h.size))
+    return out
+
+
+def diffs(test, base, is_half):
+    """(diff1, diff2, diff3) of a device result against the CPU result."""
+    test = np.ascontiguousarray(test, dtype=np.float32).ravel()
+    base = np.ascontiguousarray(base, dtype=np.float32).ravel()
+    assert test.size == base.size
+    d1, d2, d3 = ctypes.c_double(), ctypes.c_double(), ctypes.c_double()
+    lib().mluops_oracle_diffs(_p(test, _f32p), _p(base, _f32p), ctypes.c_int64(test.size),
+                              ctypes.c_int32(int(is_half)), ctypes.byref(d1), ctypes.byref(d2),
+                              ctypes.byref(d3))
+    return d1.value, d2.value, d3.value

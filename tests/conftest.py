@@ -1,0 +1,65 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+# Argument-check tests need a handle even on a machine without a GPU; the
+# library then hands out a handle that can validate but not launch.
+os.environ.setdefault("MLUOP_B200_HOST_ONLY_HANDLE", "1")
+os.environ.setdefault("MLUOP_MIN_LOG_LEVEL", "3")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def pkg():
+    import __graft_entry__ as entry
+    entry.build()
+    return entry.load_package()
+
+
+@pytest.fixture(scope="session")
+def ops(pkg):
+    return pkg[0]
+
+
+@pytest.fixture(scope="session")
+def workloads(pkg):
+    return pkg[1]
+
+
+@pytest.fixture(scope="session")
+def backbone(pkg):
+    return pkg[2]
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    import __graft_entry__ as entry
+    o = entry.load_oracle()
+    o.build()
+    return o
+
+
+@pytest.fixture(scope="session")
+def golden():
+    import numpy as np
+    path = os.path.join(ROOT, "tests", "golden", "sparse_conv_golden.npz")
+    return np.load(path)
+
+
+@pytest.fixture(scope="session")
+def gpu_handle(ops):
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    torch.cuda.set_device(0)
+    h = ops.Handle(torch.cuda.current_stream().cuda_stream)
+    yield h
+    h.destroy()

@@ -1,0 +1,160 @@
+"""GPU parity of mluOpIndiceConvolutionForward against the CPU oracle, through
+the C ABI.  Acceptance: diff1 and diff2 <= 3e-3 for half, <= 1e-5 for float
+(the reference's thresholds for this operator)."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_conv(oracle, feat, w_array, layout, ks, pairs, num, n_out, co, is_half):
+    f32 = feat.astype(np.float32)
+    w32 = helpers.permute_filter(w_array.astype(np.float32), layout)
+    ref = oracle.indice_convolution_forward(f32, w32, layout, ks, pairs, num, n_out, co)
+    return oracle.round_through_half(ref) if is_half else ref
+
+
+def gpu_conv(ops, handle, feat, w_array, layout, ks, pairs, num, n_out, sub_m):
+    w = helpers.permute_filter(w_array, layout)
+    out = ops.indice_convolution_forward(handle, torch.from_numpy(feat).cuda(), torch.from_numpy(w).cuda(), layout,
+                                         ks, torch.from_numpy(pairs).cuda(), [int(v) for v in num], n_out, sub_m)
+    torch.cuda.synchronize()
+    return out.float().cpu().numpy()
+
+
+def assert_close(oracle, got, ref, is_half):
+    d1, d2, _ = oracle.diffs(got, ref, is_half)
+    tol = helpers.TOL_HALF if is_half else helpers.TOL_FLOAT
+    assert d1 <= tol and d2 <= tol, (d1, d2)
+    return d1, d2
+
+
+@pytest.mark.parametrize("layout", ["ARRAY", "NDHWC", "NCDHW"])
+def test_golden_vectors_float(ops, oracle, gpu_handle, golden, layout):
+    """features_out the reference's own CPU code produced."""
+    for name in helpers.golden_names(golden):
+        c = helpers.golden_case(golden, name)
+        n_rows = c["features_out"].shape[0]
+        got = gpu_conv(ops, gpu_handle, c["features"], c["filters_array"], layout, c["ks"], c["indice_pairs"],
+                       c["indice_num"], n_rows, c["sub_m"])
+        assert_close(oracle, got, c["features_out"], False)
+
+
+def make_case(oracle, rng, batch, space, n, ks, stride, pad, sub_m, ci, co, dtype):
+    osp = list(space) if sub_m else helpers.out_space(space, pad, stride, [1] * 3, ks)
+    idx = helpers.random_indices(rng, batch, space, n)
+    pairs, _, num, n_out = oracle.get_indice_pairs(idx, batch, pad, stride, [1] * 3, ks, osp, sub_m)
+    feat = rng.standard_normal((n, ci)).astype(np.float32).astype(dtype)
+    K = int(np.prod(ks))
+    w = (rng.standard_normal(tuple(ks) + (ci, co)) / np.sqrt(K * ci)).astype(np.float32).astype(dtype)
+    return pairs, num, n_out, feat, w
+
+
+CHANNELS = [(4, 16), (16, 16), (16, 32), (32, 32), (32, 64), (64, 64), (64, 128), (128, 128), (3, 5), (20, 48),
+            (128, 16), (130, 140)]
+
+
+@pytest.mark.parametrize("ci,co", CHANNELS)
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_channel_sweep(ops, oracle, gpu_handle, ci, co, dtype):
+    """Every kernel variant: tensor-core tiles for half with power-of-two channels, FMA otherwise."""
+    rng = np.random.default_rng(ci * 1000 + co)
+    is_half = dtype == np.float16
+    for sub_m, stride in ((1, [1] * 3), (0, [2] * 3)):
+        pairs, num, n_out, feat, w = make_case(oracle, rng, 2, [8, 14, 12], 700, [3] * 3, stride, [1] * 3, sub_m, ci,
+                                               co, dtype)
+        ref = oracle_conv(oracle, feat, w, "ARRAY", [3] * 3, pairs, num, n_out, co, is_half)
+        got = gpu_conv(ops, gpu_handle, feat, w, "ARRAY", [3] * 3, pairs, num, n_out, sub_m)
+        assert_close(oracle, got, ref, is_half)
+
+
+def test_output_rows_without_pairs_are_zero(ops, oracle, gpu_handle):
+    rng = np.random.default_rng(4)
+    pairs, num, n_out, feat, w = make_case(oracle, rng, 1, [6, 6, 6], 50, [3] * 3, [1] * 3, [1] * 3, 1, 16, 16,
+                                           np.float16)
+    extra = n_out + 77  # more output rows than any pair touches
+    got = gpu_conv(ops, gpu_handle, feat, w, "ARRAY", [3] * 3, pairs, num, extra, 1)
+    assert np.all(got[n_out:] == 0)
+    zero_num = np.zeros_like(num)
+    got = gpu_conv(ops, gpu_handle, feat, w, "ARRAY", [3] * 3, pairs, zero_num, n_out, 1)
+    assert np.all(got == 0)
+
+
+def test_dense_neighbourhood(ops, oracle, gpu_handle):
+    """A fully occupied grid: all 27 offsets live for interior voxels."""
+    rng = np.random.default_rng(8)
+    space = [6, 10, 10]
+    n = 2 * 6 * 10 * 10
+    for ci, co, dtype in ((64, 64, np.float16), (16, 16, np.float32)):
+        pairs, num, n_out, feat, w = make_case(oracle, rng, 2, space, n, [3] * 3, [1] * 3, [1] * 3, 1, ci, co, dtype)
+        is_half = dtype == np.float16
+        ref = oracle_conv(oracle, feat, w, "ARRAY", [3] * 3, pairs, num, n_out, co, is_half)
+        got = gpu_conv(ops, gpu_handle, feat, w, "ARRAY", [3] * 3, pairs, num, n_out, 1)
+        assert_close(oracle, got, ref, is_half)
+
+
+def test_config0_full_size(ops, oracle, workloads, gpu_handle):
+    idx, feat, layers, weights = workloads.make_inputs("c0")
+    ly = layers[0]
+    grid = list(workloads.CONFIGS["c0"]["grid"])
+    pairs, _, num, n_out = oracle.get_indice_pairs(idx, 1, ly.pad, ly.stride, ly.dilation, ly.filter_space, grid, 1)
+    for layout in ("ARRAY", "NDHWC"):
+        ref = oracle_conv(oracle, feat, weights[0], layout, ly.filter_space, pairs, num, n_out, ly.co, False)
+        got = gpu_conv(ops, gpu_handle, feat, weights[0], layout, ly.filter_space, pairs, num, n_out, 1)
+        assert_close(oracle, got, ref, False)
+
+
+def test_config1_full_size(ops, oracle, workloads, gpu_handle):
+    idx, feat, layers, weights = workloads.make_inputs("c1")
+    ly = layers[0]
+    grid = list(workloads.CONFIGS["c1"]["grid"])
+    osp = helpers.out_space(grid, ly.pad, ly.stride, ly.dilation, ly.filter_space)
+    pairs, _, num, n_out = oracle.get_indice_pairs(idx, 2, ly.pad, ly.stride, ly.dilation, ly.filter_space, osp, 0)
+    ref = oracle_conv(oracle, feat, weights[0], "ARRAY", ly.filter_space, pairs, num, n_out, ly.co, True)
+    got = gpu_conv(ops, gpu_handle, feat, weights[0], "ARRAY", ly.filter_space, pairs, num, n_out, 0)
+    assert_close(oracle, got, ref, True)
+
+
+def test_config3_one_sample(ops, oracle, workloads, gpu_handle):
+    """128 -> 128 channels, half, submanifold, one 200k-voxel sample of the GEMM-heavy config."""
+    idx, feat, layers, weights = workloads.make_inputs("c3", batch=1)
+    ly = layers[0]
+    grid = list(workloads.CONFIGS["c3"]["grid"])
+    pairs, _, num, n_out = oracle.get_indice_pairs(idx, 1, ly.pad, ly.stride, ly.dilation, ly.filter_space, grid, 1)
+    ref = oracle_conv(oracle, feat, weights[0], "ARRAY", ly.filter_space, pairs, num, n_out, ly.co, True)
+    got = gpu_conv(ops, gpu_handle, feat, weights[0], "ARRAY", ly.filter_space, pairs, num, n_out, 1)
+    assert_close(oracle, got, ref, True)
+
+
+def test_linearity_at_full_size(ops, oracle, workloads, gpu_handle):
+    """conv(a*x) == a*conv(x) exactly for a power of two, and conv is additive
+    in the features within tolerance, on the full 8 x 200k-voxel 128-channel config
+    (where the CPU oracle would take minutes)."""
+    idx, feat, layers, weights = workloads.make_inputs("c3")
+    ly = layers[0]
+    grid = list(workloads.CONFIGS["c3"]["grid"])
+    conv = ops.SparseConvDesc(8, ly.pad, ly.stride, ly.dilation, grid, ly.filter_space, grid, 1)
+    d_idx = torch.from_numpy(idx).cuda()
+    pairs, _, num, n_out = ops.get_indice_pairs(gpu_handle, conv, d_idx)
+    num_h = num.cpu().tolist()
+    x = torch.from_numpy(feat).cuda()
+    w = torch.from_numpy(weights[0]).cuda()
+    y = ops.indice_convolution_forward(gpu_handle, x, w, "ARRAY", ly.filter_space, pairs, num_h, n_out, 1)
+    y2 = ops.indice_convolution_forward(gpu_handle, x * 2, w, "ARRAY", ly.filter_space, pairs, num_h, n_out, 1)
+    assert torch.equal(y2, y * 2)
+    # a row whose only neighbour is itself equals x @ W_centre
+    only_self = torch.ones(n_out, dtype=torch.bool, device="cuda")
+    for k in range(27):
+        if k != 13:
+            only_self[pairs[k, 1, :num_h[k]].long()] = False
+    rows = only_self.nonzero().flatten()[:4096]
+    ref = (x[rows].float() @ w[1, 1, 1].float()).half()
+    d1, d2, _ = oracle.diffs(y[rows].float().cpu().numpy(), ref.float().cpu().numpy(), True)
+    assert d1 <= helpers.TOL_HALF and d2 <= helpers.TOL_HALF
+    # determinism: two runs are bit-identical
+    y3 = ops.indice_convolution_forward(gpu_handle, x, w, "ARRAY", ly.filter_space, pairs, num_h, n_out, 1)
+    assert torch.equal(y, y3)
+    conv.destroy()

@@ -1,0 +1,37 @@
+"""The C-ABI library loads and exports every function include/mlu_op.h declares."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "mlu_op.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mluOp[A-Za-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_function_is_exported(ops):
+    names = declared_functions()
+    assert len(names) >= 29
+    lib = ctypes.CDLL(ops.LIB_PATH)
+    for name in names:
+        assert hasattr(lib, name), name
+    assert set(names) == set(ops.SIGNATURES), set(names) ^ set(ops.SIGNATURES)
+
+
+def test_header_compiles_as_plain_c(tmp_path):
+    import subprocess
+    src = tmp_path / "use.c"
+    src.write_text('#include "mlu_op.h"\nint main(void) { mluOpHandle_t h = 0; (void)h; return MLUOP_STATUS_SUCCESS; }\n')
+    subprocess.check_call(["gcc", "-std=c11", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), "-c",
+                           str(src), "-o", str(tmp_path / "use.o")])
+
+
+def test_missing_library_fails_loudly(ops, monkeypatch):
+    import pytest
+    monkeypatch.setattr(ops, "_lib", None)
+    monkeypatch.setattr(ops, "LIB_PATH", "/nonexistent/libmluops_b200.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        ops.lib()

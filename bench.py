@@ -1,0 +1,435 @@
+"""Benchmark of the sparse-convolution forward path (rulebook generation +
+convolution) on the SECOND-style backbone.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2]
+
+A step is one forward pass of the 12-layer backbone (8 rulebooks, 12
+convolutions) over one batch of synthetic voxels through the C ABI of
+libmluops_b200.so.  At N GPUs every rank runs its own batch of 4 samples x
+120,000 voxels (weak scaling: samples are independent), then the final features
+and out_indices of all ranks are gathered on rank 0 with NCCL.
+
+Printed (rank 0, one JSON line):
+  value      active input voxels per second, inputs already resident in HBM
+  e2e        the same metric with host buffers: pinned host -> device copies of
+             the step's indices and features and the device -> host read of the
+             final features and out_indices are inside the timed region
+  roofline   the kernel with the largest share of device time: algorithmic bytes
+             per launch / measured duration, against the measured HBM bandwidth
+  cpu_baseline  the reference's CPU implementation of the path, one core, on a
+             bounded sample (one sample of the workload)
+
+--impl reference times the reference's own CPU code (oracle/_ref when it was
+built from the reference tree, else the C restatement in oracle/) on the host
+cores: the same metric, each step a bounded sample of the workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "active voxels/sec for sparse-conv fwd incl. indice pairs"
+UNIT = "voxels/s"
+HBM_FALLBACK_GBS = 6650.0
+TENSOR_FALLBACK_TFLOPS = 1400.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", TENSOR_FALLBACK_TFLOPS)), "measured"
+    return HBM_FALLBACK_GBS, TENSOR_FALLBACK_TFLOPS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while running."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = str(gpu_index)
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", self.gpu_index], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power = [], [], []
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
+
+
+def read_trace(ops):
+    """Parses the library's kernel trace into {name: (launches, total_ms, bytes, flops)}."""
+    lib = ops.lib()
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib.mluOpTraceKernelReport(buf, len(buf), None)
+    rows = {}
+    for line in buf.value.decode().splitlines()[1:]:
+        name, launches, ms, nbytes, flops = line.rsplit(",", 4)
+        rows[name] = (int(launches), float(ms), float(nbytes), float(flops))
+    return rows
+
+
+def run_b200(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+
+    ops, workloads, backbone = entry.load_package()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path for the product)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = workloads.CONFIGS[args.workload]
+    batch = cfg["batch"]
+    grid = list(cfg["grid"])
+    # every rank draws its own samples (seed offset by rank); weights are shared
+    if args.workload == "c4":
+        assert batch % world == 0, "c4 shards 16 samples over the ranks"
+        batch //= world
+    idx_np, feat_np, layers, weights_np = workloads.make_inputs(args.workload, batch=batch,
+                                                                seed=cfg["seed"] + 1000 * rank)
+    L = idx_np.shape[0]
+    elem = feat_np.dtype.itemsize
+
+    stream = torch.cuda.current_stream()
+    handle = ops.Handle(stream.cuda_stream)
+    weights = [torch.from_numpy(w).to(dev) for w in weights_np]
+    net = backbone.SparseNetwork(handle, layers, weights, grid, batch)
+
+    h_idx = torch.from_numpy(idx_np).pin_memory()
+    h_feat = torch.from_numpy(feat_np).pin_memory()
+    d_idx = torch.empty_like(h_idx, device=dev)
+    d_feat = torch.empty_like(h_feat, device=dev)
+    d_idx.copy_(h_idx)
+    d_feat.copy_(h_feat)
+    flush = torch.empty((256 << 20,), dtype=torch.uint8, device=dev)
+    host_out = {}
+
+    def gather_outputs(out, out_idx):
+        """Final features and out_indices of every rank -> rank 0 (NCCL send/recv, exact sizes).
+        The batch index of rank r is shifted by r*batch so that rows stay globally unique."""
+        if world == 1:
+            return out, out_idx
+        rows = torch.tensor([out.shape[0]], dtype=torch.int64, device=dev)
+        all_rows = [torch.zeros_like(rows) for _ in range(world)]
+        dist.all_gather(all_rows, rows)
+        counts = [int(r.item()) for r in all_rows]
+        shifted = out_idx.clone()
+        shifted[:, 0] += rank * batch
+        if rank == 0:
+            feats = torch.empty((sum(counts), out.shape[1]), dtype=out.dtype, device=dev)
+            idxs = torch.empty((sum(counts), 4), dtype=torch.int32, device=dev)
+            feats[:counts[0]] = out
+            idxs[:counts[0]] = shifted
+            reqs, off = [], counts[0]
+            for r in range(1, world):
+                reqs.append(dist.P2POp(dist.irecv, feats[off:off + counts[r]], r))
+                reqs.append(dist.P2POp(dist.irecv, idxs[off:off + counts[r]], r))
+                off += counts[r]
+            for w in dist.batch_isend_irecv(reqs):
+                w.wait()
+            return feats, idxs
+        reqs = [dist.P2POp(dist.isend, out.contiguous(), 0), dist.P2POp(dist.isend, shifted, 0)]
+        for w in dist.batch_isend_irecv(reqs):
+            w.wait()
+        return out, shifted
+
+    def step_resident():
+        out, out_idx, records = net.forward(d_idx, d_feat)
+        gather_outputs(out, out_idx)
+        return records
+
+    def step_e2e():
+        d_idx.copy_(h_idx, non_blocking=True)
+        d_feat.copy_(h_feat, non_blocking=True)
+        out, out_idx, records = net.forward(d_idx, d_feat)
+        g_out, g_idx = gather_outputs(out, out_idx)
+        if rank == 0 or world == 1:
+            key = (g_out.shape[0], g_out.shape[1])
+            if key not in host_out:
+                host_out.clear()
+                host_out[key] = (torch.empty(g_out.shape, dtype=g_out.dtype).pin_memory(),
+                                 torch.empty(g_idx.shape, dtype=g_idx.dtype).pin_memory())
+            host_out[key][0].copy_(g_out, non_blocking=True)
+            host_out[key][1].copy_(g_idx, non_blocking=True)
+        torch.cuda.synchronize()
+        return records, (g_out.shape[0] * g_out.shape[1] * elem + g_idx.shape[0] * 16)
+
+    def timed(step, steps):
+        """Per-step CUDA-event timing on the launching stream; L2 is flushed
+        between steps outside the event pairs.  Returns per-step ms."""
+        times = []
+        for _ in range(steps):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            step()
+            t1.record(stream)
+            torch.cuda.synchronize()
+            times.append(t0.elapsed_time(t1))
+        return times
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+        step_e2e()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
+    if rank == 0:
+        sampler.start()
+    res_ms = timed(step_resident, args.steps)
+    d2h = [0]
+
+    def e2e_once():
+        _, nbytes = step_e2e()
+        d2h[0] = nbytes
+    e2e_ms = timed(e2e_once, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # traced pass: per-kernel durations (CUDA events around every launch) and launch counts
+    ops.lib().mluOpTraceKernelReset()
+    ops.lib().mluOpTraceKernelEnable(1)
+    records = None
+    for _ in range(args.steps):
+        flush.fill_(1)
+        records = step_resident()
+    torch.cuda.synchronize()
+    trace = read_trace(ops)
+    ops.lib().mluOpTraceKernelEnable(0)
+
+    def reduce_max(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    total_res = reduce_max(sum(res_ms))
+    total_e2e = reduce_max(sum(e2e_ms))
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    hbm_gbs, tensor_tflops, peak_kind = measured_peaks()
+    voxels = L * world * args.steps
+    value = voxels / (total_res * 1e-3)
+    e2e_value = voxels / (total_e2e * 1e-3)
+
+    kernels = {k: v for k, v in trace.items() if not k.startswith(("memset:", "memcpy:"))}
+    gpu_launches = sum(v[0] for v in kernels.values()) // args.steps
+    total_kernel_ms = sum(v[1] for v in trace.values())
+    top = max(kernels.items(), key=lambda kv: kv[1][1])
+    top_name, (top_launches, top_ms, top_bytes, top_flops) = top
+    achieved = (top_bytes / top_launches) / ((top_ms / top_launches) * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
+                "frac": round(achieved / hbm_gbs, 4), "traffic": KNOWN_TRAFFIC.get(top_name),
+                "kernel": top_name, "launches_per_step": top_launches // args.steps,
+                "avg_launch_ms": round(top_ms / top_launches, 5), "peak_source": peak_kind + " copy bandwidth",
+                "share_of_device_time": round(top_ms / total_kernel_ms, 4),
+                "tensor_tflops_achieved": round(top_flops / (top_ms * 1e-3) / 1e12, 2)}
+
+    # whole-step roofline: sum over layers of max(flops/peak, bytes/BW) + rulebook bytes / BW
+    conv_rows, pair_bytes = backbone.roofline_bytes_and_flops(records, elem)
+    t_roof = sum(max(c["flops"] / (tensor_tflops * 1e12), c["bytes"] / (hbm_gbs * 1e9)) for c in conv_rows)
+    t_roof += pair_bytes / (hbm_gbs * 1e9)
+    ms_per_step = total_res / args.steps
+    whole = {"t_roof_ms": round(t_roof * 1e3, 4), "frac_resident": round(t_roof * 1e3 / ms_per_step, 4),
+             "frac_e2e": round(t_roof * 1e3 / (total_e2e / args.steps), 4),
+             "conv_bytes": sum(c["bytes"] for c in conv_rows), "conv_flops": sum(c["flops"] for c in conv_rows),
+             "rulebook_bytes": pair_bytes, "pairs_per_step": sum(c["P"] for c in conv_rows)}
+
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "strong" if args.workload == "c4" else "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": "%s: SECOND-style sparse backbone (12 convs, 8 rulebooks), batch %d x %d voxels "
+                               "per GPU, grid %dx%dx%d, fp16 storage / fp32 accumulate" %
+                               (args.workload, batch, cfg["per_sample"], *grid),
+                   "voxels_per_gpu": L, "l2": "flushed between steps (256 MiB write)",
+                   "parallelism": "batch samples per rank, NCCL gather of final rows" if world > 1 else "1 GPU"},
+        "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": int(h_idx.numel() * 4 +
+                                                                                      h_feat.numel() * elem),
+                "d2h_bytes_per_step": int(d2h[0]), "ms_per_step": round(total_e2e / args.steps, 4)},
+        "gpu_launches": int(gpu_launches),
+        "clocks": clocks,
+        "roofline": roofline,
+        "roofline_whole_step": whole,
+        "kernels": {k: {"launches_per_step": v[0] // args.steps, "ms_per_step": round(v[1] / args.steps, 4)}
+                    for k, v in sorted(trace.items(), key=lambda kv: -kv[1][1])},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_one_sample(args.workload)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
+# summarised under profiles/ (kernel name -> bytes); None until captured.
+KNOWN_TRAFFIC = {}
+
+
+def cpu_backend():
+    import oracle
+    return ("reference", True) if oracle.ref_lib() is not None else ("port", False)
+
+
+def cpu_baseline_one_sample(workload):
+    """The reference's CPU implementation of the path on one sample of the workload, one core."""
+    import __graft_entry__ as entry
+    _, workloads, _ = entry.load_package()
+    import oracle
+    from oracle import backbone_cpu
+    oracle.build()
+    kind, use_ref = cpu_backend()
+    cfg = workloads.CONFIGS[workload]
+    idx, feat, layers, weights = workloads.make_inputs(workload, batch=1)
+    t0 = time.perf_counter()
+    backbone_cpu.run_layers(idx, feat, layers, weights, cfg["grid"], 1, True, use_ref=use_ref, fast=not use_ref)
+    dt = time.perf_counter() - t0
+    return {"value": round(idx.shape[0] / dt, 1), "unit": UNIT, "cores": 1, "kind": kind,
+            "sample": "one sample of the workload (%d voxels, batch 1), full 12-layer backbone, %.1f s" %
+                      (idx.shape[0], dt)}
+
+
+def _reference_worker(task):
+    workload, scale, seed, use_ref = task
+    import __graft_entry__ as entry
+    _, workloads, _ = entry.load_package()
+    from oracle import backbone_cpu
+    cfg = workloads.CONFIGS[workload]
+    idx, feat, layers, weights = workloads.make_inputs(workload, scale=scale, batch=1, seed=seed)
+    t0 = time.perf_counter()
+    backbone_cpu.run_layers(idx, feat, layers, weights, cfg["grid"], 1, True, use_ref=use_ref, fast=not use_ref)
+    return idx.shape[0], time.perf_counter() - t0
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU code on all host cores; each step is one
+    reduced sample of the workload per worker process."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import multiprocessing as mp
+    import __graft_entry__ as entry
+    _, workloads, _ = entry.load_package()
+    import oracle
+    oracle.build()
+    kind, use_ref = cpu_backend()
+    cores = os.cpu_count() or 1
+    try:
+        import psutil
+        cores = max(1, min(cores, int(psutil.virtual_memory().available / (2 << 30))))
+    except Exception:
+        pass
+    workers = min(cores, 64)
+    scale = 0.2
+    cfg = workloads.CONFIGS[args.workload]
+    warmup = max(args.warmup, 1)
+    ctx = mp.get_context("fork")
+    times, voxels = [], 0
+    with ctx.Pool(workers) as pool:
+        for step in range(warmup + args.steps):
+            tasks = [(args.workload, scale, cfg["seed"] + 7919 * (step * workers + w), use_ref)
+                     for w in range(workers)]
+            t0 = time.perf_counter()
+            results = pool.map(_reference_worker, tasks)
+            dt = time.perf_counter() - t0
+            if step >= warmup:
+                times.append(dt)
+                voxels += sum(r[0] for r in results)
+    total = sum(times)
+    value = voxels / total
+    sample = ("per step %d worker processes, each one sample of the workload reduced to %d voxels (batch 1), "
+              "full 12-layer backbone" % (workers, int(round(cfg["per_sample"] * scale))))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": round(total / args.steps * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "%s: SECOND-style sparse backbone, reference CPU implementation; %s" %
+                               (args.workload, sample)},
+        "cpu_baseline": {"value": round(value, 1), "unit": UNIT, "cores": workers, "kind": kind, "sample": sample},
+        "e2e": {"value": round(value, 1), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c4"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

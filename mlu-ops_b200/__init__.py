@@ -35,7 +35,7 @@ _szt = ctypes.c_size_t
 _intp = ctypes.POINTER(ctypes.c_int)
 _i64p = ctypes.POINTER(ctypes.c_int64)
 
-# name -> (restype, argtypes); exactly the entry points include/mlu_op.h declares
+# name -> (restype, argtypes); exactly the entry points include/mlu_op.h and include/mlu_op_trace.h declare
 SIGNATURES = {
     "mluOpCreate": (_int, [ctypes.POINTER(_vp)]),
     "mluOpDestroy": (_int, [_vp]),
@@ -69,6 +69,10 @@ SIGNATURES = {
                                                             ctypes.POINTER(_szt)]),
     "mluOpIndiceConvolutionForward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64, _i64, _vp,
                                             _szt, _vp, _vp]),
+    # include/mlu_op_trace.h
+    "mluOpTraceKernelEnable": (_int, [_int]),
+    "mluOpTraceKernelReset": (_int, []),
+    "mluOpTraceKernelReport": (_int, [ctypes.c_char_p, _szt, ctypes.POINTER(_szt)]),
 }
 
 _lib = None

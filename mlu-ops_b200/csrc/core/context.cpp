@@ -3,6 +3,7 @@
 // :462 mluOpGetLibVersion, atomics mode).
 #include "core/context.h"
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -28,7 +29,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpCreate(mluOpHandle_t *handle) {
     if (host_only && std::strcmp(host_only, "1") == 0) {
       ctx->host_only = true;
       ctx->arch = MLUOP_B200;
-      std::strncpy(ctx->device_name, "host-only", CONTEXT_DEVICENAME_BUFFER_SIZE - 1);
+      std::snprintf(ctx->device_name, CONTEXT_DEVICENAME_BUFFER_SIZE, "%s", "host-only");
       ctx->host_words = new int32_t[mluOpContext::kHostWords]();
       *handle = ctx;
       return MLUOP_STATUS_SUCCESS;
@@ -46,7 +47,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpCreate(mluOpHandle_t *handle) {
   }
   ctx->device = dev;
   ctx->arch = (prop.major == 10) ? MLUOP_B200 : MLUOP_UNKNOWN_DEVICE;
-  std::strncpy(ctx->device_name, prop.name, CONTEXT_DEVICENAME_BUFFER_SIZE - 1);
+  std::snprintf(ctx->device_name, CONTEXT_DEVICENAME_BUFFER_SIZE, "%.63s", prop.name);
   ctx->sm_count = prop.multiProcessorCount;
   ctx->max_smem_per_block = (int32_t)prop.sharedMemPerBlockOptin;
   ctx->l2cache_size = prop.l2CacheSize;

@@ -31,6 +31,8 @@
 
 #include <cuda_runtime.h>
 
+#include "core/trace.h"
+
 namespace mluop {
 namespace sparse_conv {
 
@@ -383,49 +385,90 @@ cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePla
   const int4 *rows = reinterpret_cast<const int4 *>(indices);
   const int tiles = plan.tiles;
   const size_t count_smem = (size_t)g.K * sizeof(int);
+  const double L = g.L, KL = (double)g.K * g.L;
   cudaError_t err;
 
   if ((err = cudaMemsetAsync(status, 0, 64 * sizeof(int32_t), stream)) != cudaSuccess) return err;
   if (g.sub_m) {
     unsigned long long *slots = reinterpret_cast<unsigned long long *>(base + plan.table);
     const uint32_t mask = plan.hash_capacity - 1;
-    if ((err = cudaMemsetAsync(slots, 0xFF, (size_t)plan.hash_capacity * sizeof(unsigned long long),
-                               stream)) != cudaSuccess)
-      return err;
-    hashInsertKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, slots, mask, status);
-    // out_indices = indices for the first L rows, -1 beyond
-    const int64_t copy_rows = out_rows < g.L ? out_rows : (int64_t)g.L;
-    if ((err = cudaMemcpyAsync(out_indices, indices, (size_t)copy_rows * 4 * sizeof(int32_t),
-                               cudaMemcpyDeviceToDevice, stream)) != cudaSuccess)
-      return err;
-    if (out_rows > g.L) {
-      if ((err = cudaMemsetAsync(out_indices + (size_t)g.L * 4, 0xFF,
-                                 (size_t)(out_rows - g.L) * 4 * sizeof(int32_t), stream)) != cudaSuccess)
+    {
+      trace::Scope t("memset:hash_table", stream, 8.0 * plan.hash_capacity);
+      if ((err = cudaMemsetAsync(slots, 0xFF, (size_t)plan.hash_capacity * sizeof(unsigned long long),
+                                 stream)) != cudaSuccess)
         return err;
     }
-    probeCountKernel<true><<<tiles, kPairsTile, count_smem, stream>>>(
-        g, rows, slots, mask, nullptr, match, tile_count, tiles, status);
+    {
+      trace::Scope t("hashInsertKernel", stream, 16.0 * L + 8.0 * L);
+      hashInsertKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, slots, mask, status);
+    }
+    {
+      // out_indices = indices for the first L rows, -1 beyond
+      trace::Scope t("memcpy:out_indices", stream, 32.0 * L);
+      const int64_t copy_rows = out_rows < g.L ? out_rows : (int64_t)g.L;
+      if ((err = cudaMemcpyAsync(out_indices, indices, (size_t)copy_rows * 4 * sizeof(int32_t),
+                                 cudaMemcpyDeviceToDevice, stream)) != cudaSuccess)
+        return err;
+      if (out_rows > g.L) {
+        if ((err = cudaMemsetAsync(out_indices + (size_t)g.L * 4, 0xFF,
+                                   (size_t)(out_rows - g.L) * 4 * sizeof(int32_t), stream)) != cudaSuccess)
+          return err;
+      }
+    }
+    {
+      trace::Scope t("probeCountKernel<subm>", stream, 16.0 * L + 4.0 * KL);
+      probeCountKernel<true><<<tiles, kPairsTile, count_smem, stream>>>(
+          g, rows, slots, mask, nullptr, match, tile_count, tiles, status);
+    }
   } else {
     uint2 *rank_table = reinterpret_cast<uint2 *>(base + plan.table);
     int32_t *chunk_count = reinterpret_cast<int32_t *>(base + plan.chunk_count);
-    if ((err = cudaMemsetAsync(rank_table, 0, (size_t)plan.rank_words * sizeof(uint2), stream)) !=
-        cudaSuccess)
-      return err;
-    markOutputsKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table);
-    countBitsKernel<<<plan.rank_chunks, 256, 0, stream>>>(rank_table, plan.rank_words, chunk_count);
-    scanSingleBlockKernel<<<1, 1024, 0, stream>>>(chunk_count, plan.rank_chunks, status + 1);
-    rankAndDecodeKernel<<<plan.rank_chunks, 256, 0, stream>>>(
-        g, rank_table, plan.rank_words, chunk_count, reinterpret_cast<int4 *>(out_indices), out_rows,
-        status);
-    const unsigned fill_blocks = (unsigned)((out_rows + 255) / 256);
-    fillInactiveRowsKernel<<<fill_blocks, 256, 0, stream>>>(reinterpret_cast<int4 *>(out_indices),
-                                                           out_rows, status + 1);
-    probeCountKernel<false><<<tiles, kPairsTile, count_smem, stream>>>(
-        g, rows, nullptr, 0, rank_table, match, tile_count, tiles, status);
+    const double words = (double)plan.rank_words;
+    {
+      trace::Scope t("memset:rank_table", stream, 8.0 * words);
+      if ((err = cudaMemsetAsync(rank_table, 0, (size_t)plan.rank_words * sizeof(uint2), stream)) !=
+          cudaSuccess)
+        return err;
+    }
+    {
+      trace::Scope t("markOutputsKernel", stream, 16.0 * L);
+      markOutputsKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table);
+    }
+    {
+      trace::Scope t("countBitsKernel", stream, 8.0 * words);
+      countBitsKernel<<<plan.rank_chunks, 256, 0, stream>>>(rank_table, plan.rank_words, chunk_count);
+    }
+    {
+      trace::Scope t("scanSingleBlockKernel", stream, 8.0 * plan.rank_chunks);
+      scanSingleBlockKernel<<<1, 1024, 0, stream>>>(chunk_count, plan.rank_chunks, status + 1);
+    }
+    {
+      trace::Scope t("rankAndDecodeKernel", stream, 16.0 * words);
+      rankAndDecodeKernel<<<plan.rank_chunks, 256, 0, stream>>>(
+          g, rank_table, plan.rank_words, chunk_count, reinterpret_cast<int4 *>(out_indices), out_rows,
+          status);
+    }
+    {
+      trace::Scope t("fillInactiveRowsKernel", stream, 16.0 * (double)out_rows);
+      const unsigned fill_blocks = (unsigned)((out_rows + 255) / 256);
+      fillInactiveRowsKernel<<<fill_blocks, 256, 0, stream>>>(reinterpret_cast<int4 *>(out_indices),
+                                                             out_rows, status + 1);
+    }
+    {
+      trace::Scope t("probeCountKernel<default>", stream, 16.0 * L + 4.0 * KL);
+      probeCountKernel<false><<<tiles, kPairsTile, count_smem, stream>>>(
+          g, rows, nullptr, 0, rank_table, match, tile_count, tiles, status);
+    }
   }
-  scanTilesKernel<<<g.K, 1024, 0, stream>>>(tile_count, tiles, indice_num);
-  writePairsKernel<<<dim3(tiles, g.K), kPairsTile, 0, stream>>>(g.L, match, tile_count, tiles, indice_num,
-                                                               indice_pairs);
+  {
+    trace::Scope t("scanTilesKernel", stream, 8.0 * g.K * tiles);
+    scanTilesKernel<<<g.K, 1024, 0, stream>>>(tile_count, tiles, indice_num);
+  }
+  {
+    trace::Scope t("writePairsKernel", stream, 12.0 * KL);
+    writePairsKernel<<<dim3(tiles, g.K), kPairsTile, 0, stream>>>(g.L, match, tile_count, tiles, indice_num,
+                                                                 indice_pairs);
+  }
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
   return cudaMemcpyAsync(status_host, status, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, stream);
 }

@@ -29,6 +29,10 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <string>
+
+#include "core/trace.h"
+
 namespace mluop {
 namespace sparse_conv {
 
@@ -76,7 +80,9 @@ buildNeighbourKernel(const int32_t *__restrict__ pairs, int64_t L, int64_t n_out
   for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < pk;
        p += (int64_t)gridDim.x * blockDim.x) {
     const int32_t src = in_row[p], dst = out_row[p];
-    if (src >= 0 && src < L && dst >= 0 && dst < n_out) nbr[(size_t)k * n_pad + dst] = src;
+    // A rulebook holds one pair per (k, output row).  Should a caller hand in
+    // more, the largest input id is kept so that the result stays deterministic.
+    if (src >= 0 && src < L && dst >= 0 && dst < n_out) atomicMax(&nbr[(size_t)k * n_pad + dst], src);
   }
 }
 
@@ -330,13 +336,17 @@ convMmaF16Kernel(const __half *__restrict__ features, const __half *__restrict__
 
 template <int CI, int CO, int STAGES>
 cudaError_t launchMma(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
-                      const __half *filter, const int32_t *nbr, __half *out, cudaStream_t stream) {
+                      const __half *filter, const int32_t *nbr, __half *out, double algo_bytes,
+                      double algo_flops, cudaStream_t stream) {
   using Cfg = MmaConfig<CI, CO, STAGES>;
   auto kernel = convMmaF16Kernel<CI, CO, STAGES>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)Cfg::kSmemBytes);
   if (err != cudaSuccess) return err;
   const unsigned blocks = (unsigned)(plan.n_pad / kConvTileRows);
+  static const std::string name =
+      "convMmaF16Kernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
+  trace::Scope t(name.c_str(), stream, algo_bytes, algo_flops);
   kernel<<<blocks, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K,
                                                              out);
   return cudaGetLastError();
@@ -344,13 +354,14 @@ cudaError_t launchMma(const ConvProblem &p, const ConvWorkspacePlan &plan, const
 
 template <int CI>
 cudaError_t dispatchMmaCo(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
-                          const __half *filter, const int32_t *nbr, __half *out, cudaStream_t stream) {
+                          const __half *filter, const int32_t *nbr, __half *out, double algo_bytes,
+                          double algo_flops, cudaStream_t stream) {
   constexpr int kStages = (CI >= 128) ? 3 : 4;
   switch (p.co) {
-    case 16: return launchMma<CI, 16, kStages>(p, plan, features, filter, nbr, out, stream);
-    case 32: return launchMma<CI, 32, kStages>(p, plan, features, filter, nbr, out, stream);
-    case 64: return launchMma<CI, 64, kStages>(p, plan, features, filter, nbr, out, stream);
-    case 128: return launchMma<CI, 128, kStages>(p, plan, features, filter, nbr, out, stream);
+    case 16: return launchMma<CI, 16, kStages>(p, plan, features, filter, nbr, out, algo_bytes, algo_flops, stream);
+    case 32: return launchMma<CI, 32, kStages>(p, plan, features, filter, nbr, out, algo_bytes, algo_flops, stream);
+    case 64: return launchMma<CI, 64, kStages>(p, plan, features, filter, nbr, out, algo_bytes, algo_flops, stream);
+    case 128: return launchMma<CI, 128, kStages>(p, plan, features, filter, nbr, out, algo_bytes, algo_flops, stream);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -389,10 +400,23 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
   int32_t *counts_dev = reinterpret_cast<int32_t *>(base + plan.counts);
   cudaError_t err;
 
+  double pairs_total = 0;
+  int64_t max_pairs = 0;
+  for (int k = 0; k < p.K; ++k) {
+    pairs_total += (double)indice_num[k];
+    max_pairs = indice_num[k] > max_pairs ? indice_num[k] : max_pairs;
+  }
+  const double elem = p.is_half ? 2.0 : 4.0;
+  // Algorithmic work of the convolution: per pair one gathered input row, one
+  // scattered output row and two int32 ids; 2*Ci*Co flops.
+  const double conv_bytes = pairs_total * ((p.ci + p.co) * elem + 8.0);
+  const double conv_flops = 2.0 * pairs_total * p.ci * p.co;
+
   // 1. filter -> [K][Co][Ci]
   {
     const int64_t total = (int64_t)p.K * p.ci * p.co;
     const unsigned blocks = (unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+    trace::Scope t("repackFilterKernel", stream, 2.0 * total * elem);
     if (p.is_half) {
       repackFilterKernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half *>(filters),
                                                              static_cast<__half *>(filter_packed), p.K,
@@ -405,15 +429,17 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
   }
 
   // 2. neighbour table
-  if ((err = cudaMemsetAsync(nbr, 0xFF, (size_t)p.K * plan.n_pad * sizeof(int32_t), stream)) != cudaSuccess)
-    return err;
-  int64_t max_pairs = 0;
-  for (int k = 0; k < p.K; ++k) max_pairs = indice_num[k] > max_pairs ? indice_num[k] : max_pairs;
+  {
+    trace::Scope t("memset:neighbour_table", stream, 4.0 * p.K * plan.n_pad);
+    if ((err = cudaMemsetAsync(nbr, 0xFF, (size_t)p.K * plan.n_pad * sizeof(int32_t), stream)) != cudaSuccess)
+      return err;
+  }
   if (max_pairs > 0) {
     int64_t bx = (max_pairs + 255) / 256;
     const int64_t cap = (int64_t)sm_count * 32;
     if (bx > cap) bx = cap;
     const dim3 grid((unsigned)bx, (unsigned)p.K);
+    trace::Scope t("buildNeighbourKernel", stream, 12.0 * pairs_total);
     if (p.K <= kMaxCountsByValue) {
       PairCounts counts{};
       for (int k = 0; k < p.K; ++k) counts.n[k] = (int32_t)indice_num[k];
@@ -439,18 +465,20 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
     const __half *w = static_cast<const __half *>(filter_packed);
     __half *o = static_cast<__half *>(features_out);
     switch (p.ci) {
-      case 16: return dispatchMmaCo<16>(p, plan, f, w, nbr, o, stream);
-      case 32: return dispatchMmaCo<32>(p, plan, f, w, nbr, o, stream);
-      case 64: return dispatchMmaCo<64>(p, plan, f, w, nbr, o, stream);
-      default: return dispatchMmaCo<128>(p, plan, f, w, nbr, o, stream);
+      case 16: return dispatchMmaCo<16>(p, plan, f, w, nbr, o, conv_bytes, conv_flops, stream);
+      case 32: return dispatchMmaCo<32>(p, plan, f, w, nbr, o, conv_bytes, conv_flops, stream);
+      case 64: return dispatchMmaCo<64>(p, plan, f, w, nbr, o, conv_bytes, conv_flops, stream);
+      default: return dispatchMmaCo<128>(p, plan, f, w, nbr, o, conv_bytes, conv_flops, stream);
     }
   }
   const dim3 grid((unsigned)((p.n_out + kGenRows - 1) / kGenRows), (unsigned)((p.co + kGenCols - 1) / kGenCols));
   if (p.is_half) {
+    trace::Scope t("convGenericKernel<half>", stream, conv_bytes, conv_flops);
     convGenericKernel<__half><<<grid, kGenRows * kGenLanes, 0, stream>>>(
         static_cast<const __half *>(features), static_cast<const __half *>(filter_packed), nbr, p.n_out,
         plan.n_pad, p.K, p.ci, p.co, static_cast<__half *>(features_out));
   } else {
+    trace::Scope t("convGenericKernel<float>", stream, conv_bytes, conv_flops);
     convGenericKernel<float><<<grid, kGenRows * kGenLanes, 0, stream>>>(
         static_cast<const float *>(features), static_cast<const float *>(filter_packed), nbr, p.n_out,
         plan.n_pad, p.K, p.ci, p.co, static_cast<float *>(features_out));

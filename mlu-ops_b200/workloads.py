@@ -153,5 +153,6 @@ def make_inputs(config, scale=1.0, batch=None, first_batch_index=0, seed=None):
     dtype = np.float16 if cfg["dtype"] == "float16" else np.float32
     layers = second_backbone_layers() if config in ("c2", "c4") else [single_layer(config)]
     features = normal(rng, (indices.shape[0], layers[0].ci), 1.0, dtype)
-    weights = layer_weights(rng, layers, dtype)
+    # weights come from their own stream so that every shard of a workload sees the same filters
+    weights = layer_weights(np.random.default_rng([cfg["seed"], 0x5EED]), layers, dtype)
     return indices, features, layers, weights

@@ -35,6 +35,7 @@ def random_indices(rng, batch, space, n):
 CASES = [
     # name, batch, space, n, ks, stride, pad, dil, sub_m, ci, co
     ("subm_k3", 2, (6, 9, 8), 150, (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 1, 5, 7),
+    ("subm_k3_repeated", 2, (6, 9, 8), 150, (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 1, 5, 7),
     ("down_k3_s2", 2, (7, 10, 9), 120, (3, 3, 3), (2, 2, 2), (1, 1, 1), (1, 1, 1), 0, 4, 6),
     ("dilated_k3_d2", 1, (8, 8, 8), 90, (3, 3, 3), (1, 1, 1), (2, 2, 2), (2, 2, 2), 0, 3, 3),
     ("k311_s211_p0", 2, (6, 7, 5), 100, (3, 1, 1), (2, 1, 1), (0, 0, 0), (1, 1, 1), 0, 8, 4),
@@ -52,7 +53,7 @@ def main():
     for name, batch, space, n, ks, stride, pad, dil, sub_m, ci, co in CASES:
         osp = list(space) if sub_m else out_space(space, pad, stride, dil, ks)
         idx = random_indices(rng, batch, space, n)
-        if name == "subm_k3":
+        if name == "subm_k3_repeated":
             idx[-3:] = idx[:3]  # repeated coordinates: the last row wins
         pairs, out_idx, num, n_out = oracle.get_indice_pairs(idx, batch, pad, stride, dil, ks, osp, sub_m,
                                                              use_ref=True)

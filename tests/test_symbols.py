@@ -7,14 +7,17 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_functions():
-    text = open(os.path.join(ROOT, "include", "mlu_op.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(mluOp[A-Za-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in ("mlu_op.h", "mlu_op_trace.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(mluOp[A-Za-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_every_declared_function_is_exported(ops):
     names = declared_functions()
-    assert len(names) >= 29
+    assert len(names) >= 32
     lib = ctypes.CDLL(ops.LIB_PATH)
     for name in names:
         assert hasattr(lib, name), name
@@ -24,7 +27,7 @@ def test_every_declared_function_is_exported(ops):
 def test_header_compiles_as_plain_c(tmp_path):
     import subprocess
     src = tmp_path / "use.c"
-    src.write_text('#include "mlu_op.h"\nint main(void) { mluOpHandle_t h = 0; (void)h; return MLUOP_STATUS_SUCCESS; }\n')
+    src.write_text('#include "mlu_op.h"\n#include "mlu_op_trace.h"\nint main(void) { mluOpHandle_t h = 0; (void)h; return MLUOP_STATUS_SUCCESS; }\n')
     subprocess.check_call(["gcc", "-std=c11", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), "-c",
                            str(src), "-o", str(tmp_path / "use.o")])
 

@@ -80,9 +80,8 @@ buildNeighbourKernel(const int32_t *__restrict__ pairs, int64_t L, int64_t n_out
   for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < pk;
        p += (int64_t)gridDim.x * blockDim.x) {
     const int32_t src = in_row[p], dst = out_row[p];
-    // A rulebook holds one pair per (k, output row).  Should a caller hand in
-    // more, the largest input id is kept so that the result stays deterministic.
-    if (src >= 0 && src < L && dst >= 0 && dst < n_out) atomicMax(&nbr[(size_t)k * n_pad + dst], src);
+    // A rulebook holds one pair per (k, output row), so plain stores never collide.
+    if (src >= 0 && src < L && dst >= 0 && dst < n_out) nbr[(size_t)k * n_pad + dst] = src;
   }
 }
 
@@ -97,6 +96,7 @@ constexpr int kGenRows = 32;      // output rows per block
 constexpr int kGenLanes = 8;      // threads per row
 constexpr int kGenCols = 128;     // output channels per block (blockIdx.y walks the rest)
 constexpr int kGenCiChunk = 64;   // input channels staged per step
+constexpr int kSmallFilterFloats = 8192;  // K*Ci*Co up to this many values stay resident in shared memory
 
 // Thread (row, lane) owns output channels lane, lane+8, ... of its row.
 template <typename T>
@@ -148,6 +148,45 @@ convGenericKernel(const T *__restrict__ features, const T *__restrict__ filter_k
   }
 }
 
+// Small filters (K*Ci*Co <= 8192 values, Co <= 32): the whole filter sits in
+// shared memory as float [K][Ci][Co]; a thread owns NOUT consecutive output
+// channels of one output row and walks the K offsets without block-wide
+// synchronisation.  Same accumulation order as the general kernel.
+template <typename T, int NOUT>
+__global__ void __launch_bounds__(256)
+convSmallFilterKernel(const T *__restrict__ features, const T *__restrict__ filter_kcoci,
+                      const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, int ci, int co,
+                      T *__restrict__ out) {
+  extern __shared__ float wf_s[];  // [K][ci][co]
+  for (int e = threadIdx.x; e < K * ci * co; e += blockDim.x) {
+    const int c = e % ci, n = (e / ci) % co, k = e / (ci * co);
+    wf_s[((size_t)k * ci + c) * co + n] = toFloat(filter_kcoci[e]);
+  }
+  __syncthreads();
+  const int groups = co / NOUT;  // threads per output row
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t r = t / groups;
+  const int n0 = (int)(t % groups) * NOUT;
+  if (r >= n_out) return;
+  float acc[NOUT];
+#pragma unroll
+  for (int i = 0; i < NOUT; ++i) acc[i] = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int idx = nbr[(size_t)k * n_pad + r];
+    if (idx < 0) continue;
+    const T *f = features + (size_t)idx * ci;
+    const float *w = wf_s + (size_t)k * ci * co + n0;
+    for (int c = 0; c < ci; ++c) {
+      const float a = toFloat(f[c]);
+#pragma unroll
+      for (int i = 0; i < NOUT; ++i) acc[i] = fmaf(a, w[c * co + i], acc[i]);
+    }
+  }
+  T *dst = out + (size_t)r * co + n0;
+#pragma unroll
+  for (int i = 0; i < NOUT; ++i) fromFloat(acc[i], dst + i);
+}
+
 // ------------------------------------------------------------ tensor cores
 
 constexpr int kMmaMaxOffsets = 32;  // kernel volumes up to 32 keep the tile's table in shared memory
@@ -189,9 +228,9 @@ struct MmaConfig {
   static constexpr int kRowHalfs = CI + 8;  // 16-byte pad: conflict-free ldmatrix
   static constexpr int kAStage = kConvTileRows * kRowHalfs;
   static constexpr int kBStage = CO * kRowHalfs;
-  static constexpr size_t kSmemBytes =
-      (size_t)STAGES * (kAStage + kBStage) * sizeof(__half) + (size_t)kMmaMaxOffsets * kConvTileRows * 4 +
-      kMmaMaxOffsets * 8;
+  static constexpr size_t kStageBytes = (size_t)STAGES * (kAStage + kBStage) * sizeof(__half);
+  // stages + live-offset list and masks + the tile's slice of the neighbour table for K offsets
+  static size_t smemBytes(int K) { return kStageBytes + kMmaMaxOffsets * 8 + (size_t)K * kConvTileRows * 4; }
 };
 
 template <int CI, int CO, int STAGES>
@@ -203,9 +242,9 @@ convMmaF16Kernel(const __half *__restrict__ features, const __half *__restrict__
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __half *a_s = reinterpret_cast<__half *>(smem_raw);
   __half *b_s = a_s + STAGES * Cfg::kAStage;
-  int32_t *nbr_s = reinterpret_cast<int32_t *>(b_s + STAGES * Cfg::kBStage);  // [K][128]
-  int32_t *klist_s = nbr_s + kMmaMaxOffsets * kConvTileRows;                 // live offsets
-  int32_t *kmask_s = klist_s + kMmaMaxOffsets;                               // 16-row group masks
+  int32_t *klist_s = reinterpret_cast<int32_t *>(b_s + STAGES * Cfg::kBStage);  // live offsets
+  int32_t *kmask_s = klist_s + kMmaMaxOffsets;                                 // 16-row group masks
+  int32_t *nbr_s = kmask_s + kMmaMaxOffsets;                                   // [K][128]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t r0 = (int64_t)blockIdx.x * kConvTileRows;
@@ -340,15 +379,14 @@ cudaError_t launchMma(const ConvProblem &p, const ConvWorkspacePlan &plan, const
                       double algo_flops, cudaStream_t stream) {
   using Cfg = MmaConfig<CI, CO, STAGES>;
   auto kernel = convMmaF16Kernel<CI, CO, STAGES>;
-  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)Cfg::kSmemBytes);
+  const size_t smem = Cfg::smemBytes(p.K);
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess) return err;
   const unsigned blocks = (unsigned)(plan.n_pad / kConvTileRows);
   static const std::string name =
       "convMmaF16Kernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
   trace::Scope t(name.c_str(), stream, algo_bytes, algo_flops);
-  kernel<<<blocks, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K,
-                                                             out);
+  kernel<<<blocks, Cfg::kThreads, smem, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K, out);
   return cudaGetLastError();
 }
 
@@ -356,7 +394,7 @@ template <int CI>
 cudaError_t dispatchMmaCo(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
                           const __half *filter, const int32_t *nbr, __half *out, double algo_bytes,
                           double algo_flops, cudaStream_t stream) {
-  constexpr int kStages = (CI >= 128) ? 3 : 4;
+  constexpr int kStages = (CI >= 64) ? 3 : 4;
   switch (p.co) {
     case 16: return launchMma<CI, 16, kStages>(p, plan, features, filter, nbr, out, algo_bytes, algo_flops, stream);
     case 32: return launchMma<CI, 32, kStages>(p, plan, features, filter, nbr, out, algo_bytes, algo_flops, stream);
@@ -470,6 +508,24 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
       case 64: return dispatchMmaCo<64>(p, plan, f, w, nbr, o, conv_bytes, conv_flops, stream);
       default: return dispatchMmaCo<128>(p, plan, f, w, nbr, o, conv_bytes, conv_flops, stream);
     }
+  }
+  if ((int64_t)p.K * p.ci * p.co <= kSmallFilterFloats && p.co <= 32 && p.co % 4 == 0) {
+    constexpr int kNout = 4;
+    const int64_t threads = p.n_out * (p.co / kNout);
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    const size_t smem = (size_t)p.K * p.ci * p.co * sizeof(float);
+    if (p.is_half) {
+      trace::Scope t("convSmallFilterKernel<half>", stream, conv_bytes, conv_flops);
+      convSmallFilterKernel<__half, kNout><<<blocks, 256, smem, stream>>>(
+          static_cast<const __half *>(features), static_cast<const __half *>(filter_packed), nbr, p.n_out,
+          plan.n_pad, p.K, p.ci, p.co, static_cast<__half *>(features_out));
+    } else {
+      trace::Scope t("convSmallFilterKernel<float>", stream, conv_bytes, conv_flops);
+      convSmallFilterKernel<float, kNout><<<blocks, 256, smem, stream>>>(
+          static_cast<const float *>(features), static_cast<const float *>(filter_packed), nbr, p.n_out,
+          plan.n_pad, p.K, p.ci, p.co, static_cast<float *>(features_out));
+    }
+    return cudaGetLastError();
   }
   const dim3 grid((unsigned)((p.n_out + kGenRows - 1) / kGenRows), (unsigned)((p.co + kGenCols - 1) / kGenCols));
   if (p.is_half) {

@@ -9,6 +9,7 @@
 // every tensor has fewer than 2^31 elements.
 #include <cuda_runtime_api.h>
 
+#include <cstdlib>
 #include <string>
 
 #include "core/context.h"
@@ -205,6 +206,24 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForward(
   if (err != cudaSuccess) {
     LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
     return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  // The call is asynchronous; a kernel whose bounded waits gave up records that
+  // in a status word of the workspace.  MLUOP_B200_CHECK_STATUS=1 makes the call
+  // wait for the stream and report such a failure (debugging and tests).
+  static const char *check = std::getenv("MLUOP_B200_CHECK_STATUS");
+  if (check && check[0] == '1') {
+    int32_t word = 0;
+    const char *base = reinterpret_cast<const char *>((reinterpret_cast<size_t>(workspace) + 255) / 256 * 256);
+    err = cudaMemcpyAsync(&word, base + plan.status, sizeof(word), cudaMemcpyDeviceToHost, handle->queue);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(handle->queue);
+    if (err != cudaSuccess) {
+      LOG(ERROR) << api << " execution failed: " << cudaGetErrorString(err);
+      return MLUOP_STATUS_EXECUTION_FAILED;
+    }
+    if (word != 0) {
+      LOG(ERROR) << api << " device reported error bits " << word << " (a bounded wait gave up).";
+      return MLUOP_STATUS_EXECUTION_FAILED;
+    }
   }
   return MLUOP_STATUS_SUCCESS;
 }

@@ -26,12 +26,16 @@
 //   convGenericKernel       float, and half with other channel counts: fp32 FMA
 #include "kernels/sparse_conv/indice_convolution_kernels.h"
 
+#include <cstdlib>
+#include <cstring>
+
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <string>
 
 #include "core/trace.h"
+#include "kernels/sparse_conv/indice_convolution_tcgen05.h"
 
 namespace mluop {
 namespace sparse_conv {
@@ -417,6 +421,8 @@ ConvWorkspacePlan planConvWorkspace(const ConvProblem &p) {
   const size_t elem = p.is_half ? 2 : 4;
   plan.n_pad = (p.n_out + kConvTileRows - 1) / kConvTileRows * kConvTileRows;
   size_t off = 0;
+  plan.status = off;
+  off = alignUp(off + 64 * sizeof(int32_t), 256);
   plan.filter = off;
   off = alignUp(off + (size_t)p.K * p.ci * p.co * elem, 256);
   plan.neighbour = off;
@@ -436,6 +442,7 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
   void *filter_packed = base + plan.filter;
   int32_t *nbr = reinterpret_cast<int32_t *>(base + plan.neighbour);
   int32_t *counts_dev = reinterpret_cast<int32_t *>(base + plan.counts);
+  int32_t *status = reinterpret_cast<int32_t *>(base + plan.status);
   cudaError_t err;
 
   double pairs_total = 0;
@@ -497,8 +504,19 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
   }
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
 
-  // 3. convolution
-  if (mmaEligible(p, features, features_out)) {
+  // 3. convolution.  Half with channel counts 16/32/64/128 runs on the tcgen05
+  // tensor cores; MLUOP_B200_CONV_KERNEL=mma selects the mma.sync variant instead
+  // (kept for cross-checking), =fma the plain FMA kernels.
+  static const char *forced = std::getenv("MLUOP_B200_CONV_KERNEL");
+  const bool force_mma = forced && std::strcmp(forced, "mma") == 0;
+  const bool force_fma = forced && std::strcmp(forced, "fma") == 0;
+  if ((err = cudaMemsetAsync(status, 0, 64 * sizeof(int32_t), stream)) != cudaSuccess) return err;
+  if (!force_mma && !force_fma && tcgen05Eligible(p, features, features_out)) {
+    return launchConvTcgen05(p, plan, static_cast<const __half *>(features),
+                             static_cast<const __half *>(filter_packed), nbr,
+                             static_cast<__half *>(features_out), status, conv_bytes, conv_flops, stream);
+  }
+  if (!force_fma && mmaEligible(p, features, features_out)) {
     const __half *f = static_cast<const __half *>(features);
     const __half *w = static_cast<const __half *>(filter_packed);
     __half *o = static_cast<__half *>(features_out);

@@ -27,6 +27,7 @@ struct ConvProblem {
 };
 
 struct ConvWorkspacePlan {
+  size_t status;     // int32[64]: [0] error bits of the tensor-memory kernel's bounded waits
   size_t filter;     // T[K][Co][Ci]: filter repacked so that Ci is contiguous
   size_t neighbour;  // int32[K][n_pad]: input row feeding (k, output row), -1 if none
   size_t counts;     // int32[K]: pair counts, only used when K is too large for kernel arguments

@@ -1,0 +1,26 @@
+// tcgen05 / tensor-memory variant of the convolution kernel (half, channel
+// counts 16/32/64/128, kernel volume up to 32).
+#ifndef MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_TCGEN05_H_
+#define MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_TCGEN05_H_
+
+#include <cuda_fp16.h>
+#include <cuda_runtime_api.h>
+
+#include "kernels/sparse_conv/indice_convolution_kernels.h"
+
+namespace mluop {
+namespace sparse_conv {
+
+bool tcgen05Eligible(const ConvProblem &p, const void *features, const void *out);
+
+// status: one int32 of device memory, zero before the launch; a non-zero value
+// afterwards means a bounded wait inside the kernel gave up (bit 0 producer, bit
+// 1 MMA issuer, bit 2 epilogue).
+cudaError_t launchConvTcgen05(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
+                              const __half *filter_kcoci, const int32_t *nbr, __half *out, int32_t *status,
+                              double algo_bytes, double algo_flops, cudaStream_t stream);
+
+}  // namespace sparse_conv
+}  // namespace mluop
+
+#endif  // MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_TCGEN05_H_

@@ -12,6 +12,8 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 # library then hands out a handle that can validate but not launch.
 os.environ.setdefault("MLUOP_B200_HOST_ONLY_HANDLE", "1")
 os.environ.setdefault("MLUOP_MIN_LOG_LEVEL", "3")
+# Convolution calls wait for the stream and report a kernel whose bounded waits gave up.
+os.environ.setdefault("MLUOP_B200_CHECK_STATUS", "1")
 
 
 def pytest_configure(config):

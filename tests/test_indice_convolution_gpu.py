@@ -166,3 +166,18 @@ def test_linearity_at_full_size(ops, oracle, workloads, gpu_handle):
     y3 = ops.indice_convolution_forward(gpu_handle, x, w, "ARRAY", ly.filter_space, pairs, num_h, n_out, 1)
     assert torch.equal(y, y3)
     conv.destroy()
+
+
+@pytest.mark.parametrize("variant", ["mma", "fma"])
+def test_other_kernel_variants(variant):
+    """The mma.sync and plain-FMA variants of the convolution pass the same parity
+    cases (selected per process by MLUOP_B200_CONV_KERNEL, hence the child process)."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, MLUOP_B200_CONV_KERNEL=variant)
+    here = os.path.dirname(os.path.abspath(__file__))
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_indice_convolution_gpu.py"), "-m",
+                        "gpu", "-x", "-q", "-k", "channel_sweep or dense_neighbourhood or config1_full"], env=env,
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

@@ -272,6 +272,34 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForward(
     const int64_t sub_m, void *workspace, const size_t workspace_size,
     const mluOpTensorDescriptor_t features_out_desc, void *features_out);
 
+/* No counterpart in the reference.  Same computation and arguments as
+ * mluOpIndiceConvolutionForward, without the workspace pair: the scratch is a
+ * fixed array of MLUOP_BUILTIN_CONV_WORKSPACE_BYTES in device memory that
+ * belongs to the library itself.  It exists for callers that cannot allocate
+ * device memory where they call the library: inference loops that forbid
+ * allocator calls once running (cudaMalloc synchronises the device and can fail
+ * late), and plugins inside a process whose device memory is owned by another
+ * component's pool.  The entry point allocates and frees nothing.
+ *   - A problem whose workspace query exceeds the built-in size is refused with
+ *     MLUOP_STATUS_NOT_SUPPORTED and a log line naming both sizes (with 3x3x3
+ *     kernels and 64 channels that is about 300,000 output rows).
+ *   - Every GPU on which the process loads the library holds the array from
+ *     load until exit, used or not.
+ *   - The first call on each device looks the array's device address up
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array, which still holds what the
+ *     previous call left there; the call itself resets what it needs reset.
+ *     Two such calls whose GPU work overlaps (different streams or threads) race
+ *     on it: serialise them. */
+#define MLUOP_BUILTIN_CONV_WORKSPACE_BYTES (32u << 20)
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForwardBuiltinWorkspace(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc, const void *features,
+    const mluOpTensorDescriptor_t filters_desc, const void *filters,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *indice_pairs,
+    const int64_t indice_num[], const int64_t num_act_out, const int64_t inverse,
+    const int64_t sub_m, const mluOpTensorDescriptor_t features_out_desc, void *features_out);
+
 #if defined(__cplusplus)
 }
 #endif

@@ -69,6 +69,8 @@ SIGNATURES = {
                                                             ctypes.POINTER(_szt)]),
     "mluOpIndiceConvolutionForward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64, _i64, _vp,
                                             _szt, _vp, _vp]),
+    "mluOpIndiceConvolutionForwardBuiltinWorkspace": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64,
+                                                            _i64, _vp, _vp]),
     # include/mlu_op_trace.h
     "mluOpTraceKernelEnable": (_int, [_int]),
     "mluOpTraceKernelReset": (_int, []),

@@ -51,7 +51,7 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 200 ms while running."""
+    """Samples nvidia-smi clocks and throttle reasons every 25 ms while running."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -65,7 +65,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "25",
                  "-i", self.gpu_index], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -125,6 +125,8 @@ def run_b200(args):
     import __graft_entry__ as entry
 
     ops, workloads, backbone = entry.load_package()
+    import importlib
+    sharding = importlib.import_module("mluops_b200.sharding")
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -160,34 +162,11 @@ def run_b200(args):
     flush = torch.empty((256 << 20,), dtype=torch.uint8, device=dev)
     host_out = {}
 
+    first_sample = rank * batch  # batch index of this rank's first sample in the whole job
+
     def gather_outputs(out, out_idx):
-        """Final features and out_indices of every rank -> rank 0 (NCCL send/recv, exact sizes).
-        The batch index of rank r is shifted by r*batch so that rows stay globally unique."""
-        if world == 1:
-            return out, out_idx
-        rows = torch.tensor([out.shape[0]], dtype=torch.int64, device=dev)
-        all_rows = [torch.zeros_like(rows) for _ in range(world)]
-        dist.all_gather(all_rows, rows)
-        counts = [int(r.item()) for r in all_rows]
-        shifted = out_idx.clone()
-        shifted[:, 0] += rank * batch
-        if rank == 0:
-            feats = torch.empty((sum(counts), out.shape[1]), dtype=out.dtype, device=dev)
-            idxs = torch.empty((sum(counts), 4), dtype=torch.int32, device=dev)
-            feats[:counts[0]] = out
-            idxs[:counts[0]] = shifted
-            reqs, off = [], counts[0]
-            for r in range(1, world):
-                reqs.append(dist.P2POp(dist.irecv, feats[off:off + counts[r]], r))
-                reqs.append(dist.P2POp(dist.irecv, idxs[off:off + counts[r]], r))
-                off += counts[r]
-            for w in dist.batch_isend_irecv(reqs):
-                w.wait()
-            return feats, idxs
-        reqs = [dist.P2POp(dist.isend, out.contiguous(), 0), dist.P2POp(dist.isend, shifted, 0)]
-        for w in dist.batch_isend_irecv(reqs):
-            w.wait()
-        return out, shifted
+        """Final features and out_indices of every rank -> rank 0 over NCCL (exact sizes)."""
+        return sharding.gather_rows(out, out_idx, first_sample, rank, world)
 
     def step_resident():
         out, out_idx, records = net.forward(d_idx, d_feat)
@@ -419,7 +398,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c4"])

@@ -363,12 +363,17 @@ def run_reference(args):
     except Exception:
         pass
     workers = min(cores, 64)
-    scale = 0.2
     cfg = workloads.CONFIGS[args.workload]
     warmup = max(args.warmup, 1)
     ctx = mp.get_context("fork")
     times, voxels = [], 0
     with ctx.Pool(workers) as pool:
+        # Size the per-step sample so that the whole run stays within about three
+        # minutes: probe at 5% of a sample, then scale (cost grows roughly linearly).
+        t0 = time.perf_counter()
+        pool.map(_reference_worker, [(args.workload, 0.05, cfg["seed"] + w, use_ref) for w in range(workers)])
+        probe = time.perf_counter() - t0
+        scale = max(0.05, min(0.25, 0.05 * (180.0 / (warmup + args.steps)) / probe))
         for step in range(warmup + args.steps):
             tasks = [(args.workload, scale, cfg["seed"] + 7919 * (step * workers + w), use_ref)
                      for w in range(workers)]

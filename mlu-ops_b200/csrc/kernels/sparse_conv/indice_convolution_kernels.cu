@@ -419,7 +419,7 @@ bool mmaEligible(const ConvProblem &p, const void *features, const void *out) {
 ConvWorkspacePlan planConvWorkspace(const ConvProblem &p) {
   ConvWorkspacePlan plan{};
   const size_t elem = p.is_half ? 2 : 4;
-  plan.n_pad = (p.n_out + kConvTileRows - 1) / kConvTileRows * kConvTileRows;
+  plan.n_pad = (p.n_out + kConvPadRows - 1) / kConvPadRows * kConvPadRows;
   size_t off = 0;
   plan.status = off;
   off = alignUp(off + 64 * sizeof(int32_t), 256);
@@ -444,6 +444,7 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
   int32_t *counts_dev = reinterpret_cast<int32_t *>(base + plan.counts);
   int32_t *status = reinterpret_cast<int32_t *>(base + plan.status);
   cudaError_t err;
+  if ((err = cudaMemsetAsync(status, 0, 64 * sizeof(int32_t), stream)) != cudaSuccess) return err;
 
   double pairs_total = 0;
   int64_t max_pairs = 0;
@@ -510,7 +511,6 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
   static const char *forced = std::getenv("MLUOP_B200_CONV_KERNEL");
   const bool force_mma = forced && std::strcmp(forced, "mma") == 0;
   const bool force_fma = forced && std::strcmp(forced, "fma") == 0;
-  if ((err = cudaMemsetAsync(status, 0, 64 * sizeof(int32_t), stream)) != cudaSuccess) return err;
   if (!force_mma && !force_fma && tcgen05Eligible(p, features, features_out)) {
     return launchConvTcgen05(p, plan, static_cast<const __half *>(features),
                              static_cast<const __half *>(filter_packed), nbr,

@@ -14,6 +14,9 @@ namespace sparse_conv {
 // Output rows owned by one thread block of the tensor-core kernel; the
 // neighbour table is padded to a multiple of it.
 constexpr int kConvTileRows = 128;
+// The neighbour table is padded to a multiple of this many rows (the largest
+// block of rows any kernel variant owns).
+constexpr int kConvPadRows = 512;
 
 enum FilterLayout { kFilterArray = 0, kFilterNDHWC = 1, kFilterNCDHW = 2 };
 

@@ -1,20 +1,24 @@
 // Sparse convolution forward on the 5th-generation tensor cores (tcgen05) of
 // sm_100a: half inputs, fp32 accumulation in tensor memory.
 //
-// One thread block owns 128 output rows and keeps their [128 x Co] fp32
-// accumulator in TMEM for the whole kernel.  It walks the kernel offsets that
-// have at least one live row in the tile, in ascending order; per offset
+// One thread block owns a few consecutive tiles of 128 output rows and keeps
+// one [128 x Co] fp32 accumulator per tile in TMEM for the whole kernel.  It
+// walks the kernel offsets in ascending order; for each offset k the filter
+// slice W_k ([Co x Ci], Ci contiguous) is copied to shared memory once and
+// reused by all tiles of the block, and for every tile with at least one live
+// row at k (a per-tile bit mask the block derives from the neighbour table)
 //   * four producer warps (one thread per output row) gather the input rows
 //     named by the neighbour table into a shared-memory A tile with cp.async
-//     (16-byte chunks, zero fill for rows without a neighbour) and copy W_k
-//     ([Co x Ci], Ci contiguous) into a B tile; both tiles are written in the
-//     K-major swizzled layout tcgen05.mma reads;
+//     (16-byte chunks; rows without a neighbour are zeroed in place, nothing is
+//     fetched for them); A and W_k are written in the K-major swizzled layout
+//     tcgen05.mma reads;
 //   * one elected thread issues Ci/16 tcgen05.mma instructions (M=128, N=Co,
-//     K=16) that accumulate into TMEM, then tcgen05.commit releases the stage.
+//     K=16) that accumulate into the tile's TMEM columns, then tcgen05.commit
+//     releases the stage (and, after the last tile of k, the filter buffer).
 // Stages form a ring guarded by mbarriers (full: 128 producer arrivals after
 // cp.async.wait_group + fence.proxy.async; empty: one arrival from
 // tcgen05.commit).  After the last offset the producer warps read the
-// accumulator back with tcgen05.ld, round to half and store each output row
+// accumulators back with tcgen05.ld, round to half and store each output row
 // once.  The reduction over offsets happens in TMEM in a fixed order, so the
 // result is deterministic.
 //
@@ -127,7 +131,9 @@ __device__ __forceinline__ void tmemLoad16(unsigned taddr, unsigned (&r)[16]) {
 }
 __device__ __forceinline__ void tmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
-template <int CI, int CO, int STAGES>
+// Tile configuration.  A block owns TILES consecutive tiles of 128 output rows
+// and one [128 x CO] fp32 accumulator per tile in tensor memory.
+template <int CI, int CO>
 struct TcConfig {
   // K is split into blocks of at most 64 halfs (128 bytes, one swizzle atom wide)
   static constexpr int kBlockK = CI < 64 ? CI : 64;
@@ -137,17 +143,26 @@ struct TcConfig {
   // tcgen05 shared-memory descriptor layout type: 128B = 2, 64B = 4, 32B = 6
   static constexpr unsigned long long kLayoutType = kRowBytes == 128 ? 2 : (kRowBytes == 64 ? 4 : 6);
   static constexpr int kABlockBytes = kTile * kRowBytes;
-  static constexpr int kBBlockBytes = CO * kRowBytes;  // a multiple of 1024 when CO*kRowBytes >= 1024
+  static constexpr int kBBlockBytes = CO * kRowBytes;
   static constexpr int kBBlockStride = (kBBlockBytes + 1023) / 1024 * 1024;
-  static constexpr int kAStageBytes = kKBlocks * kABlockBytes;
-  static constexpr int kBStageBytes = kKBlocks * kBBlockStride;
-  static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-  static constexpr int kTmemCols = CO < 32 ? 32 : CO;
+  static constexpr int kAStageBytes = kKBlocks * kABlockBytes;  // one gathered [128 x CI] tile
+  static constexpr int kBBufBytes = kKBlocks * kBBlockStride;   // one filter slice W_k [CO x CI]
+  static constexpr int kTiles = CO >= 128 ? 2 : 4;              // tiles per block
+  static constexpr int kTmemCols = kTiles * CO < 32 ? 32 : kTiles * CO;  // 64, 128 or 256
+  static constexpr int kBlocksPerSmByTmem = 512 / kTmemCols;
+  static constexpr int kLag = 2;             // cp.async groups in flight before a stage is signalled
+  static constexpr int kBBuffers = kLag + 1;  // filter slices in flight (see the producer loop)
+  static constexpr int kAStages = CI >= 128 ? 3 : (CI >= 64 ? 5 : 6);
   static constexpr int kChunksPerRow = CI / 8;  // 16-byte chunks of one feature row
   // instruction descriptor: D fp32, A and B fp16, both K-major, N = CO, M = 128
   static constexpr unsigned kIdesc = (1u << 4) | ((unsigned)(CO >> 3) << 17) | ((unsigned)(kTile >> 4) << 24);
-  static size_t smemBytes(int K) {
-    return 1024 /* alignment slack */ + (size_t)STAGES * kStageBytes + (size_t)K * kTile * sizeof(int32_t) + 1024;
+  static constexpr size_t kOperandBytes = (size_t)kAStages * kAStageBytes + (size_t)kBBuffers * kBBufBytes;
+  // Dynamic shared memory: operands (+ alignment slack), raised where needed so
+  // that no more blocks fit on an SM than tensor memory has columns for.
+  static size_t smemBytes() {
+    size_t need = 1024 + kOperandBytes;
+    const size_t per_block_floor = (size_t)(227 * 1024) / (kBlocksPerSmByTmem + 1) + 1024;
+    return need > per_block_floor ? need : per_block_floor;
   }
 };
 
@@ -163,136 +178,175 @@ __device__ __forceinline__ unsigned long long makeDesc(unsigned smem_byte_addr) 
   return d;
 }
 
-template <int CI, int CO, int STAGES>
+// Work items of a block: (offset k ascending, tile t ascending) for which the
+// tile has at least one live row at k; producers and the MMA issuer walk the
+// same sequence, derived from the per-tile live masks.
+struct ItemCursor {
+  int k, t;
+  __device__ __forceinline__ bool next(const unsigned *masks, int K, int tiles) {
+    for (;;) {
+      if (++t >= tiles) {
+        t = 0;
+        if (++k >= K) return false;
+      }
+      if ((masks[t] >> k) & 1u) return true;
+    }
+  }
+};
+
+template <int CI, int CO>
 __global__ void __launch_bounds__(kThreads)
 convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict__ filter_kcoci,
-                  const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K,
-                  __half *__restrict__ out, int32_t *status) {
-  using Cfg = TcConfig<CI, CO, STAGES>;
+                  const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, __half *__restrict__ out,
+                  int32_t *status) {
+  using Cfg = TcConfig<CI, CO>;
+  constexpr int S = Cfg::kAStages, NB = Cfg::kBBuffers, T = Cfg::kTiles;
   extern __shared__ unsigned char smem_raw[];
   // operand blocks must sit on 1024-byte boundaries (swizzle atoms)
-  unsigned char *stage_base =
-      reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
-  int32_t *nbr_s = reinterpret_cast<int32_t *>(stage_base + (size_t)STAGES * Cfg::kStageBytes);  // [K][128]
-  __shared__ unsigned long long full_bar[STAGES], empty_bar[STAGES], accum_bar;
+  unsigned char *a_ring = reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
+  unsigned char *b_ring = a_ring + (size_t)S * Cfg::kAStageBytes;
+  __shared__ unsigned long long a_full[S], a_empty[S], b_empty[NB], accum_bar;
   __shared__ unsigned tmem_base_s;
-  __shared__ int klist_s[kMaxOffsets];
-  __shared__ unsigned live_mask_s;
-  __shared__ int n_live_s;
+  __shared__ unsigned masks_s[T];
   __shared__ int abort_s;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int64_t r0 = (int64_t)blockIdx.x * kTile;
+  const int64_t row0 = (int64_t)blockIdx.x * (T * kTile);
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbarInit(&full_bar[s], kProducerThreads);
-      mbarInit(&empty_bar[s], 1);
+    for (int s = 0; s < S; ++s) {
+      mbarInit(&a_full[s], kProducerThreads);
+      mbarInit(&a_empty[s], 1);
     }
+    for (int b = 0; b < NB; ++b) mbarInit(&b_empty[b], 1);
     mbarInit(&accum_bar, 1);
-    live_mask_s = 0;
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
+  if (tid < T) masks_s[tid] = 0u;
   if (warp == 4) tmemAlloc(&tmem_base_s, Cfg::kTmemCols);
-  for (int e = tid; e < K * kTile; e += kThreads) {
-    const int k = e / kTile, r = e % kTile;
-    nbr_s[e] = nbr[(size_t)k * n_pad + r0 + r];
-  }
   tcFenceBefore();
   __syncthreads();
   tcFenceAfter();
-  if (warp < 4) {
-    unsigned mine = 0;
-    for (int k = 0; k < K; ++k) {
-      const unsigned any = __ballot_sync(0xffffffffu, nbr_s[k * kTile + tid] >= 0);
-      if (any) mine |= 1u << k;
-    }
-    if (lane == 0 && mine) atomicOr(&live_mask_s, mine);
+  // Live masks: bit k of masks_s[t] is set when some row of tile t has a
+  // neighbour at offset k.  Each warp scans (offset, tile) slices of the table,
+  // four rows per lane.
+  for (int e = warp; e < K * T; e += kThreads / 32) {
+    const int k = e / T, t = e % T;
+    const int4 v = __ldg(reinterpret_cast<const int4 *>(nbr + (size_t)k * n_pad + row0 + t * kTile) + lane);
+    const unsigned any = __ballot_sync(0xffffffffu, (v.x & v.y & v.z & v.w) >= 0);
+    if (lane == 0 && any) atomicOr(&masks_s[t], 1u << k);
   }
   __syncthreads();
-  if (tid == 0) {
-    int n = 0;
-    for (int k = 0; k < K; ++k)
-      if ((live_mask_s >> k) & 1u) klist_s[n++] = k;
-    n_live_s = n;
-  }
-  __syncthreads();
-  const int n_live = n_live_s;
   const unsigned tmem_base = tmem_base_s;
   volatile int *abort_flag = &abort_s;
+  unsigned any_mask = 0;
+#pragma unroll
+  for (int t = 0; t < T; ++t) any_mask |= masks_s[t];
 
   if (warp < 4) {
     // ------------------------------------------------------------ producers
-    const int row = tid;  // tile row this thread gathers
-    constexpr int kLag = STAGES > 2 ? 2 : 1;  // cp.async groups allowed in flight before signalling
-    int signalled = 0;
-    for (int it = 0; it < n_live; ++it) {
-      const int s = it % STAGES;
-      if (it >= STAGES) {
-        if (!mbarWait(&empty_bar[s], ((it / STAGES) - 1) & 1, abort_flag, status, 1)) break;
+    // Thread `tid` gathers row `tid` of every tile.  Groups of cp.async are
+    // committed per item; a stage is signalled kLag items later, after
+    // cp.async.wait_group + fence.proxy.async, so up to kLag + 1 gathers are in
+    // flight.  The filter slice of offset k travels in the group of the first
+    // item of k; with kLag + 1 filter buffers the slice being overwritten was
+    // last read by items whose stages have all been signalled already, so the
+    // wait on b_empty cannot deadlock.
+    ItemCursor cur{0, -1};
+    bool more = cur.next(masks_s, K, T);
+    // lane l of warp w holds the neighbour id of tile row 32*w + l
+    int idx_next = more ? __ldg(nbr + (size_t)cur.k * n_pad + row0 + cur.t * kTile + tid) : -1;
+    int it = 0, signalled = 0, k_ord = -1, last_k = -1;
+    while (more) {
+      const int k = cur.k;
+      const int idx = idx_next;
+      more = cur.next(masks_s, K, T);
+      if (more) idx_next = __ldg(nbr + (size_t)cur.k * n_pad + row0 + cur.t * kTile + tid);
+      const int s = it % S;
+      if (it >= S) {
+        if (!mbarWait(&a_empty[s], ((it / S) - 1) & 1, abort_flag, status, 1)) break;
       }
-      const int k = klist_s[it];
-      unsigned char *a_stage = stage_base + (size_t)s * Cfg::kStageBytes;
-      unsigned char *b_stage = a_stage + Cfg::kAStageBytes;
-      const int idx = nbr_s[k * kTile + row];
-      const __half *src = features + (idx >= 0 ? (size_t)idx * CI : 0);
+      if (k != last_k) {
+        last_k = k;
+        ++k_ord;
+        const int b = k_ord % NB;
+        if (k_ord >= NB) {
+          if (!mbarWait(&b_empty[b], ((k_ord / NB) - 1) & 1, abort_flag, status, 8)) break;
+        }
+        unsigned char *b_buf = b_ring + (size_t)b * Cfg::kBBufBytes;
+        const __half *wk = filter_kcoci + (size_t)k * CO * CI;
+        for (int e = tid; e < CO * Cfg::kChunksPerRow; e += kProducerThreads) {
+          const int n = e / Cfg::kChunksPerRow, c = e % Cfg::kChunksPerRow;
+          const int kb = c / (Cfg::kRowBytes / 16), cc = c % (Cfg::kRowBytes / 16);
+          unsigned off = (unsigned)(n * Cfg::kRowBytes + cc * 16);
+          off ^= ((off >> 7) & Cfg::kSwizzleMask) << 4;
+          cpAsync16(smemAddr(b_buf + kb * Cfg::kBBlockStride + off), wk + (size_t)n * CI + c * 8, true);
+        }
+      }
+      unsigned char *a_stage = a_ring + (size_t)s * Cfg::kAStageBytes;
+      // Consecutive lanes fetch consecutive 16-byte chunks of the same feature
+      // row, so one warp instruction touches 32/CPR rows instead of 32.
 #pragma unroll
-      for (int c = 0; c < Cfg::kChunksPerRow; ++c) {
+      for (int i = 0; i < Cfg::kChunksPerRow; ++i) {
+        const int e = i * 32 + lane;
+        const int rr = e / Cfg::kChunksPerRow, c = e % Cfg::kChunksPerRow;
+        const int src_row = __shfl_sync(0xffffffffu, idx, rr);
+        const int row = warp * 32 + rr;
         const int kb = c / (Cfg::kRowBytes / 16), cc = c % (Cfg::kRowBytes / 16);
         unsigned off = (unsigned)(row * Cfg::kRowBytes + cc * 16);
         off ^= ((off >> 7) & Cfg::kSwizzleMask) << 4;
-        cpAsync16(smemAddr(a_stage + kb * Cfg::kABlockBytes + off), src + c * 8, idx >= 0);
-      }
-      const __half *wk = filter_kcoci + (size_t)k * CO * CI;
-      for (int e = tid; e < CO * Cfg::kChunksPerRow; e += kProducerThreads) {
-        const int n = e / Cfg::kChunksPerRow, c = e % Cfg::kChunksPerRow;
-        const int kb = c / (Cfg::kRowBytes / 16), cc = c % (Cfg::kRowBytes / 16);
-        unsigned off = (unsigned)(n * Cfg::kRowBytes + cc * 16);
-        off ^= ((off >> 7) & Cfg::kSwizzleMask) << 4;
-        cpAsync16(smemAddr(b_stage + kb * Cfg::kBBlockStride + off), wk + (size_t)n * CI + c * 8, true);
+        unsigned char *dst = a_stage + kb * Cfg::kABlockBytes + off;
+        if (src_row >= 0) {
+          cpAsync16(smemAddr(dst), features + (size_t)src_row * CI + c * 8, true);
+        } else {
+          // no neighbour at this offset: the row contributes zeros (nothing is fetched)
+          *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
       cpAsyncCommit();
-      if (it >= kLag) {
-        cpAsyncWait<kLag>();
+      if (it >= Cfg::kLag) {
+        cpAsyncWait<Cfg::kLag>();
         fenceProxyAsync();
-        mbarArrive(&full_bar[signalled % STAGES]);
+        mbarArrive(&a_full[signalled % S]);
         ++signalled;
       }
+      ++it;
     }
     cpAsyncWait<0>();
     fenceProxyAsync();
     if (!*abort_flag) {
-      for (; signalled < n_live; ++signalled) mbarArrive(&full_bar[signalled % STAGES]);
+      for (; signalled < it; ++signalled) mbarArrive(&a_full[signalled % S]);
     }
 
     // ------------------------------------------------------------- epilogue
-    const int64_t r = r0 + row;
-    bool have_acc = n_live > 0;
+    bool have_acc = any_mask != 0;
     if (have_acc) have_acc = mbarWait(&accum_bar, 0, abort_flag, status, 4);
     tcFenceAfter();
     if (!*abort_flag) {
-      __half *dst = out + (size_t)r * CO;
+#pragma unroll 1
+      for (int t = 0; t < T; ++t) {
+        const int64_t r = row0 + t * kTile + tid;
+        const bool tile_has_acc = have_acc && masks_s[t] != 0;
+        __half *dst = out + (size_t)r * CO;
 #pragma unroll
-      for (int c0 = 0; c0 < CO; c0 += 16) {
-        unsigned v[16];
-        if (have_acc) {
-          tmemLoad16(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c0, v);
-          tmemLoadWait();
-        } else {
+        for (int c0 = 0; c0 < CO; c0 += 16) {
+          unsigned v[16];
+          if (tile_has_acc) {
+            tmemLoad16(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(t * CO + c0), v);
+            tmemLoadWait();
+          } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = 0u;
-        }
-        if (r < n_out) {
-          uint4 lo, hi;
-          __half2 h[8];
+            for (int i = 0; i < 16; ++i) v[i] = 0u;
+          }
+          if (r < n_out) {
+            __half2 h[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            h[i] = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-          lo = *reinterpret_cast<uint4 *>(&h[0]);
-          hi = *reinterpret_cast<uint4 *>(&h[4]);
-          *reinterpret_cast<uint4 *>(dst + c0) = lo;
-          *reinterpret_cast<uint4 *>(dst + c0 + 8) = hi;
+            for (int i = 0; i < 8; ++i)
+              h[i] = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            *reinterpret_cast<uint4 *>(dst + c0) = *reinterpret_cast<uint4 *>(&h[0]);
+            *reinterpret_cast<uint4 *>(dst + c0 + 8) = *reinterpret_cast<uint4 *>(&h[4]);
+          }
         }
       }
     }
@@ -300,22 +354,36 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   } else {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      for (int it = 0; it < n_live; ++it) {
-        const int s = it % STAGES;
-        if (!mbarWait(&full_bar[s], (it / STAGES) & 1, abort_flag, status, 2)) break;
+      ItemCursor cur{0, -1};
+      bool more = cur.next(masks_s, K, T);
+      unsigned started = 0;  // tiles whose accumulator has been written
+      int it = 0, k_ord = -1, last_k = -1;
+      while (more) {
+        const int k = cur.k, t = cur.t;
+        more = cur.next(masks_s, K, T);
+        if (k != last_k) {
+          last_k = k;
+          ++k_ord;
+        }
+        const int s = it % S, b = k_ord % NB;
+        if (!mbarWait(&a_full[s], (it / S) & 1, abort_flag, status, 2)) break;
         tcFenceAfter();
-        const unsigned a_addr = smemAddr(stage_base + (size_t)s * Cfg::kStageBytes);
-        const unsigned b_addr = a_addr + Cfg::kAStageBytes;
+        const unsigned a_addr = smemAddr(a_ring + (size_t)s * Cfg::kAStageBytes);
+        const unsigned b_addr = smemAddr(b_ring + (size_t)b * Cfg::kBBufBytes);
+        const unsigned d_addr = tmem_base + (unsigned)(t * CO);
 #pragma unroll
         for (int j = 0; j < CI / 16; ++j) {
           const int kb = (j * 32) / Cfg::kRowBytes, within = (j * 32) % Cfg::kRowBytes;
           const unsigned long long a_desc = makeDesc<Cfg>(a_addr + kb * Cfg::kABlockBytes + within);
           const unsigned long long b_desc = makeDesc<Cfg>(b_addr + kb * Cfg::kBBlockStride + within);
-          umma(tmem_base, a_desc, b_desc, Cfg::kIdesc, (it > 0 || j > 0) ? 1u : 0u);
+          umma(d_addr, a_desc, b_desc, Cfg::kIdesc, (((started >> t) & 1u) || j > 0) ? 1u : 0u);
         }
-        ummaCommit(&empty_bar[s]);  // the stage may be refilled once these MMAs have read it
+        started |= 1u << t;
+        ummaCommit(&a_empty[s]);  // the stage may be refilled once these MMAs have read it
+        if (!more || cur.k != k) ummaCommit(&b_empty[b]);  // last item of offset k: its filter slice is free
+        ++it;
       }
-      if (n_live > 0 && !*abort_flag) ummaCommit(&accum_bar);
+      if (it > 0 && !*abort_flag) ummaCommit(&accum_bar);
     }
     __syncwarp();
     tcFenceBefore();
@@ -327,16 +395,16 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   }
 }
 
-template <int CI, int CO, int STAGES>
+template <int CI, int CO>
 cudaError_t launchTc(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
                      const __half *filter, const int32_t *nbr, __half *out, int32_t *status, double algo_bytes,
                      double algo_flops, cudaStream_t stream) {
-  using Cfg = TcConfig<CI, CO, STAGES>;
-  auto kernel = convTcgen05Kernel<CI, CO, STAGES>;
-  const size_t smem = Cfg::smemBytes(p.K);
+  using Cfg = TcConfig<CI, CO>;
+  auto kernel = convTcgen05Kernel<CI, CO>;
+  const size_t smem = Cfg::smemBytes();
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess) return err;
-  const unsigned blocks = (unsigned)(plan.n_pad / kTile);
+  const unsigned blocks = (unsigned)(plan.n_pad / (Cfg::kTiles * kTile));
   static const std::string name = "convTcgen05Kernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
   trace::Scope t(name.c_str(), stream, algo_bytes, algo_flops);
   kernel<<<blocks, kThreads, smem, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K, out, status);
@@ -347,12 +415,11 @@ template <int CI>
 cudaError_t dispatchCo(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
                        const __half *filter, const int32_t *nbr, __half *out, int32_t *status, double algo_bytes,
                        double algo_flops, cudaStream_t stream) {
-  constexpr int kStages = CI >= 128 ? 3 : 4;
   switch (p.co) {
-    case 16: return launchTc<CI, 16, kStages>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
-    case 32: return launchTc<CI, 32, kStages>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
-    case 64: return launchTc<CI, 64, kStages>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
-    case 128: return launchTc<CI, 128, kStages>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 16: return launchTc<CI, 16>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 32: return launchTc<CI, 32>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 64: return launchTc<CI, 64>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 128: return launchTc<CI, 128>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
     default: return cudaErrorInvalidValue;
   }
 }

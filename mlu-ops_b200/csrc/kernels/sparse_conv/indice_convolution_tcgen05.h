@@ -14,8 +14,8 @@ namespace sparse_conv {
 bool tcgen05Eligible(const ConvProblem &p, const void *features, const void *out);
 
 // status: one int32 of device memory, zero before the launch; a non-zero value
-// afterwards means a bounded wait inside the kernel gave up (bit 0 producer, bit
-// 1 MMA issuer, bit 2 epilogue).
+// afterwards means a bounded wait inside the kernel gave up (bit 0 producer on a gather stage,
+// bit 1 MMA issuer, bit 2 epilogue, bit 3 producer on a filter buffer).
 cudaError_t launchConvTcgen05(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
                               const __half *filter_kcoci, const int32_t *nbr, __half *out, int32_t *status,
                               double algo_bytes, double algo_flops, cudaStream_t stream);

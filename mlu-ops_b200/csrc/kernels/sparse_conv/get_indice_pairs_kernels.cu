@@ -317,29 +317,49 @@ scanTilesKernel(int32_t *tile_count, int tiles, int32_t *indice_num) {
   if (threadIdx.x == 0) indice_num[blockIdx.x] = running;
 }
 
-// Block (tile, k): order-preserving compaction of the tile's matches into the
-// two rows of indice_pairs[k], plus the -1 tail for the positions this tile
-// covers.  Every word of indice_pairs is written exactly once.
+// Block (segment of kWriteSegTiles tiles, k): order-preserving compaction of each
+// tile's matches into the two rows of indice_pairs[k], plus the -1 tail for the
+// positions the segment covers.  Every word of indice_pairs is written exactly
+// once.  A tile without a match (its count is the difference of neighbouring
+// offsets) is not read at all.
+constexpr int kWriteSegTiles = 8;
+
 __global__ void __launch_bounds__(kPairsTile)
 writePairsKernel(int L, const int32_t *__restrict__ match, const int32_t *__restrict__ tile_offset,
                  int tiles, const int32_t *__restrict__ indice_num, int32_t *__restrict__ indice_pairs) {
-  __shared__ int warp_sums[33];
+  __shared__ int warp_count[2][kPairsTile / 32];
   const int k = blockIdx.y;
-  const int j = blockIdx.x * kPairsTile + threadIdx.x;
-  const int v = j < L ? match[(size_t)k * L + j] : -1;
-  const int flag = v >= 0;
-  int total;
-  const int r = blockExclusiveScan(flag, &total, warp_sums);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int total = indice_num[k];
+  const int32_t *offsets = tile_offset + (size_t)k * tiles;
+  const int32_t *match_row = match + (size_t)k * L;
   int32_t *in_row = indice_pairs + (size_t)k * 2 * L;
   int32_t *out_row = in_row + L;
-  if (flag) {
-    const int p = tile_offset[(size_t)k * tiles + blockIdx.x] + r;
-    in_row[p] = j;
-    out_row[p] = v;
-  }
-  if (j < L && j >= indice_num[k]) {
-    in_row[j] = -1;
-    out_row[j] = -1;
+  int buffers_used = 0;
+  for (int i = 0; i < kWriteSegTiles; ++i) {
+    const int tile = blockIdx.x * kWriteSegTiles + i;
+    if (tile >= tiles) break;
+    const int j = tile * kPairsTile + threadIdx.x;
+    const int first = offsets[tile];
+    const int next = tile + 1 < tiles ? offsets[tile + 1] : total;
+    if (next > first) {  // same decision in every thread of the block
+      const int v = j < L ? match_row[j] : -1;
+      const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
+      int *counts = warp_count[buffers_used & 1];
+      ++buffers_used;
+      if (lane == 0) counts[warp] = __popc(hits);
+      __syncthreads();
+      if (v >= 0) {
+        int p = first + __popc(hits & ((1u << lane) - 1u));
+        for (int w = 0; w < warp; ++w) p += counts[w];
+        in_row[p] = j;
+        out_row[p] = v;
+      }
+    }
+    if (j < L && j >= total) {
+      in_row[j] = -1;
+      out_row[j] = -1;
+    }
   }
 }
 
@@ -466,8 +486,9 @@ cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePla
   }
   {
     trace::Scope t("writePairsKernel", stream, 12.0 * KL);
-    writePairsKernel<<<dim3(tiles, g.K), kPairsTile, 0, stream>>>(g.L, match, tile_count, tiles, indice_num,
-                                                                 indice_pairs);
+    const unsigned segments = (unsigned)((tiles + kWriteSegTiles - 1) / kWriteSegTiles);
+    writePairsKernel<<<dim3(segments, g.K), kPairsTile, 0, stream>>>(g.L, match, tile_count, tiles, indice_num,
+                                                                    indice_pairs);
   }
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
   return cudaMemcpyAsync(status_host, status, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, stream);

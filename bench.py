@@ -174,20 +174,23 @@ def run_b200(args):
         return records
 
     def step_e2e():
+        """Host buffers in, host buffers out: pinned-host -> device copies of this rank's
+        indices and features, the layer stack, the NCCL gather, and the device -> host read
+        of this rank's final features and out_indices (every rank reads its own rows back
+        over its own PCIe link, in parallel)."""
         d_idx.copy_(h_idx, non_blocking=True)
         d_feat.copy_(h_feat, non_blocking=True)
         out, out_idx, records = net.forward(d_idx, d_feat)
-        g_out, g_idx = gather_outputs(out, out_idx)
-        if rank == 0 or world == 1:
-            key = (g_out.shape[0], g_out.shape[1])
-            if key not in host_out:
-                host_out.clear()
-                host_out[key] = (torch.empty(g_out.shape, dtype=g_out.dtype).pin_memory(),
-                                 torch.empty(g_idx.shape, dtype=g_idx.dtype).pin_memory())
-            host_out[key][0].copy_(g_out, non_blocking=True)
-            host_out[key][1].copy_(g_idx, non_blocking=True)
+        gather_outputs(out, out_idx)
+        key = (out.shape[0], out.shape[1])
+        if key not in host_out:
+            host_out.clear()
+            host_out[key] = (torch.empty(out.shape, dtype=out.dtype).pin_memory(),
+                             torch.empty(out_idx.shape, dtype=out_idx.dtype).pin_memory())
+        host_out[key][0].copy_(out, non_blocking=True)
+        host_out[key][1].copy_(out_idx, non_blocking=True)
         torch.cuda.synchronize()
-        return records, (g_out.shape[0] * g_out.shape[1] * elem + g_idx.shape[0] * 16)
+        return records, (out.shape[0] * out.shape[1] * elem + out_idx.shape[0] * 16)
 
     def timed(step, steps):
         """Per-step CUDA-event timing on the launching stream; L2 is flushed
@@ -244,6 +247,10 @@ def run_b200(args):
 
     total_res = reduce_max(sum(res_ms))
     total_e2e = reduce_max(sum(e2e_ms))
+    if world > 1:
+        t = torch.tensor([d2h[0]], dtype=torch.int64, device=dev)
+        dist.all_reduce(t)
+        d2h[0] = int(t.item())
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -287,8 +294,8 @@ def run_b200(args):
                                (args.workload, batch, cfg["per_sample"], *grid),
                    "voxels_per_gpu": L, "l2": "flushed between steps (256 MiB write)",
                    "parallelism": "batch samples per rank, NCCL gather of final rows" if world > 1 else "1 GPU"},
-        "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": int(h_idx.numel() * 4 +
-                                                                                      h_feat.numel() * elem),
+        "e2e": {"value": round(e2e_value, 1), "unit": UNIT,
+                "h2d_bytes_per_step": int(h_idx.numel() * 4 + h_feat.numel() * elem) * world,
                 "d2h_bytes_per_step": int(d2h[0]), "ms_per_step": round(total_e2e / args.steps, 4)},
         "gpu_launches": int(gpu_launches),
         "clocks": clocks,

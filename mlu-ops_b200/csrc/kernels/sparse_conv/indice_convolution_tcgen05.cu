@@ -9,15 +9,15 @@
 // row at k (a per-tile bit mask the block derives from the neighbour table)
 //   * four producer warps (one thread per output row) gather the input rows
 //     named by the neighbour table into a shared-memory A tile with cp.async
-//     (16-byte chunks; rows without a neighbour are zeroed in place, nothing is
+//     (16-byte chunks; rows without a neighbour are zero-filled, nothing is
 //     fetched for them); A and W_k are written in the K-major swizzled layout
 //     tcgen05.mma reads;
 //   * one elected thread issues Ci/16 tcgen05.mma instructions (M=128, N=Co,
 //     K=16) that accumulate into the tile's TMEM columns, then tcgen05.commit
 //     releases the stage (and, after the last tile of k, the filter buffer).
-// Stages form a ring guarded by mbarriers (full: 128 producer arrivals after
-// cp.async.wait_group + fence.proxy.async; empty: one arrival from
-// tcgen05.commit).  After the last offset the producer warps read the
+// Stages form a ring guarded by mbarriers (full: one arrival per producer thread,
+// delivered by cp.async.mbarrier.arrive when that thread's copies have landed;
+// empty: one arrival from tcgen05.commit).  After the last offset the producer warps read the
 // accumulators back with tcgen05.ld, round to half and store each output row
 // once.  The reduction over offsets happens in TMEM in a fixed order, so the
 // result is deterministic.
@@ -25,7 +25,7 @@
 // Every mbarrier wait is bounded: after about one second the waiter records an
 // error in the status word, raises a block-wide abort flag and every role
 // falls through to the common exit, where outstanding cp.async groups are
-// drained and TMEM is freed.  The host side reports a non-zero status word as
+// drained (cp.async.wait_all) and TMEM is freed.  The host side reports a non-zero status word as
 // MLUOP_STATUS_EXECUTION_FAILED when asked to check it.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -51,9 +51,6 @@ __device__ __forceinline__ unsigned smemAddr(const void *p) { return (unsigned)_
 
 __device__ __forceinline__ void mbarInit(unsigned long long *bar, unsigned count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smemAddr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbarArrive(unsigned long long *bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smemAddr(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbarTryWait(unsigned long long *bar, unsigned parity) {
   unsigned ok;
@@ -88,11 +85,12 @@ __device__ __forceinline__ void cpAsync16(unsigned smem, const void *gmem, bool 
   const int bytes = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem), "l"(gmem), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cpAsyncWait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+// Makes the mbarrier receive one arrival (one of its expected arrivals) once all
+// cp.async operations this thread has issued so far have landed in shared memory.
+__device__ __forceinline__ void cpAsyncArriveOn(unsigned long long *bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smemAddr(bar)) : "memory");
 }
+__device__ __forceinline__ void cpAsyncWaitAll() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 __device__ __forceinline__ void fenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -150,8 +148,8 @@ struct TcConfig {
   static constexpr int kTiles = CO >= 128 ? 2 : 4;              // tiles per block
   static constexpr int kTmemCols = kTiles * CO < 32 ? 32 : kTiles * CO;  // 64, 128 or 256
   static constexpr int kBlocksPerSmByTmem = 512 / kTmemCols;
-  static constexpr int kLag = 2;             // cp.async groups in flight before a stage is signalled
-  static constexpr int kBBuffers = kLag + 1;  // filter slices in flight (see the producer loop)
+  static constexpr int kBBuffers = 3;  // filter slices in flight
+  // gathered tiles in flight; sized so that as many blocks share an SM as tensor memory allows
   static constexpr int kAStages = CI >= 128 ? 3 : (CI >= 64 ? 5 : 6);
   static constexpr int kChunksPerRow = CI / 8;  // 16-byte chunks of one feature row
   // instruction descriptor: D fp32, A and B fp16, both K-major, N = CO, M = 128
@@ -179,20 +177,10 @@ __device__ __forceinline__ unsigned long long makeDesc(unsigned smem_byte_addr) 
 }
 
 // Work items of a block: (offset k ascending, tile t ascending) for which the
-// tile has at least one live row at k; producers and the MMA issuer walk the
-// same sequence, derived from the per-tile live masks.
-struct ItemCursor {
-  int k, t;
-  __device__ __forceinline__ bool next(const unsigned *masks, int K, int tiles) {
-    for (;;) {
-      if (++t >= tiles) {
-        t = 0;
-        if (++k >= K) return false;
-      }
-      if ((masks[t] >> k) & 1u) return true;
-    }
-  }
-};
+// tile has at least one live row at k.  The list is built once per block in
+// shared memory, one byte per item: bit 7 = first item of its offset, bits 2..6
+// = k, bits 0..1 = t.  Producers and the MMA issuer walk the same list.
+constexpr int kMaxItems = 4 * kMaxOffsets;
 
 template <int CI, int CO>
 __global__ void __launch_bounds__(kThreads)
@@ -201,6 +189,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
                   int32_t *status) {
   using Cfg = TcConfig<CI, CO>;
   constexpr int S = Cfg::kAStages, NB = Cfg::kBBuffers, T = Cfg::kTiles;
+  constexpr int CPR = Cfg::kChunksPerRow;  // 16-byte chunks per feature row
   extern __shared__ unsigned char smem_raw[];
   // operand blocks must sit on 1024-byte boundaries (swizzle atoms)
   unsigned char *a_ring = reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
@@ -208,6 +197,8 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   __shared__ unsigned long long a_full[S], a_empty[S], b_empty[NB], accum_bar;
   __shared__ unsigned tmem_base_s;
   __shared__ unsigned masks_s[T];
+  __shared__ unsigned char items_s[kMaxItems];
+  __shared__ int n_items_s;
   __shared__ int abort_s;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -238,89 +229,102 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     if (lane == 0 && any) atomicOr(&masks_s[t], 1u << k);
   }
   __syncthreads();
+  if (tid == 0) {
+    int n = 0;
+    for (int k = 0; k < K; ++k) {
+      unsigned first = 0x80u;
+      for (int t = 0; t < T; ++t) {
+        if ((masks_s[t] >> k) & 1u) {
+          items_s[n++] = (unsigned char)(first | (unsigned)(k << 2) | (unsigned)t);
+          first = 0u;
+        }
+      }
+    }
+    n_items_s = n;
+  }
+  __syncthreads();
+  const int n_items = n_items_s;
   const unsigned tmem_base = tmem_base_s;
   volatile int *abort_flag = &abort_s;
-  unsigned any_mask = 0;
-#pragma unroll
-  for (int t = 0; t < T; ++t) any_mask |= masks_s[t];
 
   if (warp < 4) {
     // ------------------------------------------------------------ producers
-    // Thread `tid` gathers row `tid` of every tile.  Groups of cp.async are
-    // committed per item; a stage is signalled kLag items later, after
-    // cp.async.wait_group + fence.proxy.async, so up to kLag + 1 gathers are in
-    // flight.  The filter slice of offset k travels in the group of the first
-    // item of k; with kLag + 1 filter buffers the slice being overwritten was
-    // last read by items whose stages have all been signalled already, so the
-    // wait on b_empty cannot deadlock.
-    ItemCursor cur{0, -1};
-    bool more = cur.next(masks_s, K, T);
-    // lane l of warp w holds the neighbour id of tile row 32*w + l
-    int idx_next = more ? __ldg(nbr + (size_t)cur.k * n_pad + row0 + cur.t * kTile + tid) : -1;
-    int it = 0, signalled = 0, k_ord = -1, last_k = -1;
-    while (more) {
-      const int k = cur.k;
+    // Warp w gathers rows 32w..32w+31 of every tile; lane l holds the neighbour
+    // id of row 32w+l and hands it to the lanes that fetch that row by shuffle.
+    // Consecutive lanes fetch consecutive 16-byte chunks of one feature row, so a
+    // warp instruction touches 32/CPR rows.  Every byte of a stage is written by
+    // cp.async (zero fill for rows without a neighbour: nothing is read), and
+    // each thread lets the stage's mbarrier collect one arrival when its own
+    // copies have landed, so producers never wait for data: as many gathers are
+    // in flight as there are stages.  The filter slice of offset k travels with
+    // the first item of k.
+    constexpr int kRowsPerInstr = 32 / CPR > 0 ? 32 / CPR : 1;  // rows one warp instruction covers (CPR <= 32)
+    const int rr0 = lane / CPR;         // row (within the instruction's rows) this lane fetches
+    const int chunk = lane % CPR;       // its 16-byte chunk of the row
+    unsigned a_off[CPR];                // byte offset of (row, chunk) inside a stage, swizzled
+#pragma unroll
+    for (int i = 0; i < CPR; ++i) {
+      const int row = warp * 32 + rr0 + i * kRowsPerInstr;
+      const int kb = chunk / (Cfg::kRowBytes / 16), cc = chunk % (Cfg::kRowBytes / 16);
+      unsigned off = (unsigned)(row * Cfg::kRowBytes + cc * 16);
+      off ^= ((off >> 7) & Cfg::kSwizzleMask) << 4;
+      a_off[i] = (unsigned)(kb * Cfg::kABlockBytes) + off;
+    }
+    const unsigned a_ring_addr = smemAddr(a_ring);
+    const __half *feat_chunk = features + chunk * 8;
+    const int32_t *nbr_rows = nbr + row0 + tid;
+
+    int s = 0, b = -1;
+    unsigned a_parity = 0, b_uses = 0;  // a_parity: parity of the current pass over the stage ring
+    int idx_next = -1;
+    if (n_items > 0) {
+      const unsigned c0 = items_s[0];
+      idx_next = __ldg(nbr_rows + (size_t)((c0 >> 2) & 31u) * n_pad + (c0 & 3u) * kTile);
+    }
+    for (int it = 0; it < n_items; ++it) {
+      const unsigned code = items_s[it];
       const int idx = idx_next;
-      more = cur.next(masks_s, K, T);
-      if (more) idx_next = __ldg(nbr + (size_t)cur.k * n_pad + row0 + cur.t * kTile + tid);
-      const int s = it % S;
-      if (it >= S) {
-        if (!mbarWait(&a_empty[s], ((it / S) - 1) & 1, abort_flag, status, 1)) break;
+      if (it + 1 < n_items) {
+        const unsigned c1 = items_s[it + 1];
+        idx_next = __ldg(nbr_rows + (size_t)((c1 >> 2) & 31u) * n_pad + (c1 & 3u) * kTile);
       }
-      if (k != last_k) {
-        last_k = k;
-        ++k_ord;
-        const int b = k_ord % NB;
-        if (k_ord >= NB) {
-          if (!mbarWait(&b_empty[b], ((k_ord / NB) - 1) & 1, abort_flag, status, 8)) break;
+      if (it >= S) {
+        if (!mbarWait(&a_empty[s], a_parity ^ 1u, abort_flag, status, 1)) break;
+      }
+      if (code & 0x80u) {
+        const int k = (code >> 2) & 31u;
+        if (++b == NB) b = 0;
+        if (b_uses >= (unsigned)NB) {
+          if (!mbarWait(&b_empty[b], ((b_uses / NB) - 1u) & 1u, abort_flag, status, 8)) break;
         }
+        ++b_uses;
         unsigned char *b_buf = b_ring + (size_t)b * Cfg::kBBufBytes;
         const __half *wk = filter_kcoci + (size_t)k * CO * CI;
-        for (int e = tid; e < CO * Cfg::kChunksPerRow; e += kProducerThreads) {
-          const int n = e / Cfg::kChunksPerRow, c = e % Cfg::kChunksPerRow;
+        for (int e = tid; e < CO * CPR; e += kProducerThreads) {
+          const int n = e / CPR, c = e % CPR;
           const int kb = c / (Cfg::kRowBytes / 16), cc = c % (Cfg::kRowBytes / 16);
           unsigned off = (unsigned)(n * Cfg::kRowBytes + cc * 16);
           off ^= ((off >> 7) & Cfg::kSwizzleMask) << 4;
           cpAsync16(smemAddr(b_buf + kb * Cfg::kBBlockStride + off), wk + (size_t)n * CI + c * 8, true);
         }
       }
-      unsigned char *a_stage = a_ring + (size_t)s * Cfg::kAStageBytes;
-      // Consecutive lanes fetch consecutive 16-byte chunks of the same feature
-      // row, so one warp instruction touches 32/CPR rows instead of 32.
+      const unsigned stage_addr = a_ring_addr + (unsigned)s * Cfg::kAStageBytes;
 #pragma unroll
-      for (int i = 0; i < Cfg::kChunksPerRow; ++i) {
-        const int e = i * 32 + lane;
-        const int rr = e / Cfg::kChunksPerRow, c = e % Cfg::kChunksPerRow;
-        const int src_row = __shfl_sync(0xffffffffu, idx, rr);
-        const int row = warp * 32 + rr;
-        const int kb = c / (Cfg::kRowBytes / 16), cc = c % (Cfg::kRowBytes / 16);
-        unsigned off = (unsigned)(row * Cfg::kRowBytes + cc * 16);
-        off ^= ((off >> 7) & Cfg::kSwizzleMask) << 4;
-        unsigned char *dst = a_stage + kb * Cfg::kABlockBytes + off;
-        if (src_row >= 0) {
-          cpAsync16(smemAddr(dst), features + (size_t)src_row * CI + c * 8, true);
-        } else {
-          // no neighbour at this offset: the row contributes zeros (nothing is fetched)
-          *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
-        }
+      for (int i = 0; i < CPR; ++i) {
+        const int src_row = __shfl_sync(0xffffffffu, idx, rr0 + i * kRowsPerInstr);
+        const bool valid = src_row >= 0;
+        cpAsync16(stage_addr + a_off[i], feat_chunk + (valid ? (size_t)src_row * CI : 0), valid);
       }
-      cpAsyncCommit();
-      if (it >= Cfg::kLag) {
-        cpAsyncWait<Cfg::kLag>();
-        fenceProxyAsync();
-        mbarArrive(&a_full[signalled % S]);
-        ++signalled;
+      cpAsyncArriveOn(&a_full[s]);
+      if (++s == S) {
+        s = 0;
+        a_parity ^= 1u;
       }
-      ++it;
     }
-    cpAsyncWait<0>();
-    fenceProxyAsync();
-    if (!*abort_flag) {
-      for (; signalled < it; ++signalled) mbarArrive(&a_full[signalled % S]);
-    }
+    cpAsyncWaitAll();
 
     // ------------------------------------------------------------- epilogue
-    bool have_acc = any_mask != 0;
+    bool have_acc = n_items > 0;
     if (have_acc) have_acc = mbarWait(&accum_bar, 0, abort_flag, status, 4);
     tcFenceAfter();
     if (!*abort_flag) {
@@ -354,36 +358,43 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   } else {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      ItemCursor cur{0, -1};
-      bool more = cur.next(masks_s, K, T);
+      const unsigned long long a_desc0 = makeDesc<Cfg>(smemAddr(a_ring));
+      const unsigned long long b_desc0 = makeDesc<Cfg>(smemAddr(b_ring));
       unsigned started = 0;  // tiles whose accumulator has been written
-      int it = 0, k_ord = -1, last_k = -1;
-      while (more) {
-        const int k = cur.k, t = cur.t;
-        more = cur.next(masks_s, K, T);
-        if (k != last_k) {
-          last_k = k;
-          ++k_ord;
+      int s = 0, b = -1;
+      unsigned a_parity = 0;
+      int it = 0;
+      for (; it < n_items; ++it) {
+        const unsigned code = items_s[it];
+        const int t = code & 3u;
+        if (code & 0x80u) {
+          if (++b == NB) b = 0;
         }
-        const int s = it % S, b = k_ord % NB;
-        if (!mbarWait(&a_full[s], (it / S) & 1, abort_flag, status, 2)) break;
+        if (!mbarWait(&a_full[s], a_parity, abort_flag, status, 2)) break;
+        fenceProxyAsync();
         tcFenceAfter();
-        const unsigned a_addr = smemAddr(a_ring + (size_t)s * Cfg::kAStageBytes);
-        const unsigned b_addr = smemAddr(b_ring + (size_t)b * Cfg::kBBufBytes);
+        // only the start-address field (16-byte units) differs between stages and K steps
+        const unsigned long long a_desc = a_desc0 + (unsigned long long)((s * Cfg::kAStageBytes) >> 4);
+        const unsigned long long b_desc = b_desc0 + (unsigned long long)((b * Cfg::kBBufBytes) >> 4);
         const unsigned d_addr = tmem_base + (unsigned)(t * CO);
 #pragma unroll
         for (int j = 0; j < CI / 16; ++j) {
-          const int kb = (j * 32) / Cfg::kRowBytes, within = (j * 32) % Cfg::kRowBytes;
-          const unsigned long long a_desc = makeDesc<Cfg>(a_addr + kb * Cfg::kABlockBytes + within);
-          const unsigned long long b_desc = makeDesc<Cfg>(b_addr + kb * Cfg::kBBlockStride + within);
-          umma(d_addr, a_desc, b_desc, Cfg::kIdesc, (((started >> t) & 1u) || j > 0) ? 1u : 0u);
+          constexpr int kStep = 32;  // bytes of K per MMA
+          const int kb = (j * kStep) / Cfg::kRowBytes, within = (j * kStep) % Cfg::kRowBytes;
+          umma(d_addr, a_desc + (unsigned long long)((kb * Cfg::kABlockBytes + within) >> 4),
+               b_desc + (unsigned long long)((kb * Cfg::kBBlockStride + within) >> 4), Cfg::kIdesc,
+               (((started >> t) & 1u) || j > 0) ? 1u : 0u);
         }
         started |= 1u << t;
         ummaCommit(&a_empty[s]);  // the stage may be refilled once these MMAs have read it
-        if (!more || cur.k != k) ummaCommit(&b_empty[b]);  // last item of offset k: its filter slice is free
-        ++it;
+        // last item of offset k: its filter slice is free once these MMAs are done
+        if (it + 1 == n_items || (items_s[it + 1] & 0x80u)) ummaCommit(&b_empty[b]);
+        if (++s == S) {
+          s = 0;
+          a_parity ^= 1u;
+        }
       }
-      if (it > 0 && !*abort_flag) ummaCommit(&accum_bar);
+      if (it == n_items && n_items > 0 && !*abort_flag) ummaCommit(&accum_bar);
     }
     __syncwarp();
     tcFenceBefore();

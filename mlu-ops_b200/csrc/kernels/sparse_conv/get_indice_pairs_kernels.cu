@@ -15,21 +15,40 @@
 //   from position indice_num[k] on.
 //
 // How: everything is exact int32 arithmetic and every result is deterministic.
-//   subm     hash table lin(j) -> j  (64-bit slots, CAS insert + atomicMax so a
-//            repeated coordinate keeps the largest j), then one probe per (k,j).
-//   default  one occupancy bit per output cell (atomicOr), a prefix popcount
-//            over the bit words gives each active cell its ascending rank, the
-//            same pass decodes out_indices; one {bits, rank} load per (k,j).
-//   both     the matched id of every (k,j) is staged in [K][L] order while
-//            per-tile counts are taken; an exclusive scan over tiles per k
-//            gives every tile its write offset; an order-preserving block
-//            compaction writes the pair lists and the -1 tails, every output
-//            word exactly once.
-// All loops that walk the hash table are bounded by its capacity and report
-// through a status word instead of spinning.
+//
+// Lookup structure, one of
+//   rank       (default mode) one occupancy bit per output cell (atomicOr); a
+//              prefix popcount over the bit words gives each active cell its
+//              ascending rank and the same pass decodes out_indices; a lookup is
+//              one {bits, rank} load and neighbouring cells share words.
+//   hash       (submanifold, sparse grid) table lin(j) -> j in 64-bit slots, CAS
+//              insert + atomicMax so a repeated coordinate keeps the largest j.
+//   rank+perm  (submanifold, dense grid) the occupancy/rank table over the
+//              input grid plus perm[rank] = row id (atomicMax): a miss costs one
+//              shared word, a hit one more load.
+//
+// Pair lists, one of
+//   two pass   (default) matches are staged in [K][L] order with per-tile
+//              counts, an exclusive scan over tiles per offset gives the write
+//              offsets, a compaction kernel writes lists and -1 tails, every
+//              word of indice_pairs exactly once.
+//   single pass (opt-in, kernel volume <= 32): a block takes a tile of 256 voxels by
+//              ticket, keeps the tile's matches in shared memory, publishes its
+//              per-offset counts and obtains its write offsets by decoupled
+//              look-back over the preceding tiles' descriptors, then writes its
+//              pairs in place; a second kernel writes the -1 tails.  indice_pairs
+//              is written exactly once and nothing is staged in global memory.
+//
+// Every wait is bounded: hash probes by the table capacity, the look-back spin
+// by about one second of clock; both report through a status word instead of
+// spinning on.
 #include "kernels/sparse_conv/get_indice_pairs_kernels.h"
 
 #include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <string>
 
 #include "core/trace.h"
 
@@ -39,6 +58,7 @@ namespace sparse_conv {
 namespace {
 
 constexpr unsigned long long kEmptySlot = 0xFFFFFFFFFFFFFFFFull;
+constexpr long long kLookBackCycles = 2000000000ll;  // a look-back wait gives up after about a second
 
 __host__ __device__ inline size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -52,8 +72,8 @@ __device__ __forceinline__ uint32_t mixKey(uint32_t x) {
 }
 
 // Exclusive scan of one int per thread over the block; *total gets the sum.
-// blockDim.x must be a multiple of 32 and at most 1024.
-__device__ __forceinline__ int blockExclusiveScan(int v, int *total, int *warp_sums /* [32] shared */) {
+// blockDim.x must be a multiple of 32 and at most 1024; warp_sums holds 33 ints.
+__device__ __forceinline__ int blockExclusiveScan(int v, int *total, int *warp_sums) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int incl = v;
 #pragma unroll
@@ -82,12 +102,29 @@ __device__ __forceinline__ int blockExclusiveScan(int v, int *total, int *warp_s
   return result;
 }
 
+__device__ __forceinline__ int warpSum(int v) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+  return v;
+}
+
 __device__ __forceinline__ bool rowInRange(const int4 c, const PairsGeometry &g) {
   return (unsigned)c.x < (unsigned)g.batch && (unsigned)c.y < (unsigned)g.in_space[0] &&
          (unsigned)c.z < (unsigned)g.in_space[1] && (unsigned)c.w < (unsigned)g.in_space[2];
 }
 
-// ---------------------------------------------------------------- subm hash
+__device__ __forceinline__ uint32_t inputLinear(const int4 c, const PairsGeometry &g) {
+  return (uint32_t)(((c.x * g.in_space[0] + c.y) * g.in_space[1] + c.z) * g.in_space[2] + c.w);
+}
+
+struct LookupTables {
+  const unsigned long long *slots;  // hash
+  uint32_t mask;
+  const uint2 *rank_table;  // rank, rank + perm
+  const int32_t *perm;      // rank + perm
+};
+
+// ---------------------------------------------------------------- hash table
 
 __global__ void __launch_bounds__(256)
 hashInsertKernel(PairsGeometry g, const int4 *__restrict__ indices, unsigned long long *slots,
@@ -96,8 +133,7 @@ hashInsertKernel(PairsGeometry g, const int4 *__restrict__ indices, unsigned lon
   if (j >= g.L) return;
   const int4 c = indices[j];
   if (!rowInRange(c, g)) return;
-  const uint32_t lin =
-      (uint32_t)(((c.x * g.in_space[0] + c.y) * g.in_space[1] + c.z) * g.in_space[2] + c.w);
+  const uint32_t lin = inputLinear(c, g);
   const unsigned long long packed = ((unsigned long long)lin << 32) | (uint32_t)j;
   uint32_t h = mixKey(lin) & mask;
   for (uint32_t probe = 0; probe <= mask; ++probe) {
@@ -129,9 +165,15 @@ __device__ __forceinline__ int hashLookup(const unsigned long long *__restrict__
   return -1;
 }
 
-// ------------------------------------------------------- default-mode bits
+// ------------------------------------------------------- occupancy-bit table
 
-// Sets the occupancy bit of every valid output cell.
+__device__ __forceinline__ void setBit(uint2 *rank_table, uint32_t lin) {
+  const uint32_t bit = 1u << (lin & 31);
+  uint32_t *word = &rank_table[lin >> 5].x;
+  if (!(*(volatile uint32_t *)word & bit)) atomicOr(word, bit);
+}
+
+// default mode: the occupancy bit of every valid output cell
 __global__ void __launch_bounds__(256)
 markOutputsKernel(PairsGeometry g, const int4 *__restrict__ indices, uint2 *rank_table) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
@@ -154,13 +196,19 @@ markOutputsKernel(PairsGeometry g, const int4 *__restrict__ indices, uint2 *rank
         if (tw < 0 || tw % g.stride[2]) continue;
         const int ow = tw / g.stride[2];
         if (ow >= g.out_space[2]) continue;
-        const uint32_t lin = (uint32_t)(base_b + (od * g.out_space[1] + oh) * g.out_space[2] + ow);
-        const uint32_t bit = 1u << (lin & 31);
-        uint32_t *word = &rank_table[lin >> 5].x;
-        if (!(*(volatile uint32_t *)word & bit)) atomicOr(word, bit);
+        setBit(rank_table, (uint32_t)(base_b + (od * g.out_space[1] + oh) * g.out_space[2] + ow));
       }
     }
   }
+}
+
+// submanifold mode: the occupancy bit of every input voxel
+__global__ void __launch_bounds__(256)
+markInputsKernel(PairsGeometry g, const int4 *__restrict__ indices, uint2 *rank_table) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= g.L) return;
+  const int4 c = indices[j];
+  if (rowInRange(c, g)) setBit(rank_table, inputLinear(c, g));
 }
 
 // chunk_count[c] = set bits in words [c*1024, (c+1)*1024)
@@ -193,12 +241,12 @@ scanSingleBlockKernel(int32_t *data, int n, int32_t *total_out) {
   if (threadIdx.x == 0) *total_out = running;
 }
 
-// Gives every occupancy word its exclusive rank and writes the coordinates of
-// the active cells, in ascending linear order, to out_indices.
+// Gives every occupancy word its exclusive rank; with DECODE also writes the
+// coordinates of the active cells, in ascending linear order, to out_indices.
+template <bool DECODE>
 __global__ void __launch_bounds__(256)
-rankAndDecodeKernel(PairsGeometry g, uint2 *rank_table, int64_t words,
-                    const int32_t *__restrict__ chunk_offset, int4 *out_indices, int64_t out_rows,
-                    int32_t *status) {
+rankKernel(PairsGeometry g, uint2 *rank_table, int64_t words, const int32_t *__restrict__ chunk_offset,
+           int4 *out_indices, int64_t out_rows, int32_t *status) {
   __shared__ int warp_sums[33];
   const int64_t w0 = (int64_t)blockIdx.x * kRankChunkWords + threadIdx.x * 4;
   uint32_t bits[4];
@@ -215,6 +263,10 @@ rankAndDecodeKernel(PairsGeometry g, uint2 *rank_table, int64_t words,
   for (int i = 0; i < 4; ++i) {
     if (w0 + i >= words) break;
     rank_table[w0 + i].y = (uint32_t)rank;
+    if (!DECODE) {
+      rank += __popc(bits[i]);
+      continue;
+    }
     uint32_t b = bits[i];
     while (b) {
       const int bit = __ffs(b) - 1;
@@ -237,6 +289,19 @@ rankAndDecodeKernel(PairsGeometry g, uint2 *rank_table, int64_t words,
   }
 }
 
+// submanifold rank + perm: perm[rank of voxel j's cell] = j (largest j wins)
+__global__ void __launch_bounds__(256)
+permKernel(PairsGeometry g, const int4 *__restrict__ indices, const uint2 *__restrict__ rank_table,
+           int32_t *perm) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= g.L) return;
+  const int4 c = indices[j];
+  if (!rowInRange(c, g)) return;
+  const uint32_t lin = inputLinear(c, g);
+  const uint2 e = __ldg(rank_table + (lin >> 5));
+  atomicMax(&perm[e.y + __popc(e.x & ((1u << (lin & 31)) - 1u))], j);
+}
+
 // out_indices rows from the active count on are -1 (the CPU path initialises
 // the whole tensor to -1 before filling it).
 __global__ void __launch_bounds__(256)
@@ -245,26 +310,23 @@ fillInactiveRowsKernel(int4 *out_indices, int64_t out_rows, const int32_t *n_act
   if (r < out_rows && r >= *n_active) out_indices[r] = make_int4(-1, -1, -1, -1);
 }
 
-// ------------------------------------------------------------ probe + count
+// ------------------------------------------------------------------- lookups
 
-// One thread per input voxel walks the K offsets.  match[k][j] = output id or
-// -1; tile_count[k][tile] = matches of this tile at offset k.
-template <bool SUBM>
-__global__ void __launch_bounds__(kPairsTile)
-probeCountKernel(PairsGeometry g, const int4 *__restrict__ indices,
-                 const unsigned long long *__restrict__ slots, uint32_t mask,
-                 const uint2 *__restrict__ rank_table, int32_t *__restrict__ match,
-                 int32_t *__restrict__ tile_count, int tiles, int32_t *status) {
-  extern __shared__ int s_count[];  // [K]
-  for (int k = threadIdx.x; k < g.K; k += blockDim.x) s_count[k] = 0;
-  __syncthreads();
-  const int j = blockIdx.x * kPairsTile + threadIdx.x;
-  const bool live = j < g.L;
-  int4 c = make_int4(0, 0, 0, 0);
-  if (live) c = indices[j];
-  const bool row_ok = live && rowInRange(c, g);
+template <int LOOKUP>
+__device__ __forceinline__ int lookupOutput(const LookupTables &t, uint32_t lin, int32_t *status) {
+  if (LOOKUP == kLookupHash) return hashLookup(t.slots, t.mask, lin, status);
+  const uint2 e = __ldg(t.rank_table + (lin >> 5));
+  const uint32_t bit = lin & 31;
+  if (LOOKUP == kLookupRank) return (int)(e.y + __popc(e.x & ((1u << bit) - 1u)));  // always occupied
+  if (!((e.x >> bit) & 1u)) return -1;
+  return __ldg(t.perm + e.y + __popc(e.x & ((1u << bit) - 1u)));
+}
+
+// Walks the K offsets of one voxel; emit(k, output id or -1) is called for every k in order.
+template <int LOOKUP, typename Emit>
+__device__ __forceinline__ void walkOffsets(const PairsGeometry &g, const LookupTables &tables, const int4 c,
+                                            bool row_ok, int32_t *status, Emit emit) {
   const int base_b = c.x * g.out_vol;
-  const int lane = threadIdx.x & 31;
   int k = 0;
   for (int kd = 0; kd < g.ks[0]; ++kd) {
     const int td = c.y + g.pad[0] - kd * g.dil[0];
@@ -281,19 +343,140 @@ probeCountKernel(PairsGeometry g, const int4 *__restrict__ indices,
         int v = -1;
         if (ok) {
           const uint32_t lin = (uint32_t)(base_b + (od * g.out_space[1] + oh) * g.out_space[2] + ow);
-          if (SUBM) {
-            v = hashLookup(slots, mask, lin, status);
-          } else {
-            const uint2 e = __ldg(rank_table + (lin >> 5));
-            v = (int)(e.y + __popc(e.x & ((1u << (lin & 31)) - 1u)));
-          }
+          v = lookupOutput<LOOKUP>(tables, lin, status);
         }
-        if (live) match[(size_t)k * g.L + j] = v;
-        const unsigned m = __ballot_sync(0xffffffffu, v >= 0);
-        if (lane == 0 && m) atomicAdd(&s_count[k], __popc(m));
+        emit(k, v);
       }
     }
   }
+}
+
+// ------------------------------------------------------------ single pass
+
+constexpr uint32_t kStateAggregate = 1u << 30;  // the tile's own count is known
+constexpr uint32_t kStatePrefix = 2u << 30;     // the inclusive count up to this tile is known
+constexpr uint32_t kStateValue = (1u << 30) - 1u;
+constexpr int kTileWarps = kPairsTile / 32;
+
+// One block per tile of 256 voxels (tiles are handed out by ticket so that every
+// tile a block waits for is already running or done).
+//   1. probe: match[k][thread] and per-warp counts in shared memory
+//   2. per offset k (warps share the offsets): publish the tile's count, look
+//      back over earlier tiles until a published prefix is met, publish the
+//      inclusive prefix; the last tile writes indice_num
+//   3. write the tile's pairs at offset + rank inside the tile, ascending j
+template <int LOOKUP>
+__global__ void __launch_bounds__(kPairsTile)
+probeWriteKernel(PairsGeometry g, const int4 *__restrict__ indices, LookupTables tables, uint32_t *tile_state,
+                 int tiles, int32_t *__restrict__ indice_pairs, int32_t *__restrict__ indice_num,
+                 int32_t *status) {
+  extern __shared__ int smem_i[];
+  int *match_s = smem_i;                            // [K][256]
+  int *warp_count_s = match_s + g.K * kPairsTile;    // [K][8]
+  int *offset_s = warp_count_s + g.K * kTileWarps;   // [K]
+  __shared__ int tile_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) tile_s = atomicAdd(status + 2, 1);
+  __syncthreads();
+  const int tile = tile_s;
+  const int j = tile * kPairsTile + threadIdx.x;
+  const bool live = j < g.L;
+  int4 c = make_int4(0, 0, 0, 0);
+  if (live) c = indices[j];
+  walkOffsets<LOOKUP>(g, tables, c, live && rowInRange(c, g), status, [&](int k, int v) {
+    match_s[k * kPairsTile + threadIdx.x] = v;
+    const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
+    if (lane == 0) warp_count_s[k * kTileWarps + warp] = __popc(hits);
+  });
+  __syncthreads();
+
+  for (int k = warp; k < g.K; k += kTileWarps) {
+    const int mine = warpSum(lane < kTileWarps ? warp_count_s[k * kTileWarps + lane] : 0);
+    volatile uint32_t *state = tile_state + (size_t)k * tiles;
+    int before = 0;
+    if (tile > 0) {
+      if (lane == 0) state[tile] = kStateAggregate | (uint32_t)mine;
+      int pos = tile - 1;  // the window covers tiles pos, pos-1, ..., pos-31
+      const long long t0 = clock64();
+      for (;;) {
+        const int idx = pos - lane;
+        uint32_t w = 2u << 30;  // before tile 0: prefix 0
+        if (idx >= 0) w = state[idx];
+        const unsigned prefix_lanes = __ballot_sync(0xffffffffu, (w >> 30) == 2u);
+        const int first = prefix_lanes ? __ffs(prefix_lanes) - 1 : 31;
+        const unsigned needed = first == 31 ? 0xffffffffu : ((2u << first) - 1u);
+        const unsigned empty_lanes = __ballot_sync(0xffffffffu, (w >> 30) == 0u);
+        if (empty_lanes & needed) {  // a tile in the window has not published yet
+          if (clock64() - t0 > kLookBackCycles) {
+            if (lane == 0) atomicOr(status, kPairsErrLookBack);
+            break;
+          }
+          continue;
+        }
+        before += warpSum(lane <= first ? (int)(w & kStateValue) : 0);
+        if (prefix_lanes) break;
+        pos -= 32;
+      }
+    }
+    if (lane == 0) {
+      state[tile] = kStatePrefix | (uint32_t)(before + mine);
+      offset_s[k] = before;
+      if (tile == tiles - 1) indice_num[k] = before + mine;
+    }
+  }
+  __syncthreads();
+
+  for (int k = 0; k < g.K; ++k) {
+    const int v = match_s[k * kPairsTile + threadIdx.x];
+    const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
+    if (v >= 0) {
+      int p = offset_s[k] + __popc(hits & ((1u << lane) - 1u));
+      for (int w = 0; w < warp; ++w) p += warp_count_s[k * kTileWarps + w];
+      int32_t *in_row = indice_pairs + (size_t)k * 2 * g.L;
+      in_row[p] = j;
+      in_row[g.L + p] = v;
+    }
+  }
+}
+
+// -1 from position indice_num[k] on, both rows of every offset.
+__global__ void __launch_bounds__(256)
+fillTailsKernel(int L, const int32_t *__restrict__ indice_num, int32_t *__restrict__ indice_pairs) {
+  const int k = blockIdx.y;
+  const int first = indice_num[k];
+  const int base = blockIdx.x * 2048;
+  if (base + 2048 <= first) return;
+  int32_t *in_row = indice_pairs + (size_t)k * 2 * L;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int p = base + i * 256 + threadIdx.x;
+    if (p >= first && p < L) {
+      in_row[p] = -1;
+      in_row[L + p] = -1;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- two pass
+
+// match[k][j] = output id or -1; tile_count[k][tile] = matches of this tile at offset k.
+template <int LOOKUP>
+__global__ void __launch_bounds__(kPairsTile)
+probeCountKernel(PairsGeometry g, const int4 *__restrict__ indices, LookupTables tables,
+                 int32_t *__restrict__ match, int32_t *__restrict__ tile_count, int tiles, int32_t *status) {
+  extern __shared__ int s_count[];  // [K]
+  for (int k = threadIdx.x; k < g.K; k += blockDim.x) s_count[k] = 0;
+  __syncthreads();
+  const int j = blockIdx.x * kPairsTile + threadIdx.x;
+  const bool live = j < g.L;
+  int4 c = make_int4(0, 0, 0, 0);
+  if (live) c = indices[j];
+  const int lane = threadIdx.x & 31;
+  walkOffsets<LOOKUP>(g, tables, c, live && rowInRange(c, g), status, [&](int k, int v) {
+    if (live) match[(size_t)k * g.L + j] = v;
+    const unsigned m = __ballot_sync(0xffffffffu, v >= 0);
+    if (lane == 0 && m) atomicAdd(&s_count[k], __popc(m));
+  });
   __syncthreads();
   for (int kk = threadIdx.x; kk < g.K; kk += blockDim.x)
     tile_count[(size_t)kk * tiles + blockIdx.x] = s_count[kk];
@@ -327,7 +510,7 @@ constexpr int kWriteSegTiles = 8;
 __global__ void __launch_bounds__(kPairsTile)
 writePairsKernel(int L, const int32_t *__restrict__ match, const int32_t *__restrict__ tile_offset,
                  int tiles, const int32_t *__restrict__ indice_num, int32_t *__restrict__ indice_pairs) {
-  __shared__ int warp_count[2][kPairsTile / 32];
+  __shared__ int warp_count[2][kTileWarps];
   const int k = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int total = indice_num[k];
@@ -363,36 +546,123 @@ writePairsKernel(int L, const int32_t *__restrict__ match, const int32_t *__rest
   }
 }
 
+std::string envChoice(const char *name) {
+  const char *v = std::getenv(name);
+  return v ? std::string(v) : std::string();
+}
+
 }  // namespace
 
 PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g) {
+  // MLUOP_B200_PAIRS_LOOKUP=hash|rank overrides the automatic choice of the
+  // submanifold lookup structure; MLUOP_B200_PAIRS_PATH=fused selects the
+  // single-pass pair-list path (both are cross-checked by the tests).
+  static const std::string lookup_env = envChoice("MLUOP_B200_PAIRS_LOOKUP");
+  static const std::string path_env = envChoice("MLUOP_B200_PAIRS_PATH");
   PairsWorkspacePlan p{};
   p.tiles = (g.L + kPairsTile - 1) / kPairsTile;
+  const int64_t cells = (int64_t)g.batch * g.out_vol;  // submanifold: input space == output space
+  if (!g.sub_m) {
+    p.lookup = kLookupRank;
+  } else if (lookup_env == "hash") {
+    p.lookup = kLookupHash;
+  } else if (lookup_env == "rank") {
+    p.lookup = kLookupRankPerm;
+  } else {
+    p.lookup = cells <= kDenseCellsPerVoxel * (int64_t)g.L ? kLookupRankPerm : kLookupHash;
+  }
+  // The single-pass path is opt-in: on B200 about a thousand tiles finish their
+  // probes in lockstep, so the look-back chain (32 tiles per L2 round trip, per
+  // offset) costs more than the staged matches of the two-pass path save.
+  p.fused = (g.K <= kFusedMaxOffsets && path_env == "fused") ? 1 : 0;
   size_t off = 0;
   p.status = off;
   off = alignUp(off + 64 * sizeof(int32_t), 256);
+  p.tile_state = off;
   p.match = off;
-  off = alignUp(off + (size_t)g.K * g.L * sizeof(int32_t), 256);
   p.tile_count = off;
-  off = alignUp(off + (size_t)g.K * p.tiles * sizeof(int32_t), 256);
+  if (p.fused) {
+    off = alignUp(off + (size_t)g.K * p.tiles * sizeof(uint32_t), 256);
+  } else {
+    off = alignUp(off + (size_t)g.K * g.L * sizeof(int32_t), 256);
+    p.tile_count = off;
+    off = alignUp(off + (size_t)g.K * p.tiles * sizeof(int32_t), 256);
+  }
   p.table = off;
-  if (g.sub_m) {
+  p.chunk_count = off;
+  p.perm = off;
+  if (p.lookup == kLookupHash) {
     uint32_t cap = 64;
     while ((uint64_t)cap < 2ull * (uint64_t)g.L) cap <<= 1;
     p.hash_capacity = cap;
     off = alignUp(off + (size_t)cap * sizeof(unsigned long long), 256);
-    p.chunk_count = off;
   } else {
-    const int64_t cells = (int64_t)g.batch * g.out_vol;
     p.rank_words = (cells + 31) / 32;
     p.rank_chunks = (int32_t)((p.rank_words + kRankChunkWords - 1) / kRankChunkWords);
     off = alignUp(off + (size_t)p.rank_words * sizeof(uint2), 256);
     p.chunk_count = off;
     off = alignUp(off + (size_t)p.rank_chunks * sizeof(int32_t), 256);
+    if (p.lookup == kLookupRankPerm) {
+      p.perm = off;
+      off = alignUp(off + (size_t)g.L * sizeof(int32_t), 256);
+    }
   }
   p.total = off + 256;  // slack to align the caller's pointer
   return p;
 }
+
+namespace {
+
+template <int LOOKUP>
+void launchPairLists(const PairsGeometry &g, const PairsWorkspacePlan &plan, const int4 *rows,
+                     const LookupTables &tables, char *base, int32_t *indice_pairs, int32_t *indice_num,
+                     int32_t *status, cudaStream_t stream) {
+  const int tiles = plan.tiles;
+  const double L = g.L, KL = (double)g.K * g.L;
+  static const char *names_fused[] = {"probeWriteKernel<rank>", "probeWriteKernel<hash>",
+                                      "probeWriteKernel<rank+perm>"};
+  static const char *names_count[] = {"probeCountKernel<rank>", "probeCountKernel<hash>",
+                                      "probeCountKernel<rank+perm>"};
+  if (plan.fused) {
+    uint32_t *tile_state = reinterpret_cast<uint32_t *>(base + plan.tile_state);
+    {
+      trace::Scope t("memset:tile_state", stream, 4.0 * g.K * tiles);
+      cudaMemsetAsync(tile_state, 0, (size_t)g.K * tiles * sizeof(uint32_t), stream);
+    }
+    {
+      // per voxel: its coordinates; the matched pairs are written by this kernel
+      trace::Scope t(names_fused[LOOKUP], stream, 16.0 * L);
+      const size_t smem = (size_t)g.K * (kPairsTile + kTileWarps + 1) * sizeof(int);
+      probeWriteKernel<LOOKUP><<<tiles, kPairsTile, smem, stream>>>(g, rows, tables, tile_state, tiles,
+                                                                    indice_pairs, indice_num, status);
+    }
+    {
+      trace::Scope t("fillTailsKernel", stream, 8.0 * KL);
+      fillTailsKernel<<<dim3((unsigned)((g.L + 2047) / 2048), g.K), 256, 0, stream>>>(g.L, indice_num,
+                                                                                     indice_pairs);
+    }
+    return;
+  }
+  int32_t *match = reinterpret_cast<int32_t *>(base + plan.match);
+  int32_t *tile_count = reinterpret_cast<int32_t *>(base + plan.tile_count);
+  {
+    trace::Scope t(names_count[LOOKUP], stream, 16.0 * L + 4.0 * KL);
+    probeCountKernel<LOOKUP><<<tiles, kPairsTile, (size_t)g.K * sizeof(int), stream>>>(
+        g, rows, tables, match, tile_count, tiles, status);
+  }
+  {
+    trace::Scope t("scanTilesKernel", stream, 8.0 * g.K * tiles);
+    scanTilesKernel<<<g.K, 1024, 0, stream>>>(tile_count, tiles, indice_num);
+  }
+  {
+    trace::Scope t("writePairsKernel", stream, 12.0 * KL);
+    const unsigned segments = (unsigned)((tiles + kWriteSegTiles - 1) / kWriteSegTiles);
+    writePairsKernel<<<dim3(segments, g.K), kPairsTile, 0, stream>>>(g.L, match, tile_count, tiles, indice_num,
+                                                                    indice_pairs);
+  }
+}
+
+}  // namespace
 
 cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePlan &plan,
                                  const int32_t *indices, void *workspace, int32_t *indice_pairs,
@@ -400,57 +670,41 @@ cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePla
                                  int32_t *status_host, cudaStream_t stream) {
   char *base = reinterpret_cast<char *>(alignUp(reinterpret_cast<size_t>(workspace), 256));
   int32_t *status = reinterpret_cast<int32_t *>(base + plan.status);
-  int32_t *match = reinterpret_cast<int32_t *>(base + plan.match);
-  int32_t *tile_count = reinterpret_cast<int32_t *>(base + plan.tile_count);
   const int4 *rows = reinterpret_cast<const int4 *>(indices);
   const int tiles = plan.tiles;
-  const size_t count_smem = (size_t)g.K * sizeof(int);
-  const double L = g.L, KL = (double)g.K * g.L;
+  const double L = g.L;
+  LookupTables tables{};
   cudaError_t err;
 
   if ((err = cudaMemsetAsync(status, 0, 64 * sizeof(int32_t), stream)) != cudaSuccess) return err;
-  if (g.sub_m) {
+
+  if (plan.lookup == kLookupHash) {
     unsigned long long *slots = reinterpret_cast<unsigned long long *>(base + plan.table);
-    const uint32_t mask = plan.hash_capacity - 1;
+    tables.slots = slots;
+    tables.mask = plan.hash_capacity - 1;
     {
       trace::Scope t("memset:hash_table", stream, 8.0 * plan.hash_capacity);
       if ((err = cudaMemsetAsync(slots, 0xFF, (size_t)plan.hash_capacity * sizeof(unsigned long long),
                                  stream)) != cudaSuccess)
         return err;
     }
-    {
-      trace::Scope t("hashInsertKernel", stream, 16.0 * L + 8.0 * L);
-      hashInsertKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, slots, mask, status);
-    }
-    {
-      // out_indices = indices for the first L rows, -1 beyond
-      trace::Scope t("memcpy:out_indices", stream, 32.0 * L);
-      const int64_t copy_rows = out_rows < g.L ? out_rows : (int64_t)g.L;
-      if ((err = cudaMemcpyAsync(out_indices, indices, (size_t)copy_rows * 4 * sizeof(int32_t),
-                                 cudaMemcpyDeviceToDevice, stream)) != cudaSuccess)
-        return err;
-      if (out_rows > g.L) {
-        if ((err = cudaMemsetAsync(out_indices + (size_t)g.L * 4, 0xFF,
-                                   (size_t)(out_rows - g.L) * 4 * sizeof(int32_t), stream)) != cudaSuccess)
-          return err;
-      }
-    }
-    {
-      trace::Scope t("probeCountKernel<subm>", stream, 16.0 * L + 4.0 * KL);
-      probeCountKernel<true><<<tiles, kPairsTile, count_smem, stream>>>(
-          g, rows, slots, mask, nullptr, match, tile_count, tiles, status);
-    }
+    trace::Scope t("hashInsertKernel", stream, 16.0 * L + 8.0 * L);
+    hashInsertKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, slots, tables.mask, status);
   } else {
     uint2 *rank_table = reinterpret_cast<uint2 *>(base + plan.table);
     int32_t *chunk_count = reinterpret_cast<int32_t *>(base + plan.chunk_count);
     const double words = (double)plan.rank_words;
+    tables.rank_table = rank_table;
     {
       trace::Scope t("memset:rank_table", stream, 8.0 * words);
       if ((err = cudaMemsetAsync(rank_table, 0, (size_t)plan.rank_words * sizeof(uint2), stream)) !=
           cudaSuccess)
         return err;
     }
-    {
+    if (g.sub_m) {
+      trace::Scope t("markInputsKernel", stream, 16.0 * L);
+      markInputsKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table);
+    } else {
       trace::Scope t("markOutputsKernel", stream, 16.0 * L);
       markOutputsKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table);
     }
@@ -462,33 +716,55 @@ cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePla
       trace::Scope t("scanSingleBlockKernel", stream, 8.0 * plan.rank_chunks);
       scanSingleBlockKernel<<<1, 1024, 0, stream>>>(chunk_count, plan.rank_chunks, status + 1);
     }
-    {
-      trace::Scope t("rankAndDecodeKernel", stream, 16.0 * words);
-      rankAndDecodeKernel<<<plan.rank_chunks, 256, 0, stream>>>(
-          g, rank_table, plan.rank_words, chunk_count, reinterpret_cast<int4 *>(out_indices), out_rows,
-          status);
-    }
-    {
+    if (g.sub_m) {
+      int32_t *perm = reinterpret_cast<int32_t *>(base + plan.perm);
+      tables.perm = perm;
+      {
+        trace::Scope t("rankKernel", stream, 16.0 * words);
+        rankKernel<false><<<plan.rank_chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words, chunk_count,
+                                                               nullptr, 0, status);
+      }
+      if ((err = cudaMemsetAsync(perm, 0xFF, (size_t)g.L * sizeof(int32_t), stream)) != cudaSuccess) return err;
+      trace::Scope t("permKernel", stream, 20.0 * L);
+      permKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table, perm);
+    } else {
+      {
+        trace::Scope t("rankAndDecodeKernel", stream, 16.0 * words);
+        rankKernel<true><<<plan.rank_chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words, chunk_count,
+                                                              reinterpret_cast<int4 *>(out_indices), out_rows,
+                                                              status);
+      }
       trace::Scope t("fillInactiveRowsKernel", stream, 16.0 * (double)out_rows);
       const unsigned fill_blocks = (unsigned)((out_rows + 255) / 256);
-      fillInactiveRowsKernel<<<fill_blocks, 256, 0, stream>>>(reinterpret_cast<int4 *>(out_indices),
-                                                             out_rows, status + 1);
-    }
-    {
-      trace::Scope t("probeCountKernel<default>", stream, 16.0 * L + 4.0 * KL);
-      probeCountKernel<false><<<tiles, kPairsTile, count_smem, stream>>>(
-          g, rows, nullptr, 0, rank_table, match, tile_count, tiles, status);
+      fillInactiveRowsKernel<<<fill_blocks, 256, 0, stream>>>(reinterpret_cast<int4 *>(out_indices), out_rows,
+                                                             status + 1);
     }
   }
-  {
-    trace::Scope t("scanTilesKernel", stream, 8.0 * g.K * tiles);
-    scanTilesKernel<<<g.K, 1024, 0, stream>>>(tile_count, tiles, indice_num);
+
+  if (g.sub_m) {
+    // out_indices = indices for the first L rows, -1 beyond
+    trace::Scope t("memcpy:out_indices", stream, 32.0 * L);
+    const int64_t copy_rows = out_rows < g.L ? out_rows : (int64_t)g.L;
+    if ((err = cudaMemcpyAsync(out_indices, indices, (size_t)copy_rows * 4 * sizeof(int32_t),
+                               cudaMemcpyDeviceToDevice, stream)) != cudaSuccess)
+      return err;
+    if (out_rows > g.L) {
+      if ((err = cudaMemsetAsync(out_indices + (size_t)g.L * 4, 0xFF,
+                                 (size_t)(out_rows - g.L) * 4 * sizeof(int32_t), stream)) != cudaSuccess)
+        return err;
+    }
   }
-  {
-    trace::Scope t("writePairsKernel", stream, 12.0 * KL);
-    const unsigned segments = (unsigned)((tiles + kWriteSegTiles - 1) / kWriteSegTiles);
-    writePairsKernel<<<dim3(segments, g.K), kPairsTile, 0, stream>>>(g.L, match, tile_count, tiles, indice_num,
-                                                                    indice_pairs);
+
+  switch (plan.lookup) {
+    case kLookupHash:
+      launchPairLists<kLookupHash>(g, plan, rows, tables, base, indice_pairs, indice_num, status, stream);
+      break;
+    case kLookupRankPerm:
+      launchPairLists<kLookupRankPerm>(g, plan, rows, tables, base, indice_pairs, indice_num, status, stream);
+      break;
+    default:
+      launchPairLists<kLookupRank>(g, plan, rows, tables, base, indice_pairs, indice_num, status, stream);
+      break;
   }
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
   return cudaMemcpyAsync(status_host, status, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, stream);

@@ -27,25 +27,45 @@ struct PairsGeometry {
   int32_t sub_m;
 };
 
+// How (k, voxel) -> output id is looked up.
+enum PairsLookup {
+  kLookupRank = 0,      // default mode: occupancy bits + prefix rank over the output grid
+  kLookupHash = 1,      // submanifold, sparse grid: hash table lin -> row id
+  kLookupRankPerm = 2,  // submanifold, dense grid: occupancy bits + rank, then rank -> row id
+};
+
+// A submanifold rulebook uses the occupancy-bit table instead of the hash table
+// when the grid has at most this many cells per input voxel: the table is then
+// small, and neighbouring cells share its words, which a hash table cannot offer.
+constexpr int64_t kDenseCellsPerVoxel = 512;
+// Kernel volumes up to this size can take the opt-in single-pass path (matches
+// of a tile stay in shared memory).
+constexpr int kFusedMaxOffsets = 32;
+
 // Byte offsets of the scratch arrays inside the (256-byte aligned) workspace.
 struct PairsWorkspacePlan {
-  size_t status;      // int32[64]: [0] error bits, [1] number of active outputs
-  size_t match;       // int32[K][L]: output id matched by (k, j), -1 if none
-  size_t tile_count;  // int32[K][tiles]: matches per tile, then exclusive offsets
-  size_t table;       // subm: uint64[capacity] hash slots; default: uint2[words] {bits, rank}
-  size_t chunk_count; // default mode: int32[chunks]
+  size_t status;      // int32[64]: [0] error bits, [1] number of active outputs, [2] tile ticket counter
+  size_t tile_state;  // fused path: uint32[K][tiles] look-back descriptors {2-bit state, 30-bit count}
+  size_t match;       // two-pass path: int32[K][L] output id matched by (k, j), -1 if none
+  size_t tile_count;  // two-pass path: int32[K][tiles] matches per tile, then exclusive offsets
+  size_t table;       // hash: uint64[capacity] slots; rank: uint2[words] {occupancy bits, exclusive rank}
+  size_t chunk_count; // rank: int32[chunks]
+  size_t perm;        // rank + perm: int32[L] row id of the r-th occupied cell
   size_t total;       // bytes including alignment slack
   int32_t tiles;
-  uint32_t hash_capacity;  // subm: power of two >= 2L
-  int64_t rank_words;      // default: ceil(batch*out_vol / 32)
+  int32_t lookup;          // PairsLookup
+  int32_t fused;           // 1: single-pass path
+  uint32_t hash_capacity;  // hash: power of two >= 2L
+  int64_t rank_words;      // rank: ceil(cells / 32)
   int32_t rank_chunks;
 };
 
 PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g);
 
 // Error bits in status[0].
-constexpr int kPairsErrHashFull = 1;      // hash probe ran through the whole table
+constexpr int kPairsErrHashFull = 1;         // hash probe ran through the whole table
 constexpr int kPairsErrOutIndicesSmall = 2;  // more active outputs than out_indices rows
+constexpr int kPairsErrLookBack = 4;         // a bounded look-back wait gave up
 
 // Enqueues the whole rulebook computation on `stream`.  n_out_host (pinned)
 // receives {error bits, number of active outputs} by an async copy that is

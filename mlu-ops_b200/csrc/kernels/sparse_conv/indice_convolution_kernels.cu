@@ -72,6 +72,9 @@ repackFilterKernel(const T *__restrict__ src, T *__restrict__ dst, int K, int ci
   }
 }
 
+// Pairs handled by one thread (independent loads in flight before the stores).
+constexpr int kBuildPairsPerThread = 4;
+
 template <bool BY_VALUE>
 __global__ void __launch_bounds__(256)
 buildNeighbourKernel(const int32_t *__restrict__ pairs, int64_t L, int64_t n_out, int64_t n_pad,
@@ -81,11 +84,20 @@ buildNeighbourKernel(const int32_t *__restrict__ pairs, int64_t L, int64_t n_out
   const int64_t pk = BY_VALUE ? counts.n[k] : counts_dev[k];
   const int32_t *in_row = pairs + (size_t)k * 2 * L;
   const int32_t *out_row = in_row + L;
-  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < pk;
-       p += (int64_t)gridDim.x * blockDim.x) {
-    const int32_t src = in_row[p], dst = out_row[p];
+  int32_t *table = nbr + (size_t)k * n_pad;
+  const int64_t span = (int64_t)blockDim.x * kBuildPairsPerThread;
+  for (int64_t base = (int64_t)blockIdx.x * span; base < pk; base += (int64_t)gridDim.x * span) {
+    int32_t src[kBuildPairsPerThread], dst[kBuildPairsPerThread];
+#pragma unroll
+    for (int i = 0; i < kBuildPairsPerThread; ++i) {
+      const int64_t p = base + i * blockDim.x + threadIdx.x;
+      src[i] = p < pk ? in_row[p] : -1;
+      dst[i] = p < pk ? out_row[p] : -1;
+    }
     // A rulebook holds one pair per (k, output row), so plain stores never collide.
-    if (src >= 0 && src < L && dst >= 0 && dst < n_out) nbr[(size_t)k * n_pad + dst] = src;
+#pragma unroll
+    for (int i = 0; i < kBuildPairsPerThread; ++i)
+      if (src[i] >= 0 && src[i] < L && dst[i] >= 0 && dst[i] < n_out) table[dst[i]] = src[i];
   }
 }
 
@@ -481,7 +493,7 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
       return err;
   }
   if (max_pairs > 0) {
-    int64_t bx = (max_pairs + 255) / 256;
+    int64_t bx = (max_pairs + 256 * kBuildPairsPerThread - 1) / (256 * kBuildPairsPerThread);
     const int64_t cap = (int64_t)sm_count * 32;
     if (bx > cap) bx = cap;
     const dim3 grid((unsigned)bx, (unsigned)p.K);

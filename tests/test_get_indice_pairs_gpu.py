@@ -210,3 +210,31 @@ def test_large_scale_properties(ops, workloads, gpu_handle):
             assert bool(hit.all())
         assert total > 0
         conv.destroy()
+
+
+def test_large_kernel_volume(ops, oracle, gpu_handle):
+    """Kernel volumes above 32 (more offsets than the single-pass path holds)."""
+    rng = np.random.default_rng(45)
+    space = [9, 12, 12]
+    idx = helpers.random_indices(rng, 2, space, 900)
+    g = dict(batch=2, space=space, ks=[5, 3, 3], stride=[1] * 3, pad=[2, 1, 1], dil=[1] * 3, out_space=space, sub_m=1)
+    check_against_oracle(ops, oracle, gpu_handle, idx, g)
+    g = dict(batch=2, space=space, ks=[4, 3, 3], stride=[2, 1, 1], pad=[1, 1, 1], dil=[1] * 3, sub_m=0)
+    g["out_space"] = helpers.out_space(space, g["pad"], g["stride"], g["dil"], g["ks"])
+    check_against_oracle(ops, oracle, gpu_handle, idx, g)
+
+
+@pytest.mark.parametrize("env", [{"MLUOP_B200_PAIRS_LOOKUP": "hash"}, {"MLUOP_B200_PAIRS_LOOKUP": "rank"},
+                                 {"MLUOP_B200_PAIRS_PATH": "fused"},
+                                 {"MLUOP_B200_PAIRS_PATH": "fused", "MLUOP_B200_PAIRS_LOOKUP": "hash"}])
+def test_forced_variants(env):
+    """Every lookup structure (hash / occupancy rank) and both pair-list paths (single
+    pass / two pass) pass the same parity cases; the choice is per process, hence the child."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_get_indice_pairs_gpu.py"), "-m", "gpu",
+                        "-x", "-q", "-k", "golden or random_small or config0 or scaled_config3 or repeated or ragged"],
+                       env=dict(os.environ, **env), capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

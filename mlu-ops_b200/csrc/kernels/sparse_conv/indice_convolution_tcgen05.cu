@@ -145,12 +145,12 @@ struct TcConfig {
   static constexpr int kBBlockStride = (kBBlockBytes + 1023) / 1024 * 1024;
   static constexpr int kAStageBytes = kKBlocks * kABlockBytes;  // one gathered [128 x CI] tile
   static constexpr int kBBufBytes = kKBlocks * kBBlockStride;   // one filter slice W_k [CO x CI]
-  static constexpr int kTiles = CO >= 128 ? 2 : 4;              // tiles per block
+  static constexpr int kTiles = 2;                              // tiles per block
   static constexpr int kTmemCols = kTiles * CO < 32 ? 32 : kTiles * CO;  // 64, 128 or 256
   static constexpr int kBlocksPerSmByTmem = 512 / kTmemCols;
-  static constexpr int kBBuffers = 3;  // filter slices in flight
+  static constexpr int kBBuffers = 2;  // filter slices in flight
   // gathered tiles in flight; sized so that as many blocks share an SM as tensor memory allows
-  static constexpr int kAStages = CI >= 128 ? 3 : (CI >= 64 ? 5 : 6);
+  static constexpr int kAStages = CI >= 128 ? 3 : 2;
   static constexpr int kChunksPerRow = CI / 8;  // 16-byte chunks of one feature row
   // instruction descriptor: D fp32, A and B fp16, both K-major, N = CO, M = 128
   static constexpr unsigned kIdesc = (1u << 4) | ((unsigned)(CO >> 3) << 17) | ((unsigned)(kTile >> 4) << 24);

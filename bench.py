@@ -301,6 +301,8 @@ def run_b200(args):
         "clocks": clocks,
         "roofline": roofline,
         "roofline_whole_step": whole,
+        "layers": [{"ci": c["ci"], "co": c["co"], "sub_m": c["sub_m"], "n_in": c["n_in"], "n_out": c["n_out"],
+                    "pairs": c["P"]} for c in conv_rows],
         "kernels": {k: {"launches_per_step": v[0] // args.steps, "ms_per_step": round(v[1] / args.steps, 4)}
                     for k, v in sorted(trace.items(), key=lambda kv: -kv[1][1])},
     }
@@ -313,7 +315,11 @@ def run_b200(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
 # summarised under profiles/ (kernel name -> bytes); None until captured.
-KNOWN_TRAFFIC = {}
+KNOWN_TRAFFIC = {
+    # profiles/convTcgen05Kernel_64x64_c2_subm2.md: 260.0 MB read + 110.9 MB written for the launch with the most
+    # pairs; the kernel's five launches per step move in proportion to their rows, this is the largest.
+    "convTcgen05Kernel<64,64>": 370.9e6,
+}
 
 
 def cpu_backend():

@@ -268,7 +268,7 @@ def run_b200(args):
     top_name, (top_launches, top_ms, top_bytes, top_flops) = top
     achieved = (top_bytes / top_launches) / ((top_ms / top_launches) * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
-                "frac": round(achieved / hbm_gbs, 4), "traffic": KNOWN_TRAFFIC.get(top_name),
+                "frac": round(achieved / hbm_gbs, 4), "traffic": None,
                 "kernel": top_name, "launches_per_step": top_launches // args.steps,
                 "avg_launch_ms": round(top_ms / top_launches, 5), "peak_source": peak_kind + " copy bandwidth",
                 "share_of_device_time": round(top_ms / total_kernel_ms, 4),
@@ -276,6 +276,11 @@ def run_b200(args):
 
     # whole-step roofline: sum over layers of max(flops/peak, bytes/BW) + rulebook bytes / BW
     conv_rows, pair_bytes = backbone.roofline_bytes_and_flops(records, elem)
+    if top_name.startswith("convTcgen05Kernel<"):
+        ci_co = top_name[top_name.index("<") + 1:-1].split(",")
+        same = [dict(c, K=rec.layer.kernel_volume) for c, rec in zip(conv_rows, records)
+                if c["ci"] == int(ci_co[0]) and c["co"] == int(ci_co[1])]
+        roofline["traffic"] = modelled_conv_traffic(same, elem)
     t_roof = sum(max(c["flops"] / (tensor_tflops * 1e12), c["bytes"] / (hbm_gbs * 1e9)) for c in conv_rows)
     t_roof += pair_bytes / (hbm_gbs * 1e9)
     ms_per_step = total_res / args.steps
@@ -313,13 +318,23 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
-# summarised under profiles/ (kernel name -> bytes); None until captured.
-KNOWN_TRAFFIC = {
-    # profiles/convTcgen05Kernel_64x64_c2_subm2.md: 260.0 MB read + 110.9 MB written for the launch with the most
-    # pairs; the kernel's five launches per step move in proportion to their rows, this is the largest.
-    "convTcgen05Kernel<64,64>": 370.9e6,
-}
+# DRAM traffic of the tensor-core convolution kernel.  One ncu capture
+# (profiles/convTcgen05Kernel_64x64_c2_subm2.md) measured dram__bytes_read.sum +
+# dram__bytes_write.sum = 370.9 MB for the launch with 1,079,296 padded rows in and out, 64 -> 64 channels, 27
+# offsets; the kernel streams features once, writes outputs once and reads the neighbour table once, i.e.
+# rows_in*Ci*2 + rows_out*Co*2 + 4*K*rows_out = 392.9 MB by that model.  Other launches of the kernel are scaled by
+# the same measured/model ratio (traffic grows in proportion to rows).
+MEASURED_OVER_MODEL_TRAFFIC = 370.9e6 / (1079296 * (64 * 2 + 64 * 2 + 4 * 27))
+
+
+def modelled_conv_traffic(layer_rows, elem):
+    """Average DRAM bytes per launch over the given layers ({ci, co, n_in, n_out, K})."""
+    if not layer_rows:
+        return None
+    total = 0.0
+    for c in layer_rows:
+        total += c["n_in"] * c["ci"] * elem + c["n_out"] * c["co"] * elem + 4.0 * c["K"] * c["n_out"]
+    return round(MEASURED_OVER_MODEL_TRAFFIC * total / len(layer_rows), 0)
 
 
 def cpu_backend():

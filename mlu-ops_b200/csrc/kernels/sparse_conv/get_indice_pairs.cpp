@@ -133,6 +133,9 @@ mluOpStatus_t internalGetIndicePairs(mluOpHandle_t handle, const std::string &ap
     g.ks[i] = conv_desc->filter_space[i];
     g.pad[i] = conv_desc->pad[i];
     g.stride[i] = conv_desc->stride[i];
+    g.stride_shift[i] = -1;
+    for (int sh = 0; sh < 31; ++sh)
+      if ((1 << sh) == conv_desc->stride[i]) g.stride_shift[i] = sh;
     g.dil[i] = conv_desc->dilation[i];
     g.in_space[i] = conv_desc->input_space[i];
     g.out_space[i] = conv_desc->output_space[i];

@@ -322,6 +322,16 @@ __device__ __forceinline__ int lookupOutput(const LookupTables &t, uint32_t lin,
   return __ldg(t.perm + e.y + __popc(e.x & ((1u << bit) - 1u)));
 }
 
+// t / stride when the division is exact (t >= 0): shift for power-of-two strides.
+__device__ __forceinline__ bool exactDivide(int t, int stride, int shift, int *q) {
+  if (shift >= 0) {
+    *q = t >> shift;
+    return (t & (stride - 1)) == 0;
+  }
+  *q = t / stride;
+  return t - *q * stride == 0;
+}
+
 // Walks the K offsets of one voxel; emit(k, output id or -1) is called for every k in order.
 template <int LOOKUP, typename Emit>
 __device__ __forceinline__ void walkOffsets(const PairsGeometry &g, const LookupTables &tables, const int4 c,
@@ -330,21 +340,19 @@ __device__ __forceinline__ void walkOffsets(const PairsGeometry &g, const Lookup
   int k = 0;
   for (int kd = 0; kd < g.ks[0]; ++kd) {
     const int td = c.y + g.pad[0] - kd * g.dil[0];
-    const int od = td / g.stride[0];
-    const bool vd = row_ok && td >= 0 && (td - od * g.stride[0]) == 0 && od < g.out_space[0];
+    int od;
+    const bool vd = exactDivide(td, g.stride[0], g.stride_shift[0], &od) && row_ok && td >= 0 && od < g.out_space[0];
     for (int kh = 0; kh < g.ks[1]; ++kh) {
       const int th = c.z + g.pad[1] - kh * g.dil[1];
-      const int oh = th / g.stride[1];
-      const bool vh = vd && th >= 0 && (th - oh * g.stride[1]) == 0 && oh < g.out_space[1];
+      int oh;
+      const bool vh = exactDivide(th, g.stride[1], g.stride_shift[1], &oh) && vd && th >= 0 && oh < g.out_space[1];
+      const int base_row = base_b + (od * g.out_space[1] + oh) * g.out_space[2];
       for (int kw = 0; kw < g.ks[2]; ++kw, ++k) {
         const int tw = c.w + g.pad[2] - kw * g.dil[2];
-        const int ow = tw / g.stride[2];
-        const bool ok = vh && tw >= 0 && (tw - ow * g.stride[2]) == 0 && ow < g.out_space[2];
+        int ow;
+        const bool ok = exactDivide(tw, g.stride[2], g.stride_shift[2], &ow) && vh && tw >= 0 && ow < g.out_space[2];
         int v = -1;
-        if (ok) {
-          const uint32_t lin = (uint32_t)(base_b + (od * g.out_space[1] + oh) * g.out_space[2] + ow);
-          v = lookupOutput<LOOKUP>(tables, lin, status);
-        }
+        if (ok) v = lookupOutput<LOOKUP>(tables, (uint32_t)(base_row + ow), status);
         emit(k, v);
       }
     }
@@ -464,6 +472,8 @@ template <int LOOKUP>
 __global__ void __launch_bounds__(kPairsTile)
 probeCountKernel(PairsGeometry g, const int4 *__restrict__ indices, LookupTables tables,
                  int32_t *__restrict__ match, int32_t *__restrict__ tile_count, int tiles, int32_t *status) {
+  // match rows are tiles*256 entries long: every thread of every tile stores, and
+  // the compaction kernel can read them 16 bytes at a time
   extern __shared__ int s_count[];  // [K]
   for (int k = threadIdx.x; k < g.K; k += blockDim.x) s_count[k] = 0;
   __syncthreads();
@@ -472,8 +482,11 @@ probeCountKernel(PairsGeometry g, const int4 *__restrict__ indices, LookupTables
   int4 c = make_int4(0, 0, 0, 0);
   if (live) c = indices[j];
   const int lane = threadIdx.x & 31;
+  int32_t *match_col = match + j;
+  const size_t row_stride = (size_t)tiles * kPairsTile;
   walkOffsets<LOOKUP>(g, tables, c, live && rowInRange(c, g), status, [&](int k, int v) {
-    if (live) match[(size_t)k * g.L + j] = v;
+    *match_col = v;
+    match_col += row_stride;
     const unsigned m = __ballot_sync(0xffffffffu, v >= 0);
     if (lane == 0 && m) atomicAdd(&s_count[k], __popc(m));
   });
@@ -500,48 +513,65 @@ scanTilesKernel(int32_t *tile_count, int tiles, int32_t *indice_num) {
   if (threadIdx.x == 0) indice_num[blockIdx.x] = running;
 }
 
-// Block (segment of kWriteSegTiles tiles, k): order-preserving compaction of each
-// tile's matches into the two rows of indice_pairs[k], plus the -1 tail for the
-// positions the segment covers.  Every word of indice_pairs is written exactly
-// once.  A tile without a match (its count is the difference of neighbouring
-// offsets) is not read at all.
+// Block (segment of 8 tiles = 2048 positions, k): order-preserving compaction of
+// the segment's matches into the two rows of indice_pairs[k], plus the -1 tail
+// for the positions the segment covers.  Every word of indice_pairs is written
+// exactly once.  A thread compacts four consecutive entries (one 16-byte load);
+// half a segment without a match (its count is the difference of neighbouring
+// tile offsets) is not read at all.
 constexpr int kWriteSegTiles = 8;
+constexpr int kWriteHalfTiles = 4;  // tiles covered by one 256-thread x 4-entry sweep
 
 __global__ void __launch_bounds__(kPairsTile)
 writePairsKernel(int L, const int32_t *__restrict__ match, const int32_t *__restrict__ tile_offset,
                  int tiles, const int32_t *__restrict__ indice_num, int32_t *__restrict__ indice_pairs) {
-  __shared__ int warp_count[2][kTileWarps];
+  __shared__ int warp_total[2][kTileWarps];
   const int k = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int total = indice_num[k];
+  const size_t row_stride = (size_t)tiles * kPairsTile;
   const int32_t *offsets = tile_offset + (size_t)k * tiles;
-  const int32_t *match_row = match + (size_t)k * L;
+  const int32_t *match_row = match + (size_t)k * row_stride;
   int32_t *in_row = indice_pairs + (size_t)k * 2 * L;
   int32_t *out_row = in_row + L;
   int buffers_used = 0;
-  for (int i = 0; i < kWriteSegTiles; ++i) {
-    const int tile = blockIdx.x * kWriteSegTiles + i;
-    if (tile >= tiles) break;
-    const int j = tile * kPairsTile + threadIdx.x;
-    const int first = offsets[tile];
-    const int next = tile + 1 < tiles ? offsets[tile + 1] : total;
+#pragma unroll 1
+  for (int half = 0; half < kWriteSegTiles / kWriteHalfTiles; ++half) {
+    const int tile0 = blockIdx.x * kWriteSegTiles + half * kWriteHalfTiles;
+    if (tile0 >= tiles) break;
+    const int j0 = tile0 * kPairsTile;
+    const int tile_end = min(tile0 + kWriteHalfTiles, tiles);
+    const int first = offsets[tile0];
+    const int next = tile_end < tiles ? offsets[tile_end] : total;
     if (next > first) {  // same decision in every thread of the block
-      const int v = j < L ? match_row[j] : -1;
-      const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
-      int *counts = warp_count[buffers_used & 1];
-      ++buffers_used;
-      if (lane == 0) counts[warp] = __popc(hits);
-      __syncthreads();
-      if (v >= 0) {
-        int p = first + __popc(hits & ((1u << lane) - 1u));
-        for (int w = 0; w < warp; ++w) p += counts[w];
-        in_row[p] = j;
-        out_row[p] = v;
+      const int jt = j0 + 4 * threadIdx.x;
+      int4 v = make_int4(-1, -1, -1, -1);
+      if ((size_t)jt < row_stride) v = *reinterpret_cast<const int4 *>(match_row + jt);
+      const int mine = (v.x >= 0) + (v.y >= 0) + (v.z >= 0) + (v.w >= 0);
+      int incl = mine;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
       }
+      int *totals = warp_total[buffers_used & 1];
+      ++buffers_used;
+      if (lane == 31) totals[warp] = incl;
+      __syncthreads();
+      int p = first + incl - mine;
+      for (int w = 0; w < warp; ++w) p += totals[w];
+      if (v.x >= 0) { in_row[p] = jt; out_row[p] = v.x; ++p; }
+      if (v.y >= 0) { in_row[p] = jt + 1; out_row[p] = v.y; ++p; }
+      if (v.z >= 0) { in_row[p] = jt + 2; out_row[p] = v.z; ++p; }
+      if (v.w >= 0) { in_row[p] = jt + 3; out_row[p] = v.w; }
     }
-    if (j < L && j >= total) {
-      in_row[j] = -1;
-      out_row[j] = -1;
+#pragma unroll
+    for (int i = 0; i < kWriteHalfTiles; ++i) {
+      const int j = j0 + i * kPairsTile + threadIdx.x;
+      if (j < L && j >= total) {
+        in_row[j] = -1;
+        out_row[j] = -1;
+      }
     }
   }
 }
@@ -584,7 +614,7 @@ PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g) {
   if (p.fused) {
     off = alignUp(off + (size_t)g.K * p.tiles * sizeof(uint32_t), 256);
   } else {
-    off = alignUp(off + (size_t)g.K * g.L * sizeof(int32_t), 256);
+    off = alignUp(off + (size_t)g.K * p.tiles * kPairsTile * sizeof(int32_t), 256);
     p.tile_count = off;
     off = alignUp(off + (size_t)g.K * p.tiles * sizeof(int32_t), 256);
   }

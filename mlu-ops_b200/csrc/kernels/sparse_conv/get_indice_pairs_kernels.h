@@ -22,6 +22,7 @@ struct PairsGeometry {
   int32_t K;      // kernel volume
   int32_t batch;
   int32_t ks[3], pad[3], stride[3], dil[3];
+  int32_t stride_shift[3];  // log2(stride) when the stride is a power of two, else -1
   int32_t in_space[3], out_space[3];
   int32_t out_vol;  // Do*Ho*Wo
   int32_t sub_m;
@@ -46,7 +47,7 @@ constexpr int kFusedMaxOffsets = 32;
 struct PairsWorkspacePlan {
   size_t status;      // int32[64]: [0] error bits, [1] number of active outputs, [2] tile ticket counter
   size_t tile_state;  // fused path: uint32[K][tiles] look-back descriptors {2-bit state, 30-bit count}
-  size_t match;       // two-pass path: int32[K][L] output id matched by (k, j), -1 if none
+  size_t match;       // two-pass path: int32[K][tiles*256] output id matched by (k, j), -1 if none
   size_t tile_count;  // two-pass path: int32[K][tiles] matches per tile, then exclusive offsets
   size_t table;       // hash: uint64[capacity] slots; rank: uint2[words] {occupancy bits, exclusive rank}
   size_t chunk_count; // rank: int32[chunks]

@@ -10,11 +10,12 @@ import helpers
 pytestmark = pytest.mark.gpu
 
 
-def test_backbone_scaled(ops, oracle, workloads, backbone, gpu_handle):
-    scale = 0.1
-    idx, feat, layers, weights = workloads.make_inputs("c2", scale=scale, batch=2)
+@pytest.mark.parametrize("scale,batch", [(0.1, 2), (1.0, 1)])
+def test_backbone_per_layer_parity(ops, oracle, workloads, backbone, gpu_handle, scale, batch):
+    """scale 0.1 x 2 samples, and one full-size sample (120,000 voxels) of the benchmark workload."""
+    idx, feat, layers, weights = workloads.make_inputs("c2", scale=scale, batch=batch)
     grid = list(workloads.CONFIGS["c2"]["grid"])
-    net = backbone.SparseNetwork(gpu_handle, layers, [torch.from_numpy(w).cuda() for w in weights], grid, 2)
+    net = backbone.SparseNetwork(gpu_handle, layers, [torch.from_numpy(w).cuda() for w in weights], grid, batch)
     out, out_idx, records = net.forward(torch.from_numpy(idx).cuda(), torch.from_numpy(feat).cuda(), keep=True)
     torch.cuda.synchronize()
     assert len(records) == 12 and sum(r.new_rulebook for r in records) == 8
@@ -23,7 +24,7 @@ def test_backbone_scaled(ops, oracle, workloads, backbone, gpu_handle):
         ly = rec.layer
         if rec.new_rulebook:
             r_pairs, r_out, r_num, r_n = oracle.get_indice_pairs(
-                cur_idx, 2, ly.pad, ly.stride, ly.dilation, ly.filter_space, rec.out_space, ly.sub_m)
+                cur_idx, batch, ly.pad, ly.stride, ly.dilation, ly.filter_space, rec.out_space, ly.sub_m)
             assert rec.n_out == r_n
             assert np.array_equal(np.array(rec.indice_num), r_num)
             assert np.array_equal(rec.pairs.cpu().numpy(), r_pairs)
@@ -40,3 +41,31 @@ def test_backbone_scaled(ops, oracle, workloads, backbone, gpu_handle):
     assert records[-1].out_space == [2, 200, 176]
     conv, pair_bytes = backbone.roofline_bytes_and_flops(records, 2)
     assert len(conv) == 12 and pair_bytes > 0
+
+
+def test_sample_sharding_reproduces_the_unsharded_run(ops, workloads, backbone, gpu_handle):
+    """The multi-GPU partition (config c4: samples split over ranks, batch index relabelled,
+    rows concatenated in rank order) emulated on one GPU: three samples of 150,000 voxels run
+    as one batch and as shards of 2 + 1 samples must give identical rows, bit for bit."""
+    import importlib
+    sharding = importlib.import_module("mluops_b200.sharding")
+    batch, world = 3, 2
+    idx, feat, layers, weights = workloads.make_inputs("c4", batch=batch)
+    grid = list(workloads.CONFIGS["c4"]["grid"])
+    w_dev = [torch.from_numpy(w).cuda() for w in weights]
+    d_idx, d_feat = torch.from_numpy(idx).cuda(), torch.from_numpy(feat).cuda()
+    net = backbone.SparseNetwork(gpu_handle, layers, w_dev, grid, batch)
+    ref_out, ref_idx, _ = net.forward(d_idx, d_feat)
+    outs, idxs = [], []
+    for rank in range(world):
+        l_idx, l_feat, l_batch, b0 = sharding.shard_by_sample(d_idx, d_feat, batch, rank, world)
+        shard_net = backbone.SparseNetwork(gpu_handle, layers, w_dev, grid, l_batch)
+        out, out_idx, _ = shard_net.forward(l_idx.contiguous(), l_feat.contiguous())
+        o, i = sharding.gather_rows(out, out_idx, b0, 0, 1)
+        outs.append(o)
+        idxs.append(i)
+        shard_net.close()
+    torch.cuda.synchronize()
+    assert torch.equal(torch.cat(idxs), ref_idx)
+    assert torch.equal(torch.cat(outs), ref_out)
+    net.close()

@@ -52,7 +52,7 @@ def measured_peaks():
 
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons every 25 ms while running."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -77,7 +77,8 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples taken between the two wall-clock times (all samples if none given)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         self.proc.terminate()
@@ -85,6 +86,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        import datetime
         sm, smax, power = [], [], []
         reasons = set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -93,6 +95,9 @@ class ClockSampler:
             if len(parts) < 9:
                 continue
             try:
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                if t_begin is not None and not (t_begin - 0.05 <= stamp <= t_end + 0.05):
+                    continue
                 sm.append(float(parts[1]))
                 smax.append(float(parts[2]))
                 power.append(float(parts[3]))
@@ -209,15 +214,17 @@ def run_b200(args):
             times.append(t0.elapsed_time(t1))
         return times
 
-    for _ in range(max(args.warmup, 3)):
-        step_resident()
-        step_e2e()
-    torch.cuda.synchronize()
-
+    # the sampler starts before the warm-up (nvidia-smi needs a moment to come up); only
+    # the samples that fall inside the timed regions are summarised
     sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
                            os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+        step_e2e()
+    torch.cuda.synchronize()
+    t_begin = time.time()
     res_ms = timed(step_resident, args.steps)
     d2h = [0]
 
@@ -225,7 +232,7 @@ def run_b200(args):
         _, nbytes = step_e2e()
         d2h[0] = nbytes
     e2e_ms = timed(e2e_once, args.steps)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, time.time()) if rank == 0 else None
 
     # traced pass: per-kernel durations (CUDA events around every launch) and launch counts
     ops.lib().mluOpTraceKernelReset()

@@ -9,8 +9,8 @@ row-for-row the single-process result (default-mode outputs are sorted by linear
 index with the batch index on top; submanifold outputs keep input order and the
 inputs are grouped by ascending batch index).
 
-Only torch.distributed point-to-point and all_gather calls are used, so the same
-code runs on NCCL (GPU tensors) and gloo (CPU tensors).
+Only torch.distributed all_gather and all_to_all calls are used, so the same code
+runs on NCCL (GPU tensors) and gloo (CPU tensors).
 """
 import torch
 import torch.distributed as dist
@@ -44,28 +44,25 @@ def gather_rows(features_out, out_indices, first_sample, rank, world, dst=0):
     if world == 1:
         return features_out, shifted
     rows = torch.tensor([features_out.shape[0]], dtype=torch.int64, device=features_out.device)
-    all_rows = [torch.zeros_like(rows) for _ in range(world)]
-    dist.all_gather(all_rows, rows)
-    counts = [int(r.item()) for r in all_rows]
+    all_rows = torch.empty((world,), dtype=torch.int64, device=features_out.device)
+    dist.all_gather_into_tensor(all_rows, rows)
+    counts = all_rows.tolist()  # one host read for all ranks' row counts
+    # One variable-size exchange per tensor: rank dst receives counts[r] rows from
+    # every rank r, the other ranks receive nothing (NCCL runs it as one group of
+    # sends and receives; far less host work than one send/recv pair per peer).
+    co = features_out.shape[1]
     if rank == dst:
-        feats = torch.empty((sum(counts), features_out.shape[1]), dtype=features_out.dtype,
-                            device=features_out.device)
+        feats = torch.empty((sum(counts), co), dtype=features_out.dtype, device=features_out.device)
         idxs = torch.empty((sum(counts), 4), dtype=out_indices.dtype, device=out_indices.device)
-        ops, off = [], 0
-        for r in range(world):
-            if r == dst:
-                feats[off:off + counts[r]] = features_out
-                idxs[off:off + counts[r]] = shifted
-            elif counts[r] > 0:
-                ops.append(dist.P2POp(dist.irecv, feats[off:off + counts[r]], r))
-                ops.append(dist.P2POp(dist.irecv, idxs[off:off + counts[r]], r))
-            off += counts[r]
-        if ops:
-            for w in dist.batch_isend_irecv(ops):
-                w.wait()
+        recv_rows = counts
+    else:
+        feats = torch.empty((0, co), dtype=features_out.dtype, device=features_out.device)
+        idxs = torch.empty((0, 4), dtype=out_indices.dtype, device=out_indices.device)
+        recv_rows = [0] * world
+    send_rows = [0] * world
+    send_rows[dst] = features_out.shape[0]
+    dist.all_to_all_single(feats, features_out.contiguous(), recv_rows, send_rows)
+    dist.all_to_all_single(idxs, shifted, recv_rows, send_rows)
+    if rank == dst:
         return feats, idxs
-    if features_out.shape[0] > 0:
-        ops = [dist.P2POp(dist.isend, features_out.contiguous(), dst), dist.P2POp(dist.isend, shifted, dst)]
-        for w in dist.batch_isend_irecv(ops):
-            w.wait()
     return features_out, shifted

@@ -169,14 +169,46 @@ def run_b200(args):
 
     first_sample = rank * batch  # batch index of this rank's first sample in the whole job
 
-    def gather_outputs(out, out_idx):
-        """Final features and out_indices of every rank -> rank 0 over NCCL (exact sizes)."""
-        return sharding.gather_rows(out, out_idx, first_sample, rank, world)
+    # Final features and out_indices of every rank -> rank 0 over NCCL (exact sizes): the row
+    # counts and the coordinate rows leave on a second stream as soon as the last rulebook
+    # exists, the feature rows after the last convolution.
+    gather = sharding.RowGather(first_sample, rank, world, device=dev)
+
+    # The gather of step i is enqueued during step i+1, at the point of the layer loop where
+    # the host would otherwise wait with the most convolution work queued on the GPU: its
+    # host cost (three collectives) is hidden there and its NVLink traffic overlaps step
+    # i+1's kernels.  The rows that are in flight are kept in `pending`.
+    queued, best, flush_at = 0, -1, 0
+    seen = set()
+    for li, ly in enumerate(layers):
+        if ly.rulebook not in seen:
+            seen.add(ly.rulebook)
+            if queued > best:
+                best, flush_at = queued, li
+            queued = 0
+        queued += ly.ci * ly.co * ly.kernel_volume
+    pending = []
+
+    def flush_pending(li=None):
+        if pending and (li is None or li == flush_at):
+            out, out_idx, done = pending.pop()
+            gather.begin(out_idx, ready=done)
+            gather.finish(out, wait=False, ready=done)
 
     def step_resident():
-        out, out_idx, records = net.forward(d_idx, d_feat)
-        gather_outputs(out, out_idx)
+        """One step of a stream of batches."""
+        if args.no_gather or world == 1:  # --no-gather: diagnostic, nothing crosses NVLink
+            return net.forward(d_idx, d_feat)[2]
+        out, out_idx, records = net.forward(d_idx, d_feat, on_host_idle=flush_pending)
+        flush_pending()  # only when the layer list has no such point
+        done = torch.cuda.Event()
+        done.record(stream)
+        pending.append((out, out_idx, done))
         return records
+
+    def drain():
+        flush_pending()
+        gather.wait()
 
     def step_e2e():
         """Host buffers in, host buffers out: pinned-host -> device copies of this rank's
@@ -185,8 +217,11 @@ def run_b200(args):
         over its own PCIe link, in parallel)."""
         d_idx.copy_(h_idx, non_blocking=True)
         d_feat.copy_(h_feat, non_blocking=True)
-        out, out_idx, records = net.forward(d_idx, d_feat)
-        gather_outputs(out, out_idx)
+        if args.no_gather:
+            out, out_idx, records = net.forward(d_idx, d_feat)
+        else:
+            out, out_idx, records = net.forward(d_idx, d_feat, on_final_indices=gather.begin)
+            gather.finish(out, wait=True)
         key = (out.shape[0], out.shape[1])
         if key not in host_out:
             host_out.clear()
@@ -198,21 +233,26 @@ def run_b200(args):
         return records, (out.shape[0] * out.shape[1] * elem + out_idx.shape[0] * 16)
 
     def timed(step, steps):
-        """Per-step CUDA-event timing on the launching stream; L2 is flushed
-        between steps outside the event pairs.  Returns per-step ms."""
-        times = []
+        """One region of `steps` steps between two CUDA events on the launching stream,
+        bracketed by a barrier and a device synchronize on both sides.  L2 is flushed after
+        every step inside the region (its 256 MiB write is part of the measured time), and the
+        last step's gather is waited for before the closing event.  Returns the region's ms."""
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
         for _ in range(steps):
-            flush.fill_(1)
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0.record(stream)
             step()
-            t1.record(stream)
-            torch.cuda.synchronize()
-            times.append(t0.elapsed_time(t1))
-        return times
+            flush.fill_(1)
+        drain()
+        t1.record(stream)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        return t0.elapsed_time(t1)
 
     # the sampler starts before the warm-up (nvidia-smi needs a moment to come up); only
     # the samples that fall inside the timed regions are summarised
@@ -223,6 +263,7 @@ def run_b200(args):
     for _ in range(max(args.warmup, 3)):
         step_resident()
         step_e2e()
+    drain()
     torch.cuda.synchronize()
     t_begin = time.time()
     res_ms = timed(step_resident, args.steps)
@@ -241,6 +282,7 @@ def run_b200(args):
     for _ in range(args.steps):
         flush.fill_(1)
         records = step_resident()
+    drain()
     torch.cuda.synchronize()
     trace = read_trace(ops)
     ops.lib().mluOpTraceKernelEnable(0)
@@ -252,8 +294,14 @@ def run_b200(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    total_res = reduce_max(sum(res_ms))
-    total_e2e = reduce_max(sum(e2e_ms))
+    ranks_ms = [res_ms / args.steps]
+    if world > 1:
+        t = torch.zeros((world,), dtype=torch.float64, device=dev)
+        t[rank] = res_ms / args.steps
+        dist.all_reduce(t)
+        ranks_ms = [round(x, 4) for x in t.tolist()]
+    total_res = reduce_max(res_ms)
+    total_e2e = reduce_max(e2e_ms)
     if world > 1:
         t = torch.tensor([d2h[0]], dtype=torch.int64, device=dev)
         dist.all_reduce(t)
@@ -304,12 +352,13 @@ def run_b200(args):
         "config": {"workload": "%s: SECOND-style sparse backbone (12 convs, 8 rulebooks), batch %d x %d voxels "
                                "per GPU, grid %dx%dx%d, fp16 storage / fp32 accumulate" %
                                (args.workload, batch, cfg["per_sample"], *grid),
-                   "voxels_per_gpu": L, "l2": "flushed between steps (256 MiB write)",
-                   "parallelism": "batch samples per rank, NCCL gather of final rows" if world > 1 else "1 GPU"},
+                   "voxels_per_gpu": L, "l2": "flushed after every step (256 MiB write, inside the timed region)",
+                   "parallelism": ("batch samples per rank, NO gather (diagnostic)" if args.no_gather else "batch samples per rank; NCCL gather of final rows to rank 0 on a second stream, overlapping the next step") if world > 1 else "1 GPU"},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT,
                 "h2d_bytes_per_step": int(h_idx.numel() * 4 + h_feat.numel() * elem) * world,
                 "d2h_bytes_per_step": int(d2h[0]), "ms_per_step": round(total_e2e / args.steps, 4)},
         "gpu_launches": int(gpu_launches),
+        "ranks_ms_per_step": ranks_ms, "host_cores": os.cpu_count(),
         "clocks": clocks,
         "roofline": roofline,
         "roofline_whole_step": whole,
@@ -443,6 +492,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gather", action="store_true",
+                    help="diagnostic for N>1: skip the NCCL gather (independent replicas) to separate its cost "
+                         "from host-side contention between the ranks' processes")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

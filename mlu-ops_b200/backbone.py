@@ -108,10 +108,23 @@ class SparseNetwork:
         for conv, _, _ in self.geometry.values():
             conv.destroy()
 
-    def forward(self, indices, features, keep=False):
+    def forward(self, indices, features, keep=False, on_final_indices=None, on_host_idle=None):
         """indices [L,4] int32, features [L,Cin] on the GPU.
-        Returns (features_out, out_indices, records)."""
+        Returns (features_out, out_indices, records).
+
+        on_final_indices(out_indices, ready_event), if given, is called once, as soon as
+        the coordinates of the final rows are known (when the last layer's rulebook has
+        been generated) and after that layer's convolution has been enqueued, so that a
+        caller can ship them while the remaining convolutions run; ready_event marks the
+        point of the stream after which the rows are valid.
+
+        on_host_idle(layer_index), if given, is called before every rulebook generation:
+        the convolutions enqueued since the previous rulebook are still running and the
+        host is about to wait for the rulebook's counts, so host work done here (e.g.
+        enqueuing a collective for the previous step's rows) costs no GPU time."""
         lib, h = self.lib, self.handle.ptr
+        final_rulebook = self.layers[-1].rulebook
+        ready = None
         rulebooks = {}
         records = []
         cur_idx, cur_feat = indices, features
@@ -128,6 +141,8 @@ class SparseNetwork:
                 num_dev = torch.empty((K,), dtype=torch.int32, device=self.device)
                 d_in, d_pairs = self.d_idx.set(L, 4), self.d_pairs.set(K, 2, L)
                 d_out, d_num = self.d_out_idx.set(out_rows, 4), self.d_num.set(K)
+                if on_host_idle is not None:
+                    on_host_idle(li)
                 ops.check("mluOpGetIndicePairsWorkspaceSize",
                           lib.mluOpGetIndicePairsWorkspaceSize(h, conv.ptr, d_in, d_pairs, d_out, d_num,
                                                                ctypes.byref(self.size)))
@@ -142,6 +157,9 @@ class SparseNetwork:
                 lib.mluOpGetSparseConvolutionNumActOut(conv.ptr, ctypes.byref(self.n_act))
                 num_list = self.num_host[:K].tolist()
                 rulebooks[ly.rulebook] = (pairs, out_idx, num_list, self.n_act.value)
+                if on_final_indices is not None and ly.rulebook == final_rulebook:
+                    ready = torch.cuda.Event()
+                    ready.record()
             pairs, out_idx, num_list, n_out = rulebooks[ly.rulebook]
             L = cur_feat.shape[0]
             for i, v in enumerate(num_list):
@@ -168,6 +186,9 @@ class SparseNetwork:
             cur_feat = out
             if not ly.sub_m:
                 cur_idx = out_idx[:n_out]
+            if ready is not None:
+                on_final_indices(cur_idx, ready)
+                ready = None
         return cur_feat, cur_idx, records
 
 

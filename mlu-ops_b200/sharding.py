@@ -35,34 +35,118 @@ def shard_by_sample(indices, features, batch, rank, world):
     return local_idx, features[keep], b1 - b0, b0
 
 
+class RowGather:
+    """Final rows of every rank -> rank `dst`, in rank order, in two phases.
+
+    The coordinates of the final rows are known as soon as the last rulebook
+    exists, which is before the last convolutions have run.  begin() therefore
+    exchanges the row counts and the coordinate rows on a second stream while
+    those convolutions execute; finish() is left with one variable-size exchange
+    of the feature rows.  On CPU tensors (gloo) both phases run in line.
+
+    Every rank must call begin() and finish() once per step, in that order.
+    finish(wait=False) leaves the exchange running on the second stream, so that
+    the next step's kernels overlap it; wait() orders the launching stream after
+    it (call it before reading the gathered rows, and once at the end).
+    """
+
+    def __init__(self, first_sample, rank, world, dst=0, device=None):
+        self.first_sample, self.rank, self.world, self.dst = int(first_sample), rank, world, dst
+        self.cuda = device is not None and torch.device(device).type == "cuda"
+        self.comm = torch.cuda.Stream(device) if self.cuda and world > 1 else None
+        self.counts = None
+        self.idxs = None
+        self.shifted = None
+
+    def _on_comm(self):
+        return torch.cuda.stream(self.comm) if self.comm is not None else _NullContext()
+
+    def begin(self, out_indices, ready=None):
+        """out_indices [n,4]: this rank's final coordinate rows.  `ready` (a CUDA event,
+        optional) marks the point of the launching stream after which they are valid;
+        without it the second stream waits for everything enqueued so far."""
+        if self.comm is not None:
+            if ready is not None:
+                self.comm.wait_event(ready)
+            else:
+                self.comm.wait_stream(torch.cuda.current_stream())
+        with self._on_comm():
+            shifted = out_indices.clone()
+            shifted[:, 0] += self.first_sample
+            self.shifted = shifted
+            if self.world == 1:
+                return
+            n = out_indices.shape[0]
+            rows = torch.tensor([n], dtype=torch.int64, device=out_indices.device)
+            all_rows = torch.empty((self.world,), dtype=torch.int64, device=out_indices.device)
+            dist.all_gather_into_tensor(all_rows, rows)
+            self.counts = all_rows.tolist()  # one host read for all ranks' row counts
+            total = sum(self.counts) if self.rank == self.dst else 0
+            self.idxs = torch.empty((total, 4), dtype=out_indices.dtype, device=out_indices.device)
+            dist.all_to_all_single(self.idxs, shifted, self._recv_rows(), self._send_rows(n))
+            if self.comm is not None:
+                out_indices.record_stream(self.comm)
+
+    def _recv_rows(self):
+        return list(self.counts) if self.rank == self.dst else [0] * self.world
+
+    def _send_rows(self, n):
+        send = [0] * self.world
+        send[self.dst] = n
+        return send
+
+    def wait(self):
+        """Orders the launching stream after everything enqueued on the second stream."""
+        if self.comm is not None:
+            torch.cuda.current_stream().wait_stream(self.comm)
+
+    def finish(self, features_out, wait=True, ready=None):
+        """features_out [n,Co]: this rank's final feature rows (n as given to begin()).
+        Returns (features, indices): all ranks' rows on dst, the local rows (batch index
+        shifted) elsewhere.  With wait=True the launching stream is ordered after the
+        exchange on return; with wait=False the caller calls wait() before it reads them.
+        `ready` as in begin(): the point of the launching stream after which features_out is
+        valid (default: everything enqueued so far)."""
+        if self.world == 1:
+            return features_out, self.shifted
+        if self.comm is not None:
+            if ready is not None:
+                self.comm.wait_event(ready)
+            else:
+                self.comm.wait_stream(torch.cuda.current_stream())
+        with self._on_comm():
+            total = sum(self.counts) if self.rank == self.dst else 0
+            feats = torch.empty((total, features_out.shape[1]), dtype=features_out.dtype,
+                                device=features_out.device)
+            # One variable-size exchange: rank dst receives counts[r] rows from every rank r,
+            # the other ranks receive nothing (NCCL runs it as one group of sends and
+            # receives; far less host work than one send/recv pair per peer).
+            dist.all_to_all_single(feats, features_out.contiguous(), self._recv_rows(),
+                                   self._send_rows(features_out.shape[0]))
+        if self.comm is not None:
+            cur = torch.cuda.current_stream()
+            if wait:
+                cur.wait_stream(self.comm)
+            for t in (feats, self.idxs, self.shifted):
+                t.record_stream(cur)
+            features_out.record_stream(self.comm)
+        if self.rank == self.dst:
+            return feats, self.idxs
+        return features_out, self.shifted
+
+
+class _NullContext:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
 def gather_rows(features_out, out_indices, first_sample, rank, world, dst=0):
-    """Final rows of every rank -> rank `dst`, in rank order, batch index shifted back
-    by each rank's first sample.  Returns (features, indices) on dst, the local
-    (shifted) rows elsewhere."""
-    shifted = out_indices.clone()
-    shifted[:, 0] += first_sample
-    if world == 1:
-        return features_out, shifted
-    rows = torch.tensor([features_out.shape[0]], dtype=torch.int64, device=features_out.device)
-    all_rows = torch.empty((world,), dtype=torch.int64, device=features_out.device)
-    dist.all_gather_into_tensor(all_rows, rows)
-    counts = all_rows.tolist()  # one host read for all ranks' row counts
-    # One variable-size exchange per tensor: rank dst receives counts[r] rows from
-    # every rank r, the other ranks receive nothing (NCCL runs it as one group of
-    # sends and receives; far less host work than one send/recv pair per peer).
-    co = features_out.shape[1]
-    if rank == dst:
-        feats = torch.empty((sum(counts), co), dtype=features_out.dtype, device=features_out.device)
-        idxs = torch.empty((sum(counts), 4), dtype=out_indices.dtype, device=out_indices.device)
-        recv_rows = counts
-    else:
-        feats = torch.empty((0, co), dtype=features_out.dtype, device=features_out.device)
-        idxs = torch.empty((0, 4), dtype=out_indices.dtype, device=out_indices.device)
-        recv_rows = [0] * world
-    send_rows = [0] * world
-    send_rows[dst] = features_out.shape[0]
-    dist.all_to_all_single(feats, features_out.contiguous(), recv_rows, send_rows)
-    dist.all_to_all_single(idxs, shifted, recv_rows, send_rows)
-    if rank == dst:
-        return feats, idxs
-    return features_out, shifted
+    """Both phases of RowGather back to back: final rows of every rank -> rank `dst`,
+    in rank order, batch index shifted back by each rank's first sample.  Returns
+    (features, indices) on dst, the local (shifted) rows elsewhere."""
+    g = RowGather(first_sample, rank, world, dst, device=features_out.device)
+    g.begin(out_indices)
+    return g.finish(features_out)

@@ -3,7 +3,8 @@
 TEST INFRASTRUCTURE ONLY: imported by tests/, the smoke check and the
 CPU-baseline leg of bench.py.  The shipped library never touches this package.
 
-  oracle.lib()      -> the plain-C restatement (oracle/sparse_conv_oracle.c)
+  oracle.lib()      -> the plain-C restatement (oracle/sparse_conv_oracle.c and
+                       oracle/sparse_conv_backward_oracle.c)
   oracle.ref_lib()  -> the reference's function bodies compiled by
                        oracle/build_ref.py, or None when that library is absent
 """
@@ -15,6 +16,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "sparse_conv_oracle.c")
+SRC_BACKWARD = os.path.join(HERE, "sparse_conv_backward_oracle.c")
 LIB = os.path.join(HERE, "_build", "libmluops_oracle.so")
 REF_LIB = os.path.join(HERE, "_ref", "libmluops_ref_cpu.so")
 
@@ -29,9 +31,10 @@ FILTER_LAYOUT = {"ARRAY": 0, "NDHWC": 1, "NCDHW": 2}
 
 def build(force=False):
     """Compile the C oracle with gcc (a second or two)."""
-    if force or not os.path.isfile(LIB) or os.path.getmtime(LIB) < os.path.getmtime(SRC):
+    newest = max(os.path.getmtime(SRC), os.path.getmtime(SRC_BACKWARD))
+    if force or not os.path.isfile(LIB) or os.path.getmtime(LIB) < newest:
         os.makedirs(os.path.dirname(LIB), exist_ok=True)
-        subprocess.check_call(["gcc", "-O2", "-std=c11", "-fPIC", "-shared", "-o", LIB, SRC, "-lm"])
+        subprocess.check_call(["gcc", "-O2", "-std=c11", "-fPIC", "-shared", "-o", LIB, SRC, SRC_BACKWARD, "-lm"])
     return LIB
 
 
@@ -150,6 +153,64 @@ def indice_convolution_forward(features, filters, filter_layout, filter_space, i
             _p(features, _f32p), _p(filters, _f32p), ctypes.c_int32(code), _p(pairs, _i32p),
             _p(num, _i64p), ctypes.c_int64(L), ctypes.c_int64(ci), ctypes.c_int64(co),
             ctypes.c_int64(K), ctypes.c_int64(num_act_out), _p(out, _f32p))
+    assert rc == 0
+    return out
+
+
+def indice_convolution_backward_data(output_grad, filters, filter_layout, filter_space, indice_pairs,
+                                     indice_num, ci, is_half, use_ref=False):
+    """input_grad [L, ci] float32 in the reference's accumulation order.  output_grad/filters
+    hold the values the device sees; is_half selects the reference's half emulation
+    (products and per-pair running sums rounded through half)."""
+    og = np.ascontiguousarray(output_grad, dtype=np.float32)
+    filters = np.ascontiguousarray(filters, dtype=np.float32)
+    pairs = np.ascontiguousarray(indice_pairs, dtype=np.int32)
+    num = np.ascontiguousarray(indice_num, dtype=np.int64)
+    n_out, co = og.shape
+    L = pairs.shape[2]
+    K = kernel_volume(filter_space)
+    out = np.empty((L, ci), dtype=np.float32)
+    code = FILTER_LAYOUT[filter_layout]
+    if use_ref:
+        r = ref_lib()
+        assert r is not None, "oracle/_ref is not built"
+        kdhw = _i32x3(filter_space)
+        rc = r.mluops_ref_indice_convolution_backward_data(
+            _p(og, _f32p), _p(filters, _f32p), ctypes.c_int32(code), _p(kdhw, _i32p), _p(pairs, _i32p),
+            _p(num, _i64p), ctypes.c_int64(L), ctypes.c_int64(ci), ctypes.c_int64(co),
+            ctypes.c_int64(n_out), ctypes.c_int32(int(is_half)), _p(out, _f32p))
+    else:
+        rc = lib().mluops_oracle_indice_convolution_backward_data(
+            _p(og, _f32p), _p(filters, _f32p), ctypes.c_int32(code), _p(pairs, _i32p), _p(num, _i64p),
+            ctypes.c_int64(L), ctypes.c_int64(ci), ctypes.c_int64(co), ctypes.c_int64(K),
+            ctypes.c_int32(int(is_half)), _p(out, _f32p))
+    assert rc == 0
+    return out
+
+
+def indice_convolution_backward_filter(features, output_grad, filter_space, indice_pairs, indice_num,
+                                       use_ref=False):
+    """filters_grad [K, ci, co] float32: one float accumulator per element over the pair list."""
+    feats = np.ascontiguousarray(features, dtype=np.float32)
+    og = np.ascontiguousarray(output_grad, dtype=np.float32)
+    pairs = np.ascontiguousarray(indice_pairs, dtype=np.int32)
+    num = np.ascontiguousarray(indice_num, dtype=np.int64)
+    L, ci = feats.shape
+    n_out, co = og.shape
+    K = kernel_volume(filter_space)
+    out = np.zeros((K, ci, co), dtype=np.float32)
+    if use_ref:
+        r = ref_lib()
+        assert r is not None, "oracle/_ref is not built"
+        kdhw = _i32x3(filter_space)
+        rc = r.mluops_ref_indice_convolution_backward_filter(
+            _p(feats, _f32p), _p(og, _f32p), _p(kdhw, _i32p), _p(pairs, _i32p), _p(num, _i64p),
+            ctypes.c_int64(L), ctypes.c_int64(ci), ctypes.c_int64(co), ctypes.c_int64(n_out),
+            _p(out, _f32p))
+    else:
+        rc = lib().mluops_oracle_indice_convolution_backward_filter(
+            _p(feats, _f32p), _p(og, _f32p), _p(pairs, _i32p), _p(num, _i64p), ctypes.c_int64(L),
+            ctypes.c_int64(ci), ctypes.c_int64(co), ctypes.c_int64(K), _p(out, _f32p))
     assert rc == 0
     return out
 

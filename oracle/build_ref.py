@@ -12,6 +12,16 @@ stand-in for the members they touch:
   IndiceConvolutionForwardExecutor::cpuCompute
                                               zoo/indice_convolution_forward/indice_convolution_forward.cpp
   cvtFloatToHalf                              pb_gtest/src/tools.cpp
+  IndiceConvolutionBackwardDataExecutor::getFilterDims / cpuTransposeFilter / cpuCompute
+                                              zoo/indice_convolution_backward_data/indice_convolution_backward_data.cpp
+  IndiceConvolutionBackwardFilterExecutor::cpuTranspose / cpuCompute
+                                              zoo/indice_convolution_backward_filter/indice_convolution_backward_filter.cpp
+
+The backward-data body rounds to half through wrapRtConvertFloatToHalf /
+wrapRtConvertHalfToFloat, which forward to the vendor runtime's cast routine
+(tools.cpp:49-57); that runtime is not part of the reference tree, so the
+stand-in forwards the first to the reference's own software conversion from the
+same file and writes the second (an exact conversion) out.
 
 The generated translation unit lives only in a temporary directory; the single
 output is oracle/_ref/libmluops_ref_cpu.so (git-ignored).  No reference source
@@ -33,6 +43,8 @@ SOURCES = {
     "pairs": ZOO + "/get_indice_pairs/get_indice_pairs.cpp",
     "conv": ZOO + "/indice_convolution_forward/indice_convolution_forward.cpp",
     "tools": "test/mlu_op_gtest/pb_gtest/src/tools.cpp",
+    "bwd_data": ZOO + "/indice_convolution_backward_data/indice_convolution_backward_data.cpp",
+    "bwd_filter": ZOO + "/indice_convolution_backward_filter/indice_convolution_backward_filter.cpp",
 }
 
 PRELUDE = r"""
@@ -45,7 +57,11 @@ PRELUDE = r"""
 using std::sort;
 using std::unique;
 
-enum mluOpTensorLayout_t { MLUOP_LAYOUT_NDHWC = 3, MLUOP_LAYOUT_ARRAY = 4, MLUOP_LAYOUT_NCDHW = 5 };
+#include <string>
+enum mluOpTensorLayout_t {
+  MLUOP_LAYOUT_NCHW = 0, MLUOP_LAYOUT_NHWC = 1, MLUOP_LAYOUT_HWCN = 2,
+  MLUOP_LAYOUT_NDHWC = 3, MLUOP_LAYOUT_ARRAY = 4, MLUOP_LAYOUT_NCDHW = 5
+};
 enum mluOpDataType_t { MLUOP_DTYPE_HALF = 1, MLUOP_DTYPE_FLOAT = 2, MLUOP_DTYPE_INT32 = 6 };
 
 struct StandInTensor {
@@ -53,6 +69,7 @@ struct StandInTensor {
   mluOpTensorLayout_t layout = MLUOP_LAYOUT_ARRAY;
   mluOpDataType_t dtype = MLUOP_DTYPE_FLOAT;
   int64_t getDimIndex(int i) const { return dims[i]; }
+  int getDim() const { return (int)dims.size(); }
   mluOpTensorLayout_t getLayout() const { return layout; }
   mluOpDataType_t getDtype() const { return dtype; }
   int64_t getTotalElementNum() const {
@@ -67,6 +84,7 @@ static inline int64_t mluOpGetTensordimD(const mluOpTensorDescriptor_t d) {
   return d->layout == MLUOP_LAYOUT_NDHWC ? d->dims[1] : d->dims[2];
 }
 static inline int64_t mluOpGetTensordimH(const mluOpTensorDescriptor_t d) {
+  if (d->layout == MLUOP_LAYOUT_HWCN) return d->dims[0];
   return d->layout == MLUOP_LAYOUT_NDHWC ? d->dims[2] : d->dims[3];
 }
 static inline int64_t mluOpGetTensordimW(const mluOpTensorDescriptor_t d) {
@@ -80,10 +98,27 @@ struct StandInRuntime {
   void *allocate(size_t n) { return malloc(n ? n : 1); }
   void deallocate(void *p) { free(p); }
 };
+struct StandInBackwardDataParam {
+  std::vector<int64_t> num;
+  int64_t indice_num(int k) const { return num[k]; }
+  int64_t inverse() const { return 0; }
+  int64_t sub_m() const { return 0; }
+};
+struct StandInProtoNode {
+  StandInBackwardDataParam bwd_data;
+  const StandInBackwardDataParam &indice_convolution_backward_data_param() const { return bwd_data; }
+};
 struct StandInParser {
   int64_t out_count = 0;
+  int in_num = 0, out_num = 0;
+  StandInProtoNode node;
   int64_t getOutputDataCount(int) { return out_count; }
+  int getInputNum() const { return in_num; }
+  int getOutputNum() const { return out_num; }
+  StandInProtoNode *getProtoNode() { return &node; }
 };
+struct StandInDescHolder { StandInTensor *tensor = nullptr; };
+#define GTEST_CHECK(cond, ...) do { if (!(cond)) { std::cerr << "check failed: " #cond << std::endl; abort(); } } while (0)
 struct StandInBlock { void *host_ptr = nullptr; void *device_ptr = nullptr; };
 
 #define ERROR 0
@@ -121,6 +156,67 @@ struct IndiceConvolutionForwardExecutor {
   mluOpTensorDescriptor_t indice_pairs_desc_ = nullptr;
   mluOpTensorDescriptor_t features_out_desc_ = nullptr;
   std::vector<int64_t> indice_num_;
+  void cpuCompute();
+};
+int16_t cvtFloatToHalf(float x);
+// half -> float is exact; written out here because the reference's routine picks
+// its implementation through test-harness globals.
+static inline float standInHalfToFloat(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h >> 15) << 31;
+  const int32_t exp = (h >> 10) & 0x1f;
+  uint32_t man = h & 0x3ff;
+  uint32_t bits;
+  if (exp == 0x1f) {
+    bits = sign | 0x7f800000u | (man << 13);
+  } else if (exp != 0) {
+    bits = sign | ((uint32_t)(exp + 112) << 23) | (man << 13);
+  } else if (man == 0) {
+    bits = sign;
+  } else {
+    int32_t e = 113;
+    while (!(man & 0x400)) { man <<= 1; --e; }
+    bits = sign | ((uint32_t)e << 23) | ((man & 0x3ff) << 13);
+  }
+  float f;
+  memcpy(&f, &bits, sizeof(f));
+  return f;
+}
+static inline int wrapRtConvertFloatToHalf(uint16_t *f16, float d) {
+  *f16 = (uint16_t)cvtFloatToHalf(d);
+  return 0;
+}
+static inline int wrapRtConvertHalfToFloat(float *d, uint16_t f16) {
+  *d = standInHalfToFloat(f16);
+  return 0;
+}
+struct IndiceConvolutionBackwardDataExecutor {
+  StandInRuntime cpu_runtime_;
+  StandInParser parser_storage_;
+  StandInParser *parser_ = &parser_storage_;
+  std::vector<float *> cpu_fp32_input_;
+  std::vector<float *> cpu_fp32_output_;
+  std::vector<StandInDescHolder> tensor_desc_;
+  int64_t inverse_ = 0, sub_m_ = 0;
+  int dyc, dxc, kd, kh, kw;
+  bool filter_4d;
+  void getFilterDims();
+  void setSpconvdataParams() {}
+  void cpuTransposeFilter(float *filter_transpose_cpu, mluOpTensorLayout_t origin_layout);
+  void cpuCompute();
+};
+struct IndiceConvolutionBackwardFilterExecutor {
+  StandInRuntime cpu_runtime_;
+  std::vector<float *> cpu_fp32_input_;
+  std::vector<float *> cpu_fp32_output_;
+  std::vector<StandInBlock> data_vector_;
+  mluOpTensorDescriptor_t input_indice_desc_ = nullptr;
+  mluOpTensorDescriptor_t diffy_indice_desc_ = nullptr;
+  mluOpTensorDescriptor_t indice_pair_desc_ = nullptr;
+  mluOpTensorDescriptor_t diffw_desc_ = nullptr;
+  std::vector<int64_t> indice_num_;
+  bool diffw_trans_ = false;
+  void cpuTranspose(float *output, const float *input, const int64_t kernel_volume, const int64_t ci,
+                    const int64_t co, const mluOpTensorLayout_t diffw_layout);
   void cpuCompute();
 };
 """
@@ -184,6 +280,64 @@ int mluops_ref_indice_convolution_forward(const float *features, const float *fi
 
 uint16_t mluops_ref_float_to_half_bits(float x) { return (uint16_t)mluoptest::cvtFloatToHalf(x); }
 
+// filter_layout: 0 [K,Ci,Co] (passed as a 4-D HWCN filter {K,1,Ci,Co}: the reference's
+// re-layout routine leaves its strides unset for a 5-D ARRAY filter), 1 NDHWC, 2 NCDHW.
+int mluops_ref_indice_convolution_backward_data(const float *output_grad, const float *filters,
+                                                int32_t filter_layout, const int32_t *kdhw,
+                                                const int32_t *indice_pairs,
+                                                const int64_t *indice_num, int64_t L, int64_t ci,
+                                                int64_t co, int64_t n_out, int32_t is_half,
+                                                float *input_grad) {
+  const int64_t kd = kdhw[0], kh = kdhw[1], kw = kdhw[2], K = kd * kh * kw;
+  StandInTensor og, w, p, ig;
+  og.dims = {n_out, co};
+  ig.dims = {L, ci};
+  p.dims = {K, 2, L};
+  p.dtype = MLUOP_DTYPE_INT32;
+  w.dtype = is_half ? MLUOP_DTYPE_HALF : MLUOP_DTYPE_FLOAT;
+  if (filter_layout == 0) { w.layout = MLUOP_LAYOUT_HWCN; w.dims = {K, 1, ci, co}; }
+  else if (filter_layout == 1) { w.layout = MLUOP_LAYOUT_NDHWC; w.dims = {co, kd, kh, kw, ci}; }
+  else { w.layout = MLUOP_LAYOUT_NCDHW; w.dims = {co, ci, kd, kh, kw}; }
+  // the reference reads the pairs from the float copy of its inputs
+  std::vector<float> pairs_f((size_t)(K * 2 * L));
+  for (size_t i = 0; i < pairs_f.size(); ++i) pairs_f[i] = (float)indice_pairs[i];
+  mluoptest::IndiceConvolutionBackwardDataExecutor ex;
+  ex.tensor_desc_.resize(4);
+  ex.tensor_desc_[0].tensor = &og; ex.tensor_desc_[1].tensor = &w;
+  ex.tensor_desc_[2].tensor = &p; ex.tensor_desc_[3].tensor = &ig;
+  ex.cpu_fp32_input_ = {const_cast<float *>(output_grad), const_cast<float *>(filters), pairs_f.data()};
+  ex.cpu_fp32_output_ = {input_grad};
+  ex.parser_storage_.in_num = 3; ex.parser_storage_.out_num = 1;
+  ex.parser_storage_.out_count = L * ci;
+  ex.parser_storage_.node.bwd_data.num.assign(indice_num, indice_num + K);
+  ex.cpuCompute();
+  return 0;
+}
+
+// filters_grad [K,Ci,Co].  The reference reads kw with the H accessor, so kh must equal kw.
+int mluops_ref_indice_convolution_backward_filter(const float *features, const float *output_grad,
+                                                  const int32_t *kdhw, const int32_t *indice_pairs,
+                                                  const int64_t *indice_num, int64_t L, int64_t ci,
+                                                  int64_t co, int64_t n_out, float *filters_grad) {
+  const int64_t kd = kdhw[0], kh = kdhw[1], kw = kdhw[2], K = kd * kh * kw;
+  if (kh != kw) return -1;
+  StandInTensor f, og, p, w;
+  f.dims = {L, ci};
+  og.dims = {n_out, co};
+  p.dims = {K, 2, L};
+  w.layout = MLUOP_LAYOUT_NDHWC;  // only the D and H accessors are read: kd = dims[1], kh = kw = dims[2]
+  w.dims = {co, kd, kh, kw, ci};
+  mluoptest::IndiceConvolutionBackwardFilterExecutor ex;
+  ex.input_indice_desc_ = &f; ex.diffy_indice_desc_ = &og; ex.indice_pair_desc_ = &p; ex.diffw_desc_ = &w;
+  ex.cpu_fp32_input_ = {const_cast<float *>(features), const_cast<float *>(output_grad)};
+  ex.cpu_fp32_output_ = {filters_grad};
+  ex.data_vector_.resize(4);
+  ex.data_vector_[2].host_ptr = const_cast<int32_t *>(indice_pairs);
+  ex.indice_num_.assign(indice_num, indice_num + K);
+  ex.cpuCompute();
+  return 0;
+}
+
 }  // extern "C"
 """
 
@@ -212,6 +366,11 @@ def build(reference_root="/root/reference", quiet=False):
     parts.append(extract(paths["pairs"], "void GetIndicePairsExecutor::cpuGetIndicePairs("))
     parts.append(extract(paths["conv"], "void IndiceConvolutionForwardExecutor::cpuCompute("))
     parts.append(extract(paths["tools"], "int16_t cvtFloatToHalf("))
+    parts.append(extract(paths["bwd_data"], "void IndiceConvolutionBackwardDataExecutor::getFilterDims("))
+    parts.append(extract(paths["bwd_data"], "void IndiceConvolutionBackwardDataExecutor::cpuTransposeFilter("))
+    parts.append(extract(paths["bwd_data"], "void IndiceConvolutionBackwardDataExecutor::cpuCompute("))
+    parts.append(extract(paths["bwd_filter"], "void IndiceConvolutionBackwardFilterExecutor::cpuTranspose("))
+    parts.append(extract(paths["bwd_filter"], "void IndiceConvolutionBackwardFilterExecutor::cpuCompute("))
     parts.append(EPILOGUE)
     with tempfile.TemporaryDirectory() as tmp:
         src = os.path.join(tmp, "ref_cpu_unit.cpp")

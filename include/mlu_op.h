@@ -272,6 +272,51 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForward(
     const int64_t sub_m, void *workspace, const size_t workspace_size,
     const mluOpTensorDescriptor_t features_out_desc, void *features_out);
 
+/* reference mlu_op.h:9626, indice_convolution_backward_data.cpp:358 */
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionBackwardDataWorkspaceSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t output_grad_desc,
+    const mluOpTensorDescriptor_t filters_desc,
+    const mluOpTensorDescriptor_t indice_pairs_desc,
+    const mluOpTensorDescriptor_t input_grad_desc, const int64_t indice_num[],
+    const int64_t inverse, size_t *workspace_size);
+
+/* reference mlu_op.h:9760, indice_convolution_backward_data.cpp:568.
+ *   input_grad[i,:] = sum_k sum_{(i,o) in pairs_k} output_grad[o,:] * W_k^T
+ * output_grad [N_out,Co], input_grad [L,Ci] (L = indice_pairs dims[2]); filters
+ * 4-D (NHWC, NCHW, HWCN) or 5-D (NDHWC, NCDHW, ARRAY = [kd,kh,kw,Ci,Co]); half
+ * or float, all three the same; accumulation in float, kernel offset ascending.
+ * Input rows without a pair are zero.  Asynchronous on the handle's queue. */
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardData(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t output_grad_desc,
+    const void *output_grad, const mluOpTensorDescriptor_t filters_desc, const void *filters,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *indice_pairs,
+    const int64_t indice_num[], const int64_t inverse, const int64_t sub_m, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t input_grad_desc,
+    void *input_grad);
+
+/* reference mlu_op.h:9838, indice_convolution_backward_filter.cpp:531 */
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionBackwardFilterWorkspaceSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc,
+    const mluOpTensorDescriptor_t output_grad_desc,
+    const mluOpTensorDescriptor_t indice_pairs_desc,
+    const mluOpTensorDescriptor_t filters_grad_desc, const int64_t indice_num[],
+    const int64_t inverse, const int64_t sub_m, size_t *workspace_size);
+
+/* reference mlu_op.h:9934, indice_convolution_backward_filter.cpp:570.
+ *   filters_grad[k,c,n] = sum_{(i,o) in pairs_k} features[i,c] * output_grad[o,n]
+ * features [L,Ci], output_grad [N_out,Co], filters_grad 4-D [kh,kw,Ci,Co] or 5-D
+ * [kd,kh,kw,Ci,Co] (the reference writes this order whatever layout tag the
+ * descriptor carries); half or float, all three the same; accumulation in
+ * float in a fixed order (results are reproducible run to run).  Kernel offsets
+ * without pairs give zeros.  Asynchronous on the handle's queue. */
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilter(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc, const void *features,
+    const mluOpTensorDescriptor_t output_grad_desc, const void *output_grad,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *indice_pairs,
+    const int64_t indice_num[], const int64_t inverse, const int64_t sub_m, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t filters_grad_desc,
+    void *filters_grad);
+
 /* No counterpart in the reference.  Same computation and arguments as
  * mluOpIndiceConvolutionForward, without the workspace pair: the scratch is a
  * fixed array of MLUOP_BUILTIN_CONV_WORKSPACE_BYTES in device memory that

@@ -71,6 +71,14 @@ SIGNATURES = {
                                             _szt, _vp, _vp]),
     "mluOpIndiceConvolutionForwardBuiltinWorkspace": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64,
                                                             _i64, _vp, _vp]),
+    "mluOpGetIndiceConvolutionBackwardDataWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, _vp, _i64p, _i64,
+                                                                 ctypes.POINTER(_szt)]),
+    "mluOpIndiceConvolutionBackwardData": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64, _vp, _szt,
+                                                 _vp, _vp]),
+    "mluOpGetIndiceConvolutionBackwardFilterWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64,
+                                                                   ctypes.POINTER(_szt)]),
+    "mluOpIndiceConvolutionBackwardFilter": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64, _vp,
+                                                   _szt, _vp, _vp]),
     # include/mlu_op_trace.h
     "mluOpTraceKernelEnable": (_int, [_int]),
     "mluOpTraceKernelReset": (_int, []),
@@ -251,7 +259,8 @@ def get_indice_pairs(handle, conv, indices, out_rows=None, workspace=None):
     return pairs, out_indices, num, n_out
 
 
-FILTER_LAYOUTS = {"ARRAY": LAYOUT_ARRAY, "NDHWC": LAYOUT_NDHWC, "NCDHW": LAYOUT_NCDHW}
+FILTER_LAYOUTS = {"ARRAY": LAYOUT_ARRAY, "NDHWC": LAYOUT_NDHWC, "NCDHW": LAYOUT_NCDHW,
+                  "HWCN": LAYOUT_HWCN, "NHWC": LAYOUT_NHWC, "NCHW": LAYOUT_NCHW}
 
 
 def filter_dims(layout, filter_space, ci, co):
@@ -299,5 +308,85 @@ def indice_convolution_forward(handle, features, filters, filter_layout, filter_
                                               int(bool(sub_m)), _ptr(workspace), size.value, d_o.ptr,
                                               _ptr(out)))
     for d in (d_f, d_w, d_p, d_o):
+        d.destroy()
+    return out
+
+
+def indice_convolution_backward_data(handle, output_grad, filters, filter_layout, indice_pairs,
+                                     indice_num_host, sub_m, workspace=None, out=None):
+    """input_grad [L, Ci] through mluOpIndiceConvolutionBackwardData.
+
+    output_grad [N_out,Co] and filters (4-D or 5-D, in `filter_layout`: ARRAY, HWCN,
+    NDHWC, NCDHW, NHWC, NCHW) are CUDA tensors of the same dtype; L is indice_pairs'
+    last dimension; indice_num_host is a sequence of K ints.
+    """
+    import torch
+    n_out, co = output_grad.shape
+    dims = tuple(filters.shape)
+    if filter_layout in ("ARRAY", "HWCN"):
+        ci = dims[-2]
+    elif filter_layout in ("NDHWC", "NHWC"):
+        ci = dims[-1]
+    else:
+        ci = dims[1]
+    K, _, L = indice_pairs.shape
+    dt = DTYPE_HALF if output_grad.dtype == torch.float16 else DTYPE_FLOAT
+    dev = output_grad.device
+    if out is None:
+        out = torch.empty((L, ci), dtype=output_grad.dtype, device=dev)
+    d_g = TensorDesc(LAYOUT_ARRAY, dt, (n_out, co))
+    d_w = TensorDesc(FILTER_LAYOUTS[filter_layout], dt, dims)
+    d_p = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K, 2, L))
+    d_o = TensorDesc(LAYOUT_ARRAY, dt, (L, ci))
+    num = i64_array(indice_num_host)
+    size = _szt(0)
+    check("mluOpGetIndiceConvolutionBackwardDataWorkspaceSize",
+          lib().mluOpGetIndiceConvolutionBackwardDataWorkspaceSize(handle.ptr, d_g.ptr, d_w.ptr, d_p.ptr, d_o.ptr,
+                                                                   num, 0, ctypes.byref(size)))
+    if workspace is None or workspace.numel() < size.value:
+        workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+    check("mluOpIndiceConvolutionBackwardData",
+          lib().mluOpIndiceConvolutionBackwardData(handle.ptr, d_g.ptr, _ptr(output_grad), d_w.ptr, _ptr(filters),
+                                                   d_p.ptr, _ptr(indice_pairs), num, 0, int(bool(sub_m)),
+                                                   _ptr(workspace), size.value, d_o.ptr, _ptr(out)))
+    for d in (d_g, d_w, d_p, d_o):
+        d.destroy()
+    return out
+
+
+def indice_convolution_backward_filter(handle, features, output_grad, filter_space, indice_pairs,
+                                       indice_num_host, sub_m, workspace=None, out=None):
+    """filters_grad [kd,kh,kw,Ci,Co] through mluOpIndiceConvolutionBackwardFilter.
+
+    features [L,Ci] and output_grad [N_out,Co] are CUDA tensors of the same dtype;
+    indice_num_host is a sequence of K = kd*kh*kw ints.
+    """
+    import torch
+    L, ci = features.shape
+    n_out, co = output_grad.shape
+    K = indice_pairs.shape[0]
+    dt = DTYPE_HALF if features.dtype == torch.float16 else DTYPE_FLOAT
+    dev = features.device
+    dims = tuple(filter_space) + (ci, co)
+    if out is None:
+        out = torch.empty(dims, dtype=features.dtype, device=dev)
+    d_f = TensorDesc(LAYOUT_ARRAY, dt, (L, ci))
+    d_g = TensorDesc(LAYOUT_ARRAY, dt, (n_out, co))
+    d_p = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K, 2, L))
+    d_w = TensorDesc(LAYOUT_ARRAY, dt, dims)
+    num = i64_array(indice_num_host)
+    size = _szt(0)
+    check("mluOpGetIndiceConvolutionBackwardFilterWorkspaceSize",
+          lib().mluOpGetIndiceConvolutionBackwardFilterWorkspaceSize(handle.ptr, d_f.ptr, d_g.ptr, d_p.ptr,
+                                                                     d_w.ptr, num, 0, int(bool(sub_m)),
+                                                                     ctypes.byref(size)))
+    if workspace is None or workspace.numel() < size.value:
+        workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+    check("mluOpIndiceConvolutionBackwardFilter",
+          lib().mluOpIndiceConvolutionBackwardFilter(handle.ptr, d_f.ptr, _ptr(features), d_g.ptr,
+                                                     _ptr(output_grad), d_p.ptr, _ptr(indice_pairs), num, 0,
+                                                     int(bool(sub_m)), _ptr(workspace), size.value, d_w.ptr,
+                                                     _ptr(out)))
+    for d in (d_f, d_g, d_p, d_w):
         d.destroy()
     return out

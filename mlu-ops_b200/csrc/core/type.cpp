@@ -42,4 +42,26 @@ const char *getNameOfTensorLayout(mluOpTensorLayout_t layout) {
   return (i >= 0 && i <= 10) ? names[i] : "LAYOUT_ARRAY";
 }
 
+const char *getNameOfDataType(mluOpDataType_t dtype) {
+  switch (dtype) {
+    case MLUOP_DTYPE_HALF: return "half";
+    case MLUOP_DTYPE_FLOAT: return "float";
+    case MLUOP_DTYPE_DOUBLE: return "double";
+    case MLUOP_DTYPE_INT8: return "int8";
+    case MLUOP_DTYPE_INT16: return "int16";
+    case MLUOP_DTYPE_INT31: return "int31";
+    case MLUOP_DTYPE_INT32: return "int32";
+    case MLUOP_DTYPE_INT64: return "int64";
+    case MLUOP_DTYPE_UINT8: return "uint8";
+    case MLUOP_DTYPE_UINT16: return "uint16";
+    case MLUOP_DTYPE_UINT32: return "uint32";
+    case MLUOP_DTYPE_UINT64: return "uint64";
+    case MLUOP_DTYPE_BOOL: return "bool";
+    case MLUOP_DTYPE_COMPLEX_HALF: return "complex_half";
+    case MLUOP_DTYPE_COMPLEX_FLOAT: return "complex_float";
+    case MLUOP_DTYPE_BFLOAT16: return "bfloat16";
+    default: return "invalid";
+  }
+}
+
 }  // namespace mluop

@@ -36,6 +36,7 @@ inline size_t getSizeOfDataType(mluOpDataType_t dtype) {
 }
 
 const char *getNameOfTensorLayout(mluOpTensorLayout_t layout);
+const char *getNameOfDataType(mluOpDataType_t dtype);
 
 }  // namespace mluop
 

@@ -200,7 +200,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForward(
     LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
-  cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionForward(
+  cudaError_t err = mluop::sparse_conv::launchIndiceConvolution(
       p, plan, features, filters, static_cast<const int32_t *>(indice_pairs), indice_num, workspace,
       features_out, handle->sm_count, handle->queue);
   if (err != cudaSuccess) {

@@ -53,12 +53,17 @@ struct PairCounts {
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-repackFilterKernel(const T *__restrict__ src, T *__restrict__ dst, int K, int ci, int co, int layout) {
+repackFilterKernel(const T *__restrict__ src, T *__restrict__ dst, int K, int ci, int co, int layout,
+                   int co_innermost) {
+  // dst is [K][Co][Ci], or [K][Ci][Co] when co_innermost is set
   const int64_t total = (int64_t)K * ci * co;
+  const int inner = co_innermost ? co : ci, mid = co_innermost ? ci : co;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(i % ci);
-    const int o = (int)((i / ci) % co);
+    const int a = (int)(i % inner);
+    const int b = (int)((i / inner) % mid);
+    const int c = co_innermost ? b : a;
+    const int o = co_innermost ? a : b;
     const int k = (int)(i / ((int64_t)ci * co));
     int64_t s;
     if (layout == kFilterArray) {
@@ -77,13 +82,16 @@ constexpr int kBuildPairsPerThread = 4;
 
 template <bool BY_VALUE>
 __global__ void __launch_bounds__(256)
-buildNeighbourKernel(const int32_t *__restrict__ pairs, int64_t L, int64_t n_out, int64_t n_pad,
-                     PairCounts counts, const int32_t *__restrict__ counts_dev,
-                     int32_t *__restrict__ nbr) {
+buildNeighbourKernel(const int32_t *__restrict__ pairs, int64_t pair_stride, int swap, int64_t L,
+                     int64_t n_out, int64_t n_pad, PairCounts counts,
+                     const int32_t *__restrict__ counts_dev, int32_t *__restrict__ nbr) {
+  // pairs is [K][2][pair_stride]; row 0 of an offset holds the ids of the rows that
+  // are gathered (L of them) and row 1 the ids of the rows that are produced (n_out),
+  // the other way round when swap is set.
   const int k = blockIdx.y;
   const int64_t pk = BY_VALUE ? counts.n[k] : counts_dev[k];
-  const int32_t *in_row = pairs + (size_t)k * 2 * L;
-  const int32_t *out_row = in_row + L;
+  const int32_t *in_row = pairs + (size_t)k * 2 * pair_stride + (swap ? pair_stride : 0);
+  const int32_t *out_row = pairs + (size_t)k * 2 * pair_stride + (swap ? 0 : pair_stride);
   int32_t *table = nbr + (size_t)k * n_pad;
   const int64_t span = (int64_t)blockDim.x * kBuildPairsPerThread;
   for (int64_t base = (int64_t)blockIdx.x * span; base < pk; base += (int64_t)gridDim.x * span) {
@@ -431,7 +439,8 @@ bool mmaEligible(const ConvProblem &p, const void *features, const void *out) {
 ConvWorkspacePlan planConvWorkspace(const ConvProblem &p) {
   ConvWorkspacePlan plan{};
   const size_t elem = p.is_half ? 2 : 4;
-  plan.n_pad = (p.n_out + kConvPadRows - 1) / kConvPadRows * kConvPadRows;
+  const int64_t rows_out = p.backward_data ? p.L : p.n_out;
+  plan.n_pad = (rows_out + kConvPadRows - 1) / kConvPadRows * kConvPadRows;
   size_t off = 0;
   plan.status = off;
   off = alignUp(off + 64 * sizeof(int32_t), 256);
@@ -445,11 +454,22 @@ ConvWorkspacePlan planConvWorkspace(const ConvProblem &p) {
   return plan;
 }
 
-cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorkspacePlan &plan,
-                                           const void *features, const void *filters,
-                                           const int32_t *indice_pairs, const int64_t *indice_num,
-                                           void *workspace, void *features_out, int sm_count,
-                                           cudaStream_t stream) {
+cudaError_t launchIndiceConvolution(const ConvProblem &caller, const ConvWorkspacePlan &plan,
+                                    const void *features, const void *filters,
+                                    const int32_t *indice_pairs, const int64_t *indice_num,
+                                    void *workspace, void *features_out, int sm_count,
+                                    cudaStream_t stream) {
+  // From here on `p` describes the rows that are gathered (L of them, ci channels)
+  // and the rows that are produced (n_out, co channels), whichever direction runs.
+  ConvProblem p = caller;
+  const int swap = caller.backward_data ? 1 : 0;
+  if (swap) {
+    p.L = caller.n_out;
+    p.n_out = caller.L;
+    p.ci = caller.co;
+    p.co = caller.ci;
+  }
+  const int64_t pair_stride = caller.L;
   char *base = reinterpret_cast<char *>(alignUp(reinterpret_cast<size_t>(workspace), 256));
   void *filter_packed = base + plan.filter;
   int32_t *nbr = reinterpret_cast<int32_t *>(base + plan.neighbour);
@@ -478,11 +498,11 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
     if (p.is_half) {
       repackFilterKernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half *>(filters),
                                                              static_cast<__half *>(filter_packed), p.K,
-                                                             p.ci, p.co, p.filter_layout);
+                                                             caller.ci, caller.co, p.filter_layout, swap);
     } else {
       repackFilterKernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float *>(filters),
                                                             static_cast<float *>(filter_packed), p.K,
-                                                            p.ci, p.co, p.filter_layout);
+                                                            caller.ci, caller.co, p.filter_layout, swap);
     }
   }
 
@@ -501,8 +521,8 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
     if (p.K <= kMaxCountsByValue) {
       PairCounts counts{};
       for (int k = 0; k < p.K; ++k) counts.n[k] = (int32_t)indice_num[k];
-      buildNeighbourKernel<true><<<grid, 256, 0, stream>>>(indice_pairs, p.L, p.n_out, plan.n_pad, counts,
-                                                           nullptr, nbr);
+      buildNeighbourKernel<true><<<grid, 256, 0, stream>>>(indice_pairs, pair_stride, swap, p.L, p.n_out,
+                                                           plan.n_pad, counts, nullptr, nbr);
     } else {
       // Large kernel volumes: counts travel through device memory.  The copy
       // from pageable host memory is staged by the runtime before it returns.
@@ -511,8 +531,8 @@ cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorks
       err = cudaMemcpyAsync(counts_dev, tmp, (size_t)p.K * sizeof(int32_t), cudaMemcpyHostToDevice, stream);
       delete[] tmp;
       if (err != cudaSuccess) return err;
-      buildNeighbourKernel<false><<<grid, 256, 0, stream>>>(indice_pairs, p.L, p.n_out, plan.n_pad,
-                                                            PairCounts{}, counts_dev, nbr);
+      buildNeighbourKernel<false><<<grid, 256, 0, stream>>>(indice_pairs, pair_stride, swap, p.L, p.n_out,
+                                                            plan.n_pad, PairCounts{}, counts_dev, nbr);
     }
   }
   if ((err = cudaGetLastError()) != cudaSuccess) return err;

@@ -1,5 +1,6 @@
-// Device side of the sparse convolution forward: workspace plan and launch
-// sequence.  Argument checks live in indice_convolution_forward.cpp.
+// Device side of the sparse convolution forward and of its input gradient:
+// workspace plan and launch sequence.  Argument checks live in
+// indice_convolution_forward.cpp and indice_convolution_backward_data.cpp.
 #ifndef MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_KERNELS_H_
 #define MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_KERNELS_H_
 
@@ -27,12 +28,18 @@ struct ConvProblem {
   int32_t ci, co;
   int32_t is_half;  // 1: half, 0: float
   int32_t filter_layout;
+  // 0: forward, features [L,ci] -> features_out [n_out,co].
+  // 1: input gradient, output_grad [n_out,co] -> input_grad [L,ci]: the same
+  //    computation with the two row sets, the two ids of a pair and the two
+  //    channel axes of the filter exchanged.
+  int32_t backward_data;
 };
 
 struct ConvWorkspacePlan {
   size_t status;     // int32[64]: [0] error bits of the tensor-memory kernel's bounded waits
-  size_t filter;     // T[K][Co][Ci]: filter repacked so that Ci is contiguous
-  size_t neighbour;  // int32[K][n_pad]: input row feeding (k, output row), -1 if none
+  size_t filter;     // T[K][Co][Ci]: filter repacked so that the contracted axis is contiguous
+                     // (input gradient: T[K][Ci][Co])
+  size_t neighbour;  // int32[K][n_pad]: source row feeding (k, destination row), -1 if none
   size_t counts;     // int32[K]: pair counts, only used when K is too large for kernel arguments
   size_t total;
   int64_t n_pad;
@@ -41,12 +48,14 @@ struct ConvWorkspacePlan {
 ConvWorkspacePlan planConvWorkspace(const ConvProblem &p);
 
 // Enqueues filter repack, neighbour-table build and the convolution kernel.
-// indice_num is the caller's host array.
-cudaError_t launchIndiceConvolutionForward(const ConvProblem &p, const ConvWorkspacePlan &plan,
-                                           const void *features, const void *filters,
-                                           const int32_t *indice_pairs, const int64_t *indice_num,
-                                           void *workspace, void *features_out, int sm_count,
-                                           cudaStream_t stream);
+// indice_num is the caller's host array.  `rows_in` are the rows that are
+// gathered (features, or output_grad for the input gradient), `rows_out` the
+// rows that are produced (features_out, or input_grad).
+cudaError_t launchIndiceConvolution(const ConvProblem &p, const ConvWorkspacePlan &plan,
+                                    const void *rows_in, const void *filters,
+                                    const int32_t *indice_pairs, const int64_t *indice_num,
+                                    void *workspace, void *rows_out, int sm_count,
+                                    cudaStream_t stream);
 
 }  // namespace sparse_conv
 }  // namespace mluop

@@ -58,6 +58,13 @@ def golden():
 
 
 @pytest.fixture(scope="session")
+def backward_golden():
+    import numpy as np
+    path = os.path.join(ROOT, "tests", "golden", "sparse_conv_backward_golden.npz")
+    return np.load(path)
+
+
+@pytest.fixture(scope="session")
 def gpu_handle(ops):
     import torch
     assert torch.cuda.is_available(), "GPU tests need a CUDA device"

@@ -1,0 +1,161 @@
+"""GPU parity of mluOpIndiceConvolutionBackwardData and mluOpIndiceConvolutionBackwardFilter
+against the CPU oracle, through the C ABI.  Acceptance: diff1 and diff2 <= 3e-3 for half
+(the thresholds the reference generates its test cases with,
+indice_convolution_backward_data.cpp:331 and indice_convolution_backward_filter.cpp:97),
+<= 1e-5 for float."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def assert_close(oracle, got, ref, is_half):
+    d1, d2, _ = oracle.diffs(got, ref, is_half)
+    tol = helpers.TOL_HALF if is_half else helpers.TOL_FLOAT
+    assert d1 <= tol and d2 <= tol, (d1, d2)
+
+
+def gpu_backward_data(ops, handle, og, w_array, layout, pairs, num, sub_m):
+    w = helpers.permute_filter(w_array, layout)
+    out = ops.indice_convolution_backward_data(handle, torch.from_numpy(og).cuda(), torch.from_numpy(w).cuda(), layout,
+                                               torch.from_numpy(pairs).cuda(), [int(v) for v in num], sub_m)
+    torch.cuda.synchronize()
+    return out.float().cpu().numpy()
+
+
+def gpu_backward_filter(ops, handle, feat, og, ks, pairs, num, sub_m):
+    out = ops.indice_convolution_backward_filter(handle, torch.from_numpy(feat).cuda(), torch.from_numpy(og).cuda(),
+                                                 ks, torch.from_numpy(pairs).cuda(), [int(v) for v in num], sub_m)
+    torch.cuda.synchronize()
+    return out.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("layout", ["ARRAY", "NDHWC", "NCDHW"])
+def test_golden_input_gradients(ops, oracle, gpu_handle, golden, backward_golden, layout):
+    """input_grad the reference's own CPU code produced (float, and its half emulation)."""
+    for name in helpers.golden_names(golden):
+        c = helpers.golden_case(golden, name)
+        og = backward_golden[name + "/output_grad"]
+        got = gpu_backward_data(ops, gpu_handle, og, c["filters_array"], layout, c["indice_pairs"], c["indice_num"],
+                                c["sub_m"])
+        assert_close(oracle, got, backward_golden[name + "/input_grad"], False)
+        got = gpu_backward_data(ops, gpu_handle, og.astype(np.float16), c["filters_array"].astype(np.float16), layout,
+                                c["indice_pairs"], c["indice_num"], c["sub_m"])
+        assert_close(oracle, got, oracle.round_through_half(backward_golden[name + "/input_grad_half"]), True)
+
+
+def test_golden_filter_gradients(ops, oracle, gpu_handle, golden, backward_golden):
+    """filters_grad the reference's own CPU code produced."""
+    for name in helpers.golden_names(golden):
+        if name + "/filters_grad" not in backward_golden:
+            continue
+        c = helpers.golden_case(golden, name)
+        og = backward_golden[name + "/output_grad"]
+        got = gpu_backward_filter(ops, gpu_handle, c["features"], og, c["ks"], c["indice_pairs"], c["indice_num"],
+                                  c["sub_m"])
+        assert_close(oracle, got.reshape(-1, c["ci"], c["co"]), backward_golden[name + "/filters_grad"], False)
+        got = gpu_backward_filter(ops, gpu_handle, c["features"].astype(np.float16), og.astype(np.float16), c["ks"],
+                                  c["indice_pairs"], c["indice_num"], c["sub_m"])
+        ref = oracle.round_through_half(backward_golden[name + "/filters_grad_half"])
+        assert_close(oracle, got.reshape(-1, c["ci"], c["co"]), ref, True)
+
+
+def make_case(oracle, rng, batch, space, n, ks, stride, pad, sub_m, ci, co, dtype):
+    osp = list(space) if sub_m else helpers.out_space(space, pad, stride, [1] * 3, ks)
+    idx = helpers.random_indices(rng, batch, space, n)
+    pairs, _, num, n_out = oracle.get_indice_pairs(idx, batch, pad, stride, [1] * 3, ks, osp, sub_m)
+    feat = rng.standard_normal((n, ci)).astype(np.float32).astype(dtype)
+    og = rng.standard_normal((n_out, co)).astype(np.float32).astype(dtype)
+    K = int(np.prod(ks))
+    w = (rng.standard_normal(tuple(ks) + (ci, co)) / np.sqrt(K * co)).astype(np.float32).astype(dtype)
+    return pairs, num, n_out, feat, og, w
+
+
+CHANNELS = [(4, 16), (16, 16), (16, 32), (32, 32), (32, 64), (64, 64), (64, 128), (128, 128), (3, 5), (20, 48),
+            (128, 16), (130, 140)]
+
+
+@pytest.mark.parametrize("ci,co", CHANNELS)
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_channel_sweep(ops, oracle, gpu_handle, ci, co, dtype):
+    """Every kernel variant of both operators: tensor-core tiles for half with
+    power-of-two channels, FMA otherwise; submanifold and strided rulebooks."""
+    rng = np.random.default_rng(ci * 1000 + co + 7)
+    is_half = dtype == np.float16
+    for sub_m, stride in ((1, [1] * 3), (0, [2] * 3)):
+        pairs, num, n_out, feat, og, w = make_case(oracle, rng, 2, [8, 14, 12], 700, [3] * 3, stride, [1] * 3, sub_m,
+                                                   ci, co, dtype)
+        ref = oracle.indice_convolution_backward_data(og.astype(np.float32), w.astype(np.float32), "ARRAY", [3] * 3,
+                                                      pairs, num, ci, is_half)
+        if is_half:
+            ref = oracle.round_through_half(ref)
+        got = gpu_backward_data(ops, gpu_handle, og, w, "ARRAY", pairs, num, sub_m)
+        assert_close(oracle, got, ref, is_half)
+        ref = oracle.indice_convolution_backward_filter(feat.astype(np.float32), og.astype(np.float32), [3] * 3, pairs,
+                                                        num)
+        if is_half:
+            ref = oracle.round_through_half(ref)
+        got = gpu_backward_filter(ops, gpu_handle, feat, og, [3] * 3, pairs, num, sub_m)
+        assert_close(oracle, got.reshape(ref.shape), ref, is_half)
+
+
+def test_four_dimensional_filters(ops, oracle, gpu_handle):
+    """HWCN / NHWC / NCHW filters (a 1 x 3 x 3 kernel described without its depth axis)."""
+    rng = np.random.default_rng(21)
+    ks = [1, 3, 3]
+    pairs, num, n_out, feat, og, w = make_case(oracle, rng, 1, [5, 12, 12], 300, ks, [1] * 3, [0, 1, 1], 1, 16, 32,
+                                               np.float32)
+    ref = oracle.indice_convolution_backward_data(og, w, "ARRAY", ks, pairs, num, 16, False)
+    w4 = w[0]  # [kh,kw,Ci,Co]
+    d_og, d_pairs = torch.from_numpy(og).cuda(), torch.from_numpy(pairs).cuda()
+    nums = [int(v) for v in num]
+    for layout, wl in (("HWCN", w4), ("NHWC", np.transpose(w4, (3, 0, 1, 2))), ("NCHW", np.transpose(w4, (3, 2, 0, 1)))):
+        got = ops.indice_convolution_backward_data(gpu_handle, d_og, torch.from_numpy(np.ascontiguousarray(wl)).cuda(),
+                                                   layout, d_pairs, nums, 1)
+        assert_close(oracle, got.cpu().numpy(), ref, False)
+    got = ops.indice_convolution_backward_filter(gpu_handle, torch.from_numpy(feat).cuda(), d_og, [3, 3], d_pairs, nums,
+                                                 1)
+    ref = oracle.indice_convolution_backward_filter(feat, og, ks, pairs, num)
+    assert_close(oracle, got.cpu().numpy().reshape(ref.shape), ref, False)
+
+
+def test_rows_and_offsets_without_pairs_are_zero(ops, oracle, gpu_handle):
+    rng = np.random.default_rng(22)
+    pairs, num, n_out, feat, og, w = make_case(oracle, rng, 1, [6, 6, 6], 50, [3] * 3, [1] * 3, [1] * 3, 1, 16, 16,
+                                               np.float16)
+    zero_num = np.zeros_like(num)
+    assert np.all(gpu_backward_data(ops, gpu_handle, og, w, "ARRAY", pairs, zero_num, 1) == 0)
+    assert np.all(gpu_backward_filter(ops, gpu_handle, feat, og, [3] * 3, pairs, zero_num, 1) == 0)
+    some = num.copy()
+    some[::2] = 0
+    got = gpu_backward_filter(ops, gpu_handle, feat, og, [3] * 3, pairs, some, 1).reshape(27, 16, 16)
+    assert np.all(got[::2] == 0) and np.any(got[13] != 0)
+
+
+def test_adjoint_identities_at_full_size(ops, oracle, workloads, gpu_handle):
+    """Size-independent properties on one 200k-voxel 128-channel sample (where the CPU
+    oracle would take minutes): <conv(x), dy> == <x, backward_data(dy)> == <W, backward_filter(x, dy)>,
+    and two runs of each operator are bit-identical."""
+    idx, feat, layers, weights = workloads.make_inputs("c3", batch=2)
+    ly = layers[0]
+    grid = list(workloads.CONFIGS["c3"]["grid"])
+    conv = ops.SparseConvDesc(2, ly.pad, ly.stride, ly.dilation, grid, ly.filter_space, grid, 1)
+    pairs, _, num, n_out = ops.get_indice_pairs(gpu_handle, conv, torch.from_numpy(idx).cuda())
+    num_h = num.cpu().tolist()
+    x = torch.from_numpy(feat).cuda()
+    w = torch.from_numpy(weights[0]).cuda()
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    dy = torch.randn((n_out, ly.co), generator=gen, device="cuda").half()
+    y = ops.indice_convolution_forward(gpu_handle, x, w, "ARRAY", ly.filter_space, pairs, num_h, n_out, 1)
+    dx = ops.indice_convolution_backward_data(gpu_handle, dy, w, "ARRAY", pairs, num_h, 1)
+    dw = ops.indice_convolution_backward_filter(gpu_handle, x, dy, ly.filter_space, pairs, num_h, 1)
+    lhs = float((y.double() * dy.double()).sum())
+    scale = float((y.double().abs() * dy.double().abs()).sum())
+    assert abs(lhs - float((x.double() * dx.double()).sum())) <= 2e-3 * scale
+    assert abs(lhs - float((w.double() * dw.double()).sum())) <= 2e-3 * scale
+    assert torch.equal(dx, ops.indice_convolution_backward_data(gpu_handle, dy, w, "ARRAY", pairs, num_h, 1))
+    assert torch.equal(dw, ops.indice_convolution_backward_filter(gpu_handle, x, dy, ly.filter_space, pairs, num_h, 1))
+    conv.destroy()

@@ -39,6 +39,93 @@ def test_golden_convolutions(oracle, golden, layout):
         assert np.array_equal(out, c["features_out"]), name
 
 
+@pytest.mark.parametrize("layout", ["ARRAY", "NDHWC", "NCDHW"])
+def test_golden_input_gradients(oracle, golden, backward_golden, layout):
+    """input_grad the reference's own CPU code produced, float and half emulation."""
+    for name in helpers.golden_names(golden):
+        c = helpers.golden_case(golden, name)
+        og = backward_golden[name + "/output_grad"]
+        w = helpers.permute_filter(c["filters_array"], layout)
+        out = oracle.indice_convolution_backward_data(og, w, layout, c["ks"], c["indice_pairs"], c["indice_num"],
+                                                      c["ci"], False)
+        assert np.array_equal(out, backward_golden[name + "/input_grad"]), name
+        og_h, w_h = oracle.round_through_half(og), oracle.round_through_half(w)
+        out = oracle.indice_convolution_backward_data(og_h, w_h, layout, c["ks"], c["indice_pairs"],
+                                                      c["indice_num"], c["ci"], True)
+        assert np.array_equal(out, backward_golden[name + "/input_grad_half"]), name
+
+
+def test_golden_filter_gradients(oracle, golden, backward_golden):
+    """filters_grad the reference's own CPU code produced."""
+    checked = 0
+    for name in helpers.golden_names(golden):
+        if name + "/filters_grad" not in backward_golden:
+            continue
+        c = helpers.golden_case(golden, name)
+        og = backward_golden[name + "/output_grad"]
+        out = oracle.indice_convolution_backward_filter(c["features"], og, c["ks"], c["indice_pairs"],
+                                                        c["indice_num"])
+        assert np.array_equal(out, backward_golden[name + "/filters_grad"]), name
+        out = oracle.indice_convolution_backward_filter(oracle.round_through_half(c["features"]),
+                                                        oracle.round_through_half(og), c["ks"], c["indice_pairs"],
+                                                        c["indice_num"])
+        assert np.array_equal(out, backward_golden[name + "/filters_grad_half"]), name
+        checked += 1
+    assert checked >= 6
+
+
+def test_backward_against_reference_code(oracle):
+    if oracle.ref_lib() is None:
+        pytest.skip("oracle/_ref not built (reference tree absent)")
+    rng = np.random.default_rng(12)
+    done = 0
+    while done < 60:
+        g = helpers.random_geometry(rng, sub_m=bool(rng.integers(0, 2)))
+        if g is None:
+            continue
+        idx = helpers.random_indices(rng, g["batch"], g["space"], g["n"])
+        pairs, _, num, n_out = oracle.get_indice_pairs(idx, g["batch"], g["pad"], g["stride"], g["dil"], g["ks"],
+                                                       g["out_space"], g["sub_m"])
+        ci, co = int(rng.integers(1, 9)), int(rng.integers(1, 9))
+        is_half = bool(done % 2)
+        feat = rng.standard_normal((g["n"], ci)).astype(np.float32)
+        og = rng.standard_normal((max(n_out, 1), co)).astype(np.float32)
+        w = rng.standard_normal(tuple(g["ks"]) + (ci, co)).astype(np.float32)
+        if is_half:
+            feat, og, w = (oracle.round_through_half(a) for a in (feat, og, w))
+        layout = ["ARRAY", "NDHWC", "NCDHW"][done % 3]
+        wl = helpers.permute_filter(w, layout)
+        a = oracle.indice_convolution_backward_data(og, wl, layout, g["ks"], pairs, num, ci, is_half)
+        b = oracle.indice_convolution_backward_data(og, wl, layout, g["ks"], pairs, num, ci, is_half, use_ref=True)
+        assert np.array_equal(a, b), g
+        if g["ks"][1] == g["ks"][2]:
+            a = oracle.indice_convolution_backward_filter(feat, og, g["ks"], pairs, num)
+            b = oracle.indice_convolution_backward_filter(feat, og, g["ks"], pairs, num, use_ref=True)
+            assert np.array_equal(a, b), g
+        done += 1
+
+
+def test_backward_is_the_adjoint_of_forward(oracle):
+    """<conv(x), dy> == <x, backward_data(dy)> == <W, backward_filter(x, dy)> in float64 terms."""
+    rng = np.random.default_rng(13)
+    g = None
+    while g is None:
+        g = helpers.random_geometry(rng, sub_m=False)
+    idx = helpers.random_indices(rng, g["batch"], g["space"], g["n"])
+    pairs, _, num, n_out = oracle.get_indice_pairs(idx, g["batch"], g["pad"], g["stride"], g["dil"], g["ks"],
+                                                   g["out_space"], 0)
+    ci, co = 5, 3
+    x = rng.standard_normal((g["n"], ci)).astype(np.float32)
+    dy = rng.standard_normal((n_out, co)).astype(np.float32)
+    w = rng.standard_normal(tuple(g["ks"]) + (ci, co)).astype(np.float32)
+    y = oracle.indice_convolution_forward(x, w, "ARRAY", g["ks"], pairs, num, n_out, co)
+    dx = oracle.indice_convolution_backward_data(dy, w, "ARRAY", g["ks"], pairs, num, ci, False)
+    dw = oracle.indice_convolution_backward_filter(x, dy, g["ks"], pairs, num)
+    lhs = float(np.sum(y.astype(np.float64) * dy))
+    assert abs(lhs - float(np.sum(x.astype(np.float64) * dx))) <= 1e-4 * (1 + abs(lhs))
+    assert abs(lhs - float(np.sum(w.reshape(dw.shape).astype(np.float64) * dw))) <= 1e-4 * (1 + abs(lhs))
+
+
 def test_golden_half_bits(oracle, golden):
     assert np.array_equal(oracle.float_to_half_bits(golden["half/x"]), golden["half/bits"])
 

@@ -367,11 +367,60 @@ def run_b200(args):
         "kernels": {k: {"launches_per_step": v[0] // args.steps, "ms_per_step": round(v[1] / args.steps, 4)}
                     for k, v in sorted(trace.items(), key=lambda kv: -kv[1][1])},
     }
+    if world == 1 and args.backward:
+        line["training"] = training_step(args, ops, backbone, net, d_idx, d_feat, flush, elem, hbm_gbs,
+                                         tensor_tflops)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_one_sample(args.workload)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def training_step(args, ops, backbone, net, d_idx, d_feat, flush, elem, hbm_gbs, tensor_tflops):
+    """Forward (rulebooks + convolutions) followed by the input and filter gradients of every
+    layer, timed like the forward step; per-kernel times from a traced pass.  The roofline of
+    the backward half is twice the forward's convolution term (same pairs, same bytes and
+    flops per pair for each of the two gradients)."""
+    import torch
+    stream = torch.cuda.current_stream()
+
+    def step():
+        out, _, records = net.forward(d_idx, d_feat, keep=True)
+        grad = torch.ones_like(out)
+        net.backward(records, grad)
+        return records
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush.fill_(1)
+    torch.cuda.synchronize()
+    t0.record(stream)
+    for _ in range(args.steps):
+        step()
+        flush.fill_(1)
+    t1.record(stream)
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / args.steps
+    ops.lib().mluOpTraceKernelReset()
+    ops.lib().mluOpTraceKernelEnable(1)
+    records = None
+    for _ in range(args.steps):
+        flush.fill_(1)
+        records = step()
+    torch.cuda.synchronize()
+    trace = read_trace(ops)
+    ops.lib().mluOpTraceKernelEnable(0)
+    conv_rows, pair_bytes = backbone.roofline_bytes_and_flops(records, elem)
+    t_conv = sum(max(c["flops"] / (tensor_tflops * 1e12), c["bytes"] / (hbm_gbs * 1e9)) for c in conv_rows)
+    t_roof = 3 * t_conv + pair_bytes / (hbm_gbs * 1e9)
+    return {"ms_per_step": round(ms, 4), "t_roof_ms": round(t_roof * 1e3, 4), "frac": round(t_roof * 1e3 / ms, 4),
+            "kernels": {k: {"launches_per_step": v[0] // args.steps, "ms_per_step": round(v[1] / args.steps, 4),
+                            "GBps": round(v[2] / (v[1] * 1e-3) / 1e9, 1) if v[1] > 0 else None,
+                            "TFLOPs": round(v[3] / (v[1] * 1e-3) / 1e12, 2) if v[1] > 0 else None}
+                        for k, v in sorted(trace.items(), key=lambda kv: -kv[1][1])}}
 
 
 # DRAM traffic of the tensor-core convolution kernel.  One ncu capture
@@ -492,6 +541,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--backward", action="store_true",
+                    help="1 GPU: also time forward + backward (input and filter gradients of every layer) and "
+                         "add a \"training\" object with its per-kernel times to the JSON line")
     ap.add_argument("--no-gather", action="store_true",
                     help="diagnostic for N>1: skip the NCCL gather (independent replicas) to separate its cost "
                          "from host-side contention between the ranks' processes")

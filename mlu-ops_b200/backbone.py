@@ -191,6 +191,47 @@ class SparseNetwork:
                 ready = None
         return cur_feat, cur_idx, records
 
+    def backward(self, records, grad_out):
+        """Gradients of the layer stack, last layer first, from the records of
+        forward(keep=True) and the gradient of its final features.  Per layer one
+        mluOpIndiceConvolutionBackwardFilter and one mluOpIndiceConvolutionBackwardData
+        call on the rulebook the forward pass generated.  Returns (input_grad of the
+        first layer, [filters_grad per layer])."""
+        lib, h = self.lib, self.handle.ptr
+        grad = grad_out
+        filter_grads = [None] * len(records)
+        for li in range(len(records) - 1, -1, -1):
+            rec, w = records[li], self.weights[li]
+            ly = rec.layer
+            K, L, n_out = ly.kernel_volume, rec.n_in, rec.n_out
+            for i, v in enumerate(rec.indice_num):
+                self.num_i64[i] = v
+            d_f, d_g = self.d_feat.set(L, ly.ci), self.d_fout.set(n_out, ly.co)
+            d_p, d_w = self.d_pairs.set(K, 2, L), self.d_filt[li].ptr
+            dw = torch.empty_like(w)
+            ops.check("mluOpGetIndiceConvolutionBackwardFilterWorkspaceSize",
+                      lib.mluOpGetIndiceConvolutionBackwardFilterWorkspaceSize(h, d_f, d_g, d_p, d_w, self.num_i64, 0,
+                                                                               ly.sub_m, ctypes.byref(self.size)))
+            ws = self.workspace.get(self.size.value)
+            ops.check("mluOpIndiceConvolutionBackwardFilter",
+                      lib.mluOpIndiceConvolutionBackwardFilter(h, d_f, _vp(rec.features_in.data_ptr()), d_g,
+                                                               _vp(grad.data_ptr()), d_p, _vp(rec.pairs.data_ptr()),
+                                                               self.num_i64, 0, ly.sub_m, _vp(ws.data_ptr()),
+                                                               self.size.value, d_w, _vp(dw.data_ptr())))
+            filter_grads[li] = dw
+            dx = torch.empty((L, ly.ci), dtype=grad.dtype, device=self.device)
+            ops.check("mluOpGetIndiceConvolutionBackwardDataWorkspaceSize",
+                      lib.mluOpGetIndiceConvolutionBackwardDataWorkspaceSize(h, d_g, d_w, d_p, d_f, self.num_i64, 0,
+                                                                             ctypes.byref(self.size)))
+            ws = self.workspace.get(self.size.value)
+            ops.check("mluOpIndiceConvolutionBackwardData",
+                      lib.mluOpIndiceConvolutionBackwardData(h, d_g, _vp(grad.data_ptr()), d_w, _vp(w.data_ptr()), d_p,
+                                                             _vp(rec.pairs.data_ptr()), self.num_i64, 0, ly.sub_m,
+                                                             _vp(ws.data_ptr()), self.size.value, d_f,
+                                                             _vp(dx.data_ptr())))
+            grad = dx
+        return grad, filter_grads
+
 
 def roofline_bytes_and_flops(records, elem_size):
     """Algorithmic bytes and flops of a run, from its actual pair counts.

@@ -11,9 +11,11 @@
 // the pair list.  A thread block takes one segment of one pair list, gathers
 // the two rows of every pair into shared memory (cp.async, 16 bytes at a time),
 // and accumulates the [Ci x Co] product in float:
-//   filterGradMmaKernel      half, Ci and Co in {16,32,64,128}: mma.sync m16n8k16;
+//   filterGradMmaKernel      half, Ci in {4,8,16,32,64,128}, Co in {16,32,64,128}: mma.sync m16n8k16;
 //                            both operands lie pair-major in shared memory, so
 //                            both fragments come from ldmatrix.trans
+//   filterGradSmallKernel    Ci*Co <= 256 (a backbone's first layer): one thread per
+//                            output element, pairs dealt round-robin to thread groups
 //   filterGradGenericKernel  float, and half with other channel counts: FMA
 // Every block writes its float partial; reduceFilterGradKernel adds the partials
 // of an offset in ascending segment order and converts to the output type, so
@@ -68,10 +70,13 @@ __device__ __forceinline__ void mmaF16(float (&d)[4], const unsigned (&a)[4], un
 
 // ------------------------------------------------------------ tensor cores
 
-// 8 warps tile the [Ci x Co] product as kWarpsM x kWarpsN; when the product is
-// too small for eight tiles the remaining factor kWarpsK splits the pairs of a
-// stage between warps (summed through shared memory at the end).
-template <int CI, int CO>
+// 8 warps tile the [Ci x Co] product as kWarpsM x kWarpsN (up to 4 x 2); when the
+// product is too small for eight tiles the remaining factor kWarpsK splits the
+// pairs of a stage between warps (summed through shared memory at the end).
+// (Wider warp tiles with a four-way pair split measured 35 % slower at 64 x 64.)
+// CI_REAL < CI (4 or 8 channels, a backbone's first layer): feature rows are
+// CI_REAL halves long and sit in the first columns of zero-filled 16-column rows.
+template <int CI, int CO, int CI_REAL>
 struct GradMmaConfig {
   static constexpr int kThreads = 256;
   static constexpr int kTilesM = CI / 16, kTilesN = CO / 8;
@@ -80,21 +85,34 @@ struct GradMmaConfig {
   static constexpr int kWarpsK = 8 / (kWarpsM * kWarpsN);
   static constexpr int kMI = kTilesM / kWarpsM;  // m16 tiles per warp
   static constexpr int kNI = kTilesN / kWarpsN;  // n8 tiles per warp (even)
-  static constexpr int kStagePairs = 16 * (kWarpsK > 4 ? kWarpsK : 4);
+  // about 16 KB of rows per stage: 64 pairs at 64+64 channels, up to 256 at 16+16;
+  // every warp of a split needs a 16-pair slice per stage
+  static constexpr int kByBytes = 8192 / (CI + CO);
+  static constexpr int kByBytesPow2 = kByBytes >= 256 ? 256 : (kByBytes >= 128 ? 128 : 64);
+  static constexpr int kStagePairs = kByBytesPow2 > 16 * kWarpsK ? kByBytesPow2 : 16 * kWarpsK;
   static constexpr int kStages = 3;
   static constexpr int kStrideA = CI + 8, kStrideB = CO + 8;  // halves; 16-byte pad: conflict-free ldmatrix
   static constexpr int kStageHalves = kStagePairs * (kStrideA + kStrideB);
   static constexpr size_t kPipeBytes = (size_t)kStages * kStageHalves * sizeof(__half);
   static constexpr size_t kSumBytes = (size_t)kWarpsK * CI * CO * sizeof(float);
-  static constexpr size_t kSmemBytes = kPipeBytes > kSumBytes ? kPipeBytes : kSumBytes;
+  static constexpr size_t kRowsBytes = kPipeBytes > kSumBytes ? kPipeBytes : kSumBytes;
+  // after the rows: two slots of pair ids (feature row, output_grad row) of one stage each
+  static constexpr size_t kIdBytes = (size_t)2 * 2 * kStagePairs * sizeof(int32_t);
+  static constexpr size_t kSmemBytes = kRowsBytes + kIdBytes;
 };
 
-template <int CI, int CO>
+__device__ __forceinline__ void cpAsync8(void *smem, const void *gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 8 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+
+template <int CI, int CO, int CI_REAL>
 __global__ void __launch_bounds__(256)
 filterGradMmaKernel(const __half *__restrict__ features, const __half *__restrict__ output_grad,
                     const int32_t *__restrict__ pairs, const int32_t *__restrict__ counts, int64_t L,
                     int seg_pairs, int max_segments, float *__restrict__ partial) {
-  using Cfg = GradMmaConfig<CI, CO>;
+  using Cfg = GradMmaConfig<CI, CO, CI_REAL>;
   const int k = blockIdx.y, seg = blockIdx.x;
   const int64_t pk = counts[k];
   const int64_t begin = (int64_t)seg * seg_pairs;
@@ -122,40 +140,67 @@ filterGradMmaKernel(const __half *__restrict__ features, const __half *__restric
 
   const int n_stages = (int)((end - begin + Cfg::kStagePairs - 1) / Cfg::kStagePairs);
 
+  // Pair ids reach shared memory one stage before the rows that they address are
+  // requested, so that no cp.async waits for a dependent global load.
+  int32_t *ids_s = reinterpret_cast<int32_t *>(smem_raw + Cfg::kRowsBytes);  // [2][2][kStagePairs]
+  auto loadIds = [&](int s) {
+    int32_t *slot = ids_s + (s & 1) * 2 * Cfg::kStagePairs;
+    const int64_t base = begin + (int64_t)s * Cfg::kStagePairs;
+    for (int r = tid; r < 2 * Cfg::kStagePairs; r += Cfg::kThreads) {
+      const int rr = r < Cfg::kStagePairs ? r : r - Cfg::kStagePairs;
+      const int32_t *src = r < Cfg::kStagePairs ? in_row : out_row;
+      slot[r] = base + rr < end ? src[base + rr] : -1;
+    }
+  };
   // 16-byte chunks of one stage: first the feature rows, then the output_grad rows
-  constexpr int kChunksA = CI / 8, kChunksB = CO / 8;
+  constexpr int kChunksA = CI_REAL < 8 ? 1 : CI_REAL / 8, kChunksB = CO / 8;
   constexpr int kStageChunks = Cfg::kStagePairs * (kChunksA + kChunksB);
-  auto issue = [&](int s) {
+  auto issue = [&](int s, bool ids_in_smem) {
     __half *a_s = stage_s + (size_t)(s % Cfg::kStages) * Cfg::kStageHalves;
     __half *b_s = a_s + Cfg::kStagePairs * Cfg::kStrideA;
+    const int32_t *slot = ids_s + (s & 1) * 2 * Cfg::kStagePairs;
     const int64_t base = begin + (int64_t)s * Cfg::kStagePairs;
     for (int c = tid; c < kStageChunks; c += Cfg::kThreads) {
       if (c < Cfg::kStagePairs * kChunksA) {
         const int r = c / kChunksA, ch = c % kChunksA;
-        const bool live = base + r < end;
-        const int64_t id = live ? in_row[base + r] : 0;
-        cpAsync16(a_s + r * Cfg::kStrideA + ch * 8, features + id * CI + ch * 8, live);
+        const int32_t id = ids_in_smem ? slot[r] : (base + r < end ? in_row[base + r] : -1);
+        const __half *src = features + (int64_t)(id < 0 ? 0 : id) * CI_REAL + ch * 8;
+        if (CI_REAL < 8) {
+          cpAsync8(a_s + r * Cfg::kStrideA, src, id >= 0);
+        } else {
+          cpAsync16(a_s + r * Cfg::kStrideA + ch * 8, src, id >= 0);
+        }
       } else {
         const int c2 = c - Cfg::kStagePairs * kChunksA;
         const int r = c2 / kChunksB, ch = c2 % kChunksB;
-        const bool live = base + r < end;
-        const int64_t id = live ? out_row[base + r] : 0;
-        cpAsync16(b_s + r * Cfg::kStrideB + ch * 8, output_grad + id * CO + ch * 8, live);
+        const int32_t id =
+            ids_in_smem ? slot[Cfg::kStagePairs + r] : (base + r < end ? out_row[base + r] : -1);
+        cpAsync16(b_s + r * Cfg::kStrideB + ch * 8, output_grad + (int64_t)(id < 0 ? 0 : id) * CO + ch * 8, id >= 0);
       }
     }
   };
 
+  if (CI_REAL < CI) {
+    // columns CI_REAL.. of the feature rows are never copied to: zero them once
+    for (int e = tid; e < Cfg::kStages * Cfg::kStageHalves / 8; e += Cfg::kThreads)
+      reinterpret_cast<uint4 *>(stage_s)[e] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+  }
+  // prologue: the first stages read their ids straight from global memory; the ids of
+  // the stage that iteration 0 requests go to shared memory
 #pragma unroll
   for (int s = 0; s < Cfg::kStages - 1; ++s) {
-    if (s < n_stages) issue(s);
+    if (s < n_stages) issue(s, false);
     cpAsyncCommit();
   }
+  if (Cfg::kStages - 1 < n_stages) loadIds(Cfg::kStages - 1);
   const int j = lane >> 3, r8 = lane & 7;
   for (int s = 0; s < n_stages; ++s) {
     cpAsyncWait<Cfg::kStages - 2>();
     __syncthreads();
-    if (s + Cfg::kStages - 1 < n_stages) issue(s + Cfg::kStages - 1);
+    if (s + Cfg::kStages - 1 < n_stages) issue(s + Cfg::kStages - 1, true);
     cpAsyncCommit();
+    if (s + Cfg::kStages < n_stages) loadIds(s + Cfg::kStages);
     const __half *a_s = stage_s + (size_t)(s % Cfg::kStages) * Cfg::kStageHalves;
     const __half *b_s = a_s + Cfg::kStagePairs * Cfg::kStrideA;
 #pragma unroll
@@ -200,8 +245,8 @@ filterGradMmaKernel(const __half *__restrict__ features, const __half *__restric
       *reinterpret_cast<float2 *>(dst + (m + 8) * CO + n) = make_float2(acc[mi][ni][2], acc[mi][ni][3]);
     }
   __syncthreads();
-  float *dst = partial + ((size_t)k * max_segments + seg) * CI * CO;
-  for (int e = tid; e < CI * CO; e += Cfg::kThreads) {
+  float *dst = partial + ((size_t)k * max_segments + seg) * CI_REAL * CO;
+  for (int e = tid; e < CI_REAL * CO; e += Cfg::kThreads) {
     float v = sum_s[e];
 #pragma unroll
     for (int w = 1; w < Cfg::kWarpsK; ++w) v += sum_s[(size_t)w * CI * CO + e];
@@ -267,6 +312,54 @@ filterGradGenericKernel(const T *__restrict__ features, const T *__restrict__ ou
     }
 }
 
+// ------------------------------------------------------------ narrow filters
+
+constexpr int kSmallOutputs = 256;  // Ci*Co up to this: one thread per output element
+constexpr int kSmallUnroll = 4;
+
+// Ci*Co <= 256 (the first layer of a backbone: 4 -> 16 channels).  Thread t owns
+// output element t % (Ci*Co) and, of its segment, the pairs g, g+G, ... with
+// g = t / (Ci*Co) and G = 256 / (Ci*Co); the G sums are added in ascending g.
+template <typename T>
+__global__ void __launch_bounds__(256)
+filterGradSmallKernel(const T *__restrict__ features, const T *__restrict__ output_grad,
+                      const int32_t *__restrict__ pairs, const int32_t *__restrict__ counts, int64_t L,
+                      int ci, int co, int seg_pairs, int max_segments, float *__restrict__ partial) {
+  const int k = blockIdx.y, seg = blockIdx.x;
+  const int64_t pk = counts[k];
+  const int64_t begin = (int64_t)seg * seg_pairs;
+  if (begin >= pk) return;
+  const int64_t end = begin + seg_pairs < pk ? begin + seg_pairs : pk;
+  const int32_t *in_row = pairs + (size_t)k * 2 * L;
+  const int32_t *out_row = in_row + L;
+  const int per = ci * co, groups = 256 / per;
+  const int tid = threadIdx.x, g = tid / per, e = tid % per;
+  const int c = e / co, n = e % co;
+  __shared__ float sum_s[256];
+  float acc = 0.0f;
+  if (g < groups) {
+    for (int64_t p = begin + g; p < end; p += (int64_t)kSmallUnroll * groups) {
+      float a[kSmallUnroll], b[kSmallUnroll];
+#pragma unroll
+      for (int u = 0; u < kSmallUnroll; ++u) {
+        const int64_t q = p + (int64_t)u * groups;
+        const bool live = q < end;
+        a[u] = live ? toFloat(features[(int64_t)in_row[q] * ci + c]) : 0.0f;
+        b[u] = live ? toFloat(output_grad[(int64_t)out_row[q] * co + n]) : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < kSmallUnroll; ++u) acc = fmaf(a[u], b[u], acc);
+    }
+  }
+  sum_s[tid] = acc;
+  __syncthreads();
+  if (tid < per) {
+    float v = sum_s[tid];
+    for (int w = 1; w < groups; ++w) v += sum_s[w * per + tid];
+    partial[((size_t)k * max_segments + seg) * per + tid] = v;
+  }
+}
+
 // ------------------------------------------------------------ reduction
 
 template <typename T>
@@ -286,18 +379,18 @@ reduceFilterGradKernel(const float *__restrict__ partial, const int32_t *__restr
   }
 }
 
-template <int CI, int CO>
+template <int CI, int CO, int CI_REAL>
 cudaError_t launchGradMma(const FilterGradProblem &p, const FilterGradWorkspacePlan &plan,
                           const __half *features, const __half *output_grad, const int32_t *pairs,
                           const int32_t *counts, float *partial, double bytes, double flops,
                           cudaStream_t stream) {
-  using Cfg = GradMmaConfig<CI, CO>;
-  auto kernel = filterGradMmaKernel<CI, CO>;
+  using Cfg = GradMmaConfig<CI, CO, CI_REAL>;
+  auto kernel = filterGradMmaKernel<CI, CO, CI_REAL>;
   cudaError_t err =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes);
   if (err != cudaSuccess) return err;
   static const std::string name =
-      "filterGradMmaKernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
+      "filterGradMmaKernel<" + std::to_string(CI_REAL) + "," + std::to_string(CO) + ">";
   trace::Scope t(name.c_str(), stream, bytes, flops);
   const dim3 grid((unsigned)plan.max_segments, (unsigned)p.K);
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(features, output_grad, pairs, counts, p.L,
@@ -305,23 +398,24 @@ cudaError_t launchGradMma(const FilterGradProblem &p, const FilterGradWorkspaceP
   return cudaGetLastError();
 }
 
-template <int CI>
+template <int CI, int CI_REAL>
 cudaError_t dispatchGradMmaCo(const FilterGradProblem &p, const FilterGradWorkspacePlan &plan,
-                              const __half *features, const __half *output_grad, const int32_t *pairs,
-                              const int32_t *counts, float *partial, double bytes, double flops,
-                              cudaStream_t stream) {
+                              const __half *f, const __half *g, const int32_t *pairs, const int32_t *counts,
+                              float *partial, double bytes, double flops, cudaStream_t stream) {
   switch (p.co) {
-    case 16: return launchGradMma<CI, 16>(p, plan, features, output_grad, pairs, counts, partial, bytes, flops, stream);
-    case 32: return launchGradMma<CI, 32>(p, plan, features, output_grad, pairs, counts, partial, bytes, flops, stream);
-    case 64: return launchGradMma<CI, 64>(p, plan, features, output_grad, pairs, counts, partial, bytes, flops, stream);
-    case 128: return launchGradMma<CI, 128>(p, plan, features, output_grad, pairs, counts, partial, bytes, flops, stream);
+    case 16: return launchGradMma<CI, 16, CI_REAL>(p, plan, f, g, pairs, counts, partial, bytes, flops, stream);
+    case 32: return launchGradMma<CI, 32, CI_REAL>(p, plan, f, g, pairs, counts, partial, bytes, flops, stream);
+    case 64: return launchGradMma<CI, 64, CI_REAL>(p, plan, f, g, pairs, counts, partial, bytes, flops, stream);
+    case 128: return launchGradMma<CI, 128, CI_REAL>(p, plan, f, g, pairs, counts, partial, bytes, flops, stream);
     default: return cudaErrorInvalidValue;
   }
 }
 
 bool gradMmaEligible(const FilterGradProblem &p, const void *features, const void *output_grad) {
-  auto ok = [](int c) { return c == 16 || c == 32 || c == 64 || c == 128; };
-  return p.is_half && ok(p.ci) && ok(p.co) && reinterpret_cast<size_t>(features) % 16 == 0 &&
+  auto ok_ci = [](int c) { return c == 4 || c == 8 || c == 16 || c == 32 || c == 64 || c == 128; };
+  auto ok_co = [](int c) { return c == 16 || c == 32 || c == 64 || c == 128; };
+  const size_t row_align = p.ci == 4 ? 8 : 16;
+  return p.is_half && ok_ci(p.ci) && ok_co(p.co) && reinterpret_cast<size_t>(features) % row_align == 0 &&
          reinterpret_cast<size_t>(output_grad) % 16 == 0;
 }
 
@@ -390,11 +484,27 @@ cudaError_t launchIndiceConvolutionBackwardFilter(const FilterGradProblem &p,
     const __half *f = static_cast<const __half *>(features);
     const __half *g = static_cast<const __half *>(output_grad);
     switch (p.ci) {
-      case 16: err = dispatchGradMmaCo<16>(p, plan, f, g, indice_pairs, counts, partial, bytes, flops, stream); break;
-      case 32: err = dispatchGradMmaCo<32>(p, plan, f, g, indice_pairs, counts, partial, bytes, flops, stream); break;
-      case 64: err = dispatchGradMmaCo<64>(p, plan, f, g, indice_pairs, counts, partial, bytes, flops, stream); break;
-      default: err = dispatchGradMmaCo<128>(p, plan, f, g, indice_pairs, counts, partial, bytes, flops, stream); break;
+      case 4: err = dispatchGradMmaCo<16, 4>(p, plan, f, g, indice_pairs, counts, partial, bytes, flops, stream); break;
+      case 8: err = dispatchGradMmaCo<16, 8>(p, plan, f, g, indice_pairs, counts, partial, bytes, flops, stream); break;
+      case 16: err = dispatchGradMmaCo<16, 16>(p, plan, f, g, indice_pairs, counts, partial, bytes, flops, stream); break;
+      case 32: err = dispatchGradMmaCo<32, 32>(p, plan, f, g, indice_pairs, counts, partial, bytes, flops, stream); break;
+      case 64: err = dispatchGradMmaCo<64, 64>(p, plan, f, g, indice_pairs, counts, partial, bytes, flops, stream); break;
+      default: err = dispatchGradMmaCo<128, 128>(p, plan, f, g, indice_pairs, counts, partial, bytes, flops, stream); break;
     }
+  } else if (p.ci * p.co <= kSmallOutputs) {
+    const dim3 grid((unsigned)plan.max_segments, (unsigned)p.K);
+    if (p.is_half) {
+      trace::Scope t("filterGradSmallKernel<half>", stream, bytes, flops);
+      filterGradSmallKernel<__half><<<grid, 256, 0, stream>>>(
+          static_cast<const __half *>(features), static_cast<const __half *>(output_grad), indice_pairs, counts,
+          p.L, p.ci, p.co, plan.seg_pairs, plan.max_segments, partial);
+    } else {
+      trace::Scope t("filterGradSmallKernel<float>", stream, bytes, flops);
+      filterGradSmallKernel<float><<<grid, 256, 0, stream>>>(
+          static_cast<const float *>(features), static_cast<const float *>(output_grad), indice_pairs, counts,
+          p.L, p.ci, p.co, plan.seg_pairs, plan.max_segments, partial);
+    }
+    err = cudaGetLastError();
   } else {
     const int tiles = ((p.ci + kGenTile - 1) / kGenTile) * ((p.co + kGenTile - 1) / kGenTile);
     const dim3 grid((unsigned)plan.max_segments, (unsigned)p.K, (unsigned)tiles);

@@ -416,8 +416,10 @@ cudaError_t launchTc(const ConvProblem &p, const ConvWorkspacePlan &plan, const 
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess) return err;
   const unsigned blocks = (unsigned)(plan.n_pad / (Cfg::kTiles * kTile));
+  // the input gradient runs the same kernel; its launches are listed apart in the trace
   static const std::string name = "convTcgen05Kernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
-  trace::Scope t(name.c_str(), stream, algo_bytes, algo_flops);
+  static const std::string name_dgrad = name + ":input_grad";
+  trace::Scope t(p.backward_data ? name_dgrad.c_str() : name.c_str(), stream, algo_bytes, algo_flops);
   kernel<<<blocks, kThreads, smem, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K, out, status);
   return cudaGetLastError();
 }

@@ -141,15 +141,27 @@ filterGradMmaKernel(const __half *__restrict__ features, const __half *__restric
   const int n_stages = (int)((end - begin + Cfg::kStagePairs - 1) / Cfg::kStagePairs);
 
   // Pair ids reach shared memory one stage before the rows that they address are
-  // requested, so that no cp.async waits for a dependent global load.
+  // requested, so that no cp.async waits for a dependent global load: they are
+  // read into registers before a stage is computed and stored after it.
   int32_t *ids_s = reinterpret_cast<int32_t *>(smem_raw + Cfg::kRowsBytes);  // [2][2][kStagePairs]
-  auto loadIds = [&](int s) {
-    int32_t *slot = ids_s + (s & 1) * 2 * Cfg::kStagePairs;
+  constexpr int kIdsPerThread = (2 * Cfg::kStagePairs + Cfg::kThreads - 1) / Cfg::kThreads;
+  int32_t id_reg[kIdsPerThread];
+  auto fetchIds = [&](int s) {
     const int64_t base = begin + (int64_t)s * Cfg::kStagePairs;
-    for (int r = tid; r < 2 * Cfg::kStagePairs; r += Cfg::kThreads) {
+#pragma unroll
+    for (int i = 0; i < kIdsPerThread; ++i) {
+      const int r = tid + i * Cfg::kThreads;
       const int rr = r < Cfg::kStagePairs ? r : r - Cfg::kStagePairs;
       const int32_t *src = r < Cfg::kStagePairs ? in_row : out_row;
-      slot[r] = base + rr < end ? src[base + rr] : -1;
+      id_reg[i] = (r < 2 * Cfg::kStagePairs && base + rr < end) ? src[base + rr] : -1;
+    }
+  };
+  auto storeIds = [&](int s) {
+    int32_t *slot = ids_s + (s & 1) * 2 * Cfg::kStagePairs;
+#pragma unroll
+    for (int i = 0; i < kIdsPerThread; ++i) {
+      const int r = tid + i * Cfg::kThreads;
+      if (r < 2 * Cfg::kStagePairs) slot[r] = id_reg[i];
     }
   };
   // 16-byte chunks of one stage: first the feature rows, then the output_grad rows
@@ -193,14 +205,18 @@ filterGradMmaKernel(const __half *__restrict__ features, const __half *__restric
     if (s < n_stages) issue(s, false);
     cpAsyncCommit();
   }
-  if (Cfg::kStages - 1 < n_stages) loadIds(Cfg::kStages - 1);
+  if (Cfg::kStages - 1 < n_stages) {
+    fetchIds(Cfg::kStages - 1);
+    storeIds(Cfg::kStages - 1);
+  }
   const int j = lane >> 3, r8 = lane & 7;
   for (int s = 0; s < n_stages; ++s) {
     cpAsyncWait<Cfg::kStages - 2>();
     __syncthreads();
     if (s + Cfg::kStages - 1 < n_stages) issue(s + Cfg::kStages - 1, true);
     cpAsyncCommit();
-    if (s + Cfg::kStages < n_stages) loadIds(s + Cfg::kStages);
+    const bool more_ids = s + Cfg::kStages < n_stages;
+    if (more_ids) fetchIds(s + Cfg::kStages);
     const __half *a_s = stage_s + (size_t)(s % Cfg::kStages) * Cfg::kStageHalves;
     const __half *b_s = a_s + Cfg::kStagePairs * Cfg::kStrideA;
 #pragma unroll
@@ -228,6 +244,7 @@ filterGradMmaKernel(const __half *__restrict__ features, const __half *__restric
         }
       }
     }
+    if (more_ids) storeIds(s + Cfg::kStages);
   }
   cpAsyncWait<0>();
   __syncthreads();
@@ -424,13 +441,17 @@ bool gradMmaEligible(const FilterGradProblem &p, const void *features, const voi
 FilterGradWorkspacePlan planFilterGradWorkspace(const FilterGradProblem &p, const int64_t *indice_num,
                                                 int sm_count) {
   FilterGradWorkspacePlan plan{};
-  int64_t max_pairs = 0;
-  for (int k = 0; k < p.K; ++k) max_pairs = indice_num[k] > max_pairs ? indice_num[k] : max_pairs;
-  // About six blocks per SM if every list were as long as the longest; at least 512
-  // pairs per block so that the partials stay small next to the gathered rows.
-  const int64_t blocks = (int64_t)(sm_count > 0 ? sm_count : 148) * 6;
-  int64_t seg = (max_pairs * p.K + blocks - 1) / blocks;
-  if (seg < 512) seg = 512;
+  int64_t max_pairs = 0, total_pairs = 0;
+  for (int k = 0; k < p.K; ++k) {
+    max_pairs = indice_num[k] > max_pairs ? indice_num[k] : max_pairs;
+    total_pairs += indice_num[k];
+  }
+  // About sixteen blocks per SM (four waves at four resident blocks, so that the
+  // last wave costs little); at least 1024 pairs per block so that the partials
+  // stay small next to the gathered rows.
+  const int64_t blocks = (int64_t)(sm_count > 0 ? sm_count : 148) * 16;
+  int64_t seg = (total_pairs + blocks - 1) / blocks;
+  if (seg < 1024) seg = 1024;
   seg = (seg + 127) / 128 * 128;
   // Wide filters: fewer, longer segments so that the partials stay below 128 MiB.
   const int64_t partial_cap = (int64_t)128 << 20;

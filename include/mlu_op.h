@@ -26,6 +26,7 @@
 #define MLUOP_VERSION (MLUOP_MAJOR * 1000 + MLUOP_MINOR * 100 + MLUOP_PATCHLEVEL)
 #define MLUOP_DIM_MAX 8     /* reference mlu_op.h:39 */
 
+#include <stdbool.h>
 #include <stddef.h>
 #include <stdint.h>
 
@@ -316,6 +317,39 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilter(
     const int64_t indice_num[], const int64_t inverse, const int64_t sub_m, void *workspace,
     const size_t workspace_size, const mluOpTensorDescriptor_t filters_grad_desc,
     void *filters_grad);
+
+/* ------------------------------------------------ the step before the path */
+
+/* reference mlu_op.h:5942, kernels/voxelization/voxelization.cpp:178.  Bytes of
+ * device scratch mluOpVoxelization needs (this implementation's own figure). */
+mluOpStatus_t MLUOP_WIN_API mluOpGetVoxelizationWorkspaceSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t points_desc,
+    const mluOpTensorDescriptor_t voxel_size_desc,
+    const mluOpTensorDescriptor_t coors_range_desc, const int32_t max_points,
+    const int32_t max_voxels, const int32_t NDim, const bool deterministic,
+    const mluOpTensorDescriptor_t voxels_desc, const mluOpTensorDescriptor_t coors_desc,
+    const mluOpTensorDescriptor_t num_points_per_voxel_desc,
+    const mluOpTensorDescriptor_t voxel_num_desc, size_t *size);
+
+/* reference mlu_op.h:6051, kernels/voxelization/voxelization.cpp:226.  Hard
+ * voxelization, deterministic mode (the only mode the reference supports):
+ *   points [N,F] float (x, y, z first), voxel_size [3], coors_range [6] =
+ *   (x_min, y_min, z_min, x_max, y_max, z_max), all float, on the device
+ *   voxels [max_voxels,max_points,F] float, coors [max_voxels,3] int32 (z, y, x),
+ *   num_points_per_voxel [max_voxels] int32, voxel_num [1] int32
+ * Voxels are numbered in the order of their first points; a voxel keeps its
+ * first max_points points in index order; rows past voxel_num are zero.
+ * Asynchronous on the handle's queue. */
+mluOpStatus_t MLUOP_WIN_API mluOpVoxelization(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t points_desc, const void *points,
+    const mluOpTensorDescriptor_t voxel_size_desc, const void *voxel_size,
+    const mluOpTensorDescriptor_t coors_range_desc, const void *coors_range,
+    const int32_t max_points, const int32_t max_voxels, const int32_t NDim,
+    const bool deterministic, void *workspace, size_t workspace_size,
+    const mluOpTensorDescriptor_t voxels_desc, void *voxels,
+    const mluOpTensorDescriptor_t coors_desc, void *coors,
+    const mluOpTensorDescriptor_t num_points_per_voxel_desc, void *num_points_per_voxel,
+    const mluOpTensorDescriptor_t voxel_num_desc, void *voxel_num);
 
 /* No counterpart in the reference.  Same computation and arguments as
  * mluOpIndiceConvolutionForward, without the workspace pair: the scratch is a

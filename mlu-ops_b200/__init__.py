@@ -79,6 +79,11 @@ SIGNATURES = {
                                                                    ctypes.POINTER(_szt)]),
     "mluOpIndiceConvolutionBackwardFilter": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64, _vp,
                                                    _szt, _vp, _vp]),
+    "mluOpGetVoxelizationWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32,
+                                                ctypes.c_int32, ctypes.c_bool, _vp, _vp, _vp, _vp,
+                                                ctypes.POINTER(_szt)]),
+    "mluOpVoxelization": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                ctypes.c_bool, _vp, _szt, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     # include/mlu_op_trace.h
     "mluOpTraceKernelEnable": (_int, [_int]),
     "mluOpTraceKernelReset": (_int, []),
@@ -390,3 +395,38 @@ def indice_convolution_backward_filter(handle, features, output_grad, filter_spa
     for d in (d_f, d_g, d_p, d_w):
         d.destroy()
     return out
+
+
+def voxelization(handle, points, voxel_size, coors_range, max_points, max_voxels, workspace=None):
+    """Deterministic hard voxelization through mluOpVoxelization.
+
+    points [N,F] float32 (x, y, z first), voxel_size [3] and coors_range [6] float32,
+    all CUDA tensors.  Returns (voxels [max_voxels,max_points,F], coors [max_voxels,3]
+    int32 (z,y,x), num_points_per_voxel [max_voxels] int32, voxel_num [1] int32), all on
+    the device.
+    """
+    import torch
+    n, f = points.shape
+    dev = points.device
+    voxels = torch.empty((max_voxels, max_points, f), dtype=torch.float32, device=dev)
+    coors = torch.empty((max_voxels, 3), dtype=torch.int32, device=dev)
+    npv = torch.empty((max_voxels,), dtype=torch.int32, device=dev)
+    num = torch.zeros((1,), dtype=torch.int32, device=dev)
+    descs = [TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (n, f)), TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (3,)),
+             TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (6,)), TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, tuple(voxels.shape)),
+             TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (max_voxels, 3)), TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (max_voxels,)),
+             TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (1,))]
+    d_p, d_vs, d_cr, d_v, d_c, d_n, d_num = (d.ptr for d in descs)
+    size = _szt(0)
+    check("mluOpGetVoxelizationWorkspaceSize",
+          lib().mluOpGetVoxelizationWorkspaceSize(handle.ptr, d_p, d_vs, d_cr, max_points, max_voxels, 3, True, d_v,
+                                                  d_c, d_n, d_num, ctypes.byref(size)))
+    if workspace is None or workspace.numel() < size.value:
+        workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+    check("mluOpVoxelization",
+          lib().mluOpVoxelization(handle.ptr, d_p, _ptr(points), d_vs, _ptr(voxel_size), d_cr, _ptr(coors_range),
+                                  max_points, max_voxels, 3, True, _ptr(workspace), size.value, d_v, _ptr(voxels),
+                                  d_c, _ptr(coors), d_n, _ptr(npv), d_num, _ptr(num)))
+    for d in descs:
+        d.destroy()
+    return voxels, coors, npv, num

@@ -20,14 +20,15 @@ LIB = os.path.join(LIB_DIR, "libmluops_b200.so")
 
 def sources():
     out = []
-    for pattern in ("core/*.cpp", "kernels/sparse_conv/*.cpp", "kernels/sparse_conv/*.cu"):
+    for pattern in ("core/*.cpp", "kernels/sparse_conv/*.cpp", "kernels/sparse_conv/*.cu",
+                    "kernels/voxelization/*.cpp", "kernels/voxelization/*.cu"):
         out += sorted(glob.glob(os.path.join(CSRC, pattern)))
     return out
 
 
 def headers():
     out = glob.glob(os.path.join(ROOT, "include", "*.h"))
-    for pattern in ("core/*.h", "kernels/sparse_conv/*.h", "kernels/sparse_conv/*.cuh"):
+    for pattern in ("core/*.h", "kernels/sparse_conv/*.h", "kernels/sparse_conv/*.cuh", "kernels/voxelization/*.h"):
         out += glob.glob(os.path.join(CSRC, pattern))
     return out
 

@@ -3,8 +3,8 @@
 TEST INFRASTRUCTURE ONLY: imported by tests/, the smoke check and the
 CPU-baseline leg of bench.py.  The shipped library never touches this package.
 
-  oracle.lib()      -> the plain-C restatement (oracle/sparse_conv_oracle.c and
-                       oracle/sparse_conv_backward_oracle.c)
+  oracle.lib()      -> the plain-C restatement (oracle/sparse_conv_oracle.c,
+                       oracle/sparse_conv_backward_oracle.c, oracle/voxelization_oracle.c)
   oracle.ref_lib()  -> the reference's function bodies compiled by
                        oracle/build_ref.py, or None when that library is absent
 """
@@ -17,6 +17,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "sparse_conv_oracle.c")
 SRC_BACKWARD = os.path.join(HERE, "sparse_conv_backward_oracle.c")
+SRC_VOXEL = os.path.join(HERE, "voxelization_oracle.c")
 LIB = os.path.join(HERE, "_build", "libmluops_oracle.so")
 REF_LIB = os.path.join(HERE, "_ref", "libmluops_ref_cpu.so")
 
@@ -31,10 +32,10 @@ FILTER_LAYOUT = {"ARRAY": 0, "NDHWC": 1, "NCDHW": 2}
 
 def build(force=False):
     """Compile the C oracle with gcc (a second or two)."""
-    newest = max(os.path.getmtime(SRC), os.path.getmtime(SRC_BACKWARD))
+    newest = max(os.path.getmtime(SRC), os.path.getmtime(SRC_BACKWARD), os.path.getmtime(SRC_VOXEL))
     if force or not os.path.isfile(LIB) or os.path.getmtime(LIB) < newest:
         os.makedirs(os.path.dirname(LIB), exist_ok=True)
-        subprocess.check_call(["gcc", "-O2", "-std=c11", "-fPIC", "-shared", "-o", LIB, SRC, SRC_BACKWARD, "-lm"])
+        subprocess.check_call(["gcc", "-O2", "-std=c11", "-fPIC", "-shared", "-o", LIB, SRC, SRC_BACKWARD, SRC_VOXEL, "-lm"])
     return LIB
 
 
@@ -213,6 +214,32 @@ def indice_convolution_backward_filter(features, output_grad, filter_space, indi
             ctypes.c_int64(ci), ctypes.c_int64(co), ctypes.c_int64(K), _p(out, _f32p))
     assert rc == 0
     return out
+
+
+def voxelization(points, voxel_size, coors_range, max_points, max_voxels, use_ref=False):
+    """Deterministic hard voxelization of points [N,F] float32.  Returns (voxels
+    [max_voxels,max_points,F] float32, coors [max_voxels,3] int32 (z,y,x),
+    num_points_per_voxel [max_voxels] int32, voxel_num int)."""
+    pts = np.ascontiguousarray(points, dtype=np.float32)
+    vs = np.ascontiguousarray(voxel_size, dtype=np.float32)
+    cr = np.ascontiguousarray(coors_range, dtype=np.float32)
+    n, f = pts.shape
+    voxels = np.zeros((max_voxels, max_points, f), dtype=np.float32)
+    coors = np.zeros((max_voxels, 3), dtype=np.int32)
+    npv = np.zeros((max_voxels,), dtype=np.int32)
+    num = ctypes.c_int32(0)
+    fn = None
+    if use_ref:
+        r = ref_lib()
+        assert r is not None, "oracle/_ref is not built"
+        fn = r.mluops_ref_voxelization
+    else:
+        fn = lib().mluops_oracle_voxelization
+    rc = fn(_p(pts, _f32p), ctypes.c_int64(n), ctypes.c_int64(f), _p(vs, _f32p), _p(cr, _f32p),
+            ctypes.c_int32(max_points), ctypes.c_int32(max_voxels), _p(voxels, _f32p), _p(coors, _i32p),
+            _p(npv, _i32p), ctypes.byref(num))
+    assert rc == 0
+    return voxels, coors, npv, int(num.value)
 
 
 def round_through_half(x):

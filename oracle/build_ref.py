@@ -17,6 +17,10 @@ stand-in for the members they touch:
   IndiceConvolutionBackwardFilterExecutor::cpuTranspose / cpuCompute
                                               zoo/indice_convolution_backward_filter/indice_convolution_backward_filter.cpp
 
+  dynamicVoxelize / pointToVoxelidx / determinVoxelNum / assignPointToVoxel / assignVoxelCoors and
+  VoxelizationExecutor::deterministic_hard_voxelize
+                                              zoo/voxelization/voxelization.cpp
+
 The backward-data body rounds to half through wrapRtConvertFloatToHalf /
 wrapRtConvertHalfToFloat, which forward to the vendor runtime's cast routine
 (tools.cpp:49-57); that runtime is not part of the reference tree, so the
@@ -45,10 +49,12 @@ SOURCES = {
     "tools": "test/mlu_op_gtest/pb_gtest/src/tools.cpp",
     "bwd_data": ZOO + "/indice_convolution_backward_data/indice_convolution_backward_data.cpp",
     "bwd_filter": ZOO + "/indice_convolution_backward_filter/indice_convolution_backward_filter.cpp",
+    "voxel": ZOO + "/voxelization/voxelization.cpp",
 }
 
 PRELUDE = r"""
 #include <algorithm>
+#include <cmath>
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
@@ -204,6 +210,14 @@ struct IndiceConvolutionBackwardDataExecutor {
   void cpuTransposeFilter(float *filter_transpose_cpu, mluOpTensorLayout_t origin_layout);
   void cpuCompute();
 };
+struct VoxelizationExecutor {
+  StandInRuntime cpu_runtime_;
+  void deterministic_hard_voxelize(const float *points, const float *voxel_size, const float *coors_range,
+                                   const int32_t num_points, const int32_t num_features,
+                                   const int32_t max_points, const int32_t max_voxels, const int32_t NDim,
+                                   float *voxels, float *coors, float *num_points_per_voxel,
+                                   float *voxel_num);
+};
 struct IndiceConvolutionBackwardFilterExecutor {
   StandInRuntime cpu_runtime_;
   std::vector<float *> cpu_fp32_input_;
@@ -275,6 +289,25 @@ int mluops_ref_indice_convolution_forward(const float *features, const float *fi
   ex.indice_num_.assign(indice_num, indice_num + K);
   ex.parser_storage_.out_count = num_act_out * co;
   ex.cpuCompute();
+  return 0;
+}
+
+// The reference's CPU path holds coors, num_points_per_voxel and voxel_num as float
+// copies of integers and expects zero-initialised outputs; converted here.
+int mluops_ref_voxelization(const float *points, int64_t num_points, int64_t num_features,
+                            const float *voxel_size, const float *coors_range, int32_t max_points,
+                            int32_t max_voxels, float *voxels, int32_t *coors,
+                            int32_t *num_points_per_voxel, int32_t *voxel_num) {
+  std::vector<float> coors_f((size_t)max_voxels * 3, 0.0f), npv_f((size_t)max_voxels, 0.0f);
+  float num_f = 0.0f;
+  std::fill(voxels, voxels + (size_t)max_voxels * max_points * num_features, 0.0f);
+  mluoptest::VoxelizationExecutor ex;
+  ex.deterministic_hard_voxelize(points, voxel_size, coors_range, (int32_t)num_points,
+                                 (int32_t)num_features, max_points, max_voxels, 3, voxels,
+                                 coors_f.data(), npv_f.data(), &num_f);
+  for (size_t i = 0; i < coors_f.size(); ++i) coors[i] = (int32_t)coors_f[i];
+  for (size_t i = 0; i < npv_f.size(); ++i) num_points_per_voxel[i] = (int32_t)npv_f[i];
+  *voxel_num = (int32_t)num_f;
   return 0;
 }
 
@@ -371,6 +404,10 @@ def build(reference_root="/root/reference", quiet=False):
     parts.append(extract(paths["bwd_data"], "void IndiceConvolutionBackwardDataExecutor::cpuCompute("))
     parts.append(extract(paths["bwd_filter"], "void IndiceConvolutionBackwardFilterExecutor::cpuTranspose("))
     parts.append(extract(paths["bwd_filter"], "void IndiceConvolutionBackwardFilterExecutor::cpuCompute("))
+    for fn in ("void dynamicVoxelize(", "void pointToVoxelidx(", "void determinVoxelNum(",
+               "void assignPointToVoxel(", "void assignVoxelCoors(",
+               "void VoxelizationExecutor::deterministic_hard_voxelize("):
+        parts.append(extract(paths["voxel"], fn))
     parts.append(EPILOGUE)
     with tempfile.TemporaryDirectory() as tmp:
         src = os.path.join(tmp, "ref_cpu_unit.cpp")

@@ -370,11 +370,57 @@ def run_b200(args):
     if world == 1 and args.backward:
         line["training"] = training_step(args, ops, backbone, net, d_idx, d_feat, flush, elem, hbm_gbs,
                                          tensor_tflops)
+    if world == 1 and args.voxelization:
+        line["voxelization"] = voxelization_step(args, ops, handle, flush, hbm_gbs)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_one_sample(args.workload)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def voxelization_step(args, ops, handle, flush, hbm_gbs):
+    """mluOpVoxelization on one synthetic frame: 300,000 points (x, y from a wide normal, z from a
+    narrow one, one intensity), 0.05 x 0.05 x 0.1 m voxels over 80 x 80 x 4 m, at most 5 points per
+    voxel and 160,000 voxels.  Algorithmic bytes: the points read once, the four outputs written once."""
+    import numpy as np
+    import torch
+    rng = np.random.default_rng(0x70)
+    n, f, mp, mv = 300000, 4, 5, 160000
+    pts = np.concatenate([rng.normal(0, 18, (n, 2)), rng.normal(-1, 0.8, (n, 1)), rng.random((n, 1))], 1)
+    d_pts = torch.from_numpy(pts.astype(np.float32)).cuda()
+    d_vs = torch.tensor([0.05, 0.05, 0.1], dtype=torch.float32, device="cuda")
+    d_cr = torch.tensor([-40, -40, -3, 40, 40, 1], dtype=torch.float32, device="cuda")
+    ws = torch.empty((256 << 20,), dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream()
+    for _ in range(3):
+        out = ops.voxelization(handle, d_pts, d_vs, d_cr, mp, mv, workspace=ws)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        out = ops.voxelization(handle, d_pts, d_vs, d_cr, mp, mv, workspace=ws)
+        t1.record(stream)
+        torch.cuda.synchronize()
+        times.append(t0.elapsed_time(t1))
+    ms = sum(times) / len(times)
+    ops.lib().mluOpTraceKernelReset()
+    ops.lib().mluOpTraceKernelEnable(1)
+    for _ in range(args.steps):
+        flush.fill_(1)
+        ops.voxelization(handle, d_pts, d_vs, d_cr, mp, mv, workspace=ws)
+    torch.cuda.synchronize()
+    trace = read_trace(ops)
+    ops.lib().mluOpTraceKernelEnable(0)
+    algo = n * f * 4 + mv * mp * f * 4 + mv * 12 + mv * 4 + 4
+    return {"points": n, "voxel_num": int(out[3].item()), "ms": round(ms, 4), "points_per_s": round(n / (ms * 1e-3), 1),
+            "algorithmic_bytes": algo, "GBps": round(algo / (ms * 1e-3) / 1e9, 1),
+            "frac_of_copy_bandwidth": round(algo / (ms * 1e-3) / 1e9 / hbm_gbs, 4),
+            "kernels": {k: {"launches": v[0] // args.steps, "ms": round(v[1] / args.steps, 4)}
+                        for k, v in sorted(trace.items(), key=lambda kv: -kv[1][1])}}
 
 
 def training_step(args, ops, backbone, net, d_idx, d_feat, flush, elem, hbm_gbs, tensor_tflops):
@@ -544,6 +590,9 @@ def main():
     ap.add_argument("--backward", action="store_true",
                     help="1 GPU: also time forward + backward (input and filter gradients of every layer) and "
                          "add a \"training\" object with its per-kernel times to the JSON line")
+    ap.add_argument("--voxelization", action="store_true",
+                    help="1 GPU: also time mluOpVoxelization on a synthetic 300,000-point LiDAR-like frame and add a "
+                         "\"voxelization\" object to the JSON line")
     ap.add_argument("--no-gather", action="store_true",
                     help="diagnostic for N>1: skip the NCCL gather (independent replicas) to separate its cost "
                          "from host-side contention between the ranks' processes")

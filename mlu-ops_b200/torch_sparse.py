@@ -169,3 +169,25 @@ class SparseConv3d(SparseConvolution):
 class SubMConv3d(SparseConvolution):
     def __init__(self, in_channels, out_channels, kernel_size, bias=True, indice_key=None, dtype=torch.float32):
         super().__init__(in_channels, out_channels, kernel_size, 1, 0, 1, bias, True, indice_key, dtype)
+
+
+class Voxelization(nn.Module):
+    """Hard voxelization of a point cloud (mluOpVoxelization, deterministic mode): the step
+    before the sparse backbone.  forward(points [N,F] float32) returns (voxels [M,max_points,F],
+    coors [M,3] int32 (z,y,x), num_points_per_voxel [M] int32) with M = the number of voxels
+    found (one host read), as mmcv's Voxelization module does."""
+
+    def __init__(self, voxel_size, point_cloud_range, max_num_points, max_voxels=20000):
+        super().__init__()
+        self.register_buffer("voxel_size", torch.tensor(voxel_size, dtype=torch.float32))
+        self.register_buffer("point_cloud_range", torch.tensor(point_cloud_range, dtype=torch.float32))
+        self.max_num_points, self.max_voxels = int(max_num_points), int(max_voxels)
+
+    def forward(self, points):
+        assert points.is_cuda and points.dtype == torch.float32
+        h = _handle(points.device)
+        voxels, coors, npv, num = ops.voxelization(h, points.contiguous(), self.voxel_size.to(points.device),
+                                                   self.point_cloud_range.to(points.device), self.max_num_points,
+                                                   self.max_voxels)
+        m = int(num.item())
+        return voxels[:m], coors[:m], npv[:m]

@@ -114,3 +114,20 @@ def test_a_few_optimiser_steps_reduce_the_loss(sp):
         opt.step()
         losses.append(float(loss.detach()))
     assert all(b < a for a, b in zip(losses, losses[1:])) and losses[-1] < 0.9 * losses[0], losses
+
+
+def test_points_to_backbone_features(sp, oracle):
+    """points -> Voxelization -> mean of the points of a voxel -> SparseConvTensor -> two layers."""
+    rng = np.random.default_rng(34)
+    n = 4000
+    pts = np.concatenate([rng.random((n, 3)) * [8, 8, 2], rng.random((n, 1))], 1).astype(np.float32)
+    vox = sp.Voxelization([0.5, 0.5, 0.5], [0, 0, 0, 8, 8, 2], 4, 3000).cuda()
+    voxels, coors, npv = vox(torch.from_numpy(pts).cuda())
+    ref = oracle.voxelization(pts, [0.5, 0.5, 0.5], [0, 0, 0, 8, 8, 2], 4, 3000)
+    m = ref[3]
+    assert voxels.shape[0] == m and np.array_equal(coors.cpu().numpy(), ref[1][:m])
+    feats = voxels.sum(1) / npv.unsqueeze(1).float()
+    idx = torch.cat([torch.zeros((m, 1), dtype=torch.int32, device="cuda"), coors], 1)
+    x = sp.SparseConvTensor(feats, idx, [4, 16, 16], 1)
+    y = sp.SparseConv3d(16, 8, 3, stride=2, padding=1).cuda()(sp.SubMConv3d(4, 16, 3).cuda()(x))
+    assert y.features.shape[1] == 8 and y.spatial_shape == [2, 8, 8] and torch.isfinite(y.features).all()

@@ -370,6 +370,14 @@ def run_b200(args):
     if world == 1 and args.backward:
         line["training"] = training_step(args, ops, backbone, net, d_idx, d_feat, flush, elem, hbm_gbs,
                                          tensor_tflops)
+    if world == 1 and args.fast_path:
+        def step_fast():
+            net.forward(d_idx, d_feat, reuse_tables=True)
+        for _ in range(3):
+            step_fast()
+        fast_ms = timed(step_fast, args.steps) / args.steps
+        line["fast_path"] = {"ms_per_step": round(fast_ms, 4), "value": round(L / (fast_ms * 1e-3), 1), "unit": UNIT,
+                             "what": "one neighbour table per rulebook instead of one per convolution call"}
     if world == 1 and args.voxelization:
         line["voxelization"] = voxelization_step(args, ops, handle, flush, hbm_gbs)
     if world == 1 and not args.no_cpu_baseline:
@@ -590,6 +598,10 @@ def main():
     ap.add_argument("--backward", action="store_true",
                     help="1 GPU: also time forward + backward (input and filter gradients of every layer) and "
                          "add a \"training\" object with its per-kernel times to the JSON line")
+    ap.add_argument("--fast-path", action="store_true",
+                    help="1 GPU: also time the step with one neighbour table per rulebook "
+                         "(mluOpBuildIndiceNeighbourTable + mluOpIndiceConvolutionForwardFromTable, extensions with no "
+                         "counterpart in the reference) and add a \"fast_path\" object to the JSON line")
     ap.add_argument("--voxelization", action="store_true",
                     help="1 GPU: also time mluOpVoxelization on a synthetic 300,000-point LiDAR-like frame and add a "
                          "\"voxelization\" object to the JSON line")

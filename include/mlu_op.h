@@ -318,6 +318,45 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilter(
     const size_t workspace_size, const mluOpTensorDescriptor_t filters_grad_desc,
     void *filters_grad);
 
+/* ------------------------------------------- neighbour-table fast path */
+
+/* No counterpart in the reference (the four entry points below).
+ * mluOpIndiceConvolutionForward converts indice_pairs into a neighbour table
+ * (int32 [K][rows padded to 512]: the input row that feeds an output row at a
+ * kernel offset, -1 if none) on every call.  Layers that share a rulebook can
+ * build that table once and run every convolution from it:
+ *   mluOpGetIndiceNeighbourTableSize  -> bytes of the table (caller allocates, 16-byte aligned)
+ *   mluOpBuildIndiceNeighbourTable    -> fills it from indice_pairs / indice_num (kernel volume <= 128)
+ *   mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize / mluOpIndiceConvolutionForwardFromTable
+ *       -> mluOpIndiceConvolutionForward with (table, table_size) in place of the
+ *          indice_pairs pointer; same checks, same results bit for bit.
+ * The table is valid as long as indice_pairs, indice_num and num_act_out are. */
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceNeighbourTableSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t indice_pairs_desc,
+    const int64_t num_act_out, size_t *table_size);
+
+mluOpStatus_t MLUOP_WIN_API mluOpBuildIndiceNeighbourTable(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t indice_pairs_desc,
+    const void *indice_pairs, const int64_t indice_num[], const int64_t num_act_out,
+    void *table, const size_t table_size);
+
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc,
+    const mluOpTensorDescriptor_t filters_desc,
+    const mluOpTensorDescriptor_t indice_pairs_desc,
+    const mluOpTensorDescriptor_t features_out_desc, const int64_t indice_num[],
+    const int64_t num_act_out, const int64_t inverse, const int64_t sub_m,
+    size_t *workspace_size);
+
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForwardFromTable(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc,
+    const void *features, const mluOpTensorDescriptor_t filters_desc, const void *filters,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *table,
+    const size_t table_size, const int64_t indice_num[], const int64_t num_act_out,
+    const int64_t inverse, const int64_t sub_m, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t features_out_desc,
+    void *features_out);
+
 /* ------------------------------------------------ the step before the path */
 
 /* reference mlu_op.h:5942, kernels/voxelization/voxelization.cpp:178.  Bytes of

@@ -79,6 +79,12 @@ SIGNATURES = {
                                                                    ctypes.POINTER(_szt)]),
     "mluOpIndiceConvolutionBackwardFilter": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64, _vp,
                                                    _szt, _vp, _vp]),
+    "mluOpGetIndiceNeighbourTableSize": (_int, [_vp, _vp, _i64, ctypes.POINTER(_szt)]),
+    "mluOpBuildIndiceNeighbourTable": (_int, [_vp, _vp, _vp, _i64p, _i64, _vp, _szt]),
+    "mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64,
+                                                                     _i64, ctypes.POINTER(_szt)]),
+    "mluOpIndiceConvolutionForwardFromTable": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _szt, _i64p, _i64, _i64,
+                                                     _i64, _vp, _szt, _vp, _vp]),
     "mluOpGetVoxelizationWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32,
                                                 ctypes.c_int32, ctypes.c_bool, _vp, _vp, _vp, _vp,
                                                 ctypes.POINTER(_szt)]),

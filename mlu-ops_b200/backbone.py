@@ -101,6 +101,7 @@ class SparseNetwork:
         self.num_i64 = (ctypes.c_int64 * max_k)()
         self.n_act = ctypes.c_int(0)
         self.size = ctypes.c_size_t(0)
+        self.tables = {}  # neighbour tables of the current step's rulebooks (reuse_tables)
 
     def close(self):
         for d in [self.d_idx, self.d_pairs, self.d_out_idx, self.d_num, self.d_feat, self.d_fout] + self.d_filt:
@@ -108,7 +109,7 @@ class SparseNetwork:
         for conv, _, _ in self.geometry.values():
             conv.destroy()
 
-    def forward(self, indices, features, keep=False, on_final_indices=None, on_host_idle=None):
+    def forward(self, indices, features, keep=False, on_final_indices=None, on_host_idle=None, reuse_tables=False):
         """indices [L,4] int32, features [L,Cin] on the GPU.
         Returns (features_out, out_indices, records).
 
@@ -121,7 +122,12 @@ class SparseNetwork:
         on_host_idle(layer_index), if given, is called before every rulebook generation:
         the convolutions enqueued since the previous rulebook are still running and the
         host is about to wait for the rulebook's counts, so host work done here (e.g.
-        enqueuing a collective for the previous step's rows) costs no GPU time."""
+        enqueuing a collective for the previous step's rows) costs no GPU time.
+
+        reuse_tables: build the neighbour table of a rulebook once
+        (mluOpBuildIndiceNeighbourTable) and run its convolutions through
+        mluOpIndiceConvolutionForwardFromTable, instead of the reference-shaped
+        mluOpIndiceConvolutionForward that rebuilds the table in every call."""
         lib, h = self.lib, self.handle.ptr
         final_rulebook = self.layers[-1].rulebook
         ready = None
@@ -156,6 +162,19 @@ class SparseNetwork:
                 torch.cuda.current_stream().synchronize()
                 lib.mluOpGetSparseConvolutionNumActOut(conv.ptr, ctypes.byref(self.n_act))
                 num_list = self.num_host[:K].tolist()
+                table = None
+                if reuse_tables:
+                    for i, v in enumerate(num_list):
+                        self.num_i64[i] = v
+                    d_p = self.d_pairs.set(K, 2, L)
+                    ops.check("mluOpGetIndiceNeighbourTableSize",
+                              lib.mluOpGetIndiceNeighbourTableSize(h, d_p, self.n_act.value, ctypes.byref(self.size)))
+                    table = torch.empty((max(self.size.value, 16),), dtype=torch.uint8, device=self.device)
+                    ops.check("mluOpBuildIndiceNeighbourTable",
+                              lib.mluOpBuildIndiceNeighbourTable(h, d_p, _vp(pairs.data_ptr()), self.num_i64,
+                                                                 self.n_act.value, _vp(table.data_ptr()),
+                                                                 table.numel()))
+                self.tables[ly.rulebook] = table
                 rulebooks[ly.rulebook] = (pairs, out_idx, num_list, self.n_act.value)
                 if on_final_indices is not None and ly.rulebook == final_rulebook:
                     ready = torch.cuda.Event()
@@ -167,15 +186,28 @@ class SparseNetwork:
             out = torch.empty((n_out, ly.co), dtype=cur_feat.dtype, device=self.device)
             d_f, d_p, d_o = self.d_feat.set(L, ly.ci), self.d_pairs.set(K, 2, L), self.d_fout.set(n_out, ly.co)
             d_w = self.d_filt[li].ptr
-            ops.check("mluOpGetIndiceConvolutionForwardWorkspaceSize",
-                      lib.mluOpGetIndiceConvolutionForwardWorkspaceSize(h, d_f, d_w, d_p, d_o, self.num_i64, n_out,
-                                                                        0, ly.sub_m, ctypes.byref(self.size)))
-            ws = self.workspace.get(self.size.value)
-            ops.check("mluOpIndiceConvolutionForward",
-                      lib.mluOpIndiceConvolutionForward(h, d_f, _vp(cur_feat.data_ptr()), d_w, _vp(w.data_ptr()), d_p,
-                                                        _vp(pairs.data_ptr()), self.num_i64, n_out, 0, ly.sub_m,
-                                                        _vp(ws.data_ptr()), self.size.value, d_o,
-                                                        _vp(out.data_ptr())))
+            table = self.tables.get(ly.rulebook) if reuse_tables else None
+            if table is not None:
+                ops.check("mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize",
+                          lib.mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize(
+                              h, d_f, d_w, d_p, d_o, self.num_i64, n_out, 0, ly.sub_m, ctypes.byref(self.size)))
+                ws = self.workspace.get(self.size.value)
+                ops.check("mluOpIndiceConvolutionForwardFromTable",
+                          lib.mluOpIndiceConvolutionForwardFromTable(
+                              h, d_f, _vp(cur_feat.data_ptr()), d_w, _vp(w.data_ptr()), d_p, _vp(table.data_ptr()),
+                              table.numel(), self.num_i64, n_out, 0, ly.sub_m, _vp(ws.data_ptr()), self.size.value,
+                              d_o, _vp(out.data_ptr())))
+            else:
+                ops.check("mluOpGetIndiceConvolutionForwardWorkspaceSize",
+                          lib.mluOpGetIndiceConvolutionForwardWorkspaceSize(h, d_f, d_w, d_p, d_o, self.num_i64,
+                                                                            n_out, 0, ly.sub_m,
+                                                                            ctypes.byref(self.size)))
+                ws = self.workspace.get(self.size.value)
+                ops.check("mluOpIndiceConvolutionForward",
+                          lib.mluOpIndiceConvolutionForward(h, d_f, _vp(cur_feat.data_ptr()), d_w, _vp(w.data_ptr()),
+                                                            d_p, _vp(pairs.data_ptr()), self.num_i64, n_out, 0,
+                                                            ly.sub_m, _vp(ws.data_ptr()), self.size.value, d_o,
+                                                            _vp(out.data_ptr())))
             rec = LayerRecord()
             rec.layer, rec.n_in, rec.n_out, rec.indice_num, rec.new_rulebook = ly, L, n_out, num_list, new_rb
             if keep:

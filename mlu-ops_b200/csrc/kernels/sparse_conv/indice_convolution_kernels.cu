@@ -436,7 +436,13 @@ bool mmaEligible(const ConvProblem &p, const void *features, const void *out) {
 
 }  // namespace
 
-ConvWorkspacePlan planConvWorkspace(const ConvProblem &p) {
+size_t neighbourTableBytes(const ConvProblem &p) {
+  const int64_t rows_out = p.backward_data ? p.L : p.n_out;
+  const int64_t n_pad = (rows_out + kConvPadRows - 1) / kConvPadRows * kConvPadRows;
+  return (size_t)p.K * n_pad * sizeof(int32_t);
+}
+
+ConvWorkspacePlan planConvWorkspace(const ConvProblem &p, bool external_table) {
   ConvWorkspacePlan plan{};
   const size_t elem = p.is_half ? 2 : 4;
   const int64_t rows_out = p.backward_data ? p.L : p.n_out;
@@ -447,7 +453,7 @@ ConvWorkspacePlan planConvWorkspace(const ConvProblem &p) {
   plan.filter = off;
   off = alignUp(off + (size_t)p.K * p.ci * p.co * elem, 256);
   plan.neighbour = off;
-  off = alignUp(off + (size_t)p.K * plan.n_pad * sizeof(int32_t), 256);
+  if (!external_table) off = alignUp(off + (size_t)p.K * plan.n_pad * sizeof(int32_t), 256);
   plan.counts = off;
   off = alignUp(off + (size_t)p.K * sizeof(int32_t), 256);
   plan.total = off + 256;
@@ -459,6 +465,18 @@ cudaError_t launchIndiceConvolution(const ConvProblem &caller, const ConvWorkspa
                                     const int32_t *indice_pairs, const int64_t *indice_num,
                                     void *workspace, void *features_out, int sm_count,
                                     cudaStream_t stream) {
+  return launchIndiceConvolutionSteps(caller, plan, features, filters, indice_pairs, indice_num, workspace,
+                                      features_out, sm_count, stream, nullptr, kTableBuildAndConvolve);
+}
+
+bool neighbourTableCountsFit(int32_t K) { return K <= kMaxCountsByValue; }
+
+cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWorkspacePlan &plan,
+                                         const void *features, const void *filters,
+                                         const int32_t *indice_pairs, const int64_t *indice_num,
+                                         void *workspace, void *features_out, int sm_count,
+                                         cudaStream_t stream, int32_t *external_table, int steps) {
+  const bool do_build = steps != kTableConvolveOnly, do_conv = steps != kTableBuildOnly;
   // From here on `p` describes the rows that are gathered (L of them, ci channels)
   // and the rows that are produced (n_out, co channels), whichever direction runs.
   ConvProblem p = caller;
@@ -470,13 +488,14 @@ cudaError_t launchIndiceConvolution(const ConvProblem &caller, const ConvWorkspa
     p.co = caller.ci;
   }
   const int64_t pair_stride = caller.L;
+  // Building a table alone needs no workspace (its counts travel by value).
   char *base = reinterpret_cast<char *>(alignUp(reinterpret_cast<size_t>(workspace), 256));
-  void *filter_packed = base + plan.filter;
-  int32_t *nbr = reinterpret_cast<int32_t *>(base + plan.neighbour);
-  int32_t *counts_dev = reinterpret_cast<int32_t *>(base + plan.counts);
-  int32_t *status = reinterpret_cast<int32_t *>(base + plan.status);
+  void *filter_packed = workspace ? base + plan.filter : nullptr;
+  int32_t *nbr = external_table ? external_table : reinterpret_cast<int32_t *>(base + plan.neighbour);
+  int32_t *counts_dev = workspace ? reinterpret_cast<int32_t *>(base + plan.counts) : nullptr;
+  int32_t *status = workspace ? reinterpret_cast<int32_t *>(base + plan.status) : nullptr;
   cudaError_t err;
-  if ((err = cudaMemsetAsync(status, 0, 64 * sizeof(int32_t), stream)) != cudaSuccess) return err;
+  if (do_conv && (err = cudaMemsetAsync(status, 0, 64 * sizeof(int32_t), stream)) != cudaSuccess) return err;
 
   double pairs_total = 0;
   int64_t max_pairs = 0;
@@ -491,7 +510,7 @@ cudaError_t launchIndiceConvolution(const ConvProblem &caller, const ConvWorkspa
   const double conv_flops = 2.0 * pairs_total * p.ci * p.co;
 
   // 1. filter -> [K][Co][Ci]
-  {
+  if (do_conv) {
     const int64_t total = (int64_t)p.K * p.ci * p.co;
     const unsigned blocks = (unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
     trace::Scope t("repackFilterKernel", stream, 2.0 * total * elem);
@@ -507,12 +526,12 @@ cudaError_t launchIndiceConvolution(const ConvProblem &caller, const ConvWorkspa
   }
 
   // 2. neighbour table
-  {
+  if (do_build) {
     trace::Scope t("memset:neighbour_table", stream, 4.0 * p.K * plan.n_pad);
     if ((err = cudaMemsetAsync(nbr, 0xFF, (size_t)p.K * plan.n_pad * sizeof(int32_t), stream)) != cudaSuccess)
       return err;
   }
-  if (max_pairs > 0) {
+  if (do_build && max_pairs > 0) {
     int64_t bx = (max_pairs + 256 * kBuildPairsPerThread - 1) / (256 * kBuildPairsPerThread);
     const int64_t cap = (int64_t)sm_count * 32;
     if (bx > cap) bx = cap;
@@ -536,6 +555,7 @@ cudaError_t launchIndiceConvolution(const ConvProblem &caller, const ConvWorkspa
     }
   }
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
+  if (!do_conv) return cudaSuccess;
 
   // 3. convolution.  Half with channel counts 16/32/64/128 runs on the tcgen05
   // tensor cores; MLUOP_B200_CONV_KERNEL=mma selects the mma.sync variant instead

@@ -45,7 +45,15 @@ struct ConvWorkspacePlan {
   int64_t n_pad;
 };
 
-ConvWorkspacePlan planConvWorkspace(const ConvProblem &p);
+// external_table: the neighbour table lives in a buffer of the caller (see
+// launchIndiceConvolutionSteps), the workspace holds the rest.
+ConvWorkspacePlan planConvWorkspace(const ConvProblem &p, bool external_table = false);
+
+// Bytes of a neighbour table int32[K][n_pad] for this problem and direction.
+size_t neighbourTableBytes(const ConvProblem &p);
+// Whether the pair counts of K offsets fit the kernel-argument path that building a
+// table without a workspace relies on.
+bool neighbourTableCountsFit(int32_t K);
 
 // Enqueues filter repack, neighbour-table build and the convolution kernel.
 // indice_num is the caller's host array.  `rows_in` are the rows that are
@@ -56,6 +64,19 @@ cudaError_t launchIndiceConvolution(const ConvProblem &p, const ConvWorkspacePla
                                     const int32_t *indice_pairs, const int64_t *indice_num,
                                     void *workspace, void *rows_out, int sm_count,
                                     cudaStream_t stream);
+
+// The same launch sequence with the neighbour table in a caller buffer, run in
+// part: a rulebook that feeds several convolutions needs its table built once.
+enum NeighbourTableSteps {
+  kTableBuildAndConvolve = 0,  // what launchIndiceConvolution does
+  kTableBuildOnly = 1,         // memset + build into external_table; features, filters, workspace, rows_out unused
+  kTableConvolveOnly = 2,      // filter repack + convolution reading external_table
+};
+cudaError_t launchIndiceConvolutionSteps(const ConvProblem &p, const ConvWorkspacePlan &plan,
+                                         const void *rows_in, const void *filters,
+                                         const int32_t *indice_pairs, const int64_t *indice_num,
+                                         void *workspace, void *rows_out, int sm_count,
+                                         cudaStream_t stream, int32_t *external_table, int steps);
 
 }  // namespace sparse_conv
 }  // namespace mluop

@@ -412,3 +412,56 @@ def test_descriptor_pool_recycles(ops):
         seen.add(p.value)
         assert lib.mluOpDestroyTensorDescriptor(p) == 0
     assert len(seen) < 10
+
+
+# ------------------------------------------------- neighbour-table fast path (extension)
+
+def test_table_entry_points_argument_checks(ops, handle):
+    lib = ops.lib()
+    d_p = tdesc(ops, ops.LAYOUT_ARRAY, I32, (4, 2, 2))
+    size = ctypes.c_size_t(0)
+    assert lib.mluOpGetIndiceNeighbourTableSize(handle.ptr, d_p.ptr, 9, ctypes.byref(size)) == 0
+    assert size.value == 4 * 512 * 4  # K rows padded to 512 output rows
+    for a in ([None, d_p.ptr, 9, ctypes.byref(size)], [handle.ptr, None, 9, ctypes.byref(size)],
+              [handle.ptr, d_p.ptr, 9, None], [handle.ptr, d_p.ptr, -1, ctypes.byref(size)]):
+        assert lib.mluOpGetIndiceNeighbourTableSize(*a) == ops.STATUS_BAD_PARAM
+    bad = tdesc(ops, ops.LAYOUT_ARRAY, I32, (4, 3, 2))
+    assert lib.mluOpGetIndiceNeighbourTableSize(handle.ptr, bad.ptr, 9, ctypes.byref(size)) == ops.STATUS_BAD_PARAM
+    dummy = (ctypes.c_char * 16384)()
+    p = VP((ctypes.addressof(dummy) + 15) // 16 * 16)
+    num = ops.i64_array([1, 1, 1, 1])
+    args = [handle.ptr, d_p.ptr, p, num, 9, p, 8192]
+    assert lib.mluOpBuildIndiceNeighbourTable(*args) == ops.STATUS_EXECUTION_FAILED  # checks pass; host-only handle
+    for i in (0, 1, 2, 3, 5):
+        a = list(args)
+        a[i] = None
+        assert lib.mluOpBuildIndiceNeighbourTable(*a) == ops.STATUS_BAD_PARAM, i
+    assert lib.mluOpBuildIndiceNeighbourTable(handle.ptr, d_p.ptr, p, num, 9, p, 100) == ops.STATUS_BAD_PARAM
+    assert lib.mluOpBuildIndiceNeighbourTable(handle.ptr, d_p.ptr, p, ops.i64_array([3, 1, 1, 1]), 9, p,
+                                              8192) == ops.STATUS_BAD_PARAM
+    big = tdesc(ops, ops.LAYOUT_ARRAY, I32, (129, 2, 2))
+    assert lib.mluOpBuildIndiceNeighbourTable(handle.ptr, big.ptr, p, ops.i64_array([1] * 129), 9, p,
+                                              1 << 20) == ops.STATUS_NOT_SUPPORTED
+    # the convolution from a table: the forward entry point's checks, plus the table size
+    d_f = tdesc(ops, ops.LAYOUT_ARRAY, F32, (2, 3))
+    d_w = tdesc(ops, ops.LAYOUT_NDHWC, F32, (5, 1, 2, 2, 3))
+    d_o = tdesc(ops, ops.LAYOUT_ARRAY, F32, (9, 5))
+    ws = ctypes.c_size_t(0)
+    assert lib.mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize(handle.ptr, d_f.ptr, d_w.ptr, d_p.ptr, d_o.ptr,
+                                                                      num, 9, 0, 0, ctypes.byref(ws)) == 0
+    full = ctypes.c_size_t(0)
+    assert lib.mluOpGetIndiceConvolutionForwardWorkspaceSize(handle.ptr, d_f.ptr, d_w.ptr, d_p.ptr, d_o.ptr, num, 9,
+                                                             0, 0, ctypes.byref(full)) == 0
+    assert 0 < ws.value < full.value  # the table no longer lives in the workspace
+    conv = [handle.ptr, d_f.ptr, p, d_w.ptr, p, d_p.ptr, p, 8192, num, 9, 0, 0, p, 8192, d_o.ptr, p]
+    assert lib.mluOpIndiceConvolutionForwardFromTable(*conv) == ops.STATUS_EXECUTION_FAILED
+    for i in (0, 1, 2, 3, 4, 5, 6, 8, 12, 14, 15):
+        a = list(conv)
+        a[i] = None
+        assert lib.mluOpIndiceConvolutionForwardFromTable(*a) == ops.STATUS_BAD_PARAM, i
+    small = list(conv)
+    small[7] = 100
+    assert lib.mluOpIndiceConvolutionForwardFromTable(*small) == ops.STATUS_BAD_PARAM
+    inv = list(conv)
+    inv[10] = 1
+    assert lib.mluOpIndiceConvolutionForwardFromTable(*inv) == ops.STATUS_NOT_SUPPORTED

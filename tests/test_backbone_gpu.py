@@ -69,3 +69,17 @@ def test_sample_sharding_reproduces_the_unsharded_run(ops, workloads, backbone, 
     assert torch.equal(torch.cat(idxs), ref_idx)
     assert torch.equal(torch.cat(outs), ref_out)
     net.close()
+
+
+def test_neighbour_table_fast_path_is_bit_identical(ops, workloads, backbone, gpu_handle):
+    """One table per rulebook (mluOpBuildIndiceNeighbourTable + ...ForwardFromTable) gives exactly the
+    features the reference-shaped entry point gives."""
+    idx, feat, layers, weights = workloads.make_inputs("c2", batch=1)
+    grid = list(workloads.CONFIGS["c2"]["grid"])
+    net = backbone.SparseNetwork(gpu_handle, layers, [torch.from_numpy(w).cuda() for w in weights], grid, 1)
+    d_idx, d_feat = torch.from_numpy(idx).cuda(), torch.from_numpy(feat).cuda()
+    a, ia, _ = net.forward(d_idx, d_feat)
+    b, ib, _ = net.forward(d_idx, d_feat, reuse_tables=True)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b) and torch.equal(ia, ib)
+    net.close()

@@ -388,8 +388,16 @@ def extract(path, signature_start):
     raise RuntimeError("definition not found: %s in %s" % (signature_start, path))
 
 
-def build(reference_root="/root/reference", quiet=False):
+def default_reference_root():
+    """MLUOPS_REFERENCE_ROOT, else the directory `reference` beside this repository."""
+    return os.environ.get("MLUOPS_REFERENCE_ROOT",
+                          os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
+
+
+def build(reference_root=None, quiet=False):
     """Compile the library; returns its path, or None when the reference tree is absent."""
+    if reference_root is None:
+        reference_root = default_reference_root()
     paths = {k: os.path.join(reference_root, v) for k, v in SOURCES.items()}
     if not all(os.path.isfile(p) for p in paths.values()):
         return None
@@ -421,6 +429,6 @@ def build(reference_root="/root/reference", quiet=False):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else default_reference_root()
     lib = build(root)
     print(lib if lib else "reference tree not found at %s; nothing built" % root)

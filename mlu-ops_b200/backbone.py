@@ -2,9 +2,9 @@
 (workloads.Layer) the way a framework plugin would call the library.
 
 Per distinct geometry one mluOpGetIndicePairs call (layers that share a
-`rulebook` name share its result), then per layer the indice_num device->host
-copy the API requires (mluOpIndiceConvolutionForward takes a host array) and one
-mluOpIndiceConvolutionForward call.  All work is enqueued on the handle's stream.
+`rulebook` name share its result) whose indice_num output is pinned host memory
+(mluOpIndiceConvolutionForward takes the counts as a host array), then per layer
+one mluOpIndiceConvolutionForward call.  All work is enqueued on the handle's stream.
 
 The driver keeps its descriptors and its pinned host buffer alive between steps
 and re-sets only the dimensions that change, so that the host side adds as little
@@ -144,7 +144,6 @@ class SparseNetwork:
                 out_rows = L if ly.sub_m else min(K * L, cells)
                 pairs = torch.empty((K, 2, L), dtype=torch.int32, device=self.device)
                 out_idx = torch.empty((out_rows, 4), dtype=torch.int32, device=self.device)
-                num_dev = torch.empty((K,), dtype=torch.int32, device=self.device)
                 d_in, d_pairs = self.d_idx.set(L, 4), self.d_pairs.set(K, 2, L)
                 d_out, d_num = self.d_out_idx.set(out_rows, 4), self.d_num.set(K)
                 if on_host_idle is not None:
@@ -156,9 +155,10 @@ class SparseNetwork:
                 ops.check("mluOpGetIndicePairs",
                           lib.mluOpGetIndicePairs(h, conv.ptr, d_in, _vp(cur_idx.data_ptr()), _vp(ws.data_ptr()),
                                                   self.size.value, d_pairs, _vp(pairs.data_ptr()), d_out,
-                                                  _vp(out_idx.data_ptr()), d_num, _vp(num_dev.data_ptr())))
-                # the convolution API takes indice_num as a host array
-                self.num_host[:K].copy_(num_dev, non_blocking=True)
+                                                  _vp(out_idx.data_ptr()), d_num, _vp(self.num_host.data_ptr())))
+                # The convolution API takes indice_num as a host array, so the rulebook writes it
+                # straight into pinned host memory (device-accessible under unified addressing):
+                # no copy is queued on the copy engines, only the stream has to drain.
                 torch.cuda.current_stream().synchronize()
                 lib.mluOpGetSparseConvolutionNumActOut(conv.ptr, ctypes.byref(self.n_act))
                 num_list = self.num_host[:K].tolist()

@@ -59,7 +59,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpCreate(mluOpHandle_t *handle) {
   ctx->clock_rate = clock_khz;
   ctx->memory_band_width = 2.0 * mem_khz * 1e3 * (bus_bits / 8.0) / 1e9;
   if (cudaHostAlloc((void **)&ctx->host_words, sizeof(int32_t) * mluOpContext::kHostWords,
-                    cudaHostAllocDefault) != cudaSuccess) {
+                    cudaHostAllocMapped) != cudaSuccess) {
     (void)cudaGetLastError();
     LOG(ERROR) << "[mluOpCreate] pinned host allocation failed.";
     delete ctx;

@@ -496,9 +496,9 @@ probeCountKernel(PairsGeometry g, const int4 *__restrict__ indices, LookupTables
 }
 
 // Per offset k (one block each): exclusive scan of the tile counts in place,
-// indice_num[k] = total.
+// indice_num[k] = counts[k] = total.
 __global__ void __launch_bounds__(1024)
-scanTilesKernel(int32_t *tile_count, int tiles, int32_t *indice_num) {
+scanTilesKernel(int32_t *tile_count, int tiles, int32_t *indice_num, int32_t *counts) {
   __shared__ int warp_sums[33];
   int32_t *row = tile_count + (size_t)blockIdx.x * tiles;
   int running = 0;
@@ -510,7 +510,12 @@ scanTilesKernel(int32_t *tile_count, int tiles, int32_t *indice_num) {
     if (i < tiles) row[i] = running + excl;
     running += total;
   }
-  if (threadIdx.x == 0) indice_num[blockIdx.x] = running;
+  if (threadIdx.x == 0) {
+    // The caller's indice_num may be pinned host memory (it wants the counts on the
+    // host anyway); later kernels read the copy that stays in the workspace.
+    indice_num[blockIdx.x] = running;
+    counts[blockIdx.x] = running;
+  }
 }
 
 // Block (segment of 8 tiles = 2048 positions, k): order-preserving compaction of
@@ -608,6 +613,8 @@ PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g) {
   size_t off = 0;
   p.status = off;
   off = alignUp(off + 64 * sizeof(int32_t), 256);
+  p.counts = off;
+  off = alignUp(off + (size_t)g.K * sizeof(int32_t), 256);
   p.tile_state = off;
   p.match = off;
   p.tile_count = off;
@@ -675,6 +682,7 @@ void launchPairLists(const PairsGeometry &g, const PairsWorkspacePlan &plan, con
   }
   int32_t *match = reinterpret_cast<int32_t *>(base + plan.match);
   int32_t *tile_count = reinterpret_cast<int32_t *>(base + plan.tile_count);
+  int32_t *counts = reinterpret_cast<int32_t *>(base + plan.counts);
   {
     trace::Scope t(names_count[LOOKUP], stream, 16.0 * L + 4.0 * KL);
     probeCountKernel<LOOKUP><<<tiles, kPairsTile, (size_t)g.K * sizeof(int), stream>>>(
@@ -682,14 +690,20 @@ void launchPairLists(const PairsGeometry &g, const PairsWorkspacePlan &plan, con
   }
   {
     trace::Scope t("scanTilesKernel", stream, 8.0 * g.K * tiles);
-    scanTilesKernel<<<g.K, 1024, 0, stream>>>(tile_count, tiles, indice_num);
+    scanTilesKernel<<<g.K, 1024, 0, stream>>>(tile_count, tiles, indice_num, counts);
   }
   {
     trace::Scope t("writePairsKernel", stream, 12.0 * KL);
     const unsigned segments = (unsigned)((tiles + kWriteSegTiles - 1) / kWriteSegTiles);
-    writePairsKernel<<<dim3(segments, g.K), kPairsTile, 0, stream>>>(g.L, match, tile_count, tiles, indice_num,
+    writePairsKernel<<<dim3(segments, g.K), kPairsTile, 0, stream>>>(g.L, match, tile_count, tiles, counts,
                                                                     indice_pairs);
   }
+}
+
+__global__ void publishStatusKernel(const int32_t *__restrict__ status, volatile int32_t *status_host) {
+  status_host[0] = status[0];
+  status_host[1] = status[1];
+  __threadfence_system();
 }
 
 }  // namespace
@@ -797,7 +811,11 @@ cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePla
       break;
   }
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
-  return cudaMemcpyAsync(status_host, status, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, stream);
+  // status_host is pinned, device-mapped host memory: a one-thread kernel stores the
+  // two words there, so the read-back does not queue behind whatever large
+  // transfers the application has on the copy engines.
+  publishStatusKernel<<<1, 1, 0, stream>>>(status, status_host);
+  return cudaGetLastError();
 }
 
 }  // namespace sparse_conv

@@ -46,6 +46,7 @@ constexpr int kFusedMaxOffsets = 32;
 // Byte offsets of the scratch arrays inside the (256-byte aligned) workspace.
 struct PairsWorkspacePlan {
   size_t status;      // int32[64]: [0] error bits, [1] number of active outputs, [2] tile ticket counter
+  size_t counts;      // int32[K]: pair counts, the copy the kernels read (indice_num may be host memory)
   size_t tile_state;  // fused path: uint32[K][tiles] look-back descriptors {2-bit state, 30-bit count}
   size_t match;       // two-pass path: int32[K][tiles*256] output id matched by (k, j), -1 if none
   size_t tile_count;  // two-pass path: int32[K][tiles] matches per tile, then exclusive offsets
@@ -68,9 +69,9 @@ constexpr int kPairsErrHashFull = 1;         // hash probe ran through the whole
 constexpr int kPairsErrOutIndicesSmall = 2;  // more active outputs than out_indices rows
 constexpr int kPairsErrLookBack = 4;         // a bounded look-back wait gave up
 
-// Enqueues the whole rulebook computation on `stream`.  n_out_host (pinned)
-// receives {error bits, number of active outputs} by an async copy that is
-// ordered after the kernels; the caller synchronises when it needs them.
+// Enqueues the whole rulebook computation on `stream`.  status_host (pinned,
+// device-mapped host memory) receives {error bits, number of active outputs}
+// from a last one-thread kernel; the caller synchronises when it needs them.
 cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePlan &plan,
                                  const int32_t *indices, void *workspace, int32_t *indice_pairs,
                                  int32_t *out_indices, int64_t out_rows, int32_t *indice_num,

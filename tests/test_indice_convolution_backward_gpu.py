@@ -159,3 +159,26 @@ def test_adjoint_identities_at_full_size(ops, oracle, workloads, gpu_handle):
     assert torch.equal(dx, ops.indice_convolution_backward_data(gpu_handle, dy, w, "ARRAY", pairs, num_h, 1))
     assert torch.equal(dw, ops.indice_convolution_backward_filter(gpu_handle, x, dy, ly.filter_space, pairs, num_h, 1))
     conv.destroy()
+
+
+@pytest.mark.parametrize("ks", [[1, 1, 1], [5, 5, 5], [7, 7, 7], [3, 1, 5]])
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_kernel_volumes_outside_the_tensor_core_range(ops, oracle, gpu_handle, ks, dtype):
+    """Kernel volumes 1, 125, 343 and 15: above 32 offsets the forward and the input gradient
+    leave the tensor-core kernels, above 128 the pair counts travel through device memory."""
+    rng = np.random.default_rng(sum(ks) + (dtype == np.float16))
+    is_half = dtype == np.float16
+    pad = [(k - 1) // 2 for k in ks]
+    pairs, num, n_out, feat, og, w = make_case(oracle, rng, 2, [7, 9, 8], 300, ks, [1] * 3, pad, 1, 16, 32, dtype)
+    f32 = lambda a: a.astype(np.float32)  # noqa: E731
+    r = (lambda a: oracle.round_through_half(a)) if is_half else (lambda a: a)
+    fwd = torch.from_numpy(feat).cuda()
+    got = ops.indice_convolution_forward(gpu_handle, fwd, torch.from_numpy(w).cuda(), "ARRAY", ks,
+                                         torch.from_numpy(pairs).cuda(), [int(v) for v in num], n_out, 1)
+    ref = r(oracle.indice_convolution_forward(f32(feat), f32(w), "ARRAY", ks, pairs, num, n_out, 32))
+    assert_close(oracle, got.float().cpu().numpy(), ref, is_half)
+    ref = r(oracle.indice_convolution_backward_data(f32(og), f32(w), "ARRAY", ks, pairs, num, 16, is_half))
+    assert_close(oracle, gpu_backward_data(ops, gpu_handle, og, w, "ARRAY", pairs, num, 1), ref, is_half)
+    ref = r(oracle.indice_convolution_backward_filter(f32(feat), f32(og), ks, pairs, num))
+    got = gpu_backward_filter(ops, gpu_handle, feat, og, ks, pairs, num, 1)
+    assert_close(oracle, got.reshape(ref.shape), ref, is_half)

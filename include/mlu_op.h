@@ -390,6 +390,42 @@ mluOpStatus_t MLUOP_WIN_API mluOpVoxelization(
     const mluOpTensorDescriptor_t num_points_per_voxel_desc, void *num_points_per_voxel,
     const mluOpTensorDescriptor_t voxel_num_desc, void *voxel_num);
 
+/* reference mlu_op.h:361-365 */
+typedef enum {
+  MLUOP_REDUCE_DSUM = 0,
+  MLUOP_REDUCE_DMEAN = 1,
+  MLUOP_REDUCE_DMAX = 2,
+} mluOpReduceMode_t;
+
+/* reference mlu_op.h:3768, dynamic_point_to_voxel_forward.cpp:193.  Bytes of
+ * device scratch mluOpDynamicPointToVoxelForward needs (this implementation's
+ * own figure: 32 bytes per point for the sort records, plus counters). */
+mluOpStatus_t MLUOP_WIN_API mluOpGetDynamicPointToVoxelForwardWorkspaceSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t feats_desc,
+    const mluOpTensorDescriptor_t coors_desc, size_t *workspace_size);
+
+/* reference mlu_op.h:3866, dynamic_point_to_voxel_forward.cpp:226.  Groups
+ * points by their integer voxel coordinates and reduces their features:
+ *   feats [N,C] float, coors [N,3] int32 (rows with a negative entry are set to
+ *   (-1,-1,-1) in place and belong to no voxel)
+ *   voxel_coors [M,3]: the distinct coordinates in ascending lexicographic order
+ *   point2voxel_map [N]: row of voxel_coors of every point, -1 for none
+ *   voxel_points_count [M], voxel_num [1], voxel_feats [M,C]: per voxel the
+ *   maximum (MLUOP_REDUCE_DMAX) or the mean (MLUOP_REDUCE_DMEAN, summed as
+ *   sum_i feats_i / count in point order) of its points' features
+ * with M <= N rows allocated by the caller (N to be safe); rows past voxel_num
+ * hold zeros (-inf in voxel_feats for the maximum).  Results are reproducible
+ * run to run.  Asynchronous on the handle's queue. */
+mluOpStatus_t MLUOP_WIN_API mluOpDynamicPointToVoxelForward(
+    const mluOpHandle_t handle, const mluOpReduceMode_t reduce_type,
+    const mluOpTensorDescriptor_t feats_desc, const void *feats,
+    const mluOpTensorDescriptor_t coors_desc, void *coors, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t voxel_feats_desc,
+    void *voxel_feats, const mluOpTensorDescriptor_t voxel_coors_desc, void *voxel_coors,
+    const mluOpTensorDescriptor_t point2voxel_map_desc, void *point2voxel_map,
+    const mluOpTensorDescriptor_t voxel_points_count_desc, void *voxel_points_count,
+    const mluOpTensorDescriptor_t voxel_num_desc, void *voxel_num);
+
 /* No counterpart in the reference.  Same computation and arguments as
  * mluOpIndiceConvolutionForward, without the workspace pair: the scratch is a
  * fixed array of MLUOP_BUILTIN_CONV_WORKSPACE_BYTES in device memory that

@@ -90,6 +90,9 @@ SIGNATURES = {
                                                 ctypes.POINTER(_szt)]),
     "mluOpVoxelization": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                 ctypes.c_bool, _vp, _szt, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mluOpGetDynamicPointToVoxelForwardWorkspaceSize": (_int, [_vp, _vp, _vp, ctypes.POINTER(_szt)]),
+    "mluOpDynamicPointToVoxelForward": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _szt, _vp, _vp, _vp, _vp, _vp, _vp,
+                                              _vp, _vp, _vp, _vp]),
     # include/mlu_op_trace.h
     "mluOpTraceKernelEnable": (_int, [_int]),
     "mluOpTraceKernelReset": (_int, []),
@@ -436,3 +439,42 @@ def voxelization(handle, points, voxel_size, coors_range, max_points, max_voxels
     for d in descs:
         d.destroy()
     return voxels, coors, npv, num
+
+
+REDUCE_MODES = {"sum": 0, "mean": 1, "max": 2}
+
+
+def dynamic_point_to_voxel_forward(handle, feats, coors, reduce_type="max", workspace=None):
+    """Groups points by voxel through mluOpDynamicPointToVoxelForward.
+
+    feats [N,C] float32 and coors [N,3] int32 are CUDA tensors; coors rows with a
+    negative entry are overwritten with -1 (as the reference does).  Returns
+    (voxel_feats [N,C], voxel_coors [N,3], point2voxel_map [N], voxel_points_count [N],
+    voxel_num [1]), all on the device; the first voxel_num rows are the voxels.
+    """
+    import torch
+    n, c = feats.shape
+    dev = feats.device
+    voxel_feats = torch.empty((n, c), dtype=torch.float32, device=dev)
+    voxel_coors = torch.empty((n, 3), dtype=torch.int32, device=dev)
+    p2v = torch.empty((n,), dtype=torch.int32, device=dev)
+    counts = torch.empty((n,), dtype=torch.int32, device=dev)
+    num = torch.zeros((1,), dtype=torch.int32, device=dev)
+    descs = [TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (n, c)), TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (n, 3)),
+             TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (n, c)), TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (n, 3)),
+             TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (n,)), TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (n,)),
+             TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (1,))]
+    d_f, d_c, d_vf, d_vc, d_map, d_cnt, d_num = (d.ptr for d in descs)
+    size = _szt(0)
+    check("mluOpGetDynamicPointToVoxelForwardWorkspaceSize",
+          lib().mluOpGetDynamicPointToVoxelForwardWorkspaceSize(handle.ptr, d_f, d_c, ctypes.byref(size)))
+    if workspace is None or workspace.numel() < size.value:
+        workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+    check("mluOpDynamicPointToVoxelForward",
+          lib().mluOpDynamicPointToVoxelForward(handle.ptr, REDUCE_MODES[reduce_type], d_f, _ptr(feats), d_c,
+                                                _ptr(coors), _ptr(workspace), size.value, d_vf, _ptr(voxel_feats),
+                                                d_vc, _ptr(voxel_coors), d_map, _ptr(p2v), d_cnt, _ptr(counts),
+                                                d_num, _ptr(num)))
+    for d in descs:
+        d.destroy()
+    return voxel_feats, voxel_coors, p2v, counts, num

@@ -21,14 +21,16 @@ LIB = os.path.join(LIB_DIR, "libmluops_b200.so")
 def sources():
     out = []
     for pattern in ("core/*.cpp", "kernels/sparse_conv/*.cpp", "kernels/sparse_conv/*.cu",
-                    "kernels/voxelization/*.cpp", "kernels/voxelization/*.cu"):
+                    "kernels/voxelization/*.cpp", "kernels/voxelization/*.cu",
+                    "kernels/dynamic_point_to_voxel/*.cpp", "kernels/dynamic_point_to_voxel/*.cu"):
         out += sorted(glob.glob(os.path.join(CSRC, pattern)))
     return out
 
 
 def headers():
     out = glob.glob(os.path.join(ROOT, "include", "*.h"))
-    for pattern in ("core/*.h", "kernels/sparse_conv/*.h", "kernels/sparse_conv/*.cuh", "kernels/voxelization/*.h"):
+    for pattern in ("core/*.h", "kernels/sparse_conv/*.h", "kernels/sparse_conv/*.cuh", "kernels/voxelization/*.h",
+                    "kernels/dynamic_point_to_voxel/*.h"):
         out += glob.glob(os.path.join(CSRC, pattern))
     return out
 

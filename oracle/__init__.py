@@ -242,6 +242,32 @@ def voxelization(points, voxel_size, coors_range, max_points, max_voxels, use_re
     return voxels, coors, npv, int(num.value)
 
 
+def dynamic_point_to_voxel_forward(feats, coors, reduce_type="max", use_ref=False):
+    """Groups points by voxel.  feats [N,C] float32, coors [N,3] int32 (a copy is modified).
+    Returns (voxel_feats [N,C], voxel_coors [N,3], point2voxel_map [N], voxel_points_count [N],
+    voxel_num, coors after the -1 fill); only the first voxel_num rows of the voxel_* arrays and
+    all of point2voxel_map are defined by the reference."""
+    f = np.ascontiguousarray(feats, dtype=np.float32)
+    c = np.array(coors, dtype=np.int32, order="C", copy=True)
+    n, cn = f.shape
+    vf = np.zeros((n, cn), dtype=np.float32)
+    vc = np.zeros((n, 3), dtype=np.int32)
+    p2v = np.zeros((n,), dtype=np.int32)
+    cnt = np.zeros((n,), dtype=np.int32)
+    num = ctypes.c_int32(0)
+    if use_ref:
+        r = ref_lib()
+        assert r is not None, "oracle/_ref is not built"
+        fn = r.mluops_ref_dynamic_point_to_voxel_forward
+    else:
+        fn = lib().mluops_oracle_dynamic_point_to_voxel_forward
+    rc = fn(_p(f, _f32p), _p(c, _i32p), ctypes.c_int64(n), ctypes.c_int64(cn), ctypes.c_int64(n),
+            ctypes.c_int32(1 if reduce_type == "max" else 0), _p(vf, _f32p), _p(vc, _i32p), _p(p2v, _i32p),
+            _p(cnt, _i32p), ctypes.byref(num))
+    assert rc == 0
+    return vf, vc, p2v, cnt, int(num.value), c
+
+
 def round_through_half(x):
     """float32 -> half (reference rounding) -> float32."""
     x = np.ascontiguousarray(x, dtype=np.float32)

@@ -21,6 +21,9 @@ stand-in for the members they touch:
   VoxelizationExecutor::deterministic_hard_voxelize
                                               zoo/voxelization/voxelization.cpp
 
+  DynamicPointToVoxelForwardExecutor::cpuCompute
+                                              zoo/dynamic_point_to_voxel_forward/dynamic_point_to_voxel_forward.cpp
+
 The backward-data body rounds to half through wrapRtConvertFloatToHalf /
 wrapRtConvertHalfToFloat, which forward to the vendor runtime's cast routine
 (tools.cpp:49-57); that runtime is not part of the reference tree, so the
@@ -50,11 +53,13 @@ SOURCES = {
     "bwd_data": ZOO + "/indice_convolution_backward_data/indice_convolution_backward_data.cpp",
     "bwd_filter": ZOO + "/indice_convolution_backward_filter/indice_convolution_backward_filter.cpp",
     "voxel": ZOO + "/voxelization/voxelization.cpp",
+    "dpv": ZOO + "/dynamic_point_to_voxel_forward/dynamic_point_to_voxel_forward.cpp",
 }
 
 PRELUDE = r"""
 #include <algorithm>
 #include <cmath>
+#include <numeric>
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
@@ -210,6 +215,30 @@ struct IndiceConvolutionBackwardDataExecutor {
   void cpuTransposeFilter(float *filter_transpose_cpu, mluOpTensorLayout_t origin_layout);
   void cpuCompute();
 };
+enum ReduceMode { REDUCE_MODE_SUM = 0, REDUCE_MODE_MEAN = 1, REDUCE_MODE_MAX = 2 };
+struct StandInDpvParam {
+  ReduceMode mode = REDUCE_MODE_MAX;
+  ReduceMode reduce_type() const { return mode; }
+};
+struct StandInDpvNode {
+  StandInDpvParam param;
+  const StandInDpvParam &dynamic_point_to_voxel_forward_param() const { return param; }
+};
+struct StandInDpvParser {
+  StandInDpvNode node;
+  int64_t in_count[2] = {0, 0};
+  StandInDpvNode *getProtoNode() { return &node; }
+  int64_t getInputDataCount(int i) { return in_count[i]; }
+};
+struct DynamicPointToVoxelForwardExecutor {
+  StandInDpvParser parser_storage_;
+  StandInDpvParser *parser_ = &parser_storage_;
+  std::vector<float *> cpu_fp32_input_;
+  std::vector<float *> cpu_fp32_output_;
+  std::vector<StandInDescHolder> tensor_desc_;
+  int64_t theory_ops_ = 0;
+  void cpuCompute();
+};
 struct VoxelizationExecutor {
   StandInRuntime cpu_runtime_;
   void deterministic_hard_voxelize(const float *points, const float *voxel_size, const float *coors_range,
@@ -307,6 +336,38 @@ int mluops_ref_voxelization(const float *points, int64_t num_points, int64_t num
                                  coors_f.data(), npv_f.data(), &num_f);
   for (size_t i = 0; i < coors_f.size(); ++i) coors[i] = (int32_t)coors_f[i];
   for (size_t i = 0; i < npv_f.size(); ++i) num_points_per_voxel[i] = (int32_t)npv_f[i];
+  *voxel_num = (int32_t)num_f;
+  return 0;
+}
+
+// The reference's CPU path holds every tensor, the coordinates included, as float.
+int mluops_ref_dynamic_point_to_voxel_forward(const float *feats, int32_t *coors, int64_t n, int64_t c_num,
+                                              int64_t voxel_rows, int32_t reduce_max, float *voxel_feats,
+                                              int32_t *voxel_coors, int32_t *point2voxel_map,
+                                              int32_t *voxel_points_count, int32_t *voxel_num) {
+  std::vector<float> coors_f((size_t)n * 3), vc_f((size_t)voxel_rows * 3, 0.0f), map_f((size_t)n, 0.0f),
+      cnt_f((size_t)voxel_rows, 0.0f);
+  float num_f = 0.0f;
+  for (size_t i = 0; i < coors_f.size(); ++i) coors_f[i] = (float)coors[i];
+  StandInTensor d_feats, d_coors, d_vf;
+  d_feats.dims = {n, c_num};
+  d_coors.dims = {n, 3};
+  d_vf.dims = {voxel_rows, c_num};
+  mluoptest::DynamicPointToVoxelForwardExecutor ex;
+  ex.parser_storage_.node.param.mode = reduce_max ? mluoptest::REDUCE_MODE_MAX : mluoptest::REDUCE_MODE_MEAN;
+  ex.parser_storage_.in_count[0] = n * c_num;
+  ex.parser_storage_.in_count[1] = n * 3;
+  ex.tensor_desc_.resize(3);
+  ex.tensor_desc_[0].tensor = &d_feats;
+  ex.tensor_desc_[1].tensor = &d_coors;
+  ex.tensor_desc_[2].tensor = &d_vf;
+  ex.cpu_fp32_input_ = {const_cast<float *>(feats), coors_f.data()};
+  ex.cpu_fp32_output_ = {voxel_feats, vc_f.data(), map_f.data(), cnt_f.data(), &num_f};
+  ex.cpuCompute();
+  for (size_t i = 0; i < coors_f.size(); ++i) coors[i] = (int32_t)coors_f[i];
+  for (size_t i = 0; i < vc_f.size(); ++i) voxel_coors[i] = (int32_t)vc_f[i];
+  for (size_t i = 0; i < map_f.size(); ++i) point2voxel_map[i] = (int32_t)map_f[i];
+  for (size_t i = 0; i < cnt_f.size(); ++i) voxel_points_count[i] = (int32_t)cnt_f[i];
   *voxel_num = (int32_t)num_f;
   return 0;
 }
@@ -416,6 +477,7 @@ def build(reference_root=None, quiet=False):
                "void assignPointToVoxel(", "void assignVoxelCoors(",
                "void VoxelizationExecutor::deterministic_hard_voxelize("):
         parts.append(extract(paths["voxel"], fn))
+    parts.append(extract(paths["dpv"], "void DynamicPointToVoxelForwardExecutor::cpuCompute("))
     parts.append(EPILOGUE)
     with tempfile.TemporaryDirectory() as tmp:
         src = os.path.join(tmp, "ref_cpu_unit.cpp")

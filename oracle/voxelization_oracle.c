@@ -108,3 +108,77 @@ int mluops_oracle_voxelization(const float *points, int64_t num_points, int64_t 
   free(c); free(first); free(rank); free(voxel_of);
   return 0;
 }
+
+/*
+ * Dynamic point-to-voxel scatter, forward (reference
+ * test/mlu_op_gtest/pb_gtest/src/zoo/dynamic_point_to_voxel_forward/
+ * dynamic_point_to_voxel_forward.cpp:107-247):
+ *   rows of coors with a negative entry become (-1,-1,-1) (in place);
+ *   point indices are sorted by their coordinates (lexicographic) and made
+ *   unique; a leading (-1,-1,-1) voxel is dropped; point2voxel_map, the points
+ *   per voxel; voxel_feats starts at -1.17549e38 (maximum) or 0 (mean) in every
+ *   row and is reduced over the points in index order, the mean as
+ *   sum_i feats_i / count.
+ * The reference sorts with std::sort, which may order equal coordinates
+ * differently; nothing that is output depends on that order.
+ * reduce_max: 1 maximum, 0 mean.  voxel_rows: rows of the voxel_* outputs.
+ */
+static const int32_t *dpv_coors;
+static int dpv_cmp(const void *a, const void *b) {
+  const int32_t i = *(const int32_t *)a, j = *(const int32_t *)b;
+  for (int d = 0; d < 3; ++d) {
+    if (dpv_coors[i * 3 + d] < dpv_coors[j * 3 + d]) return -1;
+    if (dpv_coors[i * 3 + d] > dpv_coors[j * 3 + d]) return 1;
+  }
+  return (i > j) - (i < j);
+}
+
+int mluops_oracle_dynamic_point_to_voxel_forward(const float *feats, int32_t *coors, int64_t n,
+                                                 int64_t c_num, int64_t voxel_rows, int32_t reduce_max,
+                                                 float *voxel_feats, int32_t *voxel_coors,
+                                                 int32_t *point2voxel_map, int32_t *voxel_points_count,
+                                                 int32_t *voxel_num) {
+  for (int64_t i = 0; i < n; ++i)
+    if (coors[i * 3] < 0 || coors[i * 3 + 1] < 0 || coors[i * 3 + 2] < 0)
+      coors[i * 3] = coors[i * 3 + 1] = coors[i * 3 + 2] = -1;
+  int32_t *order = (int32_t *)malloc(sizeof(int32_t) * (size_t)(n > 0 ? n : 1));
+  if (!order) return -1;
+  for (int64_t i = 0; i < n; ++i) order[i] = (int32_t)i;
+  dpv_coors = coors;
+  qsort(order, (size_t)n, sizeof(int32_t), dpv_cmp);
+  const float fill = reduce_max ? -1.17549e38f : 0.0f;
+  for (int64_t i = 0; i < voxel_rows * c_num; ++i) voxel_feats[i] = fill;
+  int32_t voxels = 0;
+  for (int64_t s = 0; s < n;) {
+    int64_t e = s + 1;
+    while (e < n && memcmp(coors + (size_t)order[s] * 3, coors + (size_t)order[e] * 3, 12) == 0) ++e;
+    const int invalid = coors[(size_t)order[s] * 3] == -1;
+    for (int64_t q = s; q < e; ++q) point2voxel_map[order[q]] = invalid ? -1 : voxels;
+    if (!invalid) {
+      if (voxels < voxel_rows) {
+        memcpy(voxel_coors + (size_t)voxels * 3, coors + (size_t)order[s] * 3, 12);
+        voxel_points_count[voxels] = (int32_t)(e - s);
+      }
+      ++voxels;
+    }
+    s = e;
+  }
+  *voxel_num = voxels;
+  for (int64_t i = 0; i < n; ++i) {
+    const int32_t v = point2voxel_map[i];
+    if (v < 0 || v >= voxel_rows) continue;
+    const int32_t count = voxel_points_count[v];
+    for (int64_t c = 0; c < c_num; ++c) {
+      float *dst = voxel_feats + (size_t)v * c_num + c;
+      const float x = feats[i * c_num + c];
+      if (reduce_max) {
+        if (x >= *dst) *dst = x;
+      } else {
+        volatile float term = x / count;
+        *dst += term;
+      }
+    }
+  }
+  free(order);
+  return 0;
+}

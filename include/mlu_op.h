@@ -426,6 +426,31 @@ mluOpStatus_t MLUOP_WIN_API mluOpDynamicPointToVoxelForward(
     const mluOpTensorDescriptor_t voxel_points_count_desc, void *voxel_points_count,
     const mluOpTensorDescriptor_t voxel_num_desc, void *voxel_num);
 
+/* reference mlu_op.h:3598, dynamic_point_to_voxel_backward.cpp:342 */
+mluOpStatus_t MLUOP_WIN_API mluOpGetDynamicPointToVoxelBackwardWorkspaceSize(
+    const mluOpHandle_t handle, const mluOpReduceMode_t reduce_type,
+    const mluOpTensorDescriptor_t grad_voxel_feats_desc,
+    const mluOpTensorDescriptor_t feats_desc, const mluOpTensorDescriptor_t voxel_feats_desc,
+    const mluOpTensorDescriptor_t point2voxel_map_desc,
+    const mluOpTensorDescriptor_t voxel_points_count_desc,
+    const mluOpTensorDescriptor_t voxel_num_desc, size_t *workspace_size);
+
+/* reference mlu_op.h:3708, dynamic_point_to_voxel_backward.cpp:232.  Gradient of
+ * mluOpDynamicPointToVoxelForward for MLUOP_REDUCE_DMAX (the only mode the
+ * reference supports): per voxel and channel, the point with the smallest index
+ * whose feature equals the voxel's maximum receives grad_voxel_feats; all other
+ * entries of grad_feats [N,C] are zero.  Asynchronous on the handle's queue. */
+mluOpStatus_t MLUOP_WIN_API mluOpDynamicPointToVoxelBackward(
+    const mluOpHandle_t handle, const mluOpReduceMode_t reduce_type,
+    const mluOpTensorDescriptor_t grad_voxel_feats_desc, const void *grad_voxel_feats,
+    const mluOpTensorDescriptor_t feats_desc, const void *feats,
+    const mluOpTensorDescriptor_t voxel_feats_desc, const void *voxel_feats,
+    const mluOpTensorDescriptor_t point2voxel_map_desc, const void *point2voxel_map,
+    const mluOpTensorDescriptor_t voxel_points_count_desc, const void *voxel_points_count,
+    const mluOpTensorDescriptor_t voxel_num_desc, const void *voxel_num, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t grad_feats_desc,
+    void *grad_feats);
+
 /* No counterpart in the reference.  Same computation and arguments as
  * mluOpIndiceConvolutionForward, without the workspace pair: the scratch is a
  * fixed array of MLUOP_BUILTIN_CONV_WORKSPACE_BYTES in device memory that

@@ -93,6 +93,10 @@ SIGNATURES = {
     "mluOpGetDynamicPointToVoxelForwardWorkspaceSize": (_int, [_vp, _vp, _vp, ctypes.POINTER(_szt)]),
     "mluOpDynamicPointToVoxelForward": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _szt, _vp, _vp, _vp, _vp, _vp, _vp,
                                               _vp, _vp, _vp, _vp]),
+    "mluOpGetDynamicPointToVoxelBackwardWorkspaceSize": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp,
+                                                               ctypes.POINTER(_szt)]),
+    "mluOpDynamicPointToVoxelBackward": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                               _vp, _szt, _vp, _vp]),
     # include/mlu_op_trace.h
     "mluOpTraceKernelEnable": (_int, [_int]),
     "mluOpTraceKernelReset": (_int, []),
@@ -478,3 +482,31 @@ def dynamic_point_to_voxel_forward(handle, feats, coors, reduce_type="max", work
     for d in descs:
         d.destroy()
     return voxel_feats, voxel_coors, p2v, counts, num
+
+
+def dynamic_point_to_voxel_backward(handle, grad_voxel_feats, feats, voxel_feats, point2voxel_map,
+                                    voxel_points_count, voxel_num):
+    """grad_feats [N,C] of the maximum reduction through mluOpDynamicPointToVoxelBackward."""
+    import torch
+    n, c = feats.shape
+    m = grad_voxel_feats.shape[0]
+    dev = feats.device
+    grad_feats = torch.empty((n, c), dtype=torch.float32, device=dev)
+    descs = [TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (m, c)), TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (n, c)),
+             TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (m, c)), TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (n,)),
+             TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (m,)), TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (1,)),
+             TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (n, c))]
+    d_g, d_f, d_vf, d_map, d_cnt, d_num, d_out = (d.ptr for d in descs)
+    size = _szt(0)
+    check("mluOpGetDynamicPointToVoxelBackwardWorkspaceSize",
+          lib().mluOpGetDynamicPointToVoxelBackwardWorkspaceSize(handle.ptr, REDUCE_MODES["max"], d_g, d_f, d_vf,
+                                                                 d_map, d_cnt, d_num, ctypes.byref(size)))
+    workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+    check("mluOpDynamicPointToVoxelBackward",
+          lib().mluOpDynamicPointToVoxelBackward(handle.ptr, REDUCE_MODES["max"], d_g, _ptr(grad_voxel_feats), d_f,
+                                                 _ptr(feats), d_vf, _ptr(voxel_feats), d_map, _ptr(point2voxel_map),
+                                                 d_cnt, _ptr(voxel_points_count), d_num, _ptr(voxel_num),
+                                                 _ptr(workspace), size.value, d_out, _ptr(grad_feats)))
+    for d in descs:
+        d.destroy()
+    return grad_feats

@@ -191,3 +191,38 @@ class Voxelization(nn.Module):
                                                    self.max_voxels)
         m = int(num.item())
         return voxels[:m], coors[:m], npv[:m]
+
+
+class _DynamicScatterMax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, feats, coors):
+        h = _handle(feats.device)
+        feats = feats.contiguous()
+        voxel_feats, voxel_coors, p2v, counts, num = ops.dynamic_point_to_voxel_forward(h, feats, coors.clone(), "max")
+        m = int(num.item())
+        ctx.save_for_backward(feats, voxel_feats, p2v, counts, num)
+        ctx.mark_non_differentiable(voxel_coors, p2v)
+        ctx.rows = m
+        return voxel_feats[:m], voxel_coors[:m], p2v
+
+    @staticmethod
+    def backward(ctx, grad_voxel_feats, _grad_coors, _grad_map):
+        feats, voxel_feats, p2v, counts, num = ctx.saved_tensors
+        grad = torch.zeros_like(voxel_feats)
+        grad[:ctx.rows] = grad_voxel_feats
+        h = _handle(feats.device)
+        return ops.dynamic_point_to_voxel_backward(h, grad, feats, voxel_feats, p2v, counts, num), None
+
+
+def dynamic_scatter(feats, coors, reduce_type="max"):
+    """Dynamic voxelization of point features (mluOpDynamicPointToVoxelForward): feats [N,C] float32,
+    coors [N,3] int32 on the GPU.  Returns (voxel_feats [M,C], voxel_coors [M,3] ascending,
+    point2voxel_map [N]).  "max" is differentiable in feats (mluOpDynamicPointToVoxelBackward);
+    "mean" is forward only, as in the reference."""
+    if reduce_type == "max":
+        return _DynamicScatterMax.apply(feats, coors)
+    h = _handle(feats.device)
+    voxel_feats, voxel_coors, p2v, _, num = ops.dynamic_point_to_voxel_forward(h, feats.detach().contiguous(),
+                                                                              coors.clone(), reduce_type)
+    m = int(num.item())
+    return voxel_feats[:m], voxel_coors[:m], p2v

@@ -268,6 +268,27 @@ def dynamic_point_to_voxel_forward(feats, coors, reduce_type="max", use_ref=Fals
     return vf, vc, p2v, cnt, int(num.value), c
 
 
+def dynamic_point_to_voxel_backward(grad_voxel_feats, feats, voxel_feats, point2voxel_map, voxel_num,
+                                    use_ref=False):
+    """grad_feats [N,C] float32 of the maximum reduction."""
+    g = np.ascontiguousarray(grad_voxel_feats, dtype=np.float32)
+    f = np.ascontiguousarray(feats, dtype=np.float32)
+    vf = np.ascontiguousarray(voxel_feats, dtype=np.float32)
+    p2v = np.ascontiguousarray(point2voxel_map, dtype=np.int32)
+    n, c = f.shape
+    out = np.zeros((n, c), dtype=np.float32)
+    if use_ref:
+        r = ref_lib()
+        assert r is not None, "oracle/_ref is not built"
+        fn = r.mluops_ref_dynamic_point_to_voxel_backward
+    else:
+        fn = lib().mluops_oracle_dynamic_point_to_voxel_backward
+    rc = fn(_p(g, _f32p), _p(f, _f32p), _p(vf, _f32p), _p(p2v, _i32p), ctypes.c_int32(int(voxel_num)),
+            ctypes.c_int64(n), ctypes.c_int64(c), _p(out, _f32p))
+    assert rc == 0
+    return out
+
+
 def round_through_half(x):
     """float32 -> half (reference rounding) -> float32."""
     x = np.ascontiguousarray(x, dtype=np.float32)

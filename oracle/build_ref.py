@@ -24,6 +24,9 @@ stand-in for the members they touch:
   DynamicPointToVoxelForwardExecutor::cpuCompute
                                               zoo/dynamic_point_to_voxel_forward/dynamic_point_to_voxel_forward.cpp
 
+  DynamicPointToVoxelBackwardExecutor::cpuCompute
+                                              zoo/dynamic_point_to_voxel_backward/dynamic_point_to_voxel_backward.cpp
+
 The backward-data body rounds to half through wrapRtConvertFloatToHalf /
 wrapRtConvertHalfToFloat, which forward to the vendor runtime's cast routine
 (tools.cpp:49-57); that runtime is not part of the reference tree, so the
@@ -54,6 +57,7 @@ SOURCES = {
     "bwd_filter": ZOO + "/indice_convolution_backward_filter/indice_convolution_backward_filter.cpp",
     "voxel": ZOO + "/voxelization/voxelization.cpp",
     "dpv": ZOO + "/dynamic_point_to_voxel_forward/dynamic_point_to_voxel_forward.cpp",
+    "dpv_bwd": ZOO + "/dynamic_point_to_voxel_backward/dynamic_point_to_voxel_backward.cpp",
 }
 
 PRELUDE = r"""
@@ -239,6 +243,14 @@ struct DynamicPointToVoxelForwardExecutor {
   int64_t theory_ops_ = 0;
   void cpuCompute();
 };
+struct DynamicPointToVoxelBackwardExecutor {
+  StandInDpvParser parser_storage_;
+  StandInDpvParser *parser_ = &parser_storage_;
+  std::vector<float *> cpu_fp32_input_;
+  std::vector<float *> cpu_fp32_output_;
+  std::vector<StandInDescHolder> tensor_desc_;
+  void cpuCompute();
+};
 struct VoxelizationExecutor {
   StandInRuntime cpu_runtime_;
   void deterministic_hard_voxelize(const float *points, const float *voxel_size, const float *coors_range,
@@ -372,6 +384,27 @@ int mluops_ref_dynamic_point_to_voxel_forward(const float *feats, int32_t *coors
   return 0;
 }
 
+int mluops_ref_dynamic_point_to_voxel_backward(const float *grad_voxel_feats, const float *feats,
+                                               const float *voxel_feats, const int32_t *point2voxel_map,
+                                               int32_t voxel_num, int64_t n, int64_t c_num, float *grad_feats) {
+  std::vector<float> map_f((size_t)n), cnt_f((size_t)(voxel_num > 0 ? voxel_num : 1), 0.0f);
+  for (size_t i = 0; i < map_f.size(); ++i) map_f[i] = (float)point2voxel_map[i];
+  float num_f = (float)voxel_num;
+  std::fill(grad_feats, grad_feats + n * c_num, 0.0f);  // the harness hands the body a zeroed output
+  StandInTensor d_feats;
+  d_feats.dims = {n, c_num};
+  mluoptest::DynamicPointToVoxelBackwardExecutor ex;
+  ex.parser_storage_.in_count[0] = (int64_t)voxel_num * c_num;
+  ex.parser_storage_.in_count[1] = n * c_num;
+  ex.tensor_desc_.resize(2);
+  ex.tensor_desc_[1].tensor = &d_feats;
+  ex.cpu_fp32_input_ = {const_cast<float *>(grad_voxel_feats), const_cast<float *>(feats),
+                        const_cast<float *>(voxel_feats), map_f.data(), cnt_f.data(), &num_f};
+  ex.cpu_fp32_output_ = {grad_feats};
+  ex.cpuCompute();
+  return 0;
+}
+
 uint16_t mluops_ref_float_to_half_bits(float x) { return (uint16_t)mluoptest::cvtFloatToHalf(x); }
 
 // filter_layout: 0 [K,Ci,Co] (passed as a 4-D HWCN filter {K,1,Ci,Co}: the reference's
@@ -478,6 +511,7 @@ def build(reference_root=None, quiet=False):
                "void VoxelizationExecutor::deterministic_hard_voxelize("):
         parts.append(extract(paths["voxel"], fn))
     parts.append(extract(paths["dpv"], "void DynamicPointToVoxelForwardExecutor::cpuCompute("))
+    parts.append(extract(paths["dpv_bwd"], "void DynamicPointToVoxelBackwardExecutor::cpuCompute("))
     parts.append(EPILOGUE)
     with tempfile.TemporaryDirectory() as tmp:
         src = os.path.join(tmp, "ref_cpu_unit.cpp")

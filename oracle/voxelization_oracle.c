@@ -182,3 +182,33 @@ int mluops_oracle_dynamic_point_to_voxel_forward(const float *feats, int32_t *co
   free(order);
   return 0;
 }
+
+/*
+ * Gradient of the maximum reduction of the dynamic point-to-voxel scatter
+ * (reference test/mlu_op_gtest/pb_gtest/src/zoo/dynamic_point_to_voxel_backward/
+ * dynamic_point_to_voxel_backward.cpp:108-163): per voxel and channel the
+ * smallest point index whose feature equals the voxel's maximum receives the
+ * voxel's gradient; everything else in grad_feats [n,c] is zero.
+ */
+int mluops_oracle_dynamic_point_to_voxel_backward(const float *grad_voxel_feats, const float *feats,
+                                                  const float *voxel_feats, const int32_t *point2voxel_map,
+                                                  int32_t voxel_num, int64_t n, int64_t c_num,
+                                                  float *grad_feats) {
+  memset(grad_feats, 0, sizeof(float) * (size_t)(n * c_num));
+  if (voxel_num <= 0 || n == 0) return 0;
+  int32_t *from = (int32_t *)malloc(sizeof(int32_t) * (size_t)voxel_num * c_num);
+  if (!from) return -1;
+  for (int64_t i = 0; i < (int64_t)voxel_num * c_num; ++i) from[i] = (int32_t)n;
+  for (int64_t x = 0; x < n; ++x) {
+    const int32_t v = point2voxel_map[x];
+    if (v == -1) continue;
+    for (int64_t c = 0; c < c_num; ++c)
+      if (feats[x * c_num + c] == voxel_feats[(int64_t)v * c_num + c] && x < from[(int64_t)v * c_num + c])
+        from[(int64_t)v * c_num + c] = (int32_t)x;
+  }
+  for (int64_t v = 0; v < voxel_num; ++v)
+    for (int64_t c = 0; c < c_num; ++c)
+      if (from[v * c_num + c] < n) grad_feats[(int64_t)from[v * c_num + c] * c_num + c] = grad_voxel_feats[v * c_num + c];
+  free(from);
+  return 0;
+}

@@ -5,7 +5,8 @@ Run where the reference tree is available:
     python oracle/build_ref.py && python tests/golden/make_dynamic_point_to_voxel_golden.py
 Per case: seeded feats and coors, and for both reductions what the reference code
 produced (voxel_feats / voxel_coors / voxel_points_count cut to voxel_num rows,
-point2voxel_map, voxel_num, coors after the in-place -1 fill).
+point2voxel_map, voxel_num, coors after the in-place -1 fill), and for the maximum a seeded
+grad_voxel_feats with the grad_feats the reference's backward code made of it.
 """
 import os
 import sys
@@ -45,6 +46,11 @@ def main():
             store["%s/point2voxel_map" % name] = p2v
             store["%s/voxel_num" % name] = np.array([num], dtype=np.int32)
             store["%s/coors_filled" % name] = filled
+        vf, vc, p2v, cnt, num, _ = oracle.dynamic_point_to_voxel_forward(feats, coors, "max", use_ref=True)
+        grad = rng.standard_normal((max(num, 1), c)).astype(np.float32)
+        store[name + "/grad_voxel_feats"] = grad
+        store[name + "/grad_feats"] = oracle.dynamic_point_to_voxel_backward(grad, feats, vf[:max(num, 1)], p2v, num,
+                                                                             use_ref=True)
         print(name, "voxel_num", num)
     np.savez_compressed(OUT, **store)
     print(OUT, os.path.getsize(OUT), "bytes")

@@ -59,6 +59,58 @@ def test_oracle_against_reference_code(oracle):
             assert np.array_equal(a[0][:m].view(np.uint32), b[0][:m].view(np.uint32))
 
 
+def test_backward_oracle(oracle, dpv_golden):
+    for name in [str(n) for n in dpv_golden["names"]]:
+        feats, coors = dpv_golden[name + "/feats"], dpv_golden[name + "/coors"]
+        vf, vc, p2v, cnt, num, _ = oracle.dynamic_point_to_voxel_forward(feats, coors, "max")
+        grad = dpv_golden[name + "/grad_voxel_feats"]
+        got = oracle.dynamic_point_to_voxel_backward(grad, feats, vf[:max(num, 1)], p2v, num)
+        assert np.array_equal(got, dpv_golden[name + "/grad_feats"]), name
+        # each voxel hands every channel's gradient to exactly one of its points
+        assert int((got != 0).sum()) <= num * feats.shape[1]
+        if oracle.ref_lib() is not None:
+            assert np.array_equal(got, oracle.dynamic_point_to_voxel_backward(grad, feats, vf[:max(num, 1)], p2v, num,
+                                                                              use_ref=True))
+
+
+def test_backward_status_codes(ops, handle):
+    lib = ops.lib()
+    shapes = dict(g=(F32, (6, 4)), f=(F32, (6, 4)), vf=(F32, (6, 4)), m=(I32, (6,)), c=(I32, (6,)), n=(I32, (1,)),
+                  o=(F32, (6, 4)))
+
+    def call(reduce=MAX, null_at=None, **over):
+        a = dict(shapes)
+        a.update(over)
+        descs = [ops.TensorDesc(ARRAY, *a[k]) for k in ("g", "f", "vf", "m", "c", "n", "o")]
+        d = [x.ptr for x in descs]
+        buf = (ctypes.c_char * 8192)()
+        p = VP(ctypes.addressof(buf))
+        args = [handle.ptr, reduce, d[0], p, d[1], p, d[2], p, d[3], p, d[4], p, d[5], p, p, 8192, d[6], p]
+        if null_at is not None:
+            args[null_at] = None
+        st = lib.mluOpDynamicPointToVoxelBackward(*args)
+        for x in descs:
+            x.destroy()
+        return st
+
+    assert call() == ops.STATUS_EXECUTION_FAILED  # checks pass; a host-only handle cannot launch
+    assert call(reduce=MEAN) == ops.STATUS_BAD_PARAM
+    assert call(f=(F32, (0, 4)), m=(I32, (0,)), o=(F32, (0, 4)), g=(F32, (0, 4)), vf=(F32, (0, 4)), c=(I32, (0,))) == 0
+    for over in (dict(g=(F16, (6, 4))), dict(f=(F32, (6, 5))), dict(vf=(F32, (5, 4))), dict(m=(I32, (5,))),
+                 dict(c=(I32, (5,))), dict(n=(I32, (2,))), dict(o=(F32, (5, 4))), dict(o=(F32, (6, 3))),
+                 dict(g=(F32, (7, 4)), vf=(F32, (7, 4)), c=(I32, (7,)))):
+        assert call(**over) == ops.STATUS_BAD_PARAM, over
+    for i in (0, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 16, 17):
+        assert call(null_at=i) == ops.STATUS_BAD_PARAM, i
+    d = [ops.TensorDesc(ARRAY, *shapes[k]) for k in ("g", "f", "vf", "m", "c", "n")]
+    size = ctypes.c_size_t(0)
+    assert lib.mluOpGetDynamicPointToVoxelBackwardWorkspaceSize(handle.ptr, MAX, *[x.ptr for x in d],
+                                                                ctypes.byref(size)) == 0
+    assert size.value == 6 * 4 * 4
+    assert lib.mluOpGetDynamicPointToVoxelBackwardWorkspaceSize(handle.ptr, MAX, *[x.ptr for x in d],
+                                                                None) == ops.STATUS_BAD_PARAM
+
+
 def test_by_hand(oracle):
     coors = np.array([[1, 0, 2], [0, 5, 5], [1, 0, 2], [-1, 3, 3], [0, 5, 4]], dtype=np.int32)
     feats = np.array([[1.0], [2.0], [5.0], [9.0], [4.0]], dtype=np.float32)

@@ -81,3 +81,31 @@ def test_lidar_frame_properties(ops, gpu_handle):
     ref = np.full((num, 4), -np.inf, dtype=np.float32)
     np.maximum.at(ref, p2v[valid], feats[valid])
     assert np.array_equal(vf[:num], ref)
+
+
+def test_backward_matches_oracle(ops, oracle, gpu_handle, dpv_golden):
+    """grad_feats of the maximum reduction: golden vectors of the reference's CPU code, then random
+    clouds with many tied features (the smallest point index must win a tie)."""
+    def gpu_backward(feats, coors, grad_rows):
+        d_feats = torch.from_numpy(np.ascontiguousarray(feats)).cuda()
+        d_coors = torch.from_numpy(np.ascontiguousarray(coors, dtype=np.int32)).cuda()
+        vf, vc, p2v, cnt, num = ops.dynamic_point_to_voxel_forward(gpu_handle, d_feats, d_coors, "max")
+        grad = torch.zeros_like(vf)
+        grad[:grad_rows.shape[0]] = torch.from_numpy(grad_rows).cuda()
+        out = ops.dynamic_point_to_voxel_backward(gpu_handle, grad, d_feats, vf, p2v, cnt, num)
+        torch.cuda.synchronize()
+        return out.cpu().numpy()
+
+    for name in [str(n) for n in dpv_golden["names"]]:
+        got = gpu_backward(dpv_golden[name + "/feats"], dpv_golden[name + "/coors"],
+                           dpv_golden[name + "/grad_voxel_feats"])
+        assert np.array_equal(got.view(np.uint32), dpv_golden[name + "/grad_feats"].view(np.uint32)), name
+    rng = np.random.default_rng(300)
+    for trial in range(4):
+        n, c = int(rng.integers(100, 20000)), int(rng.integers(1, 9))
+        coors = np.stack([rng.integers(-1, h, n) for h in (5, 9, 7)], 1).astype(np.int32)
+        feats = np.round(rng.standard_normal((n, c)) * 2).astype(np.float32)
+        vf, vc, p2v, cnt, num, _ = oracle.dynamic_point_to_voxel_forward(feats, coors, "max")
+        grad = rng.standard_normal((max(num, 1), c)).astype(np.float32)
+        ref = oracle.dynamic_point_to_voxel_backward(grad, feats, vf[:max(num, 1)], p2v, num)
+        assert np.array_equal(gpu_backward(feats, coors, grad), ref)

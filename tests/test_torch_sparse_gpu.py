@@ -131,3 +131,22 @@ def test_points_to_backbone_features(sp, oracle):
     x = sp.SparseConvTensor(feats, idx, [4, 16, 16], 1)
     y = sp.SparseConv3d(16, 8, 3, stride=2, padding=1).cuda()(sp.SubMConv3d(4, 16, 3).cuda()(x))
     assert y.features.shape[1] == 8 and y.spatial_shape == [2, 8, 8] and torch.isfinite(y.features).all()
+
+
+def test_dynamic_scatter_autograd(sp, oracle):
+    rng = np.random.default_rng(35)
+    n, c = 3000, 5
+    coors = np.stack([rng.integers(-1, h, n) for h in (4, 9, 8)], 1).astype(np.int32)
+    feats = np.round(rng.standard_normal((n, c)) * 3).astype(np.float32)
+    d_feats = torch.from_numpy(feats).cuda().requires_grad_(True)
+    vf, vc, p2v = sp.dynamic_scatter(d_feats, torch.from_numpy(coors).cuda(), "max")
+    ref = oracle.dynamic_point_to_voxel_forward(feats, coors, "max")
+    m = ref[4]
+    assert vf.shape == (m, c) and np.array_equal(vf.detach().cpu().numpy(), ref[0][:m])
+    assert np.array_equal(vc.cpu().numpy(), ref[1][:m]) and np.array_equal(p2v.cpu().numpy(), ref[2])
+    grad = rng.standard_normal((m, c)).astype(np.float32)
+    vf.backward(torch.from_numpy(grad).cuda())
+    assert np.array_equal(d_feats.grad.cpu().numpy(), oracle.dynamic_point_to_voxel_backward(grad, feats, ref[0][:m],
+                                                                                            ref[2], m))
+    mean, _, _ = sp.dynamic_scatter(d_feats, torch.from_numpy(coors).cuda(), "mean")
+    assert np.array_equal(mean.cpu().numpy(), oracle.dynamic_point_to_voxel_forward(feats, coors, "mean")[0][:m])

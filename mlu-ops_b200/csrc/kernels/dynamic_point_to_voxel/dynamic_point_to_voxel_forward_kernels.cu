@@ -13,13 +13,14 @@
 //   makeRecordsKernel      coordinates with a negative entry become (-1,-1,-1) in
 //                          coors (as the reference does, in place) and get the
 //                          "no voxel" flag, the most significant sort digit
-//   histKernel / scanKernel / scatterKernel, once per 8-bit digit (13 passes):
-//                          per-tile digit counts, one exclusive scan over
-//                          [digit][tile], stable scatter (ranks inside a tile from
-//                          warp match masks and per-warp counts, no atomics).  A
-//                          digit on which all records agree is found by the scan
-//                          and its scatter is skipped, so small coordinates cost
-//                          few passes; nothing is decided on the host
+//   histKernel / scanDigitRowsKernel / scatterKernel, once per 8-bit digit (13
+//                          passes): per-tile digit counts, per digit an exclusive
+//                          scan over the tiles (256 blocks), stable scatter (ranks
+//                          inside a tile from warp match masks and per-warp counts,
+//                          no atomics).  A digit on which all records agree is
+//                          seen in the digit totals and its scatter is skipped, so
+//                          small coordinates cost few passes; nothing is decided
+//                          on the host
 //   countHeadsKernel / scanHeadsKernel / numberSegmentsKernel
 //                          a sorted record starts a voxel when its coordinates
 //                          differ from its predecessor's; the prefix sum of those
@@ -88,23 +89,19 @@ histKernel(const uint4 *__restrict__ records, int64_t n, int pass, const int32_t
   block_hist[(size_t)threadIdx.x * tiles + blockIdx.x] = hist[threadIdx.x];
 }
 
-// One block: exclusive scan of block_hist in [digit][tile] order, in place.  If one
-// digit holds every record the pass would not move anything: the next pass then
-// reads the same half of the ping-pong buffer.
-__global__ void __launch_bounds__(1024)
-scanKernel(int32_t *__restrict__ block_hist, int tiles, int64_t n, int pass, int32_t *__restrict__ source) {
-  __shared__ int32_t warp_total[32];
+// Block d: exclusive scan of digit d's counts over the tiles, in place, and the
+// digit's total.  (The offsets of the digits themselves are 256 numbers: every
+// block of the scatter kernel adds them up for itself.)
+__global__ void __launch_bounds__(256)
+scanDigitRowsKernel(int32_t *__restrict__ block_hist, int tiles, int32_t *__restrict__ digit_total) {
+  __shared__ int32_t warp_total[8];
   __shared__ int32_t carry;
-  __shared__ int32_t single_digit;
-  if (threadIdx.x == 0) {
-    carry = 0;
-    single_digit = 0;
-  }
+  int32_t *row = block_hist + (size_t)blockIdx.x * tiles;
+  if (threadIdx.x == 0) carry = 0;
   __syncthreads();
-  const int total_items = kRadixBins * tiles;
-  for (int base = 0; base < total_items; base += 1024) {
+  for (int base = 0; base < tiles; base += 256) {
     const int i = base + threadIdx.x;
-    const int32_t v = i < total_items ? block_hist[i] : 0;
+    const int32_t v = i < tiles ? row[i] : 0;
     int32_t incl = v;
     for (int o = 1; o < 32; o <<= 1) {
       const int32_t t = __shfl_up_sync(0xffffffffu, incl, o);
@@ -112,42 +109,52 @@ scanKernel(int32_t *__restrict__ block_hist, int tiles, int64_t n, int pass, int
     }
     if ((threadIdx.x & 31) == 31) warp_total[threadIdx.x >> 5] = incl;
     __syncthreads();
-    if (threadIdx.x < 32) {
-      int32_t w = warp_total[threadIdx.x];
-      for (int o = 1; o < 32; o <<= 1) {
-        const int32_t t = __shfl_up_sync(0xffffffffu, w, o);
-        if (threadIdx.x >= o) w += t;
-      }
-      warp_total[threadIdx.x] = w;
-    }
+    int32_t before = carry;
+    for (int w = 0; w < (threadIdx.x >> 5); ++w) before += warp_total[w];
+    if (i < tiles) row[i] = before + incl - v;
     __syncthreads();
-    const int32_t before = carry + (threadIdx.x >= 32 ? warp_total[(threadIdx.x >> 5) - 1] : 0);
-    const int32_t excl = before + incl - v;
-    if (i < total_items) block_hist[i] = excl;
-    __syncthreads();
-    if (threadIdx.x == 0) carry += warp_total[31];
+    if (threadIdx.x == 255) carry = before + incl;
     __syncthreads();
   }
-  // after the scan block_hist[d * tiles] is the number of records with a smaller digit
-  for (int d = threadIdx.x; d < kRadixBins; d += 1024) {
-    const int64_t start = block_hist[(size_t)d * tiles];
-    const int64_t end = d + 1 < kRadixBins ? block_hist[(size_t)(d + 1) * tiles] : n;
-    if (end - start == n) single_digit = 1;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) source[pass + 1] = single_digit ? source[pass] : 1 - source[pass];
+  if (threadIdx.x == 0) digit_total[blockIdx.x] = carry;
 }
 
+// Stable scatter of one tile.  A pass on whose digit all records agree moves
+// nothing: it is skipped and the next pass reads the same half of the ping-pong
+// buffer (every block reaches that decision from the 256 digit totals; block 0
+// records it for the kernels that follow).
 __global__ void __launch_bounds__(256)
-scatterKernel(uint4 *__restrict__ records, int64_t n, int pass, const int32_t *__restrict__ source, int tiles,
-              const int32_t *__restrict__ block_hist) {
-  if (source[pass + 1] == source[pass]) return;  // every record has the same digit: nothing moves
-  const uint4 *src = records + (size_t)source[pass] * n;
-  uint4 *dst = records + (size_t)source[pass + 1] * n;
+scatterKernel(uint4 *__restrict__ records, int64_t n, int pass, int32_t *__restrict__ source, int tiles,
+              const int32_t *__restrict__ block_hist, const int32_t *__restrict__ digit_total) {
   __shared__ int32_t warp_count[8][kRadixBins];  // this round: records per (warp, digit)
   __shared__ int32_t running[kRadixBins];        // records of earlier rounds per digit
+  __shared__ int32_t digit_base[kRadixBins];     // records with a smaller digit
+  __shared__ int32_t warp_sums[8];
+  __shared__ int32_t single_digit;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  running[threadIdx.x] = 0;
+  {
+    if (threadIdx.x == 0) single_digit = 0;
+    const int32_t mine = digit_total[threadIdx.x];
+    int32_t incl = mine;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    int32_t before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_sums[w];
+    digit_base[threadIdx.x] = before + incl - mine;
+    if ((int64_t)mine == n) single_digit = 1;
+    running[threadIdx.x] = 0;
+    __syncthreads();
+  }
+  const int from = source[pass];
+  const int to = single_digit ? from : 1 - from;
+  if (blockIdx.x == 0 && threadIdx.x == 0) source[pass + 1] = to;
+  if (single_digit) return;
+  const uint4 *src = records + (size_t)from * n;
+  uint4 *dst = records + (size_t)to * n;
   const int64_t base = (int64_t)blockIdx.x * kSortTile;
   for (int round = 0; round < kSortTile / 256; ++round) {
     for (int w = 0; w < 8; ++w) warp_count[w][threadIdx.x] = 0;
@@ -177,8 +184,8 @@ scatterKernel(uint4 *__restrict__ records, int64_t n, int pass, const int32_t *_
     }
     __syncthreads();
     if (live) {
-      const int64_t pos = (int64_t)block_hist[(size_t)digit * tiles + blockIdx.x] + warp_count[warp][digit] +
-                          rank_in_warp;
+      const int64_t pos = (int64_t)digit_base[digit] + block_hist[(size_t)digit * tiles + blockIdx.x] +
+                          warp_count[warp][digit] + rank_in_warp;
       dst[pos] = r;
     }
     __syncthreads();
@@ -358,7 +365,7 @@ PointToVoxelWorkspacePlan planPointToVoxelWorkspace(const PointToVoxelProblem &p
   plan.block_hist = off;
   off = alignUp(off + (size_t)kRadixBins * plan.tiles * sizeof(int32_t), 256);
   plan.source = off;
-  off = alignUp(off + (kRadixPasses + 1) * sizeof(int32_t), 256);
+  off = alignUp(off + (32 + kRadixBins) * sizeof(int32_t), 256);
   plan.chunk_count = off;
   off = alignUp(off + (size_t)plan.tiles * sizeof(int32_t), 256);
   plan.seg_start = off;
@@ -376,6 +383,7 @@ cudaError_t launchDynamicPointToVoxelForward(const PointToVoxelProblem &p, const
   uint4 *records = reinterpret_cast<uint4 *>(base + plan.records);
   int32_t *block_hist = reinterpret_cast<int32_t *>(base + plan.block_hist);
   int32_t *source = reinterpret_cast<int32_t *>(base + plan.source);
+  int32_t *digit_total = source + 32;  // int32[256] after the pass table
   int32_t *chunk_count = reinterpret_cast<int32_t *>(base + plan.chunk_count);
   int32_t *seg_start = reinterpret_cast<int32_t *>(base + plan.seg_start);
   const int64_t n = p.num_points;
@@ -387,8 +395,9 @@ cudaError_t launchDynamicPointToVoxelForward(const PointToVoxelProblem &p, const
     trace::Scope t("radixSortPasses", stream, 13.0 * 16.0 * n + 32.0 * n);
     for (int pass = 0; pass < kRadixPasses; ++pass) {
       histKernel<<<(unsigned)plan.tiles, 256, 0, stream>>>(records, n, pass, source, plan.tiles, block_hist);
-      scanKernel<<<1, 1024, 0, stream>>>(block_hist, plan.tiles, n, pass, source);
-      scatterKernel<<<(unsigned)plan.tiles, 256, 0, stream>>>(records, n, pass, source, plan.tiles, block_hist);
+      scanDigitRowsKernel<<<kRadixBins, 256, 0, stream>>>(block_hist, plan.tiles, digit_total);
+      scatterKernel<<<(unsigned)plan.tiles, 256, 0, stream>>>(records, n, pass, source, plan.tiles, block_hist,
+                                                             digit_total);
     }
   }
   {

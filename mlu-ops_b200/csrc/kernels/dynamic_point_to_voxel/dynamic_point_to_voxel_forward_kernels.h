@@ -28,8 +28,8 @@ struct PointToVoxelProblem {
 
 struct PointToVoxelWorkspacePlan {
   size_t records;     // uint4[2][num_points]: {c0, c1, c2, point index | invalid << 31}, ping-pong
-  size_t block_hist;  // int32[256][tiles]: digit counts per tile, then exclusive offsets
-  size_t source;      // int32[kRadixPasses + 1]: which half of `records` a pass reads
+  size_t block_hist;  // int32[256][tiles]: digit counts per tile, then per digit their exclusive prefix
+  size_t source;      // int32[32]: which half of `records` a pass reads; then int32[256] digit totals
   size_t chunk_count; // int32[tiles]: segment heads per tile, then exclusive prefix
   size_t seg_start;   // int32[num_points + 1]: first sorted position of every voxel
   size_t total;

@@ -377,7 +377,8 @@ mluOpStatus_t MLUOP_WIN_API mluOpGetVoxelizationWorkspaceSize(
  *   voxels [max_voxels,max_points,F] float, coors [max_voxels,3] int32 (z, y, x),
  *   num_points_per_voxel [max_voxels] int32, voxel_num [1] int32
  * Voxels are numbered in the order of their first points; a voxel keeps its
- * first max_points points in index order; rows past voxel_num are zero.
+ * first max_points points in index order; rows past voxel_num are zero.  The
+ * grid (round((max - min) / voxel_size) per axis) must have fewer than 2^63 cells.
  * Asynchronous on the handle's queue. */
 mluOpStatus_t MLUOP_WIN_API mluOpVoxelization(
     mluOpHandle_t handle, const mluOpTensorDescriptor_t points_desc, const void *points,

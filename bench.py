@@ -160,7 +160,15 @@ def run_b200(args):
     stream = torch.cuda.current_stream()
     handle = ops.Handle(stream.cuda_stream)
     weights = [torch.from_numpy(w).to(dev) for w in weights_np]
-    net = backbone.SparseNetwork(handle, layers, weights, grid, batch)
+    # Rulebooks depend only on coordinates: they run through a second handle on a second stream,
+    # where the host waits for their counts while the convolutions already enqueued on the first
+    # stream keep the GPU busy (--serial-rulebooks: everything on one stream).
+    rb_stream = rb_handle = None
+    if not args.serial_rulebooks:
+        rb_stream = torch.cuda.Stream(dev)
+        rb_handle = ops.Handle(rb_stream.cuda_stream)
+    net = backbone.SparseNetwork(handle, layers, weights, grid, batch, rulebook_handle=rb_handle,
+                                 rulebook_stream=rb_stream)
 
     h_idx = torch.from_numpy(idx_np).pin_memory()
     h_feat = torch.from_numpy(feat_np).pin_memory()
@@ -401,6 +409,8 @@ def run_b200(args):
                                "per GPU, grid %dx%dx%d, fp16 storage / fp32 accumulate" %
                                (args.workload, batch, cfg["per_sample"], *grid),
                    "voxels_per_gpu": L, "l2": "flushed after every step (256 MiB write, inside the timed region)",
+                   "rulebooks": "same stream as the convolutions" if args.serial_rulebooks else
+                                "second handle on a second stream, overlapping the convolutions of earlier layers",
                    "e2e_pipeline": "inputs of step i+1 and results of step i-1 are copied on two more streams while "
                                    "step i computes; every step's copies are inside the timed region",
                    "parallelism": ("batch samples per rank, NO gather (diagnostic)" if args.no_gather else "batch samples per rank; NCCL gather of final rows to rank 0 on a second stream, overlapping the next step") if world > 1 else "1 GPU"},
@@ -679,6 +689,8 @@ def main():
     ap.add_argument("--voxelization", action="store_true",
                     help="1 GPU: also time mluOpVoxelization on a synthetic 300,000-point LiDAR-like frame and add a "
                          "\"voxelization\" object to the JSON line")
+    ap.add_argument("--serial-rulebooks", action="store_true",
+                    help="run the rulebooks on the same stream as the convolutions instead of a second one")
     ap.add_argument("--no-gather", action="store_true",
                     help="diagnostic for N>1: skip the NCCL gather (independent replicas) to separate its cost "
                          "from host-side contention between the ranks' processes")

@@ -11,6 +11,7 @@ and re-sets only the dimensions that change, so that the host side adds as littl
 as possible to the gaps the API's two host round trips per rulebook leave on the
 GPU.
 """
+import contextlib
 import ctypes
 import sys
 
@@ -64,13 +65,20 @@ class _Desc:
 
 
 class SparseNetwork:
-    def __init__(self, handle, layers, weights, grid, batch):
-        """weights: per layer a CUDA tensor in ARRAY layout [kd,kh,kw,Ci,Co]."""
+    def __init__(self, handle, layers, weights, grid, batch, rulebook_handle=None, rulebook_stream=None):
+        """weights: per layer a CUDA tensor in ARRAY layout [kd,kh,kw,Ci,Co].
+
+        rulebook_handle / rulebook_stream: a second library handle bound to a second
+        (torch) stream.  Rulebooks depend only on coordinates, never on features, so with
+        them mluOpGetIndicePairs runs on that stream and the host waits there, while the
+        convolutions already enqueued on the first handle's stream keep the GPU busy."""
         self.handle, self.layers, self.weights = handle, layers, weights
+        self.rulebook_handle, self.rulebook_stream = rulebook_handle, rulebook_stream
         self.grid, self.batch = list(grid), int(batch)
         dev = weights[0].device
         self.device = dev
         self.workspace = Workspace(dev)
+        self.rulebook_workspace = Workspace(dev) if rulebook_handle is not None else None
         self.lib = ops.lib()
         ft = ops.DTYPE_HALF if weights[0].dtype == torch.float16 else ops.DTYPE_FLOAT
         self.d_idx = _Desc(ops.LAYOUT_ARRAY, ops.DTYPE_INT32)
@@ -129,6 +137,12 @@ class SparseNetwork:
         mluOpIndiceConvolutionForwardFromTable, instead of the reference-shaped
         mluOpIndiceConvolutionForward that rebuilds the table in every call."""
         lib, h = self.lib, self.handle.ptr
+        second = self.rulebook_handle is not None
+        compute = torch.cuda.current_stream()
+        if second:
+            # the coordinates are ready where the caller's stream is now
+            self.rulebook_stream.wait_stream(compute)
+        hr = self.rulebook_handle.ptr if second else h
         final_rulebook = self.layers[-1].rulebook
         ready = None
         rulebooks = {}
@@ -142,24 +156,30 @@ class SparseNetwork:
                 L = cur_idx.shape[0]
                 cells = self.batch * out_space[0] * out_space[1] * out_space[2]
                 out_rows = L if ly.sub_m else min(K * L, cells)
-                pairs = torch.empty((K, 2, L), dtype=torch.int32, device=self.device)
-                out_idx = torch.empty((out_rows, 4), dtype=torch.int32, device=self.device)
                 d_in, d_pairs = self.d_idx.set(L, 4), self.d_pairs.set(K, 2, L)
                 d_out, d_num = self.d_out_idx.set(out_rows, 4), self.d_num.set(K)
                 if on_host_idle is not None:
                     on_host_idle(li)
-                ops.check("mluOpGetIndicePairsWorkspaceSize",
-                          lib.mluOpGetIndicePairsWorkspaceSize(h, conv.ptr, d_in, d_pairs, d_out, d_num,
-                                                               ctypes.byref(self.size)))
-                ws = self.workspace.get(self.size.value)
-                ops.check("mluOpGetIndicePairs",
-                          lib.mluOpGetIndicePairs(h, conv.ptr, d_in, _vp(cur_idx.data_ptr()), _vp(ws.data_ptr()),
-                                                  self.size.value, d_pairs, _vp(pairs.data_ptr()), d_out,
-                                                  _vp(out_idx.data_ptr()), d_num, _vp(self.num_host.data_ptr())))
-                # The convolution API takes indice_num as a host array, so the rulebook writes it
-                # straight into pinned host memory (device-accessible under unified addressing):
-                # no copy is queued on the copy engines, only the stream has to drain.
-                torch.cuda.current_stream().synchronize()
+                with (torch.cuda.stream(self.rulebook_stream) if second else contextlib.nullcontext()):
+                    pairs = torch.empty((K, 2, L), dtype=torch.int32, device=self.device)
+                    out_idx = torch.empty((out_rows, 4), dtype=torch.int32, device=self.device)
+                    ops.check("mluOpGetIndicePairsWorkspaceSize",
+                              lib.mluOpGetIndicePairsWorkspaceSize(hr, conv.ptr, d_in, d_pairs, d_out, d_num,
+                                                                   ctypes.byref(self.size)))
+                    ws = (self.rulebook_workspace if second else self.workspace).get(self.size.value)
+                    ops.check("mluOpGetIndicePairs",
+                              lib.mluOpGetIndicePairs(hr, conv.ptr, d_in, _vp(cur_idx.data_ptr()), _vp(ws.data_ptr()),
+                                                      self.size.value, d_pairs, _vp(pairs.data_ptr()), d_out,
+                                                      _vp(out_idx.data_ptr()), d_num,
+                                                      _vp(self.num_host.data_ptr())))
+                    # The convolution API takes indice_num as a host array, so the rulebook writes it
+                    # straight into pinned host memory (device-accessible under unified addressing):
+                    # no copy is queued on the copy engines, only the rulebook's stream has to drain.
+                    torch.cuda.current_stream().synchronize()
+                if second:
+                    # allocated on the rulebook stream, read by the convolutions on the other one
+                    pairs.record_stream(compute)
+                    out_idx.record_stream(compute)
                 lib.mluOpGetSparseConvolutionNumActOut(conv.ptr, ctypes.byref(self.n_act))
                 num_list = self.num_host[:K].tolist()
                 table = None
@@ -178,7 +198,7 @@ class SparseNetwork:
                 rulebooks[ly.rulebook] = (pairs, out_idx, num_list, self.n_act.value)
                 if on_final_indices is not None and ly.rulebook == final_rulebook:
                     ready = torch.cuda.Event()
-                    ready.record()
+                    ready.record(self.rulebook_stream if second else compute)
             pairs, out_idx, num_list, n_out = rulebooks[ly.rulebook]
             L = cur_feat.shape[0]
             for i, v in enumerate(num_list):

@@ -83,3 +83,26 @@ def test_neighbour_table_fast_path_is_bit_identical(ops, workloads, backbone, gp
     torch.cuda.synchronize()
     assert torch.equal(a, b) and torch.equal(ia, ib)
     net.close()
+
+
+def test_rulebooks_on_a_second_stream_are_bit_identical(ops, workloads, backbone, gpu_handle):
+    """mluOpGetIndicePairs through a second handle on a second stream, overlapping the
+    convolutions of earlier layers, gives exactly the single-stream results, repeatedly."""
+    idx, feat, layers, weights = workloads.make_inputs("c2", batch=1)
+    grid = list(workloads.CONFIGS["c2"]["grid"])
+    d_w = [torch.from_numpy(w).cuda() for w in weights]
+    d_idx, d_feat = torch.from_numpy(idx).cuda(), torch.from_numpy(feat).cuda()
+    plain = backbone.SparseNetwork(gpu_handle, layers, d_w, grid, 1)
+    a, ia, _ = plain.forward(d_idx, d_feat)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    second = ops.Handle(stream.cuda_stream)
+    net = backbone.SparseNetwork(gpu_handle, layers, d_w, grid, 1, rulebook_handle=second, rulebook_stream=stream)
+    for _ in range(3):
+        b, ib, _ = net.forward(d_idx, d_feat)
+        c, ic, _ = net.forward(d_idx, d_feat, reuse_tables=True)
+        torch.cuda.synchronize()
+        assert torch.equal(a, b) and torch.equal(ia, ib) and torch.equal(a, c) and torch.equal(ia, ic)
+    net.close()
+    plain.close()
+    second.destroy()

@@ -3,6 +3,8 @@ import ctypes
 import os
 import re
 
+import pytest
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -38,3 +40,18 @@ def test_missing_library_fails_loudly(ops, monkeypatch):
     monkeypatch.setattr(ops, "LIB_PATH", "/nonexistent/libmluops_b200.so")
     with pytest.raises(RuntimeError, match="no fallback"):
         ops.lib()
+
+
+def test_public_headers_compile_as_c_and_cxx(tmp_path):
+    """include/mlu_op.h and include/mlu_op_trace.h are a C API: they must compile as C11 and as C++17."""
+    import shutil
+    import subprocess
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    if shutil.which("gcc") is None or not os.path.isfile(os.path.join(cuda_inc, "cuda_runtime_api.h")):
+        pytest.skip("gcc or the CUDA headers are not available")
+    src = tmp_path / "uses_headers.c"
+    src.write_text('#include "mlu_op.h"\n#include "mlu_op_trace.h"\n'
+                   "int main(void) { mluOpHandle_t h = 0; (void)h; return (int)MLUOP_STATUS_SUCCESS; }\n")
+    inc = ["-I", os.path.join(ROOT, "include"), "-I", cuda_inc]
+    subprocess.check_call(["gcc", "-std=c11", "-Wall", "-Werror", "-fsyntax-only"] + inc + [str(src)])
+    subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++"] + inc + [str(src)])

@@ -55,3 +55,21 @@ def test_public_headers_compile_as_c_and_cxx(tmp_path):
     inc = ["-I", os.path.join(ROOT, "include"), "-I", cuda_inc]
     subprocess.check_call(["gcc", "-std=c11", "-Wall", "-Werror", "-fsyntax-only"] + inc + [str(src)])
     subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++"] + inc + [str(src)])
+
+
+def test_cxx_caller_links_and_runs(tmp_path):
+    """tests/cabi/abi_check.cpp, a C++ caller in the style of the reference's API tests, builds
+    against include/ and the shared library and gets the expected status codes (host-only handle)."""
+    import shutil
+    import subprocess
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    if shutil.which("g++") is None or not os.path.isfile(os.path.join(cuda_inc, "cuda_runtime_api.h")):
+        pytest.skip("g++ or the CUDA headers are not available")
+    lib_dir = os.path.join(ROOT, "mlu-ops_b200", "lib")
+    exe = str(tmp_path / "abi_check")
+    subprocess.check_call(["g++", "-std=c++17", "-Wall", "-o", exe, os.path.join(ROOT, "tests", "cabi", "abi_check.cpp"),
+                           "-I", os.path.join(ROOT, "include"), "-I", cuda_inc, "-L", lib_dir, "-lmluops_b200",
+                           "-Wl,-rpath," + lib_dir])
+    env = dict(os.environ, MLUOP_B200_HOST_ONLY_HANDLE="1", MLUOP_MIN_LOG_LEVEL="3")
+    r = subprocess.run([exe], env=env, capture_output=True, text=True)
+    assert r.returncode == 0 and "abi_check: ok" in r.stdout, r.stdout + r.stderr

@@ -40,8 +40,8 @@ class Workspace:
 
 class LayerRecord:
     """What one layer consumed and produced (kept for parity checks and roofline accounting)."""
-    __slots__ = ("layer", "n_in", "n_out", "indice_num", "pairs", "out_indices", "features_in", "features_out",
-                 "new_rulebook", "in_space", "out_space")
+    __slots__ = ("layer", "n_in", "n_out", "indice_num", "pairs", "in_indices", "out_indices", "features_in",
+                 "features_out", "new_rulebook", "in_space", "out_space", "weights")
 
 
 class _Desc:
@@ -231,7 +231,7 @@ class SparseNetwork:
             rec = LayerRecord()
             rec.layer, rec.n_in, rec.n_out, rec.indice_num, rec.new_rulebook = ly, L, n_out, num_list, new_rb
             if keep:
-                rec.pairs, rec.out_indices = pairs, out_idx[:n_out]
+                rec.pairs, rec.in_indices, rec.out_indices = pairs, cur_idx, out_idx[:n_out]
                 rec.features_in, rec.features_out = cur_feat, out
                 rec.in_space, rec.out_space = list(in_space), list(out_space)
             records.append(rec)

@@ -152,8 +152,11 @@ def run_b200(args):
     if args.workload == "c4":
         assert batch % world == 0, "c4 shards 16 samples over the ranks"
         batch //= world
-    idx_np, feat_np, layers, weights_np = workloads.make_inputs(args.workload, batch=batch,
-                                                                seed=cfg["seed"] + 1000 * rank)
+    if args.workload == "c4":  # the ranks' shards of one fixed 16-sample job
+        idx_np, feat_np, layers, weights_np = workloads.make_inputs("c4", batch=batch, first_sample=rank * batch)
+    else:
+        idx_np, feat_np, layers, weights_np = workloads.make_inputs(args.workload, batch=batch,
+                                                                    seed=cfg["seed"] + 1000 * rank)
     L = idx_np.shape[0]
     elem = feat_np.dtype.itemsize
 
@@ -343,6 +346,21 @@ def run_b200(args):
     trace = read_trace(ops)
     ops.lib().mluOpTraceKernelEnable(0)
 
+    # the other configurations: c4 (strong scaling of one 16-sample job) at every N, the
+    # single-layer configurations c0 / c1 / c3 on one GPU
+    hbm_gbs, tensor_tflops, peak_kind = measured_peaks()
+    extra = {}
+    if args.workload == "c2" and not args.headline_only:
+        fp32_tflops = measure_fp32_fma_peak(torch, dev) if world == 1 else None
+        env = dict(torch=torch, dist=dist, ops=ops, workloads=workloads, backbone=backbone, sharding=sharding,
+                   dev=dev, rank=rank, world=world, flush=flush, stream=stream, handle=handle, rb_handle=rb_handle,
+                   rb_stream=rb_stream, flush_at=flush_at, hbm_gbs=hbm_gbs, tensor_tflops=tensor_tflops,
+                   fp32_tflops=fp32_tflops)
+        extra["c4"] = time_config("c4", max(5, args.steps // 2), env)
+        if world == 1:
+            extra["per_config"] = {name: time_config(name, max(5, args.steps // 2), env) for name in ("c0", "c1", "c3")}
+            extra["fp32_fma_peak_tflops"] = round(fp32_tflops, 2)
+
     def reduce_max(x):
         if world == 1:
             return x
@@ -367,7 +385,6 @@ def run_b200(args):
             dist.destroy_process_group()
         return
 
-    hbm_gbs, tensor_tflops, peak_kind = measured_peaks()
     voxels = L * world * args.steps
     value = voxels / (total_res * 1e-3)
     e2e_value = voxels / (total_e2e * 1e-3)
@@ -379,7 +396,7 @@ def run_b200(args):
     top_name, (top_launches, top_ms, top_bytes, top_flops) = top
     achieved = (top_bytes / top_launches) / ((top_ms / top_launches) * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
-                "frac": round(achieved / hbm_gbs, 4), "traffic": None,
+                "frac": round(achieved / hbm_gbs, 4), "traffic": None, "traffic_kind": None,
                 "kernel": top_name, "launches_per_step": top_launches // args.steps,
                 "avg_launch_ms": round(top_ms / top_launches, 5), "peak_source": peak_kind + " copy bandwidth",
                 "share_of_device_time": round(top_ms / total_kernel_ms, 4),
@@ -392,6 +409,9 @@ def run_b200(args):
         same = [dict(c, K=rec.layer.kernel_volume) for c, rec in zip(conv_rows, records)
                 if c["ci"] == int(ci_co[0]) and c["co"] == int(ci_co[1])]
         roofline["traffic"] = modelled_conv_traffic(same, elem)
+        roofline["traffic_kind"] = ("modelled: one ncu capture of this kernel (dram bytes read + written) scaled to "
+                                    "this run's launches by rows_in*Ci*2 + rows_out*Co*2 + 4*K*rows_out; not "
+                                    "measured in this run")
     t_roof = sum(max(c["flops"] / (tensor_tflops * 1e12), c["bytes"] / (hbm_gbs * 1e9)) for c in conv_rows)
     t_roof += pair_bytes / (hbm_gbs * 1e9)
     ms_per_step = total_res / args.steps
@@ -427,6 +447,12 @@ def run_b200(args):
         "kernels": {k: {"launches_per_step": v[0] // args.steps, "ms_per_step": round(v[1] / args.steps, 4)}
                     for k, v in sorted(trace.items(), key=lambda kv: -kv[1][1])},
     }
+    if "c4" in extra:
+        line["c4"] = extra["c4"]
+    if "per_config" in extra:
+        line["per_config"] = extra["per_config"]
+        line["fp32_fma_peak_tflops"] = {"value": extra["fp32_fma_peak_tflops"],
+                                        "how": "8192^3 float matmul, TF32 off, best of 5, CUDA events, this run"}
     if world == 1 and args.backward:
         line["training"] = training_step(args, ops, backbone, net, d_idx, d_feat, flush, elem, hbm_gbs,
                                          tensor_tflops)
@@ -445,6 +471,170 @@ def run_b200(args):
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_fp32_fma_peak(torch, dev):
+    """FP32 FMA throughput of this GPU (TFLOP/s): an 8192^3 float matmul with TF32 switched
+    off (the reference forbids TF32 for this path's matmul, reference
+    kernels/sparse_conv/indice_convolution_forward/indice_convolution_forward.cpp:227-234),
+    best of five, CUDA events.  It is the denominator of the fp32 configuration's flop term,
+    measured the way the bf16 figure of MEASURED_PEAKS.json was."""
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        n = 8192
+        a = torch.randn((n, n), dtype=torch.float32, device=dev)
+        b = torch.randn((n, n), dtype=torch.float32, device=dev)
+        c = torch.empty_like(a)
+        best = None
+        for i in range(6):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            torch.matmul(a, b, out=c)
+            t1.record()
+            torch.cuda.synchronize()
+            ms = t0.elapsed_time(t1)
+            if i > 0 and (best is None or ms < best):
+                best = ms
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
+def time_config(name, steps, env):
+    """One more configuration beside the headline: `steps` passes of its layer list (rulebook
+    generation + convolutions through the C ABI, inputs resident), its whole-step roofline from
+    the run's own pair counts and its dominant kernel from a traced pass.
+
+    c0 / c1 / c3 (one layer each, 1 GPU): every step sits between its own pair of CUDA events
+    and L2 is flushed between steps, outside the events.  c4 (the backbone at 16 x 150,000
+    voxels, strong scaling): the 16 samples are split over the ranks, the final rows are
+    gathered on rank 0 with NCCL as in the headline run, and the steps are timed as one
+    region (barrier + synchronize on both sides, L2 flush inside), max over ranks."""
+    torch, dist = env["torch"], env["dist"]
+    ops, workloads, backbone, sharding = env["ops"], env["workloads"], env["backbone"], env["sharding"]
+    dev, rank, world, flush, stream = env["dev"], env["rank"], env["world"], env["flush"], env["stream"]
+    cfg = workloads.CONFIGS[name]
+    batch, sharded = cfg["batch"], name == "c4"
+    if sharded:
+        assert batch % world == 0
+        batch //= world
+        # the shards of one fixed 16-sample job: rank r draws samples [r*batch, (r+1)*batch)
+        idx_np, feat_np, layers, weights_np = workloads.make_inputs(name, batch=batch, first_sample=rank * batch)
+    else:
+        idx_np, feat_np, layers, weights_np = workloads.make_inputs(name)
+    L = idx_np.shape[0]
+    elem = feat_np.dtype.itemsize
+    weights = [torch.from_numpy(w).to(dev) for w in weights_np]
+    net = backbone.SparseNetwork(env["handle"], layers, weights, list(cfg["grid"]), batch,
+                                 rulebook_handle=env["rb_handle"], rulebook_stream=env["rb_stream"])
+    d_idx, d_feat = torch.from_numpy(idx_np).to(dev), torch.from_numpy(feat_np).to(dev)
+    gather = sharding.RowGather(rank * batch, rank, world, device=dev) if sharded and world > 1 else None
+    pending = []
+
+    def flush_pending(li=None):
+        if pending and (li is None or li == env["flush_at"]):
+            out, out_idx, done = pending.pop()
+            gather.begin(out_idx, ready=done)
+            gather.finish(out, wait=False, ready=done)
+
+    def step():
+        if gather is None:
+            return net.forward(d_idx, d_feat)[2]
+        out, out_idx, records = net.forward(d_idx, d_feat, on_host_idle=flush_pending)
+        flush_pending()
+        done = torch.cuda.Event()
+        done.record(stream)
+        pending.append((out, out_idx, done))
+        return records
+
+    def drain():
+        if gather is not None:
+            flush_pending()
+            gather.wait()
+
+    for _ in range(3):
+        step()
+    drain()
+    torch.cuda.synchronize()
+    if sharded:
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(steps):
+            step()
+            flush.fill_(1)
+        drain()
+        t1.record(stream)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = t0.elapsed_time(t1) / steps
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        timing = "one region of %d steps, L2 flush inside, max over ranks" % steps
+    else:
+        times = []
+        for _ in range(steps):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            step()
+            t1.record(stream)
+            torch.cuda.synchronize()
+            times.append(t0.elapsed_time(t1))
+        ms = sum(times) / len(times)
+        timing = "mean of %d steps, each between its own events, L2 flushed between steps" % steps
+
+    ops.lib().mluOpTraceKernelReset()
+    ops.lib().mluOpTraceKernelEnable(1)
+    records = None
+    for _ in range(min(steps, 5)):
+        flush.fill_(1)
+        records = step()
+    drain()
+    torch.cuda.synchronize()
+    trace = read_trace(ops)
+    ops.lib().mluOpTraceKernelEnable(0)
+    traced = min(steps, 5)
+    net.close()
+    if rank != 0:
+        return None
+
+    is_half = feat_np.dtype.itemsize == 2
+    flop_peak = env["tensor_tflops"] if is_half else env["fp32_tflops"]
+    conv_rows, pair_bytes = backbone.roofline_bytes_and_flops(records, elem)
+    t_roof = sum(max(c["flops"] / (flop_peak * 1e12), c["bytes"] / (env["hbm_gbs"] * 1e9)) for c in conv_rows)
+    t_roof += pair_bytes / (env["hbm_gbs"] * 1e9)
+    kernels = {k: v for k, v in trace.items() if not k.startswith(("memset:", "memcpy:"))}
+    top_name, (top_n, top_ms, top_bytes, top_flops) = max(kernels.items(), key=lambda kv: kv[1][1])
+    total_ms = sum(v[1] for v in trace.values())
+    achieved = top_bytes / (top_ms * 1e-3) / 1e9
+    return {
+        "workload": "%s: batch %d x %d voxels%s, %s" % (
+            name, cfg["batch"], cfg["per_sample"], " split over %d ranks" % world if sharded and world > 1 else "",
+            "12-layer backbone" if len(layers) > 1 else "one %s convolution %d -> %d, %s" % (
+                "submanifold" if layers[0].sub_m else "strided", layers[0].ci, layers[0].co, cfg["dtype"])),
+        "value": round(L * world / (ms * 1e-3), 1) if sharded else round(L / (ms * 1e-3), 1), "unit": UNIT,
+        "ms_per_step": round(ms, 4), "timing": timing, "voxels": L * (world if sharded else 1),
+        "pairs_per_step": sum(c["P"] for c in conv_rows), "n_out": records[-1].n_out,
+        "t_roof_ms": round(t_roof * 1e3, 4), "roofline_frac": round(t_roof * 1e3 / ms, 4),
+        "flop_peak_tflops": round(flop_peak, 1), "scaling": "strong" if sharded else None,
+        "dominant_kernel": {"name": top_name, "launches_per_step": top_n // traced,
+                            "avg_launch_ms": round(top_ms / top_n, 5),
+                            "share_of_device_time": round(top_ms / total_ms, 4),
+                            "algorithmic_GBps": round(achieved, 1), "frac_of_copy_bandwidth": round(achieved / env["hbm_gbs"], 4),
+                            "tflops": round(top_flops / (top_ms * 1e-3) / 1e12, 2)},
+        "kernels": {k: {"launches_per_step": v[0] // traced, "ms_per_step": round(v[1] / traced, 4)}
+                    for k, v in sorted(trace.items(), key=lambda kv: -kv[1][1])},
+    }
 
 
 def voxelization_step(args, ops, handle, flush, hbm_gbs):
@@ -561,8 +751,7 @@ def training_step(args, ops, backbone, net, d_idx, d_feat, flush, elem, hbm_gbs,
                         for k, v in sorted(trace.items(), key=lambda kv: -kv[1][1])}}
 
 
-# DRAM traffic of the tensor-core convolution kernel.  One ncu capture
-# (profiles/convTcgen05Kernel_64x64_c2_subm2.md) measured dram__bytes_read.sum +
+# DRAM traffic of the tensor-core convolution kernel.  One ncu capture measured dram__bytes_read.sum +
 # dram__bytes_write.sum = 370.9 MB for the launch with 1,079,296 padded rows in and out, 64 -> 64 channels, 27
 # offsets; the kernel streams features once, writes outputs once and reads the neighbour table once, i.e.
 # rows_in*Ci*2 + rows_out*Co*2 + 4*K*rows_out = 392.9 MB by that model.  Other launches of the kernel are scaled by
@@ -679,6 +868,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="skip the c0 / c1 / c3 / c4 objects that the default line carries beside the c2 headline")
     ap.add_argument("--backward", action="store_true",
                     help="1 GPU: also time forward + backward (input and filter gradients of every layer) and "
                          "add a \"training\" object with its per-kernel times to the JSON line")

@@ -241,6 +241,8 @@ mluOpStatus_t MLUOP_WIN_API mluOpGetIndicePairsWorkspaceSize(
  *                 ascending linear order (default mode) or a copy of indices
  *                 (sub_m); rows past the active count are set to -1
  *   indice_num    [K] int32 (device)
+ * indices and out_indices must be 16-byte aligned (a coordinate row is moved as
+ * one 16-byte word); a pointer that is not is MLUOP_STATUS_BAD_PARAM.
  * Work is enqueued on the handle's queue.  In default mode the call blocks
  * once to read the number of active outputs into the descriptor. */
 mluOpStatus_t MLUOP_WIN_API mluOpGetIndicePairs(

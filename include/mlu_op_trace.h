@@ -36,7 +36,8 @@ mluOpStatus_t MLUOP_WIN_API mluOpTraceKernelReset(void);
  * starting with "memset:" or "memcpy:" are runtime operations, the rest are
  * kernels of this library.  The text is NUL terminated and truncated to
  * buffer_size; *needed (optional) receives the full length including the NUL.
- * The records are cleared. */
+ * The records are cleared once a call's buffer held the whole text: a call whose
+ * buffer was too small (a size query) keeps it for the next call. */
 mluOpStatus_t MLUOP_WIN_API mluOpTraceKernelReport(char *buffer, size_t buffer_size, size_t *needed);
 
 #if defined(__cplusplus)

@@ -10,6 +10,27 @@
 
 #include "core/logging.h"
 
+namespace mluop {
+
+bool checkStatusRequested() {
+  const char *check = std::getenv("MLUOP_B200_CHECK_STATUS");
+  return check && check[0] == '1';
+}
+
+bool takeStickyDeviceError(mluOpHandle_t handle, const char *api) {
+  if (handle == nullptr || handle->host_words == nullptr) return false;
+  volatile int32_t *word = handle->host_words + mluOpContext::kStickyWord;
+  const int32_t bits = *word;
+  if (bits == 0) return false;
+  *word = 0;
+  LOG(ERROR) << api << " an earlier asynchronous call on this handle reported device error bits " << bits
+             << " (1: hash table full, 4: look-back wait gave up, 0x100 and up: a bounded wait of the "
+             << "convolution kernel gave up); its outputs are not valid.";
+  return true;
+}
+
+}  // namespace mluop
+
 extern "C" {
 
 mluOpStatus_t MLUOP_WIN_API mluOpCreate(mluOpHandle_t *handle) {
@@ -72,6 +93,8 @@ mluOpStatus_t MLUOP_WIN_API mluOpCreate(mluOpHandle_t *handle) {
 
 mluOpStatus_t MLUOP_WIN_API mluOpDestroy(mluOpHandle_t handle) {
   PARAM_CHECK("[mluOpDestroy]", handle != NULL);
+  // an error of the last asynchronous call would otherwise never be reported
+  const bool pending_error = mluop::takeStickyDeviceError(handle, "[mluOpDestroy]");
   if (handle->host_words) {
     if (handle->host_only) {
       delete[] handle->host_words;
@@ -81,7 +104,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpDestroy(mluOpHandle_t handle) {
     }
   }
   delete handle;
-  return MLUOP_STATUS_SUCCESS;
+  return pending_error ? MLUOP_STATUS_EXECUTION_FAILED : MLUOP_STATUS_SUCCESS;
 }
 
 mluOpStatus_t MLUOP_WIN_API mluOpSetQueue(mluOpHandle_t handle, cnrtQueue_t queue) {

@@ -39,11 +39,30 @@ struct mluOpContext {
   int32_t clock_rate = 0;            // kHz
   double memory_band_width = 0;      // GB/s, from memory clock and bus width
   mluOpAtomicsMode_t atomics_mode = MLUOP_ATOMICS_NOT_ALLOWED;
-  // Pinned host words that device results are copied into when the host must
-  // read them before returning (the active-output count of a rulebook).
+  // Pinned, device-mapped host words that kernels store results into when the
+  // host must read them ([0] error bits and [1] active-output count of the last
+  // rulebook), and [kStickyWord]: error bits of asynchronous calls, which a
+  // kernel's error path (a full hash table, a bounded wait that gave up) ORs
+  // in and the next entry point on this handle reports and clears.
   int32_t *host_words = nullptr;
   static constexpr int kHostWords = 16;
+  static constexpr int kStickyWord = 2;
   bool host_only = false;  // created without a device: argument checks only
 };
+
+namespace mluop {
+
+// True when MLUOP_B200_CHECK_STATUS=1: entry points then wait for their work and
+// report device error bits themselves (debugging and tests).
+bool checkStatusRequested();
+
+// Asynchronous entry points cannot report a device-side error of their own
+// launch.  Such an error is recorded in the handle's sticky word; the next entry
+// point called on the handle calls this, which logs the bits, clears the word
+// and returns true (the caller returns MLUOP_STATUS_EXECUTION_FAILED).  No
+// synchronisation: only errors that have already reached the host are seen.
+bool takeStickyDeviceError(mluOpHandle_t handle, const char *api);
+
+}  // namespace mluop
 
 #endif  // MLUOP_B200_CORE_CONTEXT_H_

@@ -31,6 +31,7 @@ struct State {
   std::vector<Record> records;
   std::vector<cudaEvent_t> spare;
   std::string data_dir;
+  std::string unfetched;  // a report that did not fit the caller's buffer
 };
 
 std::atomic<int> g_enabled{-1};  // -1: environment not read yet
@@ -158,6 +159,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpTraceKernelReset(void) {
     if (r.stop) s.spare.push_back(r.stop);
   }
   s.records.clear();
+  s.unfetched.clear();
   return MLUOP_STATUS_SUCCESS;
 }
 
@@ -165,12 +167,26 @@ mluOpStatus_t MLUOP_WIN_API mluOpTraceKernelReport(char *buffer, size_t buffer_s
   PARAM_CHECK("[mluOpTraceKernelReport]", buffer != NULL || buffer_size == 0);
   auto &s = mluop::trace::state();
   std::lock_guard<std::mutex> guard(s.lock);
-  const std::string text = mluop::trace::summarise(s);
+  // A report that did not fit the caller's buffer is kept, so that a caller that asks
+  // for the size first and fetches second loses nothing; launches recorded in between
+  // are appended as further lines.
+  std::string text = s.unfetched;
+  if (text.empty() || !s.records.empty()) {
+    std::string more = mluop::trace::summarise(s);
+    if (!text.empty()) more.erase(0, more.find('\n') + 1);  // one header line only
+    text += more;
+  }
   if (needed) *needed = text.size() + 1;
+  const bool fits = buffer_size >= text.size() + 1;
   if (buffer_size > 0) {
-    const size_t n = text.size() < buffer_size - 1 ? text.size() : buffer_size - 1;
+    const size_t n = fits ? text.size() : buffer_size - 1;
     std::memcpy(buffer, text.data(), n);
     buffer[n] = '\0';
+  }
+  if (fits) {
+    s.unfetched.clear();
+  } else {
+    s.unfetched = text;
   }
   return MLUOP_STATUS_SUCCESS;
 }

@@ -153,6 +153,11 @@ mluOpStatus_t internalGetIndicePairs(mluOpHandle_t handle, const std::string &ap
   PARAM_CHECK(api, indice_pairs != NULL);
   PARAM_CHECK(api, out_indices != NULL);
   PARAM_CHECK(api, indice_num != NULL);
+  // The kernels read and write coordinate rows (four int32) as one 16-byte word.
+  PARAM_CHECK(api, reinterpret_cast<size_t>(indices) % 16 == 0);
+  PARAM_CHECK(api, reinterpret_cast<size_t>(out_indices) % 16 == 0);
+  PARAM_CHECK(api, reinterpret_cast<size_t>(indice_pairs) % 4 == 0);
+  PARAM_CHECK(api, reinterpret_cast<size_t>(indice_num) % 4 == 0);
   if (workspace_size != 0) {
     PARAM_CHECK(api, workspace != NULL);
   }
@@ -165,6 +170,7 @@ mluOpStatus_t internalGetIndicePairs(mluOpHandle_t handle, const std::string &ap
     LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
+  if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
 
   cudaStream_t stream = handle->queue;
   int32_t *status_host = handle->host_words;
@@ -176,8 +182,7 @@ mluOpStatus_t internalGetIndicePairs(mluOpHandle_t handle, const std::string &ap
     LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
-  static const char *check = std::getenv("MLUOP_B200_CHECK_STATUS");
-  if (sub_m && !(check && check[0] == '1')) {
+  if (sub_m && !mluop::checkStatusRequested()) {
     // No host read is needed: the active outputs are the inputs.  (With
     // MLUOP_B200_CHECK_STATUS=1 the call waits and reports device error bits.)
     conv_desc->num_act_out = g.L;
@@ -190,6 +195,9 @@ mluOpStatus_t internalGetIndicePairs(mluOpHandle_t handle, const std::string &ap
     LOG(ERROR) << api << " execution failed: " << cudaGetErrorString(err);
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
+  // this call reports its own error bits below; they need not be reported a second time
+  static_assert(mluOpContext::kStickyWord == 2, "publishStatusKernel ORs the error bits into word 2");
+  status_host[mluOpContext::kStickyWord] = 0;
   if (status_host[0] & mluop::sparse_conv::kPairsErrOutIndicesSmall) {
     LOG(ERROR) << api << " out_indices has " << out_indices_desc->getDimIndex(0) << " rows but "
                << status_host[1] << " output voxels are active.";

@@ -628,9 +628,18 @@ PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g) {
   p.table = off;
   p.chunk_count = off;
   p.perm = off;
+  // Test hook: MLUOP_B200_TEST_HASH_CAPACITY=<n> makes submanifold rulebooks use the hash
+  // table with at most n slots (rounded down to a power of two, at least 64), so that the
+  // "table full" error path can be exercised: probes are bounded by the capacity, the
+  // kernels record kPairsErrHashFull and carry on.
+  uint32_t cap_limit = 0;
+  if (g.sub_m) {
+    if (const char *v = std::getenv("MLUOP_B200_TEST_HASH_CAPACITY")) cap_limit = (uint32_t)std::strtoul(v, nullptr, 10);
+    if (cap_limit) p.lookup = kLookupHash;
+  }
   if (p.lookup == kLookupHash) {
     uint32_t cap = 64;
-    while ((uint64_t)cap < 2ull * (uint64_t)g.L) cap <<= 1;
+    while ((uint64_t)cap < 2ull * (uint64_t)g.L && (cap_limit == 0 || cap * 2 <= cap_limit)) cap <<= 1;
     p.hash_capacity = cap;
     off = alignUp(off + (size_t)cap * sizeof(unsigned long long), 256);
   } else {
@@ -701,8 +710,10 @@ void launchPairLists(const PairsGeometry &g, const PairsWorkspacePlan &plan, con
 }
 
 __global__ void publishStatusKernel(const int32_t *__restrict__ status, volatile int32_t *status_host) {
-  status_host[0] = status[0];
+  const int32_t bits = status[0];
+  status_host[0] = bits;
   status_host[1] = status[1];
+  if (bits) status_host[2] |= bits;  // sticky: reported and cleared by the next entry point on the handle
   __threadfence_system();
 }
 

@@ -208,7 +208,8 @@ mluOpStatus_t foolCheckNoPtr(const std::string &api, mluOpHandle_t handle,
   return MLUOP_STATUS_SUCCESS;
 }
 
-ConvProblem makeProblem(const mluOpTensorDescriptor_t output_grad_desc, const mluOpTensorDescriptor_t filters_desc,
+ConvProblem makeProblem(mluOpHandle_t handle, const mluOpTensorDescriptor_t output_grad_desc,
+                        const mluOpTensorDescriptor_t filters_desc,
                         const mluOpTensorDescriptor_t input_grad_desc) {
   const FilterDims f = readFilterDims(filters_desc);
   ConvProblem p{};
@@ -220,6 +221,7 @@ ConvProblem makeProblem(const mluOpTensorDescriptor_t output_grad_desc, const ml
   p.is_half = output_grad_desc->getDtype() == MLUOP_DTYPE_HALF;
   p.filter_layout = filterLayoutCode(filters_desc->getLayout());
   p.backward_data = 1;
+  p.sticky_status = handle->host_only ? nullptr : handle->host_words + mluOpContext::kStickyWord;
   return p;
 }
 
@@ -242,7 +244,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionBackwardDataWorkspaceSize(
                                     inverse, 0, input_grad_desc, &is_zero);
   if (st != MLUOP_STATUS_SUCCESS) return st;
   if (is_zero) return MLUOP_STATUS_SUCCESS;
-  const ConvProblem p = makeProblem(output_grad_desc, filters_desc, input_grad_desc);
+  const ConvProblem p = makeProblem(handle, output_grad_desc, filters_desc, input_grad_desc);
   *workspace_size = mluop::sparse_conv::planConvWorkspace(p).total;
   return MLUOP_STATUS_SUCCESS;
 }
@@ -266,7 +268,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardData(
   if (workspace_size > 0) {
     PARAM_CHECK(api, workspace != nullptr);
   }
-  const ConvProblem p = makeProblem(output_grad_desc, filters_desc, input_grad_desc);
+  const ConvProblem p = makeProblem(handle, output_grad_desc, filters_desc, input_grad_desc);
   const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p);
   if (workspace_size < plan.total || workspace == nullptr) {
     LOG(ERROR) << api << " workspace of " << workspace_size << " bytes is smaller than the " << plan.total
@@ -277,6 +279,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardData(
     LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
+  if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
   cudaError_t err = mluop::sparse_conv::launchIndiceConvolution(
       p, plan, output_grad, filters, static_cast<const int32_t *>(indice_pairs), indice_num, workspace,
       input_grad, handle->sm_count, handle->queue);
@@ -286,8 +289,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardData(
   }
   // See mluOpIndiceConvolutionForward: MLUOP_B200_CHECK_STATUS=1 makes the call wait
   // for the stream and report a kernel whose bounded waits gave up.
-  static const char *check = std::getenv("MLUOP_B200_CHECK_STATUS");
-  if (check && check[0] == '1') {
+  if (mluop::checkStatusRequested()) {
     int32_t word = 0;
     const char *base = reinterpret_cast<const char *>((reinterpret_cast<size_t>(workspace) + 255) / 256 * 256);
     err = cudaMemcpyAsync(&word, base + plan.status, sizeof(word), cudaMemcpyDeviceToHost, handle->queue);

@@ -202,6 +202,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilter(
     LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
+  if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
   cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionBackwardFilter(
       p, plan, features, output_grad, static_cast<const int32_t *>(indice_pairs), indice_num, workspace,
       filters_grad, handle->queue);

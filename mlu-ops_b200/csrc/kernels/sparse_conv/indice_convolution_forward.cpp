@@ -131,7 +131,7 @@ bool anyZeroElement(const mluOpTensorDescriptor_t a, const mluOpTensorDescriptor
          mluOpGetTensorElementNum(c) == 0 || mluOpGetTensorElementNum(d) == 0;
 }
 
-ConvProblem makeProblem(const mluOpTensorDescriptor_t features_desc,
+ConvProblem makeProblem(mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc,
                         const mluOpTensorDescriptor_t filters_desc, int64_t num_act_out) {
   const FilterShape fs = readFilterShape(filters_desc);
   ConvProblem p{};
@@ -142,6 +142,7 @@ ConvProblem makeProblem(const mluOpTensorDescriptor_t features_desc,
   p.co = (int32_t)fs.co;
   p.is_half = features_desc->getDtype() == MLUOP_DTYPE_HALF;
   p.filter_layout = fs.layout;
+  p.sticky_status = handle->host_only ? nullptr : handle->host_words + mluOpContext::kStickyWord;
   return p;
 }
 
@@ -163,7 +164,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionForwardWorkspaceSize(
     return MLUOP_STATUS_SUCCESS;
   }
   PARAM_CHECK(api, size != nullptr);
-  const ConvProblem p = makeProblem(features_desc, filters_desc, num_act_out);
+  const ConvProblem p = makeProblem(handle, features_desc, filters_desc, num_act_out);
   *size = mluop::sparse_conv::planConvWorkspace(p).total;
   return MLUOP_STATUS_SUCCESS;
 }
@@ -189,7 +190,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForward(
   if (workspace_size > 0) {
     PARAM_CHECK(api, workspace != nullptr);
   }
-  const ConvProblem p = makeProblem(features_desc, filters_desc, num_act_out);
+  const ConvProblem p = makeProblem(handle, features_desc, filters_desc, num_act_out);
   const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p);
   if (workspace_size < plan.total || workspace == nullptr) {
     LOG(ERROR) << api << " workspace of " << workspace_size << " bytes is smaller than the " << plan.total
@@ -200,6 +201,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForward(
     LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
+  if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
   cudaError_t err = mluop::sparse_conv::launchIndiceConvolution(
       p, plan, features, filters, static_cast<const int32_t *>(indice_pairs), indice_num, workspace,
       features_out, handle->sm_count, handle->queue);
@@ -210,8 +212,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForward(
   // The call is asynchronous; a kernel whose bounded waits gave up records that
   // in a status word of the workspace.  MLUOP_B200_CHECK_STATUS=1 makes the call
   // wait for the stream and report such a failure (debugging and tests).
-  static const char *check = std::getenv("MLUOP_B200_CHECK_STATUS");
-  if (check && check[0] == '1') {
+  if (mluop::checkStatusRequested()) {
     int32_t word = 0;
     const char *base = reinterpret_cast<const char *>((reinterpret_cast<size_t>(workspace) + 255) / 256 * 256);
     err = cudaMemcpyAsync(&word, base + plan.status, sizeof(word), cudaMemcpyDeviceToHost, handle->queue);
@@ -294,6 +295,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpBuildIndiceNeighbourTable(mluOpHandle_t handle,
     LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
+  if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
   const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p, true);
   cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionSteps(
       p, plan, nullptr, nullptr, static_cast<const int32_t *>(indice_pairs), indice_num, nullptr, nullptr,
@@ -317,7 +319,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionForwardFromTableWorkspaceSi
   PARAM_CHECK(api, size != nullptr);
   *size = 0;
   if (anyZeroElement(features_desc, indice_pairs_desc, filters_desc, features_out_desc)) return MLUOP_STATUS_SUCCESS;
-  const ConvProblem p = makeProblem(features_desc, filters_desc, num_act_out);
+  const ConvProblem p = makeProblem(handle, features_desc, filters_desc, num_act_out);
   *size = mluop::sparse_conv::planConvWorkspace(p, true).total;
   return MLUOP_STATUS_SUCCESS;
 }
@@ -342,7 +344,8 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForwardFromTable(
   PARAM_CHECK(api, table != nullptr);
   PARAM_CHECK(api, features_out != nullptr);
   PARAM_CHECK(api, workspace != nullptr);
-  const ConvProblem p = makeProblem(features_desc, filters_desc, num_act_out);
+  PARAM_CHECK(api, reinterpret_cast<size_t>(table) % 16 == 0);  // read 16 bytes at a time
+  const ConvProblem p = makeProblem(handle, features_desc, filters_desc, num_act_out);
   const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p, true);
   const size_t need = mluop::sparse_conv::neighbourTableBytes(p);
   if (workspace_size < plan.total || table_size < need) {
@@ -354,6 +357,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForwardFromTable(
     LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
+  if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
   cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionSteps(
       p, plan, features, filters, nullptr, indice_num, workspace, features_out, handle->sm_count, handle->queue,
       const_cast<int32_t *>(static_cast<const int32_t *>(table)), mluop::sparse_conv::kTableConvolveOnly);

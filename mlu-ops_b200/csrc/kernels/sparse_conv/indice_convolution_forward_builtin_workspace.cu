@@ -35,22 +35,26 @@ constexpr int kMaxDevices = 64;
 std::mutex g_lock;
 void *g_address[kMaxDevices] = {};
 
-// Device address of the array on the current device; looked up once per device.
-mluOpStatus_t builtinWorkspaceAddress(const char *api, void **out) {
-  int device = -1;
-  cudaError_t err = cudaGetDevice(&device);
-  if (err != cudaSuccess || device < 0 || device >= kMaxDevices) {
-    (void)cudaGetLastError();
-    LOG(ERROR) << api << " no current CUDA device: " << cudaGetErrorString(err);
+// Device address of the array on the handle's device, looked up once per device
+// with that device current.  The address is keyed by the handle's device, not by
+// whatever device the calling thread has current: a caller whose current device
+// differs from the handle's must still get the array of the GPU its stream runs on.
+mluOpStatus_t builtinWorkspaceAddress(const char *api, int device, void **out) {
+  if (device < 0 || device >= kMaxDevices) {
+    LOG(ERROR) << api << " the handle's device ordinal " << device << " is out of range.";
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
   std::lock_guard<std::mutex> guard(g_lock);
   if (g_address[device] == nullptr) {
+    int current = -1;
+    cudaError_t err = cudaGetDevice(&current);
+    if (err == cudaSuccess && current != device) err = cudaSetDevice(device);
     void *ptr = nullptr;
-    err = cudaGetSymbolAddress(&ptr, g_builtin_conv_workspace);
+    if (err == cudaSuccess) err = cudaGetSymbolAddress(&ptr, g_builtin_conv_workspace);
+    if (current >= 0 && current != device) (void)cudaSetDevice(current);
     if (err != cudaSuccess || ptr == nullptr) {
       (void)cudaGetLastError();
-      LOG(ERROR) << api << " cudaGetSymbolAddress failed: " << cudaGetErrorString(err);
+      LOG(ERROR) << api << " cudaGetSymbolAddress failed on device " << device << ": " << cudaGetErrorString(err);
       return MLUOP_STATUS_EXECUTION_FAILED;
     }
     g_address[device] = ptr;
@@ -84,7 +88,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForwardBuiltinWorkspace(
   void *workspace = nullptr;
   size_t workspace_size = 0;
   if (needed > 0 && !(handle != nullptr && handle->host_only)) {
-    st = builtinWorkspaceAddress(api, &workspace);
+    st = builtinWorkspaceAddress(api, handle->device, &workspace);
     if (st != MLUOP_STATUS_SUCCESS) return st;
     workspace_size = kBuiltinWorkspaceBytes;
   } else if (needed > 0) {

@@ -33,6 +33,9 @@ struct ConvProblem {
   //    computation with the two row sets, the two ids of a pair and the two
   //    channel axes of the filter exchanged.
   int32_t backward_data;
+  // Device-visible host word (or null) that a kernel's error path stores its error
+  // bits into, so that the next entry point on the handle can report them.
+  int32_t *sticky_status;
 };
 
 struct ConvWorkspacePlan {

@@ -65,8 +65,12 @@ __device__ __forceinline__ bool mbarTryWait(unsigned long long *bar, unsigned pa
 }
 // Bounded wait.  Returns false (and raises the abort flag) when the phase did
 // not complete within kWaitCycles clock cycles or another waiter already gave up.
+struct ErrorSink {
+  int32_t *status;  // status word in the workspace
+  int32_t *sticky;  // device-visible host word of the handle, or null
+};
 __device__ __forceinline__ bool mbarWait(unsigned long long *bar, unsigned parity, volatile int *abort_flag,
-                                         int32_t *status, int code) {
+                                         const ErrorSink &sink, int code) {
   if (mbarTryWait(bar, parity)) return true;
   const long long t0 = clock64();
   for (unsigned spin = 1;; ++spin) {
@@ -77,7 +81,11 @@ __device__ __forceinline__ bool mbarWait(unsigned long long *bar, unsigned parit
     }
   }
   *abort_flag = 1;
-  atomicOr(status, code);
+  atomicOr(sink.status, code);
+  if (sink.sticky) {
+    *reinterpret_cast<volatile int32_t *>(sink.sticky) = code << 8;
+    __threadfence_system();
+  }
   return false;
 }
 
@@ -186,7 +194,7 @@ template <int CI, int CO>
 __global__ void __launch_bounds__(kThreads)
 convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict__ filter_kcoci,
                   const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, __half *__restrict__ out,
-                  int32_t *status) {
+                  int32_t *status_word, int32_t *sticky) {
   using Cfg = TcConfig<CI, CO>;
   constexpr int S = Cfg::kAStages, NB = Cfg::kBBuffers, T = Cfg::kTiles;
   constexpr int CPR = Cfg::kChunksPerRow;  // 16-byte chunks per feature row
@@ -246,6 +254,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   const int n_items = n_items_s;
   const unsigned tmem_base = tmem_base_s;
   volatile int *abort_flag = &abort_s;
+  const ErrorSink status{status_word, sticky};
 
   if (warp < 4) {
     // ------------------------------------------------------------ producers
@@ -420,7 +429,8 @@ cudaError_t launchTc(const ConvProblem &p, const ConvWorkspacePlan &plan, const 
   static const std::string name = "convTcgen05Kernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
   static const std::string name_dgrad = name + ":input_grad";
   trace::Scope t(p.backward_data ? name_dgrad.c_str() : name.c_str(), stream, algo_bytes, algo_flops);
-  kernel<<<blocks, kThreads, smem, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K, out, status);
+  kernel<<<blocks, kThreads, smem, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K, out, status,
+                                             p.sticky_status);
   return cudaGetLastError();
 }
 

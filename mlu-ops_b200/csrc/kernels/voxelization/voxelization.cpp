@@ -193,8 +193,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpVoxelization(
     LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
-  static const char *check = std::getenv("MLUOP_B200_CHECK_STATUS");
-  if (check && check[0] == '1') {
+  if (mluop::checkStatusRequested()) {
     int32_t word = 0;
     const char *base = reinterpret_cast<const char *>((reinterpret_cast<size_t>(workspace) + 255) / 256 * 256);
     err = cudaMemcpyAsync(&word, base + plan.status, sizeof(word), cudaMemcpyDeviceToHost, handle->queue);

@@ -139,20 +139,37 @@ def single_layer(config):
     raise ValueError(config)
 
 
-def make_inputs(config, scale=1.0, batch=None, first_batch_index=0, seed=None):
+def make_inputs(config, scale=1.0, batch=None, first_batch_index=0, seed=None, first_sample=0):
     """(indices [L,4] int32, features [L,Cin], layers, weights) of a configuration.
 
     scale < 1 shrinks the voxel count per sample (for parity cases the CPU oracle
     finishes quickly); batch overrides the number of samples (multi-GPU shards).
+
+    c4 is one fixed job of 16 samples that is split over ranks, so each of its
+    samples has a random stream of its own: `first_sample` and `batch` select
+    samples [first_sample, first_sample + batch) of that job (batch index
+    relabelled to start at first_batch_index), and the rows a rank draws are
+    exactly the rows of those samples in the unsharded job.
     """
     cfg = CONFIGS[config]
-    rng = np.random.default_rng(cfg["seed"] if seed is None else seed)
+    base_seed = cfg["seed"] if seed is None else seed
     b = cfg["batch"] if batch is None else batch
     per = max(1, int(round(cfg["per_sample"] * scale)))
-    indices = batch_indices(rng, cfg["grid"], b, per, cfg["distribution"], first_batch_index)
     dtype = np.float16 if cfg["dtype"] == "float16" else np.float32
     layers = second_backbone_layers() if config in ("c2", "c4") else [single_layer(config)]
-    features = normal(rng, (indices.shape[0], layers[0].ci), 1.0, dtype)
+    if config == "c4":
+        idx_rows, feat_rows = [], []
+        for i in range(b):
+            rng = np.random.default_rng([base_seed, first_sample + i])
+            idx_rows.append(batch_indices(rng, cfg["grid"], 1, per, cfg["distribution"], first_batch_index + i))
+            feat_rows.append(normal(rng, (idx_rows[-1].shape[0], layers[0].ci), 1.0, dtype))
+        indices = np.ascontiguousarray(np.concatenate(idx_rows))
+        features = np.ascontiguousarray(np.concatenate(feat_rows))
+    else:
+        assert first_sample == 0
+        rng = np.random.default_rng(base_seed)
+        indices = batch_indices(rng, cfg["grid"], b, per, cfg["distribution"], first_batch_index)
+        features = normal(rng, (indices.shape[0], layers[0].ci), 1.0, dtype)
     # weights come from their own stream so that every shard of a workload sees the same filters
     weights = layer_weights(np.random.default_rng([cfg["seed"], 0x5EED]), layers, dtype)
     return indices, features, layers, weights

@@ -52,7 +52,7 @@ def run_get_indice_pairs(ops, handle, params, indices, pairs, out_indices, num):
         if st != ops.STATUS_SUCCESS:
             return st
         dummy = (ctypes.c_char * 4096)()
-        p = VP(ctypes.addressof(dummy))
+        p = VP((ctypes.addressof(dummy) + 15) // 16 * 16)
         return lib.mluOpGetIndicePairs(handle.ptr, desc, descs[0].ptr, p, p, size.value, descs[1].ptr, p,
                                        descs[2].ptr, p, descs[3].ptr, p)
     finally:
@@ -170,6 +170,32 @@ def test_gip_null_sweep(ops, handle):
         a = list(args)
         a[i] = None
         assert lib.mluOpGetIndicePairs(*a) == ops.STATUS_BAD_PARAM, i
+
+
+def test_gip_coordinate_rows_must_be_16_byte_aligned(ops, handle):
+    """indices and out_indices rows are moved as single 16-byte words: a pointer that is only
+    4-byte aligned is refused in the argument checks instead of faulting on the device."""
+    lib = ops.lib()
+    p = conv_params()
+    desc = VP()
+    assert lib.mluOpCreateSparseConvolutionDescriptor(ctypes.byref(desc)) == 0
+    ia = ops.int_array
+    assert lib.mluOpSetSparseConvolutionDescriptor(desc, 5, 1, ia(p["pad"]), ia(p["stride"]), ia(p["dilation"]),
+                                                   ia(p["input_space"]), ia(p["filter_space"]), ia(p["output_space"]),
+                                                   0, 0, 0) == 0
+    descs = [tdesc(ops, ops.LAYOUT_ARRAY, dt, dims) for dt, dims in
+             (GOOD["indices"], GOOD["pairs"], GOOD["out_indices"], GOOD["num"])]
+    size = ctypes.c_size_t(0)
+    assert lib.mluOpGetIndicePairsWorkspaceSize(handle.ptr, desc, descs[0].ptr, descs[1].ptr, descs[2].ptr,
+                                                descs[3].ptr, ctypes.byref(size)) == 0
+    dummy = (ctypes.c_char * 4096)()
+    good = (ctypes.addressof(dummy) + 15) // 16 * 16
+    for which in (3, 9):  # indices, out_indices
+        args = [handle.ptr, desc, descs[0].ptr, VP(good), VP(good), max(size.value, 1 << 20), descs[1].ptr, VP(good),
+                descs[2].ptr, VP(good), descs[3].ptr, VP(good)]
+        args[which] = VP(good + 4)
+        assert lib.mluOpGetIndicePairs(*args) == ops.STATUS_BAD_PARAM, which
+    lib.mluOpDestroySparseConvolutionDescriptor(desc)
 
 
 def test_gip_strided_descriptor_not_supported(ops, handle):
@@ -459,6 +485,9 @@ def test_table_entry_points_argument_checks(ops, handle):
         a = list(conv)
         a[i] = None
         assert lib.mluOpIndiceConvolutionForwardFromTable(*a) == ops.STATUS_BAD_PARAM, i
+    odd = list(conv)
+    odd[6] = VP(p.value + 4)  # the table is read 16 bytes at a time
+    assert lib.mluOpIndiceConvolutionForwardFromTable(*odd) == ops.STATUS_BAD_PARAM
     small = list(conv)
     small[7] = 100
     assert lib.mluOpIndiceConvolutionForwardFromTable(*small) == ops.STATUS_BAD_PARAM

@@ -238,3 +238,31 @@ def test_forced_variants(env):
                         "-x", "-q", "-k", "golden or random_small or config0 or scaled_config3 or repeated or ragged"],
                        env=dict(os.environ, **env), capture_output=True, text=True)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
+def test_device_errors_of_asynchronous_calls_are_sticky(ops, gpu_handle, monkeypatch):
+    """A submanifold rulebook returns before its kernels have run, so a device-side error
+    (here: a hash table undersized on purpose through the test hook, whose capacity-bounded
+    probes record "table full") cannot be returned by the call itself.  It must surface as
+    MLUOP_STATUS_EXECUTION_FAILED from the next entry point on the handle, once, and with
+    MLUOP_B200_CHECK_STATUS=1 from the call itself.  Nothing waits or faults: every probe
+    loop ends after `capacity` steps."""
+    rng = np.random.default_rng(5)
+    space = [16, 64, 64]
+    idx = torch.from_numpy(helpers.random_indices(rng, 1, space, 1000)).cuda()
+    conv = ops.SparseConvDesc(1, [1] * 3, [1] * 3, [1] * 3, space, [3] * 3, space, 1)
+    monkeypatch.setenv("MLUOP_B200_TEST_HASH_CAPACITY", "64")
+    with pytest.raises(ops.MluOpError) as err:  # the tests run with MLUOP_B200_CHECK_STATUS=1
+        ops.get_indice_pairs(gpu_handle, conv, idx)
+    assert err.value.status == ops.STATUS_EXECUTION_FAILED
+    monkeypatch.setenv("MLUOP_B200_CHECK_STATUS", "0")
+    ops.get_indice_pairs(gpu_handle, conv, idx)  # asynchronous: reports success
+    torch.cuda.synchronize()
+    monkeypatch.delenv("MLUOP_B200_TEST_HASH_CAPACITY")
+    with pytest.raises(ops.MluOpError) as err:
+        ops.get_indice_pairs(gpu_handle, conv, idx)
+    assert err.value.status == ops.STATUS_EXECUTION_FAILED
+    pairs, _, num, n_out = ops.get_indice_pairs(gpu_handle, conv, idx)  # reported once, then cleared
+    torch.cuda.synchronize()
+    assert n_out == 1000 and int(num.sum()) >= 1000
+    conv.destroy()

@@ -59,3 +59,22 @@ def test_trace_records_only_while_enabled(ops, gpu_handle):
     assert kernels[conv[0]][3] >= 2.0 * pairs * 32 * 32
     assert report(ops) == {}  # a report clears the records
     assert lib.mluOpTraceKernelReport(None, 16, None) == ops.STATUS_BAD_PARAM
+
+
+def test_size_query_then_fetch_keeps_the_records(ops, gpu_handle):
+    """A report whose buffer is too small (a size query) must not drop the records."""
+    lib = ops.lib()
+    lib.mluOpTraceKernelReset()
+    lib.mluOpTraceKernelEnable(1)
+    run_layer(ops, gpu_handle, np.random.default_rng(2))
+    lib.mluOpTraceKernelEnable(0)
+    need = ctypes.c_size_t(0)
+    assert lib.mluOpTraceKernelReport(None, 0, ctypes.byref(need)) == ops.STATUS_SUCCESS
+    assert need.value > 64
+    small = ctypes.create_string_buffer(32)
+    assert lib.mluOpTraceKernelReport(small, len(small), None) == ops.STATUS_SUCCESS  # truncated, kept
+    buf = ctypes.create_string_buffer(need.value)
+    assert lib.mluOpTraceKernelReport(buf, len(buf), None) == ops.STATUS_SUCCESS
+    lines = buf.value.decode().splitlines()
+    assert lines[0].startswith("name,launches") and len(lines) > 3 and buf.value.decode().startswith(small.value.decode())
+    assert report(ops) == {}

@@ -17,12 +17,13 @@ pytestmark = pytest.mark.gpu
 VP = ctypes.c_void_p
 
 
-def builtin_conv(ops, handle, feat, w, pairs, num_host, n_out, sub_m, fill=None):
+def builtin_conv(ops, handle, feat, w, pairs, num_host, n_out, sub_m, fill=None, out=None):
     L, ci = feat.shape
     co = w.shape[4]
     K = pairs.shape[0]
     dt = ops.DTYPE_HALF if feat.dtype == torch.float16 else ops.DTYPE_FLOAT
-    out = torch.empty((n_out, co), dtype=feat.dtype, device=feat.device)
+    if out is None:
+        out = torch.empty((n_out, co), dtype=feat.dtype, device=feat.device)
     if fill is not None:
         out.fill_(fill)
     d_f = ops.TensorDesc(ops.LAYOUT_ARRAY, dt, (L, ci))
@@ -51,11 +52,22 @@ def test_builtin_workspace_matches_ordinary_entry_point(ops, oracle, gpu_handle,
                              .astype(dtype)).cuda()
         expected = ops.indice_convolution_forward(gpu_handle, feat, w, "ARRAY", [3] * 3, pairs, num_host, n_out,
                                                   sub_m)
-        # two calls in a row on the shared built-in scratch, different problems each round
-        st1, got1 = builtin_conv(ops, gpu_handle, feat, w, pairs, num_host, n_out, sub_m, fill=7.0)
-        st2, got2 = builtin_conv(ops, gpu_handle, feat, w, pairs, num_host, n_out, sub_m, fill=-3.0)
+        # The outputs exist before the calls, and one call has already run (it loads the
+        # kernels and looks the array's address up), so that the free device memory the driver
+        # reports must be the same before and after the two calls under test: the entry point
+        # allocates nothing, on the device or through torch.
+        out1, out2 = torch.empty_like(expected), torch.empty_like(expected)
+        builtin_conv(ops, gpu_handle, feat, w, pairs, num_host, n_out, sub_m, fill=1.0, out=torch.empty_like(expected))
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        reserved_before = torch.cuda.memory_reserved()
+        # two calls in a row on the shared built-in scratch, different problems each round
+        st1, got1 = builtin_conv(ops, gpu_handle, feat, w, pairs, num_host, n_out, sub_m, fill=7.0, out=out1)
+        st2, got2 = builtin_conv(ops, gpu_handle, feat, w, pairs, num_host, n_out, sub_m, fill=-3.0, out=out2)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
         assert st1 == ops.STATUS_SUCCESS and st2 == ops.STATUS_SUCCESS
+        assert free_after == free_before and torch.cuda.memory_reserved() == reserved_before
         assert torch.equal(got1, expected) and torch.equal(got2, expected)
         results.append(got2)
         conv.destroy()

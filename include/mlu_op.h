@@ -332,6 +332,12 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilter(
  *   mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize / mluOpIndiceConvolutionForwardFromTable
  *       -> mluOpIndiceConvolutionForward with (table, table_size) in place of the
  *          indice_pairs pointer; same checks, same results bit for bit.
+ *   mluOpGetIndicePairsWithNeighbourTable
+ *       -> mluOpGetIndicePairs that also fills the table while it has every match
+ *          in hand (no separate build).  Only for submanifold rulebooks with odd
+ *          kernel sizes (volume <= 32), unit stride and dilation and pad = size / 2;
+ *          any other rulebook is MLUOP_STATUS_NOT_SUPPORTED before anything is
+ *          launched, and the caller builds the table from indice_pairs instead.
  * The table is valid as long as indice_pairs, indice_num and num_act_out are. */
 mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceNeighbourTableSize(
     mluOpHandle_t handle, const mluOpTensorDescriptor_t indice_pairs_desc,
@@ -341,6 +347,14 @@ mluOpStatus_t MLUOP_WIN_API mluOpBuildIndiceNeighbourTable(
     mluOpHandle_t handle, const mluOpTensorDescriptor_t indice_pairs_desc,
     const void *indice_pairs, const int64_t indice_num[], const int64_t num_act_out,
     void *table, const size_t table_size);
+
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndicePairsWithNeighbourTable(
+    mluOpHandle_t handle, mluOpSparseConvolutionDescriptor_t sparse_conv_desc,
+    const mluOpTensorDescriptor_t indices_desc, const void *indices, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t indice_pairs_desc,
+    void *indice_pairs, const mluOpTensorDescriptor_t out_indices_desc, void *out_indices,
+    const mluOpTensorDescriptor_t indice_num_desc, void *indice_num, void *table,
+    const size_t table_size);
 
 mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize(
     mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc,

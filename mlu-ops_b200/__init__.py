@@ -65,6 +65,8 @@ SIGNATURES = {
     "mluOpGetSparseConvolutionNumActOut": (_int, [_vp, _intp]),
     "mluOpGetIndicePairsWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_szt)]),
     "mluOpGetIndicePairs": (_int, [_vp, _vp, _vp, _vp, _vp, _szt, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mluOpGetIndicePairsWithNeighbourTable": (_int, [_vp, _vp, _vp, _vp, _vp, _szt, _vp, _vp, _vp, _vp, _vp, _vp,
+                                                    _vp, _szt]),
     "mluOpGetIndiceConvolutionForwardWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64, _i64,
                                                             ctypes.POINTER(_szt)]),
     "mluOpIndiceConvolutionForward": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64p, _i64, _i64, _i64, _vp,
@@ -244,18 +246,35 @@ def get_indice_pairs_workspace_size(handle, conv, indices_desc, pairs_desc, out_
     return size.value
 
 
-def get_indice_pairs(handle, conv, indices, out_rows=None, workspace=None):
+def max_active_outputs(L, batch, output_space, filter_space, stride, dilation):
+    """Upper bound on the active outputs of a default-mode rulebook with L inputs: an input
+    reaches an output through offset k only when (i + pad - k*dilation) is a multiple of the
+    stride, so per dimension at most ceil(kernel / (stride / gcd(stride, dilation))) offsets
+    can be valid for one input (2 of 3 for a 3-wide kernel at stride 2).  Callers size
+    out_indices by it instead of by the whole output grid."""
+    import math
+    per_input = 1
+    for k, s, d in zip(filter_space, stride, dilation):
+        period = s // math.gcd(s, d)
+        per_input *= -(-k // period)
+    cells = batch * output_space[0] * output_space[1] * output_space[2]
+    return max(1, min(L * per_input, cells))
+
+
+def get_indice_pairs(handle, conv, indices, out_rows=None, workspace=None, with_table=False):
     """Rulebook of one layer through mluOpGetIndicePairs.
 
     indices: int32 CUDA tensor [L,4].  Returns (indice_pairs [K,2,L], out_indices
-    [out_rows,4], indice_num [K] (device), num_act_out (host int)).
+    [out_rows,4], indice_num [K] (device), num_act_out (host int)); with_table the call
+    goes through mluOpGetIndicePairsWithNeighbourTable and the table (int32 [K, rows padded
+    to 512]) is appended to the result.
     """
     import torch
     L = indices.shape[0]
     K = conv.kernel_volume
     if out_rows is None:
-        cells = conv.batch * conv.output_space[0] * conv.output_space[1] * conv.output_space[2]
-        out_rows = L if conv.sub_m else min(K * L, cells)
+        out_rows = L if conv.sub_m else max_active_outputs(L, conv.batch, conv.output_space, conv.filter_space,
+                                                           conv.stride, conv.dilation)
     dev = indices.device
     pairs = torch.empty((K, 2, L), dtype=torch.int32, device=dev)
     out_indices = torch.empty((out_rows, 4), dtype=torch.int32, device=dev)
@@ -267,14 +286,46 @@ def get_indice_pairs(handle, conv, indices, out_rows=None, workspace=None):
     ws_size = get_indice_pairs_workspace_size(handle, conv, d_in, d_pairs, d_out, d_num)
     if workspace is None or workspace.numel() < ws_size:
         workspace = torch.empty((max(ws_size, 1),), dtype=torch.uint8, device=dev)
-    check("mluOpGetIndicePairs",
-          lib().mluOpGetIndicePairs(handle.ptr, conv.ptr, d_in.ptr, _ptr(indices), _ptr(workspace), ws_size,
-                                    d_pairs.ptr, _ptr(pairs), d_out.ptr, _ptr(out_indices), d_num.ptr,
-                                    _ptr(num)))
+    args = [handle.ptr, conv.ptr, d_in.ptr, _ptr(indices), _ptr(workspace), ws_size, d_pairs.ptr, _ptr(pairs),
+            d_out.ptr, _ptr(out_indices), d_num.ptr, _ptr(num)]
+    table = None
+    try:
+        if with_table:
+            size = _szt(0)
+            check("mluOpGetIndiceNeighbourTableSize",
+                  lib().mluOpGetIndiceNeighbourTableSize(handle.ptr, d_pairs.ptr, L, ctypes.byref(size)))
+            table = torch.empty((K, size.value // (4 * K)), dtype=torch.int32, device=dev)
+            check("mluOpGetIndicePairsWithNeighbourTable",
+                  lib().mluOpGetIndicePairsWithNeighbourTable(*args, _ptr(table), size.value))
+        else:
+            check("mluOpGetIndicePairs", lib().mluOpGetIndicePairs(*args))
+    finally:
+        for d in (d_in, d_pairs, d_out, d_num):
+            d.destroy()
     n_out = conv.num_act_out()
-    for d in (d_in, d_pairs, d_out, d_num):
-        d.destroy()
+    if with_table:
+        return pairs, out_indices, num, n_out, table
     return pairs, out_indices, num, n_out
+
+
+def build_neighbour_table(handle, indice_pairs, indice_num, num_act_out):
+    """The neighbour table of a rulebook from its pair lists (mluOpBuildIndiceNeighbourTable):
+    int32 [K, rows padded to 512]."""
+    import torch
+    K, _, L = indice_pairs.shape
+    d_pairs = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K, 2, L))
+    size = _szt(0)
+    try:
+        check("mluOpGetIndiceNeighbourTableSize",
+              lib().mluOpGetIndiceNeighbourTableSize(handle.ptr, d_pairs.ptr, num_act_out, ctypes.byref(size)))
+        table = torch.empty((K, size.value // (4 * K)), dtype=torch.int32, device=indice_pairs.device)
+        check("mluOpBuildIndiceNeighbourTable",
+              lib().mluOpBuildIndiceNeighbourTable(handle.ptr, d_pairs.ptr, _ptr(indice_pairs),
+                                                   i64_array([int(v) for v in indice_num]), num_act_out,
+                                                   _ptr(table), size.value))
+    finally:
+        d_pairs.destroy()
+    return table
 
 
 FILTER_LAYOUTS = {"ARRAY": LAYOUT_ARRAY, "NDHWC": LAYOUT_NDHWC, "NCDHW": LAYOUT_NCDHW,

@@ -154,24 +154,37 @@ class SparseNetwork:
             K = ly.kernel_volume
             if new_rb:
                 L = cur_idx.shape[0]
-                cells = self.batch * out_space[0] * out_space[1] * out_space[2]
-                out_rows = L if ly.sub_m else min(K * L, cells)
+                out_rows = L if ly.sub_m else ops.max_active_outputs(L, self.batch, out_space, ly.filter_space,
+                                                                     ly.stride, ly.dilation)
                 d_in, d_pairs = self.d_idx.set(L, 4), self.d_pairs.set(K, 2, L)
                 d_out, d_num = self.d_out_idx.set(out_rows, 4), self.d_num.set(K)
                 if on_host_idle is not None:
                     on_host_idle(li)
+                table = None
                 with (torch.cuda.stream(self.rulebook_stream) if second else contextlib.nullcontext()):
                     pairs = torch.empty((K, 2, L), dtype=torch.int32, device=self.device)
                     out_idx = torch.empty((out_rows, 4), dtype=torch.int32, device=self.device)
                     ops.check("mluOpGetIndicePairsWorkspaceSize",
                               lib.mluOpGetIndicePairsWorkspaceSize(hr, conv.ptr, d_in, d_pairs, d_out, d_num,
                                                                    ctypes.byref(self.size)))
-                    ws = (self.rulebook_workspace if second else self.workspace).get(self.size.value)
-                    ops.check("mluOpGetIndicePairs",
-                              lib.mluOpGetIndicePairs(hr, conv.ptr, d_in, _vp(cur_idx.data_ptr()), _vp(ws.data_ptr()),
-                                                      self.size.value, d_pairs, _vp(pairs.data_ptr()), d_out,
-                                                      _vp(out_idx.data_ptr()), d_num,
-                                                      _vp(self.num_host.data_ptr())))
+                    ws_bytes = self.size.value
+                    ws = (self.rulebook_workspace if second else self.workspace).get(ws_bytes)
+                    args = [hr, conv.ptr, d_in, _vp(cur_idx.data_ptr()), _vp(ws.data_ptr()), ws_bytes, d_pairs,
+                            _vp(pairs.data_ptr()), d_out, _vp(out_idx.data_ptr()), d_num,
+                            _vp(self.num_host.data_ptr())]
+                    st = ops.STATUS_NOT_SUPPORTED
+                    if reuse_tables and ly.sub_m:
+                        # submanifold rulebooks leave their neighbour table behind themselves
+                        ops.check("mluOpGetIndiceNeighbourTableSize",
+                                  lib.mluOpGetIndiceNeighbourTableSize(hr, d_pairs, L, ctypes.byref(self.size)))
+                        table = torch.empty((max(self.size.value, 16),), dtype=torch.uint8, device=self.device)
+                        st = lib.mluOpGetIndicePairsWithNeighbourTable(*args, _vp(table.data_ptr()), table.numel())
+                        if st == ops.STATUS_NOT_SUPPORTED:
+                            table = None
+                        else:
+                            ops.check("mluOpGetIndicePairsWithNeighbourTable", st)
+                    if table is None:
+                        ops.check("mluOpGetIndicePairs", lib.mluOpGetIndicePairs(*args))
                     # The convolution API takes indice_num as a host array, so the rulebook writes it
                     # straight into pinned host memory (device-accessible under unified addressing):
                     # no copy is queued on the copy engines, only the rulebook's stream has to drain.
@@ -180,10 +193,11 @@ class SparseNetwork:
                     # allocated on the rulebook stream, read by the convolutions on the other one
                     pairs.record_stream(compute)
                     out_idx.record_stream(compute)
+                    if table is not None:
+                        table.record_stream(compute)
                 lib.mluOpGetSparseConvolutionNumActOut(conv.ptr, ctypes.byref(self.n_act))
                 num_list = self.num_host[:K].tolist()
-                table = None
-                if reuse_tables:
+                if reuse_tables and table is None:
                     for i, v in enumerate(num_list):
                         self.num_i64[i] = v
                     d_p = self.d_pairs.set(K, 2, L)

@@ -37,7 +37,8 @@ mluOpStatus_t internalGetIndicePairs(mluOpHandle_t handle, const std::string &ap
                                      const mluOpTensorDescriptor_t indice_pairs_desc, void *indice_pairs,
                                      const mluOpTensorDescriptor_t out_indices_desc, void *out_indices,
                                      const mluOpTensorDescriptor_t indice_num_desc, void *indice_num,
-                                     bool is_get_workspace, size_t *return_ws) {
+                                     bool is_get_workspace, size_t *return_ws, bool with_table = false,
+                                     void *table = NULL, size_t table_size = 0) {
   PARAM_CHECK(api, handle != NULL);
   PARAM_CHECK(api, conv_desc != NULL);
   PARAM_CHECK(api, indices_desc != NULL);
@@ -166,6 +167,24 @@ mluOpStatus_t internalGetIndicePairs(mluOpHandle_t handle, const std::string &ap
                << plan.total << " bytes mluOpGetIndicePairsWorkspaceSize reports.";
     return MLUOP_STATUS_BAD_PARAM;
   }
+  int32_t *neighbour_table = NULL;
+  if (with_table) {
+    if (!mluop::sparse_conv::pairsCanEmitTable(g, plan)) {
+      LOG(ERROR) << api << " the rulebook kernels emit a neighbour table only for submanifold rulebooks with odd "
+                 << "kernel sizes up to volume 32, unit stride and dilation and pad = size / 2; build the table "
+                 << "from indice_pairs with mluOpBuildIndiceNeighbourTable instead.";
+      return MLUOP_STATUS_NOT_SUPPORTED;
+    }
+    PARAM_CHECK(api, table != NULL);
+    PARAM_CHECK(api, reinterpret_cast<size_t>(table) % 16 == 0);
+    const size_t need = (size_t)g.K * (size_t)mluop::sparse_conv::pairsTableStride(g.L) * sizeof(int32_t);
+    if (table_size < need) {
+      LOG(ERROR) << api << " table of " << table_size << " bytes is smaller than the " << need
+                 << " bytes mluOpGetIndiceNeighbourTableSize reports.";
+      return MLUOP_STATUS_BAD_PARAM;
+    }
+    neighbour_table = static_cast<int32_t *>(table);
+  }
   if (handle->host_only) {
     LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
     return MLUOP_STATUS_EXECUTION_FAILED;
@@ -177,7 +196,7 @@ mluOpStatus_t internalGetIndicePairs(mluOpHandle_t handle, const std::string &ap
   cudaError_t err = mluop::sparse_conv::launchGetIndicePairs(
       g, plan, static_cast<const int32_t *>(indices), workspace, static_cast<int32_t *>(indice_pairs),
       static_cast<int32_t *>(out_indices), out_indices_desc->getDimIndex(0),
-      static_cast<int32_t *>(indice_num), status_host, stream);
+      static_cast<int32_t *>(indice_num), status_host, neighbour_table, stream);
   if (err != cudaSuccess) {
     LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
     return MLUOP_STATUS_EXECUTION_FAILED;
@@ -224,6 +243,23 @@ mluOpStatus_t MLUOP_WIN_API mluOpGetIndicePairs(
   return internalGetIndicePairs(handle, "[mluOpGetIndicesPairs]", sparse_conv_desc, indices_desc, indices,
                                 workspace, workspace_size, indice_pairs_desc, indice_pairs,
                                 out_indices_desc, out_indices, indice_num_desc, indice_num, false, NULL);
+}
+
+// No counterpart in the reference: mluOpGetIndicePairs that also leaves the
+// neighbour table of the rulebook in `table` (see the neighbour-table entry
+// points next to mluOpIndiceConvolutionForward).  The probe kernel has every
+// match in hand, so the table costs one more coalesced store per slot and the
+// separate build (a memset and a scatter over all pairs) disappears.
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndicePairsWithNeighbourTable(
+    mluOpHandle_t handle, mluOpSparseConvolutionDescriptor_t sparse_conv_desc,
+    const mluOpTensorDescriptor_t indices_desc, const void *indices, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t indice_pairs_desc, void *indice_pairs,
+    const mluOpTensorDescriptor_t out_indices_desc, void *out_indices,
+    const mluOpTensorDescriptor_t indice_num_desc, void *indice_num, void *table, const size_t table_size) {
+  return internalGetIndicePairs(handle, "[mluOpGetIndicePairsWithNeighbourTable]", sparse_conv_desc, indices_desc,
+                                indices, workspace, workspace_size, indice_pairs_desc, indice_pairs,
+                                out_indices_desc, out_indices, indice_num_desc, indice_num, false, NULL, true, table,
+                                table_size);
 }
 
 mluOpStatus_t MLUOP_WIN_API mluOpGetIndicePairsWorkspaceSize(

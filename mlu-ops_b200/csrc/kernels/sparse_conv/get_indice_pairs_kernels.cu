@@ -15,33 +15,40 @@
 //   from position indice_num[k] on.
 //
 // How: everything is exact int32 arithmetic and every result is deterministic.
+// One cudaMemsetAsync clears all scratch that must start at zero (status words,
+// scan descriptors, lookup table), then
 //
-// Lookup structure, one of
-//   rank       (default mode) one occupancy bit per output cell (atomicOr); a
-//              prefix popcount over the bit words gives each active cell its
-//              ascending rank and the same pass decodes out_indices; a lookup is
-//              one {bits, rank} load and neighbouring cells share words.
-//   hash       (submanifold, sparse grid) table lin(j) -> j in 64-bit slots, CAS
-//              insert + atomicMax so a repeated coordinate keeps the largest j.
-//   rank+perm  (submanifold, dense grid) the occupancy/rank table over the
-//              input grid plus perm[rank] = row id (atomicMax): a miss costs one
-//              shared word, a hit one more load.
+//   lookup structure, one of
+//     rank       (default mode) markOutputsKernel sets one occupancy bit per valid
+//                output cell; rankScanKernel turns the bit words into {bits,
+//                exclusive rank} in one pass (chained scan over chunks of words
+//                with decoupled look-back) and decodes out_indices in ascending
+//                order.
+//     hash       (submanifold, sparse grid) hashInsertKernel: lin(j) -> j in
+//                64-bit slots, CAS insert + atomicMax so that a repeated coordinate
+//                keeps the largest j.
+//     rank+perm  (submanifold, dense grid) the same occupancy/rank table over the
+//                input grid plus permKernel: perm[rank] = row id.
 //
-// Pair lists, one of
-//   two pass   (default) matches are staged in [K][L] order with per-tile
-//              counts, an exclusive scan over tiles per offset gives the write
-//              offsets, a compaction kernel writes lists and -1 tails, every
-//              word of indice_pairs exactly once.
-//   single pass (opt-in, kernel volume <= 32): a block takes a tile of 256 voxels by
-//              ticket, keeps the tile's matches in shared memory, publishes its
-//              per-offset counts and obtains its write offsets by decoupled
-//              look-back over the preceding tiles' descriptors, then writes its
-//              pairs in place; a second kernel writes the -1 tails.  indice_pairs
-//              is written exactly once and nothing is staged in global memory.
+//   pair lists, one of
+//     single pass (kernel volume <= 32) pairListsKernel: a block takes a tile of
+//                256 voxels by ticket, probes its K x 256 slots (3x3x3 kernels with
+//                stride 1 or 2 run a fully unrolled walk that keeps the matches
+//                in registers), publishes its K counts as one descriptor and
+//                obtains its K write offsets by a two-level look-back (tiles of
+//                its group of 32, then group descriptors), and writes its pairs
+//                in place.  Nothing is staged in global memory and one chain of
+//                K-wide descriptors serves all offsets.
+//     two pass   (larger kernel volumes) matches staged in [K][L] order with
+//                per-tile counts, a scan per offset, a compaction kernel.
+//   finishPairsKernel writes the -1 tails of indice_pairs, the -1 rows of
+//   out_indices past the active count, and hands {error bits, active count} to
+//   the host.
 //
-// Every wait is bounded: hash probes by the table capacity, the look-back spin
-// by about one second of clock; both report through a status word instead of
-// spinning on.
+// Every wait is bounded: hash probes by the table capacity, look-back spins by
+// about 0.2 s of clock, with the give-up decision taken by the whole warp;
+// both report through the status word (and the handle's sticky host word)
+// instead of spinning on.
 #include "kernels/sparse_conv/get_indice_pairs_kernels.h"
 
 #include <cuda_runtime.h>
@@ -57,10 +64,37 @@ namespace sparse_conv {
 
 namespace {
 
-constexpr unsigned long long kEmptySlot = 0xFFFFFFFFFFFFFFFFull;
-constexpr long long kLookBackCycles = 2000000000ll;  // a look-back wait gives up after about a second
+constexpr long long kLookBackCycles = 400000000ll;  // a look-back wait gives up after about 0.2 s
+
+// status words (int32) at the start of the workspace
+constexpr int kStatusErrors = 0;       // error bits
+constexpr int kStatusActive = 1;       // number of active outputs (default mode)
+constexpr int kStatusTileTicket = 2;   // tiles handed out by pairListsKernel
+constexpr int kStatusChunkTicket = 3;  // chunks handed out by rankScanKernel
+
+// look-back descriptor words: 2-bit state, 30-bit value
+constexpr uint32_t kFlagAggregate = 1u << 30;  // value = this unit's own count
+constexpr uint32_t kFlagPrefix = 2u << 30;     // value = inclusive count up to and including this unit
+constexpr uint32_t kValueMask = (1u << 30) - 1u;
+constexpr int kGroupTiles = 32;  // tiles per group of the two-level look-back
+constexpr int kDescWords = 32;   // words per K-wide descriptor (kernel volumes up to 32)
+static_assert(kFusedMaxOffsets <= kDescWords, "one descriptor word per kernel offset");
 
 __host__ __device__ inline size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct ErrorSink {
+  int32_t *status;  // status words in the workspace
+  int32_t *sticky;  // device-visible host word of the handle, or null
+};
+
+__device__ __forceinline__ void raiseError(const ErrorSink &sink, int code) {
+  atomicOr(sink.status + kStatusErrors, code);
+  if (sink.sticky) {
+    volatile int32_t *w = sink.sticky;
+    *w = *w | code;
+    __threadfence_system();
+  }
+}
 
 __device__ __forceinline__ uint32_t mixKey(uint32_t x) {
   x ^= x >> 16;
@@ -118,50 +152,51 @@ __device__ __forceinline__ uint32_t inputLinear(const int4 c, const PairsGeometr
 }
 
 struct LookupTables {
-  const unsigned long long *slots;  // hash
+  const unsigned long long *slots;  // hash: (lin + 1) << 32 | row id, 0 = empty
   uint32_t mask;
-  const uint2 *rank_table;  // rank, rank + perm
-  const int32_t *perm;      // rank + perm
+  const uint2 *rank_table;  // rank, rank + perm: {occupancy bits, exclusive rank}
+  const int32_t *perm;      // rank + perm: row id + 1 of the r-th occupied cell
 };
 
 // ---------------------------------------------------------------- hash table
 
 __global__ void __launch_bounds__(256)
 hashInsertKernel(PairsGeometry g, const int4 *__restrict__ indices, unsigned long long *slots,
-                 uint32_t mask, int32_t *status) {
+                 uint32_t mask, ErrorSink sink) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= g.L) return;
   const int4 c = indices[j];
   if (!rowInRange(c, g)) return;
-  const uint32_t lin = inputLinear(c, g);
-  const unsigned long long packed = ((unsigned long long)lin << 32) | (uint32_t)j;
-  uint32_t h = mixKey(lin) & mask;
+  const uint32_t key = inputLinear(c, g) + 1u;
+  const unsigned long long packed = ((unsigned long long)key << 32) | (uint32_t)j;
+  uint32_t h = mixKey(key) & mask;
   for (uint32_t probe = 0; probe <= mask; ++probe) {
     unsigned long long cur = slots[h];
-    if (cur == kEmptySlot) {
-      cur = atomicCAS(&slots[h], kEmptySlot, packed);
-      if (cur == kEmptySlot) return;
+    if (cur == 0ull) {
+      cur = atomicCAS(&slots[h], 0ull, packed);
+      if (cur == 0ull) return;
     }
-    if ((uint32_t)(cur >> 32) == lin) {
+    if ((uint32_t)(cur >> 32) == key) {
       atomicMax(&slots[h], packed);  // same key: keep the largest row id
       return;
     }
     h = (h + 1) & mask;
   }
-  atomicOr(status, kPairsErrHashFull);
+  raiseError(sink, kPairsErrHashFull);
 }
 
 __device__ __forceinline__ int hashLookup(const unsigned long long *__restrict__ slots, uint32_t mask,
-                                          uint32_t lin, int32_t *status) {
-  uint32_t h = mixKey(lin) & mask;
+                                          uint32_t lin, const ErrorSink &sink) {
+  const uint32_t want = lin + 1u;
+  uint32_t h = mixKey(want) & mask;
   for (uint32_t probe = 0; probe <= mask; ++probe) {
     const unsigned long long cur = __ldg(slots + h);
     const uint32_t key = (uint32_t)(cur >> 32);
-    if (key == lin) return (int)(uint32_t)cur;
-    if (key == 0xFFFFFFFFu) return -1;
+    if (key == want) return (int)(uint32_t)cur;
+    if (key == 0u) return -1;
     h = (h + 1) & mask;
   }
-  atomicOr(status, kPairsErrHashFull);
+  raiseError(sink, kPairsErrHashFull);
   return -1;
 }
 
@@ -211,56 +246,90 @@ markInputsKernel(PairsGeometry g, const int4 *__restrict__ indices, uint2 *rank_
   if (rowInRange(c, g)) setBit(rank_table, inputLinear(c, g));
 }
 
-// chunk_count[c] = set bits in words [c*1024, (c+1)*1024)
-__global__ void __launch_bounds__(256)
-countBitsKernel(const uint2 *__restrict__ rank_table, int64_t words, int32_t *chunk_count) {
-  __shared__ int warp_sums[33];
-  const int64_t w0 = (int64_t)blockIdx.x * kRankChunkWords + threadIdx.x * 4;
-  int n = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-    if (w0 + i < words) n += __popc(rank_table[w0 + i].x);
-  int total;
-  blockExclusiveScan(n, &total, warp_sums);
-  if (threadIdx.x == 0) chunk_count[blockIdx.x] = total;
-}
-
-// In-place exclusive scan of `n` ints by one block; writes the grand total.
-__global__ void __launch_bounds__(1024)
-scanSingleBlockKernel(int32_t *data, int n, int32_t *total_out) {
-  __shared__ int warp_sums[33];
-  int running = 0;
-  for (int start = 0; start < n; start += blockDim.x) {
-    const int i = start + threadIdx.x;
-    const int v = i < n ? data[i] : 0;
-    int total;
-    const int excl = blockExclusiveScan(v, &total, warp_sums);
-    if (i < n) data[i] = running + excl;
-    running += total;
+// Exclusive prefix of `mine` over the units before `unit` by decoupled look-back
+// over one-word descriptors; called by one whole warp, every lane gets the result.
+// The unit's own aggregate is published first and its inclusive prefix last.
+// Returns -1 when a wait ran out (decided by the whole warp).
+__device__ __forceinline__ int lookBackOneWord(uint32_t *desc, int unit, int mine) {
+  const int lane = threadIdx.x & 31;
+  volatile uint32_t *state = desc;
+  int before = 0;
+  if (unit > 0) {
+    if (lane == 0) state[unit] = kFlagAggregate | (uint32_t)mine;
+    int pos = unit - 1;  // the window covers units pos, pos-1, ..., pos-31
+    const long long t0 = clock64();
+    for (;;) {
+      const int idx = pos - lane;
+      uint32_t w = kFlagPrefix;  // before unit 0: prefix 0
+      if (idx >= 0) w = state[idx];
+      const unsigned prefix_lanes = __ballot_sync(0xffffffffu, (w >> 30) == 2u);
+      const int first = prefix_lanes ? __ffs(prefix_lanes) - 1 : 31;
+      const unsigned needed = first == 31 ? 0xffffffffu : ((2u << first) - 1u);
+      const unsigned empty_lanes = __ballot_sync(0xffffffffu, (w >> 30) == 0u);
+      if (empty_lanes & needed) {  // a unit in the window has not published yet
+        const bool late = clock64() - t0 > kLookBackCycles;
+        if (__any_sync(0xffffffffu, late)) return -1;
+        continue;
+      }
+      before += warpSum(lane <= first ? (int)(w & kValueMask) : 0);
+      if (prefix_lanes) break;
+      pos -= 32;
+    }
   }
-  if (threadIdx.x == 0) *total_out = running;
+  if (lane == 0) state[unit] = kFlagPrefix | (uint32_t)(before + mine);
+  return before;
 }
 
-// Gives every occupancy word its exclusive rank; with DECODE also writes the
-// coordinates of the active cells, in ascending linear order, to out_indices.
+// One pass over the occupancy words: chunk c = words [c*W, (c+1)*W), 8 words per
+// thread.  Counts the chunk's bits, gets the count of all earlier chunks by
+// look-back (chunks are handed out by ticket, so every chunk waited for is already
+// running), stores each word's exclusive rank next to its bits and, with DECODE,
+// writes the coordinates of the chunk's active cells to out_indices in ascending
+// linear order.  The last chunk leaves the total in status[kStatusActive].
+constexpr int kRankWordsPerThread = 8;
+static_assert(kRankChunkWords == 256 * kRankWordsPerThread, "256 threads per chunk");
+
 template <bool DECODE>
 __global__ void __launch_bounds__(256)
-rankKernel(PairsGeometry g, uint2 *rank_table, int64_t words, const int32_t *__restrict__ chunk_offset,
-           int4 *out_indices, int64_t out_rows, int32_t *status) {
+rankScanKernel(PairsGeometry g, uint2 *rank_table, int64_t words, int chunks, uint32_t *chunk_desc,
+               int4 *out_indices, int64_t out_rows, ErrorSink sink) {
   __shared__ int warp_sums[33];
-  const int64_t w0 = (int64_t)blockIdx.x * kRankChunkWords + threadIdx.x * 4;
-  uint32_t bits[4];
+  __shared__ int chunk_s, before_s;
+  if (threadIdx.x == 0) chunk_s = atomicAdd(sink.status + kStatusChunkTicket, 1);
+  __syncthreads();
+  const int chunk = chunk_s;
+  const int64_t w0 = (int64_t)chunk * kRankChunkWords + threadIdx.x * kRankWordsPerThread;
+  uint32_t bits[kRankWordsPerThread];
   int n = 0;
+  if (w0 + kRankWordsPerThread <= words) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(rank_table + w0);  // two {bits, rank} entries per load
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    bits[i] = (w0 + i < words) ? rank_table[w0 + i].x : 0u;
-    n += __popc(bits[i]);
+    for (int i = 0; i < kRankWordsPerThread / 2; ++i) {
+      const uint4 v = src[i];
+      bits[2 * i] = v.x;
+      bits[2 * i + 1] = v.z;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kRankWordsPerThread; ++i) bits[i] = (w0 + i < words) ? rank_table[w0 + i].x : 0u;
   }
+#pragma unroll
+  for (int i = 0; i < kRankWordsPerThread; ++i) n += __popc(bits[i]);
   int total;
-  int rank = blockExclusiveScan(n, &total, warp_sums) + chunk_offset[blockIdx.x];
+  const int excl = blockExclusiveScan(n, &total, warp_sums);
+  if (threadIdx.x < 32) {
+    const int before = lookBackOneWord(chunk_desc, chunk, total);
+    if (threadIdx.x == 0) {
+      before_s = before < 0 ? 0 : before;
+      if (before < 0) raiseError(sink, kPairsErrLookBack);
+      if (chunk == chunks - 1) sink.status[kStatusActive] = before_s + total;
+    }
+  }
+  __syncthreads();
+  int rank = excl + before_s;
   const int hw = g.out_space[1] * g.out_space[2];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < kRankWordsPerThread; ++i) {
     if (w0 + i >= words) break;
     rank_table[w0 + i].y = (uint32_t)rank;
     if (!DECODE) {
@@ -282,14 +351,14 @@ rankKernel(PairsGeometry g, uint2 *rank_table, int64_t words, const int32_t *__r
       if (rank < out_rows) {
         out_indices[rank] = o;
       } else {
-        atomicOr(status, kPairsErrOutIndicesSmall);
+        raiseError(sink, kPairsErrOutIndicesSmall);
       }
       ++rank;
     }
   }
 }
 
-// submanifold rank + perm: perm[rank of voxel j's cell] = j (largest j wins)
+// submanifold rank + perm: perm[rank of voxel j's cell] = j + 1 (largest j wins; 0 = none)
 __global__ void __launch_bounds__(256)
 permKernel(PairsGeometry g, const int4 *__restrict__ indices, const uint2 *__restrict__ rank_table,
            int32_t *perm) {
@@ -299,27 +368,19 @@ permKernel(PairsGeometry g, const int4 *__restrict__ indices, const uint2 *__res
   if (!rowInRange(c, g)) return;
   const uint32_t lin = inputLinear(c, g);
   const uint2 e = __ldg(rank_table + (lin >> 5));
-  atomicMax(&perm[e.y + __popc(e.x & ((1u << (lin & 31)) - 1u))], j);
-}
-
-// out_indices rows from the active count on are -1 (the CPU path initialises
-// the whole tensor to -1 before filling it).
-__global__ void __launch_bounds__(256)
-fillInactiveRowsKernel(int4 *out_indices, int64_t out_rows, const int32_t *n_active) {
-  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (r < out_rows && r >= *n_active) out_indices[r] = make_int4(-1, -1, -1, -1);
+  atomicMax(&perm[e.y + __popc(e.x & ((1u << (lin & 31)) - 1u))], j + 1);
 }
 
 // ------------------------------------------------------------------- lookups
 
 template <int LOOKUP>
-__device__ __forceinline__ int lookupOutput(const LookupTables &t, uint32_t lin, int32_t *status) {
-  if (LOOKUP == kLookupHash) return hashLookup(t.slots, t.mask, lin, status);
+__device__ __forceinline__ int lookupOutput(const LookupTables &t, uint32_t lin, const ErrorSink &sink) {
+  if (LOOKUP == kLookupHash) return hashLookup(t.slots, t.mask, lin, sink);
   const uint2 e = __ldg(t.rank_table + (lin >> 5));
   const uint32_t bit = lin & 31;
   if (LOOKUP == kLookupRank) return (int)(e.y + __popc(e.x & ((1u << bit) - 1u)));  // always occupied
   if (!((e.x >> bit) & 1u)) return -1;
-  return __ldg(t.perm + e.y + __popc(e.x & ((1u << bit) - 1u)));
+  return __ldg(t.perm + e.y + __popc(e.x & ((1u << bit) - 1u))) - 1;
 }
 
 // t / stride when the division is exact (t >= 0): shift for power-of-two strides.
@@ -335,7 +396,7 @@ __device__ __forceinline__ bool exactDivide(int t, int stride, int shift, int *q
 // Walks the K offsets of one voxel; emit(k, output id or -1) is called for every k in order.
 template <int LOOKUP, typename Emit>
 __device__ __forceinline__ void walkOffsets(const PairsGeometry &g, const LookupTables &tables, const int4 c,
-                                            bool row_ok, int32_t *status, Emit emit) {
+                                            bool row_ok, const ErrorSink &sink, Emit emit) {
   const int base_b = c.x * g.out_vol;
   int k = 0;
   for (int kd = 0; kd < g.ks[0]; ++kd) {
@@ -352,8 +413,43 @@ __device__ __forceinline__ void walkOffsets(const PairsGeometry &g, const Lookup
         int ow;
         const bool ok = exactDivide(tw, g.stride[2], g.stride_shift[2], &ow) && vh && tw >= 0 && ow < g.out_space[2];
         int v = -1;
-        if (ok) v = lookupOutput<LOOKUP>(tables, (uint32_t)(base_row + ow), status);
+        if (ok) v = lookupOutput<LOOKUP>(tables, (uint32_t)(base_row + ow), sink);
         emit(k, v);
+      }
+    }
+  }
+}
+
+// The same walk for a 3x3x3 kernel with dilation 1 and stride SHIFT+1 in {1, 2},
+// fully unrolled: the index arithmetic is hoisted per dimension, the 27 lookups
+// are independent loads, and the results stay in registers.
+template <int LOOKUP, int SHIFT>
+__device__ __forceinline__ void walkCube3(const PairsGeometry &g, const LookupTables &tables, const int4 c,
+                                          bool row_ok, const ErrorSink &sink, int (&v)[27]) {
+  bool ok_d[3], ok_h[3], ok_w[3];
+  int o_d[3], o_h[3], o_w[3];
+#pragma unroll
+  for (int kk = 0; kk < 3; ++kk) {
+    const int td = c.y + g.pad[0] - kk, th = c.z + g.pad[1] - kk, tw = c.w + g.pad[2] - kk;
+    o_d[kk] = td >> SHIFT;
+    o_h[kk] = th >> SHIFT;
+    o_w[kk] = tw >> SHIFT;
+    ok_d[kk] = row_ok && td >= 0 && (td & SHIFT) == 0 && o_d[kk] < g.out_space[0];
+    ok_h[kk] = th >= 0 && (th & SHIFT) == 0 && o_h[kk] < g.out_space[1];
+    ok_w[kk] = tw >= 0 && (tw & SHIFT) == 0 && o_w[kk] < g.out_space[2];
+  }
+  const int base_b = c.x * g.out_vol;
+#pragma unroll
+  for (int kd = 0; kd < 3; ++kd) {
+#pragma unroll
+    for (int kh = 0; kh < 3; ++kh) {
+      const bool ok_dh = ok_d[kd] && ok_h[kh];
+      const int base_row = base_b + (o_d[kd] * g.out_space[1] + o_h[kh]) * g.out_space[2];
+#pragma unroll
+      for (int kw = 0; kw < 3; ++kw) {
+        int r = -1;
+        if (ok_dh && ok_w[kw]) r = lookupOutput<LOOKUP>(tables, (uint32_t)(base_row + o_w[kw]), sink);
+        v[(kd * 3 + kh) * 3 + kw] = r;
       }
     }
   }
@@ -361,106 +457,251 @@ __device__ __forceinline__ void walkOffsets(const PairsGeometry &g, const Lookup
 
 // ------------------------------------------------------------ single pass
 
-constexpr uint32_t kStateAggregate = 1u << 30;  // the tile's own count is known
-constexpr uint32_t kStatePrefix = 2u << 30;     // the inclusive count up to this tile is known
-constexpr uint32_t kStateValue = (1u << 30) - 1u;
 constexpr int kTileWarps = kPairsTile / 32;
 
-// One block per tile of 256 voxels (tiles are handed out by ticket so that every
-// tile a block waits for is already running or done).
-//   1. probe: match[k][thread] and per-warp counts in shared memory
-//   2. per offset k (warps share the offsets): publish the tile's count, look
-//      back over earlier tiles until a published prefix is met, publish the
-//      inclusive prefix; the last tile writes indice_num
-//   3. write the tile's pairs at offset + rank inside the tile, ascending j
-template <int LOOKUP>
+enum WalkKind { kWalkGeneric = 0, kWalkCube3Stride1 = 1, kWalkCube3Stride2 = 2 };
+
+struct PairListScratch {
+  uint32_t *tile_desc;   // [tiles][32]   aggregate of a tile per offset
+  uint32_t *group_desc;  // [groups][32]  aggregate / inclusive prefix of a group of 32 tiles per offset
+  uint32_t *group_sum;   // [groups][32]  running sum of the group's tile aggregates
+  int32_t *group_done;   // [groups]      tiles of the group that have published
+};
+
+// Exclusive prefix of this tile's per-offset counts (lane = offset k), by one warp.
+//   1. publish the tile's aggregate; add it to the group's running sum; the tile
+//      that completes its group publishes the group's aggregate
+//   2. sum the aggregates of the earlier tiles of the own group
+//   3. walk back over the group descriptors until an inclusive prefix is met, and
+//      publish the inclusive prefix of the preceding group for those that follow
+// Tiles are handed out by ticket, so everything waited for is running or done,
+// and nothing that is waited for waits for this tile.  Returns false when a wait
+// ran out; every exit is taken by the whole warp.
+__device__ __forceinline__ bool tilePrefix(const PairListScratch &s, int tile, int tiles, int mine, int *before_out) {
+  constexpr unsigned kFull = 0xffffffffu;
+  const int lane = threadIdx.x & 31;
+  const int group = tile / kGroupTiles, first_tile = group * kGroupTiles;
+  const int group_size = min(kGroupTiles, tiles - first_tile);
+  volatile uint32_t *tile_desc = s.tile_desc;
+  volatile uint32_t *group_desc = s.group_desc;
+  tile_desc[(size_t)tile * kDescWords + lane] = kFlagAggregate | (uint32_t)mine;
+  atomicAdd(&s.group_sum[(size_t)group * kDescWords + lane], (uint32_t)mine);
+  __threadfence();
+  __syncwarp();  // every lane's addition is ordered before lane 0's arrival count
+  int arrived = 0;
+  if (lane == 0) arrived = atomicAdd(&s.group_done[group], 1);
+  arrived = __shfl_sync(kFull, arrived, 0);
+  if (arrived == group_size - 1) {  // every tile of the group has added its counts
+    __threadfence();
+    const uint32_t sum = atomicAdd(&s.group_sum[(size_t)group * kDescWords + lane], 0u);
+    group_desc[(size_t)group * kDescWords + lane] = kFlagAggregate | sum;
+  }
+  const long long t0 = clock64();
+  int before = 0;
+  // earlier tiles of the own group, four descriptors in flight at a time
+  for (int t = first_tile; t < tile; t += 4) {
+    uint32_t w[4];
+    for (;;) {
+      bool missing = false;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        w[u] = 1u << 30;  // past the own tile: an aggregate of zero
+        if (t + u < tile) w[u] = tile_desc[(size_t)(t + u) * kDescWords + lane];
+        missing |= (w[u] >> 30) == 0u;
+      }
+      if (!__any_sync(kFull, missing)) break;
+      if (__any_sync(kFull, clock64() - t0 > kLookBackCycles)) return false;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) before += (int)(w[u] & kValueMask);
+  }
+  // groups before the own one; a lane is done when it has met an inclusive prefix
+  int groups_before = 0;
+  bool open = group > 0;
+  for (int gg = group - 1; gg >= 0; --gg) {
+    if (!__any_sync(kFull, open)) break;
+    uint32_t w = 0u;
+    for (;;) {
+      if (open) w = group_desc[(size_t)gg * kDescWords + lane];
+      if (!__any_sync(kFull, open && (w >> 30) == 0u)) break;
+      if (__any_sync(kFull, clock64() - t0 > kLookBackCycles)) return false;
+    }
+    if (open) {
+      groups_before += (int)(w & kValueMask);
+      if ((w >> 30) == 2u) open = false;
+    }
+  }
+  if (group > 0) group_desc[(size_t)(group - 1) * kDescWords + lane] = kFlagPrefix | (uint32_t)groups_before;
+  *before_out = before + groups_before;
+  return true;
+}
+
+// One block per tile of 256 voxels.
+//   A. probe: the tile's K x 256 matches (registers for the unrolled 3x3x3 walks,
+//      shared memory otherwise) and per-warp counts; submanifold mode also copies
+//      the tile's rows of indices to out_indices, and with `table` the matches are
+//      written to table[K-1-k][j] (the neighbour table of a submanifold rulebook
+//      with centred padding: the input row feeding output row j at offset K-1-k),
+//      -1 in the padding rows
+//   B. warp 0: the tile's write offsets for all K offsets (tilePrefix); the last
+//      tile writes indice_num
+//   C. the tile's pairs, ascending j, at offset + rank inside the tile
+template <int LOOKUP, int WALK>
 __global__ void __launch_bounds__(kPairsTile)
-probeWriteKernel(PairsGeometry g, const int4 *__restrict__ indices, LookupTables tables, uint32_t *tile_state,
-                 int tiles, int32_t *__restrict__ indice_pairs, int32_t *__restrict__ indice_num,
-                 int32_t *status) {
-  extern __shared__ int smem_i[];
-  int *match_s = smem_i;                            // [K][256]
-  int *warp_count_s = match_s + g.K * kPairsTile;    // [K][8]
-  int *offset_s = warp_count_s + g.K * kTileWarps;   // [K]
+pairListsKernel(PairsGeometry g, const int4 *__restrict__ indices, LookupTables tables, PairListScratch scratch,
+                int tiles, int32_t *__restrict__ indice_pairs, int32_t *__restrict__ indice_num,
+                int32_t *__restrict__ counts, int4 *__restrict__ out_indices, int64_t out_rows,
+                int32_t *__restrict__ table, int64_t table_stride, ErrorSink sink) {
+  extern __shared__ int match_s[];  // generic walk: [K][256]
+  __shared__ int warp_base_s[kDescWords][kTileWarps];
+  __shared__ int offset_s[kDescWords];
   __shared__ int tile_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) tile_s = atomicAdd(status + 2, 1);
+  if (threadIdx.x == 0) tile_s = atomicAdd(sink.status + kStatusTileTicket, 1);
   __syncthreads();
   const int tile = tile_s;
   const int j = tile * kPairsTile + threadIdx.x;
   const bool live = j < g.L;
   int4 c = make_int4(0, 0, 0, 0);
   if (live) c = indices[j];
-  walkOffsets<LOOKUP>(g, tables, c, live && rowInRange(c, g), status, [&](int k, int v) {
-    match_s[k * kPairsTile + threadIdx.x] = v;
-    const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
-    if (lane == 0) warp_count_s[k * kTileWarps + warp] = __popc(hits);
-  });
-  __syncthreads();
+  const bool row_ok = live && rowInRange(c, g);
+  if (g.sub_m && live && j < out_rows) out_indices[j] = c;
 
-  for (int k = warp; k < g.K; k += kTileWarps) {
-    const int mine = warpSum(lane < kTileWarps ? warp_count_s[k * kTileWarps + lane] : 0);
-    volatile uint32_t *state = tile_state + (size_t)k * tiles;
-    int before = 0;
-    if (tile > 0) {
-      if (lane == 0) state[tile] = kStateAggregate | (uint32_t)mine;
-      int pos = tile - 1;  // the window covers tiles pos, pos-1, ..., pos-31
-      const long long t0 = clock64();
-      for (;;) {
-        const int idx = pos - lane;
-        uint32_t w = 2u << 30;  // before tile 0: prefix 0
-        if (idx >= 0) w = state[idx];
-        const unsigned prefix_lanes = __ballot_sync(0xffffffffu, (w >> 30) == 2u);
-        const int first = prefix_lanes ? __ffs(prefix_lanes) - 1 : 31;
-        const unsigned needed = first == 31 ? 0xffffffffu : ((2u << first) - 1u);
-        const unsigned empty_lanes = __ballot_sync(0xffffffffu, (w >> 30) == 0u);
-        if (empty_lanes & needed) {  // a tile in the window has not published yet
-          if (clock64() - t0 > kLookBackCycles) {
-            if (lane == 0) atomicOr(status, kPairsErrLookBack);
-            break;
-          }
-          continue;
-        }
-        before += warpSum(lane <= first ? (int)(w & kStateValue) : 0);
-        if (prefix_lanes) break;
-        pos -= 32;
-      }
+  int v[27];
+  if (WALK == kWalkGeneric) {
+    walkOffsets<LOOKUP>(g, tables, c, row_ok, sink, [&](int k, int r) {
+      match_s[k * kPairsTile + threadIdx.x] = r;
+      const unsigned hits = __ballot_sync(0xffffffffu, r >= 0);
+      if (lane == 0) warp_base_s[k][warp] = __popc(hits);
+    });
+  } else {
+    walkCube3<LOOKUP, WALK == kWalkCube3Stride2 ? 1 : 0>(g, tables, c, row_ok, sink, v);
+#pragma unroll
+    for (int k = 0; k < 27; ++k) {
+      const unsigned hits = __ballot_sync(0xffffffffu, v[k] >= 0);
+      if (lane == 0) warp_base_s[k][warp] = __popc(hits);
     }
-    if (lane == 0) {
-      state[tile] = kStatePrefix | (uint32_t)(before + mine);
-      offset_s[k] = before;
-      if (tile == tiles - 1) indice_num[k] = before + mine;
+  }
+  if (table != nullptr) {
+    // rows [L, table_stride) are padding; the last tile also covers the 256 rows past its own
+    const bool second = tile == tiles - 1 && (int64_t)j + kPairsTile < table_stride;
+    if (WALK == kWalkGeneric) {
+      for (int k = 0; k < g.K; ++k) {
+        int32_t *row = table + (size_t)(g.K - 1 - k) * table_stride;
+        if (j < table_stride) row[j] = match_s[k * kPairsTile + threadIdx.x];
+        if (second) row[j + kPairsTile] = -1;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 27; ++k) {
+        int32_t *row = table + (size_t)(26 - k) * table_stride;
+        if (j < table_stride) row[j] = v[k];
+        if (second) row[j + kPairsTile] = -1;
+      }
     }
   }
   __syncthreads();
 
-  for (int k = 0; k < g.K; ++k) {
-    const int v = match_s[k * kPairsTile + threadIdx.x];
-    const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
-    if (v >= 0) {
-      int p = offset_s[k] + __popc(hits & ((1u << lane) - 1u));
-      for (int w = 0; w < warp; ++w) p += warp_count_s[k * kTileWarps + w];
-      int32_t *in_row = indice_pairs + (size_t)k * 2 * g.L;
-      in_row[p] = j;
-      in_row[g.L + p] = v;
+  if (warp == 0) {
+    int mine = 0;
+    if (lane < g.K) {
+#pragma unroll
+      for (int w = 0; w < kTileWarps; ++w) {
+        const int n = warp_base_s[lane][w];
+        warp_base_s[lane][w] = mine;  // exclusive count of the warps before w
+        mine += n;
+      }
+    }
+    int before = 0;
+    if (!tilePrefix(scratch, tile, tiles, mine, &before)) {
+      if (lane == 0) raiseError(sink, kPairsErrLookBack);
+      before = 0;
+    }
+    offset_s[lane] = before;
+    if (tile == tiles - 1 && lane < g.K) {
+      // indice_num may be pinned host memory (the caller wants the counts on the host
+      // anyway); later kernels read the copy that stays in the workspace
+      indice_num[lane] = before + mine;
+      counts[lane] = before + mine;
+    }
+  }
+  __syncthreads();
+
+  const unsigned lower = (1u << lane) - 1u;
+  if (WALK == kWalkGeneric) {
+    for (int k = 0; k < g.K; ++k) {
+      const int r = match_s[k * kPairsTile + threadIdx.x];
+      const unsigned hits = __ballot_sync(0xffffffffu, r >= 0);
+      if (r >= 0) {
+        const int p = offset_s[k] + warp_base_s[k][warp] + __popc(hits & lower);
+        int32_t *in_row = indice_pairs + (size_t)k * 2 * g.L;
+        in_row[p] = j;
+        in_row[g.L + p] = r;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 27; ++k) {
+      const unsigned hits = __ballot_sync(0xffffffffu, v[k] >= 0);
+      if (v[k] >= 0) {
+        const int p = offset_s[k] + warp_base_s[k][warp] + __popc(hits & lower);
+        int32_t *in_row = indice_pairs + (size_t)k * 2 * g.L;
+        in_row[p] = j;
+        in_row[g.L + p] = v[k];
+      }
     }
   }
 }
 
-// -1 from position indice_num[k] on, both rows of every offset.
+// Last kernel of every rulebook.
+//   blockIdx.y < K: -1 from position indice_num[k] on, both rows of offset k
+//     (nothing to do when the two-pass compaction already wrote its tails)
+//   blockIdx.y == K: out_indices rows from the active count (default mode) or
+//     from L (submanifold mode) on are -1, as the CPU path leaves them; block
+//     (0, K) also hands {error bits, active count} to the host.
+// A thread fills four consecutive words with one 16-byte store: positions are
+// grouped in fours that start where the row's address is 16-byte aligned.
+constexpr int kFinishSpan = 256 * 16;  // positions per block
+
 __global__ void __launch_bounds__(256)
-fillTailsKernel(int L, const int32_t *__restrict__ indice_num, int32_t *__restrict__ indice_pairs) {
+finishPairsKernel(int L, int K, int sub_m, int write_tails, const int32_t *__restrict__ counts,
+                  int32_t *__restrict__ indice_pairs, int4 *__restrict__ out_indices, int64_t out_rows,
+                  const int32_t *__restrict__ status, volatile int32_t *status_host) {
   const int k = blockIdx.y;
-  const int first = indice_num[k];
-  const int base = blockIdx.x * 2048;
-  if (base + 2048 <= first) return;
-  int32_t *in_row = indice_pairs + (size_t)k * 2 * L;
+  if (k == K) {
+    const int64_t first = sub_m ? (int64_t)L : (int64_t)status[kStatusActive];
+    for (int64_t r = first + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < out_rows;
+         r += (int64_t)gridDim.x * blockDim.x)
+      out_indices[r] = make_int4(-1, -1, -1, -1);
+    if (blockIdx.x == 0 && threadIdx.x == 0 && status_host != nullptr) {
+      const int32_t bits = status[kStatusErrors];
+      status_host[0] = bits;
+      status_host[1] = sub_m ? L : status[kStatusActive];
+      if (bits) status_host[2] |= bits;  // sticky: reported and cleared by the next entry point on the handle
+      __threadfence_system();
+    }
+    return;
+  }
+  if (!write_tails) return;
+  const int first = counts[k];
+  const int base = blockIdx.x * kFinishSpan;
+  if (base + kFinishSpan <= first) return;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int p = base + i * 256 + threadIdx.x;
-    if (p >= first && p < L) {
-      in_row[p] = -1;
-      in_row[L + p] = -1;
+  for (int row = 0; row < 2; ++row) {
+    int32_t *dst = indice_pairs + ((size_t)k * 2 + row) * L;
+    const int skew = (int)((reinterpret_cast<size_t>(dst) >> 2) & 3);  // words past a 16-byte boundary
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int p0 = base + (i * 256 + threadIdx.x) * 4 - skew;  // dst + p0 is 16-byte aligned
+      if (p0 >= first && p0 >= 0 && p0 + 3 < L) {
+        *reinterpret_cast<int4 *>(dst + p0) = make_int4(-1, -1, -1, -1);
+      } else {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int p = p0 + u;
+          if (p >= first && p >= 0 && p < L) dst[p] = -1;
+        }
+      }
     }
   }
 }
@@ -471,7 +712,8 @@ fillTailsKernel(int L, const int32_t *__restrict__ indice_num, int32_t *__restri
 template <int LOOKUP>
 __global__ void __launch_bounds__(kPairsTile)
 probeCountKernel(PairsGeometry g, const int4 *__restrict__ indices, LookupTables tables,
-                 int32_t *__restrict__ match, int32_t *__restrict__ tile_count, int tiles, int32_t *status) {
+                 int32_t *__restrict__ match, int32_t *__restrict__ tile_count, int tiles,
+                 int4 *__restrict__ out_indices, int64_t out_rows, ErrorSink sink) {
   // match rows are tiles*256 entries long: every thread of every tile stores, and
   // the compaction kernel can read them 16 bytes at a time
   extern __shared__ int s_count[];  // [K]
@@ -481,10 +723,11 @@ probeCountKernel(PairsGeometry g, const int4 *__restrict__ indices, LookupTables
   const bool live = j < g.L;
   int4 c = make_int4(0, 0, 0, 0);
   if (live) c = indices[j];
+  if (g.sub_m && live && j < out_rows) out_indices[j] = c;
   const int lane = threadIdx.x & 31;
   int32_t *match_col = match + j;
   const size_t row_stride = (size_t)tiles * kPairsTile;
-  walkOffsets<LOOKUP>(g, tables, c, live && rowInRange(c, g), status, [&](int k, int v) {
+  walkOffsets<LOOKUP>(g, tables, c, live && rowInRange(c, g), sink, [&](int k, int v) {
     *match_col = v;
     match_col += row_stride;
     const unsigned m = __ballot_sync(0xffffffffu, v >= 0);
@@ -511,8 +754,6 @@ scanTilesKernel(int32_t *tile_count, int tiles, int32_t *indice_num, int32_t *co
     running += total;
   }
   if (threadIdx.x == 0) {
-    // The caller's indice_num may be pinned host memory (it wants the counts on the
-    // host anyway); later kernels read the copy that stays in the workspace.
     indice_num[blockIdx.x] = running;
     counts[blockIdx.x] = running;
   }
@@ -590,12 +831,13 @@ std::string envChoice(const char *name) {
 
 PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g) {
   // MLUOP_B200_PAIRS_LOOKUP=hash|rank overrides the automatic choice of the
-  // submanifold lookup structure; MLUOP_B200_PAIRS_PATH=fused selects the
-  // single-pass pair-list path (both are cross-checked by the tests).
+  // submanifold lookup structure; MLUOP_B200_PAIRS_PATH=twopass selects the
+  // staged pair-list path for every kernel volume (both are cross-checked by the tests).
   static const std::string lookup_env = envChoice("MLUOP_B200_PAIRS_LOOKUP");
   static const std::string path_env = envChoice("MLUOP_B200_PAIRS_PATH");
   PairsWorkspacePlan p{};
   p.tiles = (g.L + kPairsTile - 1) / kPairsTile;
+  p.groups = (p.tiles + kGroupTiles - 1) / kGroupTiles;
   const int64_t cells = (int64_t)g.batch * g.out_vol;  // submanifold: input space == output space
   if (!g.sub_m) {
     p.lookup = kLookupRank;
@@ -606,28 +848,6 @@ PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g) {
   } else {
     p.lookup = cells <= kDenseCellsPerVoxel * (int64_t)g.L ? kLookupRankPerm : kLookupHash;
   }
-  // The single-pass path is opt-in: on B200 about a thousand tiles finish their
-  // probes in lockstep, so the look-back chain (32 tiles per L2 round trip, per
-  // offset) costs more than the staged matches of the two-pass path save.
-  p.fused = (g.K <= kFusedMaxOffsets && path_env == "fused") ? 1 : 0;
-  size_t off = 0;
-  p.status = off;
-  off = alignUp(off + 64 * sizeof(int32_t), 256);
-  p.counts = off;
-  off = alignUp(off + (size_t)g.K * sizeof(int32_t), 256);
-  p.tile_state = off;
-  p.match = off;
-  p.tile_count = off;
-  if (p.fused) {
-    off = alignUp(off + (size_t)g.K * p.tiles * sizeof(uint32_t), 256);
-  } else {
-    off = alignUp(off + (size_t)g.K * p.tiles * kPairsTile * sizeof(int32_t), 256);
-    p.tile_count = off;
-    off = alignUp(off + (size_t)g.K * p.tiles * sizeof(int32_t), 256);
-  }
-  p.table = off;
-  p.chunk_count = off;
-  p.perm = off;
   // Test hook: MLUOP_B200_TEST_HASH_CAPACITY=<n> makes submanifold rulebooks use the hash
   // table with at most n slots (rounded down to a power of two, at least 64), so that the
   // "table full" error path can be exercised: probes are bounded by the capacity, the
@@ -637,6 +857,28 @@ PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g) {
     if (const char *v = std::getenv("MLUOP_B200_TEST_HASH_CAPACITY")) cap_limit = (uint32_t)std::strtoul(v, nullptr, 10);
     if (cap_limit) p.lookup = kLookupHash;
   }
+  p.fused = (g.K <= kFusedMaxOffsets && path_env != "twopass") ? 1 : 0;
+
+  // scratch that must start at zero, cleared by one memset: [0, zero_end)
+  size_t off = 0;
+  p.status = off;
+  off = alignUp(off + 64 * sizeof(int32_t), 256);
+  p.counts = off;
+  off = alignUp(off + (size_t)g.K * sizeof(int32_t), 256);
+  p.tile_desc = p.group_desc = p.group_sum = p.group_done = off;
+  if (p.fused) {
+    p.tile_desc = off;
+    off = alignUp(off + (size_t)p.tiles * kDescWords * sizeof(uint32_t), 256);
+    p.group_desc = off;
+    off = alignUp(off + (size_t)p.groups * kDescWords * sizeof(uint32_t), 256);
+    p.group_sum = off;
+    off = alignUp(off + (size_t)p.groups * kDescWords * sizeof(uint32_t), 256);
+    p.group_done = off;
+    off = alignUp(off + (size_t)p.groups * sizeof(int32_t), 256);
+  }
+  p.table = off;
+  p.chunk_desc = off;
+  p.perm = off;
   if (p.lookup == kLookupHash) {
     uint32_t cap = 64;
     while ((uint64_t)cap < 2ull * (uint64_t)g.L && (cap_limit == 0 || cap * 2 <= cap_limit)) cap <<= 1;
@@ -646,75 +888,102 @@ PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g) {
     p.rank_words = (cells + 31) / 32;
     p.rank_chunks = (int32_t)((p.rank_words + kRankChunkWords - 1) / kRankChunkWords);
     off = alignUp(off + (size_t)p.rank_words * sizeof(uint2), 256);
-    p.chunk_count = off;
-    off = alignUp(off + (size_t)p.rank_chunks * sizeof(int32_t), 256);
+    p.chunk_desc = off;
+    off = alignUp(off + (size_t)p.rank_chunks * sizeof(uint32_t), 256);
     if (p.lookup == kLookupRankPerm) {
       p.perm = off;
       off = alignUp(off + (size_t)g.L * sizeof(int32_t), 256);
     }
   }
+  p.zero_end = off;
+  // scratch that is fully written before it is read
+  p.match = p.tile_count = off;
+  if (!p.fused) {
+    off = alignUp(off + (size_t)g.K * p.tiles * kPairsTile * sizeof(int32_t), 256);
+    p.tile_count = off;
+    off = alignUp(off + (size_t)g.K * p.tiles * sizeof(int32_t), 256);
+  }
   p.total = off + 256;  // slack to align the caller's pointer
   return p;
 }
 
+int64_t pairsTableStride(int64_t rows) { return (rows + kPairsTablePadRows - 1) / kPairsTablePadRows * kPairsTablePadRows; }
+
+bool pairsCanEmitTable(const PairsGeometry &g, const PairsWorkspacePlan &plan) {
+  if (!g.sub_m || !plan.fused) return false;
+  for (int i = 0; i < 3; ++i)
+    if (g.stride[i] != 1 || g.dil[i] != 1 || (g.ks[i] & 1) == 0 || g.pad[i] != g.ks[i] / 2) return false;
+  return true;
+}
+
 namespace {
 
+struct PairListArgs {
+  const int4 *rows;
+  LookupTables tables;
+  PairListScratch scratch;
+  int32_t *indice_pairs, *indice_num, *counts;
+  int4 *out_indices;
+  int64_t out_rows;
+  int32_t *table;
+  int64_t table_stride;
+  ErrorSink sink;
+};
+
+template <int LOOKUP, int WALK>
+void launchFused(const PairsGeometry &g, const PairsWorkspacePlan &plan, const PairListArgs &a,
+                 cudaStream_t stream) {
+  static const char *names[3][3] = {
+      {"pairListsKernel<rank>", "pairListsKernel<rank,3x3x3 s1>", "pairListsKernel<rank,3x3x3 s2>"},
+      {"pairListsKernel<hash>", "pairListsKernel<hash,3x3x3 s1>", "pairListsKernel<hash,3x3x3 s2>"},
+      {"pairListsKernel<rank+perm>", "pairListsKernel<rank+perm,3x3x3 s1>", "pairListsKernel<rank+perm,3x3x3 s2>"}};
+  const size_t smem = WALK == kWalkGeneric ? (size_t)g.K * kPairsTile * sizeof(int) : 0;
+  auto kernel = pairListsKernel<LOOKUP, WALK>;
+  // per voxel its coordinates (submanifold: and their copy in out_indices); the pairs
+  // themselves are counted with the kernel that completes indice_pairs
+  trace::Scope t(names[LOOKUP][WALK], stream, 16.0 * g.L + (g.sub_m ? 16.0 * g.L : 0.0));
+  kernel<<<plan.tiles, kPairsTile, smem, stream>>>(g, a.rows, a.tables, a.scratch, plan.tiles, a.indice_pairs,
+                                                   a.indice_num, a.counts, a.out_indices, a.out_rows, a.table,
+                                                   a.table_stride, a.sink);
+}
+
 template <int LOOKUP>
-void launchPairLists(const PairsGeometry &g, const PairsWorkspacePlan &plan, const int4 *rows,
-                     const LookupTables &tables, char *base, int32_t *indice_pairs, int32_t *indice_num,
-                     int32_t *status, cudaStream_t stream) {
-  const int tiles = plan.tiles;
-  const double L = g.L, KL = (double)g.K * g.L;
-  static const char *names_fused[] = {"probeWriteKernel<rank>", "probeWriteKernel<hash>",
-                                      "probeWriteKernel<rank+perm>"};
-  static const char *names_count[] = {"probeCountKernel<rank>", "probeCountKernel<hash>",
-                                      "probeCountKernel<rank+perm>"};
+void launchPairLists(const PairsGeometry &g, const PairsWorkspacePlan &plan, const PairListArgs &a, char *base,
+                     cudaStream_t stream) {
   if (plan.fused) {
-    uint32_t *tile_state = reinterpret_cast<uint32_t *>(base + plan.tile_state);
-    {
-      trace::Scope t("memset:tile_state", stream, 4.0 * g.K * tiles);
-      cudaMemsetAsync(tile_state, 0, (size_t)g.K * tiles * sizeof(uint32_t), stream);
-    }
-    {
-      // per voxel: its coordinates; the matched pairs are written by this kernel
-      trace::Scope t(names_fused[LOOKUP], stream, 16.0 * L);
-      const size_t smem = (size_t)g.K * (kPairsTile + kTileWarps + 1) * sizeof(int);
-      probeWriteKernel<LOOKUP><<<tiles, kPairsTile, smem, stream>>>(g, rows, tables, tile_state, tiles,
-                                                                    indice_pairs, indice_num, status);
-    }
-    {
-      trace::Scope t("fillTailsKernel", stream, 8.0 * KL);
-      fillTailsKernel<<<dim3((unsigned)((g.L + 2047) / 2048), g.K), 256, 0, stream>>>(g.L, indice_num,
-                                                                                     indice_pairs);
+    const bool cube3 = g.ks[0] == 3 && g.ks[1] == 3 && g.ks[2] == 3 && g.dil[0] == 1 && g.dil[1] == 1 && g.dil[2] == 1;
+    const bool s1 = g.stride[0] == 1 && g.stride[1] == 1 && g.stride[2] == 1;
+    const bool s2 = g.stride[0] == 2 && g.stride[1] == 2 && g.stride[2] == 2;
+    if (cube3 && s1) {
+      launchFused<LOOKUP, kWalkCube3Stride1>(g, plan, a, stream);
+    } else if (cube3 && s2) {
+      launchFused<LOOKUP, kWalkCube3Stride2>(g, plan, a, stream);
+    } else {
+      launchFused<LOOKUP, kWalkGeneric>(g, plan, a, stream);
     }
     return;
   }
+  const int tiles = plan.tiles;
+  const double L = g.L, KL = (double)g.K * g.L;
+  static const char *names_count[] = {"probeCountKernel<rank>", "probeCountKernel<hash>",
+                                      "probeCountKernel<rank+perm>"};
   int32_t *match = reinterpret_cast<int32_t *>(base + plan.match);
   int32_t *tile_count = reinterpret_cast<int32_t *>(base + plan.tile_count);
-  int32_t *counts = reinterpret_cast<int32_t *>(base + plan.counts);
   {
     trace::Scope t(names_count[LOOKUP], stream, 16.0 * L + 4.0 * KL);
     probeCountKernel<LOOKUP><<<tiles, kPairsTile, (size_t)g.K * sizeof(int), stream>>>(
-        g, rows, tables, match, tile_count, tiles, status);
+        g, a.rows, a.tables, match, tile_count, tiles, a.out_indices, a.out_rows, a.sink);
   }
   {
     trace::Scope t("scanTilesKernel", stream, 8.0 * g.K * tiles);
-    scanTilesKernel<<<g.K, 1024, 0, stream>>>(tile_count, tiles, indice_num, counts);
+    scanTilesKernel<<<g.K, 1024, 0, stream>>>(tile_count, tiles, a.indice_num, a.counts);
   }
   {
     trace::Scope t("writePairsKernel", stream, 12.0 * KL);
     const unsigned segments = (unsigned)((tiles + kWriteSegTiles - 1) / kWriteSegTiles);
-    writePairsKernel<<<dim3(segments, g.K), kPairsTile, 0, stream>>>(g.L, match, tile_count, tiles, counts,
-                                                                    indice_pairs);
+    writePairsKernel<<<dim3(segments, g.K), kPairsTile, 0, stream>>>(g.L, match, tile_count, tiles, a.counts,
+                                                                    a.indice_pairs);
   }
-}
-
-__global__ void publishStatusKernel(const int32_t *__restrict__ status, volatile int32_t *status_host) {
-  const int32_t bits = status[0];
-  status_host[0] = bits;
-  status_host[1] = status[1];
-  if (bits) status_host[2] |= bits;  // sticky: reported and cleared by the next entry point on the handle
-  __threadfence_system();
 }
 
 }  // namespace
@@ -722,40 +991,46 @@ __global__ void publishStatusKernel(const int32_t *__restrict__ status, volatile
 cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePlan &plan,
                                  const int32_t *indices, void *workspace, int32_t *indice_pairs,
                                  int32_t *out_indices, int64_t out_rows, int32_t *indice_num,
-                                 int32_t *status_host, cudaStream_t stream) {
+                                 int32_t *status_host, int32_t *neighbour_table, cudaStream_t stream) {
   char *base = reinterpret_cast<char *>(alignUp(reinterpret_cast<size_t>(workspace), 256));
   int32_t *status = reinterpret_cast<int32_t *>(base + plan.status);
   const int4 *rows = reinterpret_cast<const int4 *>(indices);
   const int tiles = plan.tiles;
-  const double L = g.L;
-  LookupTables tables{};
+  const double L = g.L, KL = (double)g.K * g.L;
+  const ErrorSink sink{status, status_host ? status_host + 2 : nullptr};
   cudaError_t err;
 
-  if ((err = cudaMemsetAsync(status, 0, 64 * sizeof(int32_t), stream)) != cudaSuccess) return err;
+  {
+    trace::Scope t("memset:rulebook_scratch", stream, (double)plan.zero_end);
+    if ((err = cudaMemsetAsync(base, 0, plan.zero_end, stream)) != cudaSuccess) return err;
+  }
+
+  PairListArgs a{};
+  a.rows = rows;
+  a.indice_pairs = indice_pairs;
+  a.indice_num = indice_num;
+  a.counts = reinterpret_cast<int32_t *>(base + plan.counts);
+  a.out_indices = reinterpret_cast<int4 *>(out_indices);
+  a.out_rows = out_rows;
+  a.table = neighbour_table;
+  a.table_stride = pairsTableStride(g.L);
+  a.sink = sink;
+  a.scratch.tile_desc = reinterpret_cast<uint32_t *>(base + plan.tile_desc);
+  a.scratch.group_desc = reinterpret_cast<uint32_t *>(base + plan.group_desc);
+  a.scratch.group_sum = reinterpret_cast<uint32_t *>(base + plan.group_sum);
+  a.scratch.group_done = reinterpret_cast<int32_t *>(base + plan.group_done);
 
   if (plan.lookup == kLookupHash) {
     unsigned long long *slots = reinterpret_cast<unsigned long long *>(base + plan.table);
-    tables.slots = slots;
-    tables.mask = plan.hash_capacity - 1;
-    {
-      trace::Scope t("memset:hash_table", stream, 8.0 * plan.hash_capacity);
-      if ((err = cudaMemsetAsync(slots, 0xFF, (size_t)plan.hash_capacity * sizeof(unsigned long long),
-                                 stream)) != cudaSuccess)
-        return err;
-    }
+    a.tables.slots = slots;
+    a.tables.mask = plan.hash_capacity - 1;
     trace::Scope t("hashInsertKernel", stream, 16.0 * L + 8.0 * L);
-    hashInsertKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, slots, tables.mask, status);
+    hashInsertKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, slots, a.tables.mask, sink);
   } else {
     uint2 *rank_table = reinterpret_cast<uint2 *>(base + plan.table);
-    int32_t *chunk_count = reinterpret_cast<int32_t *>(base + plan.chunk_count);
+    uint32_t *chunk_desc = reinterpret_cast<uint32_t *>(base + plan.chunk_desc);
     const double words = (double)plan.rank_words;
-    tables.rank_table = rank_table;
-    {
-      trace::Scope t("memset:rank_table", stream, 8.0 * words);
-      if ((err = cudaMemsetAsync(rank_table, 0, (size_t)plan.rank_words * sizeof(uint2), stream)) !=
-          cudaSuccess)
-        return err;
-    }
+    a.tables.rank_table = rank_table;
     if (g.sub_m) {
       trace::Scope t("markInputsKernel", stream, 16.0 * L);
       markInputsKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table);
@@ -763,69 +1038,46 @@ cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePla
       trace::Scope t("markOutputsKernel", stream, 16.0 * L);
       markOutputsKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table);
     }
-    {
-      trace::Scope t("countBitsKernel", stream, 8.0 * words);
-      countBitsKernel<<<plan.rank_chunks, 256, 0, stream>>>(rank_table, plan.rank_words, chunk_count);
-    }
-    {
-      trace::Scope t("scanSingleBlockKernel", stream, 8.0 * plan.rank_chunks);
-      scanSingleBlockKernel<<<1, 1024, 0, stream>>>(chunk_count, plan.rank_chunks, status + 1);
-    }
     if (g.sub_m) {
       int32_t *perm = reinterpret_cast<int32_t *>(base + plan.perm);
-      tables.perm = perm;
+      a.tables.perm = perm;
       {
-        trace::Scope t("rankKernel", stream, 16.0 * words);
-        rankKernel<false><<<plan.rank_chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words, chunk_count,
-                                                               nullptr, 0, status);
+        trace::Scope t("rankScanKernel", stream, 16.0 * words);
+        rankScanKernel<false><<<plan.rank_chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words,
+                                                                    plan.rank_chunks, chunk_desc, nullptr, 0, sink);
       }
-      if ((err = cudaMemsetAsync(perm, 0xFF, (size_t)g.L * sizeof(int32_t), stream)) != cudaSuccess) return err;
       trace::Scope t("permKernel", stream, 20.0 * L);
       permKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table, perm);
     } else {
-      {
-        trace::Scope t("rankAndDecodeKernel", stream, 16.0 * words);
-        rankKernel<true><<<plan.rank_chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words, chunk_count,
-                                                              reinterpret_cast<int4 *>(out_indices), out_rows,
-                                                              status);
-      }
-      trace::Scope t("fillInactiveRowsKernel", stream, 16.0 * (double)out_rows);
-      const unsigned fill_blocks = (unsigned)((out_rows + 255) / 256);
-      fillInactiveRowsKernel<<<fill_blocks, 256, 0, stream>>>(reinterpret_cast<int4 *>(out_indices), out_rows,
-                                                             status + 1);
-    }
-  }
-
-  if (g.sub_m) {
-    // out_indices = indices for the first L rows, -1 beyond
-    trace::Scope t("memcpy:out_indices", stream, 32.0 * L);
-    const int64_t copy_rows = out_rows < g.L ? out_rows : (int64_t)g.L;
-    if ((err = cudaMemcpyAsync(out_indices, indices, (size_t)copy_rows * 4 * sizeof(int32_t),
-                               cudaMemcpyDeviceToDevice, stream)) != cudaSuccess)
-      return err;
-    if (out_rows > g.L) {
-      if ((err = cudaMemsetAsync(out_indices + (size_t)g.L * 4, 0xFF,
-                                 (size_t)(out_rows - g.L) * 4 * sizeof(int32_t), stream)) != cudaSuccess)
-        return err;
+      trace::Scope t("rankScanKernel<decode>", stream, 16.0 * words);
+      rankScanKernel<true><<<plan.rank_chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words, plan.rank_chunks,
+                                                                 chunk_desc, reinterpret_cast<int4 *>(out_indices),
+                                                                 out_rows, sink);
     }
   }
 
   switch (plan.lookup) {
     case kLookupHash:
-      launchPairLists<kLookupHash>(g, plan, rows, tables, base, indice_pairs, indice_num, status, stream);
+      launchPairLists<kLookupHash>(g, plan, a, base, stream);
       break;
     case kLookupRankPerm:
-      launchPairLists<kLookupRankPerm>(g, plan, rows, tables, base, indice_pairs, indice_num, status, stream);
+      launchPairLists<kLookupRankPerm>(g, plan, a, base, stream);
       break;
     default:
-      launchPairLists<kLookupRank>(g, plan, rows, tables, base, indice_pairs, indice_num, status, stream);
+      launchPairLists<kLookupRank>(g, plan, a, base, stream);
       break;
   }
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
-  // status_host is pinned, device-mapped host memory: a one-thread kernel stores the
-  // two words there, so the read-back does not queue behind whatever large
-  // transfers the application has on the copy engines.
-  publishStatusKernel<<<1, 1, 0, stream>>>(status, status_host);
+  {
+    // -1 tails of indice_pairs (8 bytes per unused slot) and -1 rows of out_indices.  The
+    // status words reach the host through device-mapped pinned memory, so the read-back
+    // does not queue behind whatever large transfers the application has on the copy engines.
+    trace::Scope t("finishPairsKernel", stream, 8.0 * KL);
+    const unsigned spans = (unsigned)(((int64_t)g.L + 3 + kFinishSpan - 1) / kFinishSpan);
+    finishPairsKernel<<<dim3(spans, g.K + 1), 256, 0, stream>>>(g.L, g.K, g.sub_m, plan.fused, a.counts,
+                                                                indice_pairs, reinterpret_cast<int4 *>(out_indices),
+                                                                out_rows, status, status_host);
+  }
   return cudaGetLastError();
 }
 

@@ -35,6 +35,7 @@
 #include <string>
 
 #include "core/trace.h"
+#include "kernels/sparse_conv/get_indice_pairs_kernels.h"
 #include "kernels/sparse_conv/indice_convolution_tcgen05.h"
 
 namespace mluop {
@@ -43,6 +44,9 @@ namespace sparse_conv {
 namespace {
 
 inline size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// a table emitted by the rulebook kernels is read by the convolution as its own
+static_assert(kPairsTablePadRows == kConvPadRows, "one row padding for both producers of a neighbour table");
 
 constexpr int kMaxCountsByValue = 128;
 struct PairCounts {

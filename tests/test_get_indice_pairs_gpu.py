@@ -225,11 +225,12 @@ def test_large_kernel_volume(ops, oracle, gpu_handle):
 
 
 @pytest.mark.parametrize("env", [{"MLUOP_B200_PAIRS_LOOKUP": "hash"}, {"MLUOP_B200_PAIRS_LOOKUP": "rank"},
-                                 {"MLUOP_B200_PAIRS_PATH": "fused"},
-                                 {"MLUOP_B200_PAIRS_PATH": "fused", "MLUOP_B200_PAIRS_LOOKUP": "hash"}])
+                                 {"MLUOP_B200_PAIRS_PATH": "twopass"},
+                                 {"MLUOP_B200_PAIRS_PATH": "twopass", "MLUOP_B200_PAIRS_LOOKUP": "hash"}])
 def test_forced_variants(env):
-    """Every lookup structure (hash / occupancy rank) and both pair-list paths (single
-    pass / two pass) pass the same parity cases; the choice is per process, hence the child."""
+    """Every lookup structure (hash / occupancy rank) and both pair-list paths (single pass by
+    default / two pass on request) pass the same parity cases; the choice is per process, hence
+    the child."""
     import os
     import subprocess
     import sys
@@ -266,3 +267,31 @@ def test_device_errors_of_asynchronous_calls_are_sticky(ops, gpu_handle, monkeyp
     torch.cuda.synchronize()
     assert n_out == 1000 and int(num.sum()) >= 1000
     conv.destroy()
+
+
+def test_table_emitted_by_the_rulebook_equals_the_table_built_from_its_pairs(ops, gpu_handle):
+    """mluOpGetIndicePairsWithNeighbourTable (submanifold, centred padding) must leave exactly the
+    table mluOpBuildIndiceNeighbourTable derives from indice_pairs, padding rows included, and the
+    same rulebook as mluOpGetIndicePairs; other rulebooks are refused before anything runs."""
+    rng = np.random.default_rng(63)
+    for ks, space, n in (([3, 3, 3], [9, 30, 31], 3000), ([3, 1, 3], [7, 9, 40], 700), ([1, 3, 5], [6, 12, 33], 517),
+                         ([3, 3, 3], [41, 160, 140], 60000), ([1, 1, 1], [4, 4, 4], 20)):
+        idx = torch.from_numpy(helpers.random_indices(rng, 2, space, n)).cuda()
+        conv = ops.SparseConvDesc(2, [k // 2 for k in ks], [1] * 3, [1] * 3, space, ks, space, 1)
+        ref = ops.get_indice_pairs(gpu_handle, conv, idx)
+        pairs, out_idx, num, n_out, table = ops.get_indice_pairs(gpu_handle, conv, idx, with_table=True)
+        torch.cuda.synchronize()
+        assert n_out == ref[3] and torch.equal(pairs, ref[0]) and torch.equal(out_idx, ref[1]) and torch.equal(num, ref[2])
+        built = ops.build_neighbour_table(gpu_handle, pairs, num.cpu().tolist(), n_out)
+        torch.cuda.synchronize()
+        assert table.shape == built.shape and torch.equal(table, built), ks
+        conv.destroy()
+    # default mode and off-centre padding: not supported, nothing launched
+    space = [8, 8, 8]
+    idx = torch.from_numpy(helpers.random_indices(rng, 1, space, 50)).cuda()
+    for conv in (ops.SparseConvDesc(1, [1] * 3, [2] * 3, [1] * 3, space, [3] * 3, [4, 4, 4], 0),
+                 ops.SparseConvDesc(1, [0, 1, 1], [1] * 3, [1] * 3, space, [3] * 3, space, 1)):
+        with pytest.raises(ops.MluOpError) as err:
+            ops.get_indice_pairs(gpu_handle, conv, idx, with_table=True)
+        assert err.value.status == ops.STATUS_NOT_SUPPORTED
+        conv.destroy()

@@ -51,7 +51,8 @@ def test_trace_records_only_while_enabled(ops, gpu_handle):
     lib.mluOpTraceKernelEnable(0)
     rows = report(ops)
     kernels = {k: v for k, v in rows.items() if not k.startswith(("memset:", "memcpy:"))}
-    assert "writePairsKernel" in kernels and kernels["writePairsKernel"][0] == 2
+    lists = [k for k in kernels if k.startswith("pairListsKernel")]
+    assert len(lists) == 1 and kernels[lists[0]][0] == 2 and kernels["finishPairsKernel"][0] == 2
     conv = [k for k in kernels if k.startswith("conv")]
     assert len(conv) == 1 and kernels[conv[0]][0] == 2
     assert all(v[1] > 0 for v in kernels.values())

@@ -185,6 +185,20 @@ hashInsertKernel(PairsGeometry g, const int4 *__restrict__ indices, unsigned lon
   raiseError(sink, kPairsErrHashFull);
 }
 
+// Continues a probe sequence whose slot h held `cur` (another key).
+__device__ __noinline__ int hashLookupSlow(const unsigned long long *__restrict__ slots, uint32_t mask,
+                                           uint32_t want, uint32_t h, const ErrorSink &sink) {
+  for (uint32_t probe = 1; probe <= mask; ++probe) {
+    h = (h + 1) & mask;
+    const unsigned long long cur = __ldg(slots + h);
+    const uint32_t key = (uint32_t)(cur >> 32);
+    if (key == want) return (int)(uint32_t)cur;
+    if (key == 0u) return -1;
+  }
+  raiseError(sink, kPairsErrHashFull);
+  return -1;
+}
+
 __device__ __forceinline__ int hashLookup(const unsigned long long *__restrict__ slots, uint32_t mask,
                                           uint32_t lin, const ErrorSink &sink) {
   const uint32_t want = lin + 1u;
@@ -237,6 +251,39 @@ markOutputsKernel(PairsGeometry g, const int4 *__restrict__ indices, uint2 *rank
   }
 }
 
+// The same for a 3x3x3 kernel with stride 2 and dilation 1: per dimension only the
+// offsets with the parity of (i + pad) can be valid, at most two of the three.
+__global__ void __launch_bounds__(256)
+markOutputsCube3Stride2Kernel(PairsGeometry g, const int4 *__restrict__ indices, uint2 *rank_table) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= g.L) return;
+  const int4 c = indices[j];
+  if (!rowInRange(c, g)) return;
+  int o[3][2];
+  bool ok[3][2];
+  const int i3[3] = {c.y, c.z, c.w};
+#pragma unroll
+  for (int d = 0; d < 3; ++d) {
+    const int t0 = i3[d] + g.pad[d];
+    const int k0 = t0 & 1;  // the smallest offset with t = t0 - k even
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      const int kk = k0 + 2 * a, t = t0 - kk;
+      o[d][a] = t >> 1;
+      ok[d][a] = kk < 3 && t >= 0 && o[d][a] < g.out_space[d];
+    }
+  }
+  const int base_b = c.x * g.out_vol;
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int b = 0; b < 2; ++b)
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+        if (ok[0][a] && ok[1][b] && ok[2][e])
+          setBit(rank_table, (uint32_t)(base_b + (o[0][a] * g.out_space[1] + o[1][b]) * g.out_space[2] + o[2][e]));
+}
+
 // submanifold mode: the occupancy bit of every input voxel
 __global__ void __launch_bounds__(256)
 markInputsKernel(PairsGeometry g, const int4 *__restrict__ indices, uint2 *rank_table) {
@@ -286,13 +333,13 @@ __device__ __forceinline__ int lookBackOneWord(uint32_t *desc, int unit, int min
 // running), stores each word's exclusive rank next to its bits and, with DECODE,
 // writes the coordinates of the chunk's active cells to out_indices in ascending
 // linear order.  The last chunk leaves the total in status[kStatusActive].
-constexpr int kRankWordsPerThread = 8;
-static_assert(kRankChunkWords == 256 * kRankWordsPerThread, "256 threads per chunk");
-
-template <bool DECODE>
+// The chunk size is chosen per call (8, 4, 2 or 1 words per thread) so that small grids
+// still spread over all SMs: the decode of a chunk is serial per thread.
+template <bool DECODE, int kRankWordsPerThread>
 __global__ void __launch_bounds__(256)
 rankScanKernel(PairsGeometry g, uint2 *rank_table, int64_t words, int chunks, uint32_t *chunk_desc,
                int4 *out_indices, int64_t out_rows, ErrorSink sink) {
+  constexpr int kRankChunkWords = 256 * kRankWordsPerThread;
   __shared__ int warp_sums[33];
   __shared__ int chunk_s, before_s;
   if (threadIdx.x == 0) chunk_s = atomicAdd(sink.status + kStatusChunkTicket, 1);
@@ -301,7 +348,7 @@ rankScanKernel(PairsGeometry g, uint2 *rank_table, int64_t words, int chunks, ui
   const int64_t w0 = (int64_t)chunk * kRankChunkWords + threadIdx.x * kRankWordsPerThread;
   uint32_t bits[kRankWordsPerThread];
   int n = 0;
-  if (w0 + kRankWordsPerThread <= words) {
+  if (kRankWordsPerThread >= 2 && w0 + kRankWordsPerThread <= words) {
     const uint4 *src = reinterpret_cast<const uint4 *>(rank_table + w0);  // two {bits, rank} entries per load
 #pragma unroll
     for (int i = 0; i < kRankWordsPerThread / 2; ++i) {
@@ -439,17 +486,46 @@ __device__ __forceinline__ void walkCube3(const PairsGeometry &g, const LookupTa
     ok_w[kk] = tw >= 0 && (tw & SHIFT) == 0 && o_w[kk] < g.out_space[2];
   }
   const int base_b = c.x * g.out_vol;
+  if (LOOKUP == kLookupHash) {
+    // The first slot of every probe sequence is loaded before any is examined (27
+    // independent loads); a sequence that has to go on (its first slot holds another
+    // key) continues in the slow path.
+    unsigned long long first[27];
+    uint32_t slot[27];
 #pragma unroll
-  for (int kd = 0; kd < 3; ++kd) {
+    for (int k = 0; k < 27; ++k) {
+      const int kd = k / 9, kh = (k / 3) % 3, kw = k % 3;
+      const bool ok = ok_d[kd] && ok_h[kh] && ok_w[kw];
+      const uint32_t want = (uint32_t)(base_b + (o_d[kd] * g.out_space[1] + o_h[kh]) * g.out_space[2] + o_w[kw]) + 1u;
+      slot[k] = mixKey(want) & tables.mask;
+      first[k] = ok ? __ldg(tables.slots + slot[k]) : 0ull;
+    }
 #pragma unroll
-    for (int kh = 0; kh < 3; ++kh) {
-      const bool ok_dh = ok_d[kd] && ok_h[kh];
-      const int base_row = base_b + (o_d[kd] * g.out_space[1] + o_h[kh]) * g.out_space[2];
+    for (int k = 0; k < 27; ++k) {
+      const int kd = k / 9, kh = (k / 3) % 3, kw = k % 3;
+      const uint32_t want = (uint32_t)(base_b + (o_d[kd] * g.out_space[1] + o_h[kh]) * g.out_space[2] + o_w[kw]) + 1u;
+      const uint32_t key = (uint32_t)(first[k] >> 32);
+      int r = -1;
+      if (key == want) {
+        r = (int)(uint32_t)first[k];
+      } else if (key != 0u) {
+        r = hashLookupSlow(tables.slots, tables.mask, want, slot[k], sink);
+      }
+      v[k] = r;
+    }
+  } else {
 #pragma unroll
-      for (int kw = 0; kw < 3; ++kw) {
-        int r = -1;
-        if (ok_dh && ok_w[kw]) r = lookupOutput<LOOKUP>(tables, (uint32_t)(base_row + o_w[kw]), sink);
-        v[(kd * 3 + kh) * 3 + kw] = r;
+    for (int kd = 0; kd < 3; ++kd) {
+#pragma unroll
+      for (int kh = 0; kh < 3; ++kh) {
+        const bool ok_dh = ok_d[kd] && ok_h[kh];
+        const int base_row = base_b + (o_d[kd] * g.out_space[1] + o_h[kh]) * g.out_space[2];
+#pragma unroll
+        for (int kw = 0; kw < 3; ++kw) {
+          int r = -1;
+          if (ok_dh && ok_w[kw]) r = lookupOutput<LOOKUP>(tables, (uint32_t)(base_row + o_w[kw]), sink);
+          v[(kd * 3 + kh) * 3 + kw] = r;
+        }
       }
     }
   }
@@ -886,7 +962,11 @@ PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g) {
     off = alignUp(off + (size_t)cap * sizeof(unsigned long long), 256);
   } else {
     p.rank_words = (cells + 31) / 32;
-    p.rank_chunks = (int32_t)((p.rank_words + kRankChunkWords - 1) / kRankChunkWords);
+    // up to 8 words per thread, fewer while that leaves less than about four chunks per SM
+    p.rank_words_per_thread = 8;
+    while (p.rank_words_per_thread > 1 && p.rank_words / (256 * p.rank_words_per_thread) < 600) p.rank_words_per_thread /= 2;
+    const int64_t chunk_words = 256 * p.rank_words_per_thread;
+    p.rank_chunks = (int32_t)((p.rank_words + chunk_words - 1) / chunk_words);
     off = alignUp(off + (size_t)p.rank_words * sizeof(uint2), 256);
     p.chunk_desc = off;
     off = alignUp(off + (size_t)p.rank_chunks * sizeof(uint32_t), 256);
@@ -986,6 +1066,30 @@ void launchPairLists(const PairsGeometry &g, const PairsWorkspacePlan &plan, con
   }
 }
 
+template <bool DECODE>
+void launchRankScan(const PairsGeometry &g, const PairsWorkspacePlan &plan, uint2 *rank_table, uint32_t *chunk_desc,
+                    int4 *out_indices, int64_t out_rows, const ErrorSink &sink, cudaStream_t stream) {
+  const int chunks = plan.rank_chunks;
+  switch (plan.rank_words_per_thread) {
+    case 8:
+      rankScanKernel<DECODE, 8><<<chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words, chunks, chunk_desc,
+                                                           out_indices, out_rows, sink);
+      break;
+    case 4:
+      rankScanKernel<DECODE, 4><<<chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words, chunks, chunk_desc,
+                                                           out_indices, out_rows, sink);
+      break;
+    case 2:
+      rankScanKernel<DECODE, 2><<<chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words, chunks, chunk_desc,
+                                                           out_indices, out_rows, sink);
+      break;
+    default:
+      rankScanKernel<DECODE, 1><<<chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words, chunks, chunk_desc,
+                                                           out_indices, out_rows, sink);
+      break;
+  }
+}
+
 }  // namespace
 
 cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePlan &plan,
@@ -1036,23 +1140,27 @@ cudaError_t launchGetIndicePairs(const PairsGeometry &g, const PairsWorkspacePla
       markInputsKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table);
     } else {
       trace::Scope t("markOutputsKernel", stream, 16.0 * L);
-      markOutputsKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table);
+      bool cube3_s2 = true;
+      for (int i = 0; i < 3; ++i) cube3_s2 = cube3_s2 && g.ks[i] == 3 && g.stride[i] == 2 && g.dil[i] == 1;
+      if (cube3_s2) {
+        markOutputsCube3Stride2Kernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table);
+      } else {
+        markOutputsKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table);
+      }
     }
     if (g.sub_m) {
       int32_t *perm = reinterpret_cast<int32_t *>(base + plan.perm);
       a.tables.perm = perm;
       {
         trace::Scope t("rankScanKernel", stream, 16.0 * words);
-        rankScanKernel<false><<<plan.rank_chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words,
-                                                                    plan.rank_chunks, chunk_desc, nullptr, 0, sink);
+        launchRankScan<false>(g, plan, rank_table, chunk_desc, nullptr, 0, sink, stream);
       }
       trace::Scope t("permKernel", stream, 20.0 * L);
       permKernel<<<tiles, kPairsTile, 0, stream>>>(g, rows, rank_table, perm);
     } else {
       trace::Scope t("rankScanKernel<decode>", stream, 16.0 * words);
-      rankScanKernel<true><<<plan.rank_chunks, 256, 0, stream>>>(g, rank_table, plan.rank_words, plan.rank_chunks,
-                                                                 chunk_desc, reinterpret_cast<int4 *>(out_indices),
-                                                                 out_rows, sink);
+      launchRankScan<true>(g, plan, rank_table, chunk_desc, reinterpret_cast<int4 *>(out_indices), out_rows, sink,
+                           stream);
     }
   }
 

@@ -14,8 +14,6 @@ namespace sparse_conv {
 
 // Input voxels handled by one thread block of the probe and write kernels.
 constexpr int kPairsTile = 256;
-// 32-bit occupancy words handled by one thread block of the rank kernel.
-constexpr int kRankChunkWords = 2048;
 // A neighbour table emitted by the rulebook has rows padded to a multiple of this
 // many entries (the padding of the convolution's neighbour table).
 constexpr int kPairsTablePadRows = 512;
@@ -68,7 +66,8 @@ struct PairsWorkspacePlan {
   int32_t fused;           // 1: single-pass path
   uint32_t hash_capacity;  // hash: power of two >= 2L
   int64_t rank_words;      // rank: ceil(cells / 32)
-  int32_t rank_chunks;
+  int32_t rank_words_per_thread;  // rank: 8, 4, 2 or 1 occupancy words per thread of the scan
+  int32_t rank_chunks;            // rank: chunks of 256 * rank_words_per_thread words
 };
 
 PairsWorkspacePlan planPairsWorkspace(const PairsGeometry &g);

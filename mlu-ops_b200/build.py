@@ -57,6 +57,7 @@ def build(force=False, verbose=False):
     ]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("MLUOP_B200_NVCC_FLAGS", "").split()  # extra compiler flags (experiments)
     cmd += sources()
     cmd += ["-lcudart_static", "-lpthread", "-ldl", "-lrt"]
     if verbose:

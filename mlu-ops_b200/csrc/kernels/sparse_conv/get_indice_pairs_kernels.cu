@@ -185,20 +185,6 @@ hashInsertKernel(PairsGeometry g, const int4 *__restrict__ indices, unsigned lon
   raiseError(sink, kPairsErrHashFull);
 }
 
-// Continues a probe sequence whose slot h held `cur` (another key).
-__device__ __noinline__ int hashLookupSlow(const unsigned long long *__restrict__ slots, uint32_t mask,
-                                           uint32_t want, uint32_t h, const ErrorSink &sink) {
-  for (uint32_t probe = 1; probe <= mask; ++probe) {
-    h = (h + 1) & mask;
-    const unsigned long long cur = __ldg(slots + h);
-    const uint32_t key = (uint32_t)(cur >> 32);
-    if (key == want) return (int)(uint32_t)cur;
-    if (key == 0u) return -1;
-  }
-  raiseError(sink, kPairsErrHashFull);
-  return -1;
-}
-
 __device__ __forceinline__ int hashLookup(const unsigned long long *__restrict__ slots, uint32_t mask,
                                           uint32_t lin, const ErrorSink &sink) {
   const uint32_t want = lin + 1u;
@@ -486,46 +472,17 @@ __device__ __forceinline__ void walkCube3(const PairsGeometry &g, const LookupTa
     ok_w[kk] = tw >= 0 && (tw & SHIFT) == 0 && o_w[kk] < g.out_space[2];
   }
   const int base_b = c.x * g.out_vol;
-  if (LOOKUP == kLookupHash) {
-    // The first slot of every probe sequence is loaded before any is examined (27
-    // independent loads); a sequence that has to go on (its first slot holds another
-    // key) continues in the slow path.
-    unsigned long long first[27];
-    uint32_t slot[27];
 #pragma unroll
-    for (int k = 0; k < 27; ++k) {
-      const int kd = k / 9, kh = (k / 3) % 3, kw = k % 3;
-      const bool ok = ok_d[kd] && ok_h[kh] && ok_w[kw];
-      const uint32_t want = (uint32_t)(base_b + (o_d[kd] * g.out_space[1] + o_h[kh]) * g.out_space[2] + o_w[kw]) + 1u;
-      slot[k] = mixKey(want) & tables.mask;
-      first[k] = ok ? __ldg(tables.slots + slot[k]) : 0ull;
-    }
+  for (int kd = 0; kd < 3; ++kd) {
 #pragma unroll
-    for (int k = 0; k < 27; ++k) {
-      const int kd = k / 9, kh = (k / 3) % 3, kw = k % 3;
-      const uint32_t want = (uint32_t)(base_b + (o_d[kd] * g.out_space[1] + o_h[kh]) * g.out_space[2] + o_w[kw]) + 1u;
-      const uint32_t key = (uint32_t)(first[k] >> 32);
-      int r = -1;
-      if (key == want) {
-        r = (int)(uint32_t)first[k];
-      } else if (key != 0u) {
-        r = hashLookupSlow(tables.slots, tables.mask, want, slot[k], sink);
-      }
-      v[k] = r;
-    }
-  } else {
+    for (int kh = 0; kh < 3; ++kh) {
+      const bool ok_dh = ok_d[kd] && ok_h[kh];
+      const int base_row = base_b + (o_d[kd] * g.out_space[1] + o_h[kh]) * g.out_space[2];
 #pragma unroll
-    for (int kd = 0; kd < 3; ++kd) {
-#pragma unroll
-      for (int kh = 0; kh < 3; ++kh) {
-        const bool ok_dh = ok_d[kd] && ok_h[kh];
-        const int base_row = base_b + (o_d[kd] * g.out_space[1] + o_h[kh]) * g.out_space[2];
-#pragma unroll
-        for (int kw = 0; kw < 3; ++kw) {
-          int r = -1;
-          if (ok_dh && ok_w[kw]) r = lookupOutput<LOOKUP>(tables, (uint32_t)(base_row + o_w[kw]), sink);
-          v[(kd * 3 + kh) * 3 + kw] = r;
-        }
+      for (int kw = 0; kw < 3; ++kw) {
+        int r = -1;
+        if (ok_dh && ok_w[kw]) r = lookupOutput<LOOKUP>(tables, (uint32_t)(base_row + o_w[kw]), sink);
+        v[(kd * 3 + kh) * 3 + kw] = r;
       }
     }
   }
@@ -622,8 +579,15 @@ __device__ __forceinline__ bool tilePrefix(const PairListScratch &s, int tile, i
 //   B. warp 0: the tile's write offsets for all K offsets (tilePrefix); the last
 //      tile writes indice_num
 //   C. the tile's pairs, ascending j, at offset + rank inside the tile
+// Resident blocks per SM the compiler has to leave room for.  A tile's life is a chain
+// of dependent memory latencies (coordinates, lookups, look-back, stores), so the kernel
+// is bound by the number of tiles in flight: 6 blocks (40 registers, a few spilled
+// words) measured faster than 4 (64 registers, none).
+#ifndef MLUOP_B200_PAIRS_MIN_BLOCKS
+#define MLUOP_B200_PAIRS_MIN_BLOCKS 6
+#endif
 template <int LOOKUP, int WALK>
-__global__ void __launch_bounds__(kPairsTile)
+__global__ void __launch_bounds__(kPairsTile, MLUOP_B200_PAIRS_MIN_BLOCKS)
 pairListsKernel(PairsGeometry g, const int4 *__restrict__ indices, LookupTables tables, PairListScratch scratch,
                 int tiles, int32_t *__restrict__ indice_pairs, int32_t *__restrict__ indice_num,
                 int32_t *__restrict__ counts, int4 *__restrict__ out_indices, int64_t out_rows,

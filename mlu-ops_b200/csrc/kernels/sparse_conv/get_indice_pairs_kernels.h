@@ -39,7 +39,7 @@ enum PairsLookup {
 // A submanifold rulebook uses the occupancy-bit table instead of the hash table
 // when the grid has at most this many cells per input voxel: the table is then
 // small, and neighbouring cells share its words, which a hash table cannot offer.
-constexpr int64_t kDenseCellsPerVoxel = 512;
+constexpr int64_t kDenseCellsPerVoxel = 1024;
 // Kernel volumes up to this size take the single-pass pair-list path (one
 // descriptor word per offset; matches of a tile stay on chip).
 constexpr int kFusedMaxOffsets = 32;

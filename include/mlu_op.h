@@ -224,7 +224,12 @@ mluOpGetSparseConvolutionNumActOut(mluOpSparseConvolutionDescriptor_t desc, int 
 /* ------------------------------------------------------------ the hot path */
 
 /* reference mlu_op.h:8674, get_indice_pairs.cpp:251.  Bytes of device scratch
- * mluOpGetIndicePairs needs for these descriptors. */
+ * mluOpGetIndicePairs needs for these descriptors.  Upper bound: with an
+ * occupancy table (default mode; submanifold mode on grids of at most 1024 cells
+ * per voxel) cells / 4 + 16 * L + 1 MiB, where cells = batch * D * H * W of the
+ * output space, i.e. at most 512 MiB at the 2^31-cell limit; with a hash table
+ * (sparser submanifold grids) 40 * L + 1 MiB.  Kernel volumes above 32 add
+ * 4 * K * L for the staged matches. */
 mluOpStatus_t MLUOP_WIN_API mluOpGetIndicePairsWorkspaceSize(
     mluOpHandle_t handle, mluOpSparseConvolutionDescriptor_t sparse_conv_desc,
     const mluOpTensorDescriptor_t indices_desc,

@@ -238,6 +238,73 @@ def _ptr(t):
     return _vp(t.data_ptr() if t is not None else 0)
 
 
+class Guards:
+    """Poisoned bands around every buffer the harness allocates for a call (outputs and
+    workspace), checked after the call: a kernel that writes outside the buffer it was given
+    is caught even when the stray write lands in memory nobody reads.  The reference's own
+    harness brackets each device buffer with a mask the same way
+    (test/mlu_op_gtest/pb_gtest/src/runtime.cpp:86-145); it stands in for a memory checker.
+
+        with ops.guarded() as guards:
+            ... calls through this module ...
+        # leaving the block synchronises and asserts that every band is intact
+    """
+    BAND = 1024  # bytes before and after; a multiple of the 256-byte alignment the library assumes
+
+    def __init__(self):
+        self.items = []
+
+    def empty(self, shape, dtype, device):
+        import torch
+        shape = tuple(int(v) for v in shape)
+        count = 1
+        for v in shape:
+            count *= v
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        raw = torch.empty((2 * self.BAND + nbytes,), dtype=torch.uint8, device=device)
+        gen = torch.Generator(device="cpu").manual_seed(len(self.items) + 1)
+        band = torch.randint(0, 256, (2 * self.BAND,), dtype=torch.uint8, generator=gen).to(device)
+        raw[:self.BAND] = band[:self.BAND]
+        raw[self.BAND + nbytes:] = band[self.BAND:]
+        self.items.append((raw, nbytes, band))
+        return raw[self.BAND:self.BAND + nbytes].view(dtype).view(shape)
+
+    def check(self):
+        import torch
+        torch.cuda.synchronize()
+        for i, (raw, nbytes, band) in enumerate(self.items):
+            assert torch.equal(raw[:self.BAND], band[:self.BAND]), "buffer %d: bytes before it were overwritten" % i
+            assert torch.equal(raw[self.BAND + nbytes:], band[self.BAND:]), \
+                "buffer %d (%d bytes): bytes after it were overwritten" % (i, nbytes)
+        return len(self.items)
+
+
+_guards = None
+
+
+class guarded:
+    """Context manager: allocations of this module get guard bands inside the block."""
+
+    def __enter__(self):
+        global _guards
+        self.previous, _guards = _guards, Guards()
+        return _guards
+
+    def __exit__(self, exc_type, exc, tb):
+        global _guards
+        mine, _guards = _guards, self.previous
+        if exc_type is None:
+            mine.check()
+        return False
+
+
+def _alloc(shape, dtype, device):
+    import torch
+    if _guards is not None:
+        return _guards.empty(shape, dtype, device)
+    return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+
 def get_indice_pairs_workspace_size(handle, conv, indices_desc, pairs_desc, out_indices_desc, num_desc):
     size = _szt(0)
     check("mluOpGetIndicePairsWorkspaceSize",
@@ -276,16 +343,16 @@ def get_indice_pairs(handle, conv, indices, out_rows=None, workspace=None, with_
         out_rows = L if conv.sub_m else max_active_outputs(L, conv.batch, conv.output_space, conv.filter_space,
                                                            conv.stride, conv.dilation)
     dev = indices.device
-    pairs = torch.empty((K, 2, L), dtype=torch.int32, device=dev)
-    out_indices = torch.empty((out_rows, 4), dtype=torch.int32, device=dev)
-    num = torch.empty((K,), dtype=torch.int32, device=dev)
+    pairs = _alloc((K, 2, L), torch.int32, dev)
+    out_indices = _alloc((out_rows, 4), torch.int32, dev)
+    num = _alloc((K,), torch.int32, dev)
     d_in = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (L, 4))
     d_pairs = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K, 2, L))
     d_out = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (out_rows, 4))
     d_num = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K,))
     ws_size = get_indice_pairs_workspace_size(handle, conv, d_in, d_pairs, d_out, d_num)
     if workspace is None or workspace.numel() < ws_size:
-        workspace = torch.empty((max(ws_size, 1),), dtype=torch.uint8, device=dev)
+        workspace = _alloc((max(ws_size, 1),), torch.uint8, dev)
     args = [handle.ptr, conv.ptr, d_in.ptr, _ptr(indices), _ptr(workspace), ws_size, d_pairs.ptr, _ptr(pairs),
             d_out.ptr, _ptr(out_indices), d_num.ptr, _ptr(num)]
     table = None
@@ -294,7 +361,7 @@ def get_indice_pairs(handle, conv, indices, out_rows=None, workspace=None, with_
             size = _szt(0)
             check("mluOpGetIndiceNeighbourTableSize",
                   lib().mluOpGetIndiceNeighbourTableSize(handle.ptr, d_pairs.ptr, L, ctypes.byref(size)))
-            table = torch.empty((K, size.value // (4 * K)), dtype=torch.int32, device=dev)
+            table = _alloc((K, size.value // (4 * K)), torch.int32, dev)
             check("mluOpGetIndicePairsWithNeighbourTable",
                   lib().mluOpGetIndicePairsWithNeighbourTable(*args, _ptr(table), size.value))
         else:
@@ -318,7 +385,7 @@ def build_neighbour_table(handle, indice_pairs, indice_num, num_act_out):
     try:
         check("mluOpGetIndiceNeighbourTableSize",
               lib().mluOpGetIndiceNeighbourTableSize(handle.ptr, d_pairs.ptr, num_act_out, ctypes.byref(size)))
-        table = torch.empty((K, size.value // (4 * K)), dtype=torch.int32, device=indice_pairs.device)
+        table = _alloc((K, size.value // (4 * K)), torch.int32, indice_pairs.device)
         check("mluOpBuildIndiceNeighbourTable",
               lib().mluOpBuildIndiceNeighbourTable(handle.ptr, d_pairs.ptr, _ptr(indice_pairs),
                                                    i64_array([int(v) for v in indice_num]), num_act_out,
@@ -358,7 +425,7 @@ def indice_convolution_forward(handle, features, filters, filter_layout, filter_
     dt = DTYPE_HALF if features.dtype == torch.float16 else DTYPE_FLOAT
     dev = features.device
     if out is None:
-        out = torch.empty((num_act_out, co), dtype=features.dtype, device=dev)
+        out = _alloc((num_act_out, co), features.dtype, dev)
     d_f = TensorDesc(LAYOUT_ARRAY, dt, (L, ci))
     d_w = TensorDesc(FILTER_LAYOUTS[filter_layout], dt, dims)
     d_p = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K, 2, L))
@@ -370,7 +437,7 @@ def indice_convolution_forward(handle, features, filters, filter_layout, filter_
                                                               num, num_act_out, 0, int(bool(sub_m)),
                                                               ctypes.byref(size)))
     if workspace is None or workspace.numel() < size.value:
-        workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+        workspace = _alloc((max(size.value, 1),), torch.uint8, dev)
     check("mluOpIndiceConvolutionForward",
           lib().mluOpIndiceConvolutionForward(handle.ptr, d_f.ptr, _ptr(features), d_w.ptr, _ptr(filters),
                                               d_p.ptr, _ptr(indice_pairs), num, num_act_out, 0,
@@ -402,7 +469,7 @@ def indice_convolution_backward_data(handle, output_grad, filters, filter_layout
     dt = DTYPE_HALF if output_grad.dtype == torch.float16 else DTYPE_FLOAT
     dev = output_grad.device
     if out is None:
-        out = torch.empty((L, ci), dtype=output_grad.dtype, device=dev)
+        out = _alloc((L, ci), output_grad.dtype, dev)
     d_g = TensorDesc(LAYOUT_ARRAY, dt, (n_out, co))
     d_w = TensorDesc(FILTER_LAYOUTS[filter_layout], dt, dims)
     d_p = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K, 2, L))
@@ -413,7 +480,7 @@ def indice_convolution_backward_data(handle, output_grad, filters, filter_layout
           lib().mluOpGetIndiceConvolutionBackwardDataWorkspaceSize(handle.ptr, d_g.ptr, d_w.ptr, d_p.ptr, d_o.ptr,
                                                                    num, 0, ctypes.byref(size)))
     if workspace is None or workspace.numel() < size.value:
-        workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+        workspace = _alloc((max(size.value, 1),), torch.uint8, dev)
     check("mluOpIndiceConvolutionBackwardData",
           lib().mluOpIndiceConvolutionBackwardData(handle.ptr, d_g.ptr, _ptr(output_grad), d_w.ptr, _ptr(filters),
                                                    d_p.ptr, _ptr(indice_pairs), num, 0, int(bool(sub_m)),
@@ -438,7 +505,7 @@ def indice_convolution_backward_filter(handle, features, output_grad, filter_spa
     dev = features.device
     dims = tuple(filter_space) + (ci, co)
     if out is None:
-        out = torch.empty(dims, dtype=features.dtype, device=dev)
+        out = _alloc(dims, features.dtype, dev)
     d_f = TensorDesc(LAYOUT_ARRAY, dt, (L, ci))
     d_g = TensorDesc(LAYOUT_ARRAY, dt, (n_out, co))
     d_p = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K, 2, L))
@@ -450,7 +517,7 @@ def indice_convolution_backward_filter(handle, features, output_grad, filter_spa
                                                                      d_w.ptr, num, 0, int(bool(sub_m)),
                                                                      ctypes.byref(size)))
     if workspace is None or workspace.numel() < size.value:
-        workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+        workspace = _alloc((max(size.value, 1),), torch.uint8, dev)
     check("mluOpIndiceConvolutionBackwardFilter",
           lib().mluOpIndiceConvolutionBackwardFilter(handle.ptr, d_f.ptr, _ptr(features), d_g.ptr,
                                                      _ptr(output_grad), d_p.ptr, _ptr(indice_pairs), num, 0,
@@ -472,9 +539,9 @@ def voxelization(handle, points, voxel_size, coors_range, max_points, max_voxels
     import torch
     n, f = points.shape
     dev = points.device
-    voxels = torch.empty((max_voxels, max_points, f), dtype=torch.float32, device=dev)
-    coors = torch.empty((max_voxels, 3), dtype=torch.int32, device=dev)
-    npv = torch.empty((max_voxels,), dtype=torch.int32, device=dev)
+    voxels = _alloc((max_voxels, max_points, f), torch.float32, dev)
+    coors = _alloc((max_voxels, 3), torch.int32, dev)
+    npv = _alloc((max_voxels,), torch.int32, dev)
     num = torch.zeros((1,), dtype=torch.int32, device=dev)
     descs = [TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (n, f)), TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (3,)),
              TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (6,)), TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, tuple(voxels.shape)),
@@ -486,7 +553,7 @@ def voxelization(handle, points, voxel_size, coors_range, max_points, max_voxels
           lib().mluOpGetVoxelizationWorkspaceSize(handle.ptr, d_p, d_vs, d_cr, max_points, max_voxels, 3, True, d_v,
                                                   d_c, d_n, d_num, ctypes.byref(size)))
     if workspace is None or workspace.numel() < size.value:
-        workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+        workspace = _alloc((max(size.value, 1),), torch.uint8, dev)
     check("mluOpVoxelization",
           lib().mluOpVoxelization(handle.ptr, d_p, _ptr(points), d_vs, _ptr(voxel_size), d_cr, _ptr(coors_range),
                                   max_points, max_voxels, 3, True, _ptr(workspace), size.value, d_v, _ptr(voxels),
@@ -510,10 +577,10 @@ def dynamic_point_to_voxel_forward(handle, feats, coors, reduce_type="max", work
     import torch
     n, c = feats.shape
     dev = feats.device
-    voxel_feats = torch.empty((n, c), dtype=torch.float32, device=dev)
-    voxel_coors = torch.empty((n, 3), dtype=torch.int32, device=dev)
-    p2v = torch.empty((n,), dtype=torch.int32, device=dev)
-    counts = torch.empty((n,), dtype=torch.int32, device=dev)
+    voxel_feats = _alloc((n, c), torch.float32, dev)
+    voxel_coors = _alloc((n, 3), torch.int32, dev)
+    p2v = _alloc((n,), torch.int32, dev)
+    counts = _alloc((n,), torch.int32, dev)
     num = torch.zeros((1,), dtype=torch.int32, device=dev)
     descs = [TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (n, c)), TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (n, 3)),
              TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (n, c)), TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (n, 3)),
@@ -524,7 +591,7 @@ def dynamic_point_to_voxel_forward(handle, feats, coors, reduce_type="max", work
     check("mluOpGetDynamicPointToVoxelForwardWorkspaceSize",
           lib().mluOpGetDynamicPointToVoxelForwardWorkspaceSize(handle.ptr, d_f, d_c, ctypes.byref(size)))
     if workspace is None or workspace.numel() < size.value:
-        workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+        workspace = _alloc((max(size.value, 1),), torch.uint8, dev)
     check("mluOpDynamicPointToVoxelForward",
           lib().mluOpDynamicPointToVoxelForward(handle.ptr, REDUCE_MODES[reduce_type], d_f, _ptr(feats), d_c,
                                                 _ptr(coors), _ptr(workspace), size.value, d_vf, _ptr(voxel_feats),
@@ -542,7 +609,7 @@ def dynamic_point_to_voxel_backward(handle, grad_voxel_feats, feats, voxel_feats
     n, c = feats.shape
     m = grad_voxel_feats.shape[0]
     dev = feats.device
-    grad_feats = torch.empty((n, c), dtype=torch.float32, device=dev)
+    grad_feats = _alloc((n, c), torch.float32, dev)
     descs = [TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (m, c)), TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (n, c)),
              TensorDesc(LAYOUT_ARRAY, DTYPE_FLOAT, (m, c)), TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (n,)),
              TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (m,)), TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (1,)),
@@ -552,7 +619,7 @@ def dynamic_point_to_voxel_backward(handle, grad_voxel_feats, feats, voxel_feats
     check("mluOpGetDynamicPointToVoxelBackwardWorkspaceSize",
           lib().mluOpGetDynamicPointToVoxelBackwardWorkspaceSize(handle.ptr, REDUCE_MODES["max"], d_g, d_f, d_vf,
                                                                  d_map, d_cnt, d_num, ctypes.byref(size)))
-    workspace = torch.empty((max(size.value, 1),), dtype=torch.uint8, device=dev)
+    workspace = _alloc((max(size.value, 1),), torch.uint8, dev)
     check("mluOpDynamicPointToVoxelBackward",
           lib().mluOpDynamicPointToVoxelBackward(handle.ptr, REDUCE_MODES["max"], d_g, _ptr(grad_voxel_feats), d_f,
                                                  _ptr(feats), d_vf, _ptr(voxel_feats), d_map, _ptr(point2voxel_map),

@@ -113,4 +113,16 @@ bool isStrideTensor(int dim, const int64_t *dims, const int64_t *strides);
 
 #define LARGE_TENSOR_NUM ((uint64_t)2147483648)  // 2^31, reference core/logging.h:37
 
+// MLUOP_CHECK(call): for test and example code, not for the library itself; a status
+// other than success is logged and thrown (reference core/logging.h:232-234, core/util.cpp:30-41).
+#include <stdexcept>
+inline void mluOpCheck(mluOpStatus_t result, char const *const func, const char *const file, int const line) {
+  if (result != MLUOP_STATUS_SUCCESS) {
+    const std::string error = "\"" + std::string(mluOpGetErrorString(result)) + " in " + std::string(func) + "\"";
+    LOG(ERROR) << error << " (" << file << ":" << line << ")";
+    throw std::runtime_error(error);
+  }
+}
+#define MLUOP_CHECK(val) mluOpCheck((val), #val, __FILE__, __LINE__)
+
 #endif  // MLUOP_B200_CORE_LOGGING_H_

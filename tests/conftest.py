@@ -72,3 +72,11 @@ def gpu_handle(ops):
     h = ops.Handle(torch.cuda.current_stream().cuda_stream)
     yield h
     h.destroy()
+
+
+@pytest.fixture
+def guard_bands(ops):
+    """Every buffer the harness allocates during the test (outputs, workspace) is bracketed by
+    poisoned bands that are checked when the test ends (ops.Guards)."""
+    with ops.guarded() as guards:
+        yield guards

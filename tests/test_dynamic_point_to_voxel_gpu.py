@@ -7,7 +7,8 @@ import numpy as np
 import pytest
 import torch
 
-pytestmark = pytest.mark.gpu
+# guard_bands: outputs and workspaces of every call sit between poisoned bands, checked after the test
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("guard_bands")]
 
 
 @pytest.fixture(scope="module")

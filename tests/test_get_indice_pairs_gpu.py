@@ -6,7 +6,8 @@ import torch
 
 import helpers
 
-pytestmark = pytest.mark.gpu
+# guard_bands: outputs and workspaces of every call sit between poisoned bands, checked after the test
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("guard_bands")]
 
 
 def run_gpu(ops, handle, idx, g, out_rows=None):
@@ -295,3 +296,17 @@ def test_table_emitted_by_the_rulebook_equals_the_table_built_from_its_pairs(ops
             ops.get_indice_pairs(gpu_handle, conv, idx, with_table=True)
         assert err.value.status == ops.STATUS_NOT_SUPPORTED
         conv.destroy()
+
+
+def test_guard_bands_catch_a_stray_write(ops):
+    """The guard itself: a write one element past a guarded buffer, or one before it, is reported."""
+    for offset in (0, -1):
+        with pytest.raises(AssertionError):
+            with ops.guarded() as guards:
+                t = guards.empty((10, 4), torch.int32, "cuda")
+                flat = torch.as_strided(t, (1,), (1,), storage_offset=t.storage_offset() + (t.numel() if offset == 0 else -1))
+                flat.fill_(7)
+    with ops.guarded() as guards:
+        t = guards.empty((10, 4), torch.int32, "cuda")
+        t.fill_(7)
+    assert guards.check() == 1

@@ -9,7 +9,8 @@ import torch
 
 import helpers
 
-pytestmark = pytest.mark.gpu
+# guard_bands: outputs and workspaces of every call sit between poisoned bands, checked after the test
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("guard_bands")]
 
 
 def assert_close(oracle, got, ref, is_half):

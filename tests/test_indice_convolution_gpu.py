@@ -7,7 +7,8 @@ import torch
 
 import helpers
 
-pytestmark = pytest.mark.gpu
+# guard_bands: outputs and workspaces of every call sit between poisoned bands, checked after the test
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("guard_bands")]
 
 
 def oracle_conv(oracle, feat, w_array, layout, ks, pairs, num, n_out, co, is_half):

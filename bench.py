@@ -19,9 +19,10 @@ Printed (rank 0, one JSON line):
   cpu_baseline  the reference's CPU implementation of the path, one core, on a
              bounded sample (one sample of the workload)
 
---impl reference times the reference's own CPU code (oracle/_ref when it was
-built from the reference tree, else the C restatement in oracle/) on the host
-cores: the same metric, each step a bounded sample of the workload.
+--impl reference times the CPU implementation of the path on all host cores, on
+the same workload (the full batch, every sample at its full size): the C
+restatement built for speed as the line's value, and one pass of the
+reference's own single-threaded code (oracle/_ref) beside it.
 """
 import argparse
 import ctypes
@@ -792,21 +793,53 @@ def cpu_baseline_one_sample(workload):
                       (idx.shape[0], dt)}
 
 
-def _reference_worker(task):
-    workload, scale, seed, use_ref = task
-    import __graft_entry__ as entry
-    _, workloads, _ = entry.load_package()
+_REF_CACHE = {}
+
+
+def _reference_inputs(workload):
+    """The workload's full batch, split by sample (batch index relabelled to 0), cached per process."""
+    if workload not in _REF_CACHE:
+        import numpy as np
+        import __graft_entry__ as entry
+        _, workloads, _ = entry.load_package()
+        cfg = workloads.CONFIGS[workload]
+        idx, feat, layers, weights = workloads.make_inputs(workload)
+        samples = []
+        for b in range(cfg["batch"]):
+            rows = idx[:, 0] == b
+            local = idx[rows].copy()
+            local[:, 0] = 0
+            samples.append((np.ascontiguousarray(local), np.ascontiguousarray(feat[rows])))
+        _REF_CACHE[workload] = (samples, layers, weights, cfg["grid"])
+    return _REF_CACHE[workload]
+
+
+def _reference_sample(task):
+    """One full-size sample of the workload through the CPU layer stack.
+    mode "port": the C restatement, vectorised, the pairs of an offset shared among this
+    process's OpenMP threads.  mode "reference": the reference's own function bodies, one thread."""
+    workload, sample, mode = task
     from oracle import backbone_cpu
-    cfg = workloads.CONFIGS[workload]
-    idx, feat, layers, weights = workloads.make_inputs(workload, scale=scale, batch=1, seed=seed)
+    samples, layers, weights, grid = _reference_inputs(workload)
+    idx, feat = samples[sample % len(samples)]
     t0 = time.perf_counter()
-    backbone_cpu.run_layers(idx, feat, layers, weights, cfg["grid"], 1, True, use_ref=use_ref, fast=not use_ref)
+    if mode == "reference":
+        backbone_cpu.run_layers(idx, feat, layers, weights, grid, 1, True, use_ref=True)
+    else:
+        backbone_cpu.run_layers(idx, feat, layers, weights, grid, 1, True, threads=True)
     return idx.shape[0], time.perf_counter() - t0
 
 
 def run_reference(args):
-    """Reference arm: the reference's CPU code on all host cores; each step is one
-    reduced sample of the workload per worker process."""
+    """Reference arm: the CPU implementation of the path on all host cores, on the SAME
+    workload as the other arm (the full batch, every sample at its full size).
+
+    A step is one pass over the batch: one process per sample, the host's cores divided
+    among them as OpenMP threads, running the C restatement of the reference's CPU code
+    built for speed (-O3, AVX2, OpenMP; bit-identical to its scalar build).  That is the
+    line's `value` (kind "port").  The reference's own function bodies are single-threaded
+    and take about 35 s per sample, so they are timed beside it in one pass only
+    ("reference_code": one full-size sample per core, all cores busy)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -815,48 +848,66 @@ def run_reference(args):
     _, workloads, _ = entry.load_package()
     import oracle
     oracle.build()
-    kind, use_ref = cpu_backend()
     cores = os.cpu_count() or 1
-    try:
-        import psutil
-        cores = max(1, min(cores, int(psutil.virtual_memory().available / (2 << 30))))
-    except Exception:
-        pass
-    workers = min(cores, 64)
     cfg = workloads.CONFIGS[args.workload]
+    batch = cfg["batch"]
+    workers = max(1, min(batch, cores))
+    threads = max(1, cores // workers)
+    os.environ["OMP_NUM_THREADS"] = str(threads)  # inherited by the workers, read when OpenMP starts
     warmup = max(args.warmup, 1)
     ctx = mp.get_context("fork")
     times, voxels = [], 0
     with ctx.Pool(workers) as pool:
-        # Size the per-step sample so that the whole run stays within about three
-        # minutes: probe at 5% of a sample, then scale (cost grows roughly linearly).
-        t0 = time.perf_counter()
-        pool.map(_reference_worker, [(args.workload, 0.05, cfg["seed"] + w, use_ref) for w in range(workers)])
-        probe = time.perf_counter() - t0
-        scale = max(0.05, min(0.25, 0.05 * (180.0 / (warmup + args.steps)) / probe))
+        pool.map(_reference_inputs, [args.workload] * workers, chunksize=1)  # generate the inputs once per worker
+        # every step is the whole batch at full size; so that the run still ends within a few
+        # minutes, no more steps are timed than fit about 150 s (at least 3)
+        steps_timed = args.steps
         for step in range(warmup + args.steps):
-            tasks = [(args.workload, scale, cfg["seed"] + 7919 * (step * workers + w), use_ref)
-                     for w in range(workers)]
+            if step >= warmup + steps_timed:
+                break
             t0 = time.perf_counter()
-            results = pool.map(_reference_worker, tasks)
+            results = pool.map(_reference_sample, [(args.workload, b, "port") for b in range(batch)], chunksize=1)
             dt = time.perf_counter() - t0
+            if step == warmup - 1:
+                steps_timed = min(args.steps, max(3, int(150.0 / max(dt, 1e-3))))
             if step >= warmup:
                 times.append(dt)
                 voxels += sum(r[0] for r in results)
     total = sum(times)
     value = voxels / total
-    sample = ("per step %d worker processes, each one sample of the workload reduced to %d voxels (batch 1), "
-              "full 12-layer backbone" % (workers, int(round(cfg["per_sample"] * scale))))
+    sample = ("the full batch per step: %d samples x %d voxels, one process per sample with %d OpenMP threads each, "
+              "full 12-layer backbone" % (batch, cfg["per_sample"], threads))
     line = {
         "impl": "reference", "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": warmup, "ms_per_step": round(total / args.steps * 1e3, 2),
+        "steps": args.steps, "steps_timed": len(times), "warmup": warmup,
+        "ms_per_step": round(total / len(times) * 1e3, 2),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "%s: SECOND-style sparse backbone, reference CPU implementation; %s" %
-                               (args.workload, sample)},
-        "cpu_baseline": {"value": round(value, 1), "unit": UNIT, "cores": workers, "kind": kind, "sample": sample},
+        "config": {"workload": "%s: SECOND-style sparse backbone (12 convs, 8 rulebooks), batch %d x %d voxels, grid "
+                               "%dx%dx%d, CPU implementation of the reference's algorithm, fp32 arithmetic on "
+                               "half-rounded values" % (args.workload, batch, cfg["per_sample"], *cfg["grid"]),
+                   "voxels_per_step": batch * cfg["per_sample"]},
+        "cpu_baseline": {"value": round(value, 1), "unit": UNIT, "cores": workers * threads, "kind": "port",
+                         "sample": sample},
         "e2e": {"value": round(value, 1), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "host_cores": cores,
     }
+    if oracle.ref_lib() is not None and not args.no_reference_code:
+        procs = max(1, cores)
+        try:
+            import psutil
+            procs = max(1, min(procs, int(psutil.virtual_memory().available / (3 << 30))))
+        except Exception:
+            pass
+        os.environ["OMP_NUM_THREADS"] = "1"
+        with ctx.Pool(procs) as pool:
+            t0 = time.perf_counter()
+            results = pool.map(_reference_sample, [(args.workload, b, "reference") for b in range(procs)], chunksize=1)
+            dt = time.perf_counter() - t0
+        line["reference_code"] = {
+            "value": round(sum(r[0] for r in results) / dt, 1), "unit": UNIT, "cores": procs, "kind": "reference",
+            "per_core": round(sum(r[0] / r[1] for r in results) / procs, 1),
+            "sample": "one pass: %d processes, each one full-size sample (%d voxels) through the reference's own "
+                      "single-threaded function bodies, %.1f s" % (procs, cfg["per_sample"], dt)}
     print(json.dumps(line))
 
 
@@ -868,6 +919,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-code", action="store_true",
+                    help="--impl reference: skip the one-pass timing of the reference's own single-threaded code")
     ap.add_argument("--headline-only", action="store_true",
                     help="skip the c0 / c1 / c3 / c4 objects that the default line carries beside the c2 headline")
     ap.add_argument("--backward", action="store_true",

@@ -19,6 +19,7 @@ SRC = os.path.join(HERE, "sparse_conv_oracle.c")
 SRC_BACKWARD = os.path.join(HERE, "sparse_conv_backward_oracle.c")
 SRC_VOXEL = os.path.join(HERE, "voxelization_oracle.c")
 LIB = os.path.join(HERE, "_build", "libmluops_oracle.so")
+LIB_THREADS = os.path.join(HERE, "_build", "libmluops_oracle_threads.so")
 REF_LIB = os.path.join(HERE, "_ref", "libmluops_ref_cpu.so")
 
 _i32p = ctypes.POINTER(ctypes.c_int32)
@@ -36,7 +37,24 @@ def build(force=False):
     if force or not os.path.isfile(LIB) or os.path.getmtime(LIB) < newest:
         os.makedirs(os.path.dirname(LIB), exist_ok=True)
         subprocess.check_call(["gcc", "-O2", "-std=c11", "-fPIC", "-shared", "-o", LIB, SRC, SRC_BACKWARD, SRC_VOXEL, "-lm"])
+    if force or not os.path.isfile(LIB_THREADS) or os.path.getmtime(LIB_THREADS) < newest:
+        # the all-cores timing baseline: vectorised, OpenMP where the toolchain has it
+        base = ["gcc", "-O3", "-mavx2", "-mfma", "-std=c11", "-fPIC", "-shared", "-o", LIB_THREADS, SRC, "-lm"]
+        if subprocess.call(base[:1] + ["-fopenmp"] + base[1:], stderr=subprocess.DEVNULL) != 0:
+            subprocess.check_call(base)
     return LIB
+
+
+_threads_lib = None
+
+
+def threads_lib():
+    """The C restatement built for timing on all cores (-O3, AVX2, OpenMP)."""
+    global _threads_lib
+    if _threads_lib is None:
+        build()
+        _threads_lib = ctypes.CDLL(LIB_THREADS)
+    return _threads_lib
 
 
 _lib = None
@@ -120,12 +138,13 @@ def get_indice_pairs(indices, batch, pad, stride, dilation, filter_space, out_sp
 
 
 def indice_convolution_forward(features, filters, filter_layout, filter_space, indice_pairs,
-                               indice_num, num_act_out, co, use_ref=False, fast=False):
+                               indice_num, num_act_out, co, use_ref=False, fast=False, threads=False):
     """features_out [num_act_out, co] float32, accumulated in the reference order.
 
     features/filters are float32 arrays holding the values the device sees (for
     a half device dtype: already rounded through half).  `fast` drops the
-    product-rounding barrier (timed baseline only; filters must be ARRAY layout).
+    product-rounding barrier and `threads` also shares the pairs of an offset among
+    OpenMP threads (timed baselines only; filters must be ARRAY layout).
     """
     features = np.ascontiguousarray(features, dtype=np.float32)
     filters = np.ascontiguousarray(filters, dtype=np.float32)
@@ -143,6 +162,12 @@ def indice_convolution_forward(features, filters, filter_layout, filter_space, i
             _p(features, _f32p), _p(filters, _f32p), ctypes.c_int32(code), _p(kdhw, _i32p),
             _p(pairs, _i32p), _p(num, _i64p), ctypes.c_int64(L), ctypes.c_int64(ci),
             ctypes.c_int64(co), ctypes.c_int64(num_act_out), _p(out, _f32p))
+    elif threads:
+        assert code == 0
+        rc = threads_lib().mluops_oracle_indice_convolution_forward_threads(
+            _p(features, _f32p), _p(filters, _f32p), _p(pairs, _i32p), _p(num, _i64p),
+            ctypes.c_int64(L), ctypes.c_int64(ci), ctypes.c_int64(co), ctypes.c_int64(K),
+            ctypes.c_int64(num_act_out), _p(out, _f32p))
     elif fast:
         assert code == 0
         rc = lib().mluops_oracle_indice_convolution_forward_fast(

@@ -14,7 +14,7 @@ def output_space(space, pad, stride, dilation, ks):
 
 
 def run_layers(indices, features, layers, weights, grid, batch, is_half=True, use_ref=False, fast=False,
-               timings=None):
+               timings=None, threads=False):
     """Returns (features_out float32 [N,Co], out_indices int32 [N,4], per-layer pair totals)."""
     import time
     space = list(grid)
@@ -34,7 +34,7 @@ def run_layers(indices, features, layers, weights, grid, batch, is_half=True, us
         pairs, out_idx, num, n_out, osp = rulebooks[ly.rulebook]
         t0 = time.perf_counter()
         out = indice_convolution_forward(feat, np.asarray(w, dtype=np.float32), "ARRAY", ly.filter_space, pairs,
-                                         num, n_out, ly.co, use_ref=use_ref, fast=fast)
+                                         num, n_out, ly.co, use_ref=use_ref, fast=fast, threads=threads)
         if timings is not None:
             timings["conv"] = timings.get("conv", 0.0) + time.perf_counter() - t0
         feat = round_through_half(out) if is_half else out

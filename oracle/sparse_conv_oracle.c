@@ -296,6 +296,38 @@ int mluops_oracle_indice_convolution_forward_fast(
   return 0;
 }
 
+/* The same loop nest with the pairs of one offset shared among OpenMP threads: a
+ * rulebook holds at most one pair per (offset, output row), so the pairs of one
+ * offset write disjoint rows and need no synchronisation; the offsets stay in
+ * order.  Timed all-cores baseline only (compiled with -fopenmp into a library of
+ * its own; without OpenMP the pragma is ignored). */
+int mluops_oracle_indice_convolution_forward_threads(
+    const float *features, const float *filters_kcico,
+    const int32_t *indice_pairs, const int64_t *indice_num, int64_t L,
+    int64_t ci, int64_t co, int64_t K, int64_t num_act_out,
+    float *features_out) {
+  memset(features_out, 0, sizeof(float) * (size_t)(num_act_out * co));
+  for (int64_t k = 0; k < K; ++k) {
+    const int32_t *in_row = indice_pairs + k * 2 * L;
+    const int32_t *out_row = in_row + L;
+    const int64_t pairs = indice_num[k];
+    const float *wk = filters_kcico + k * ci * co;
+#pragma omp parallel for schedule(static)
+    for (int64_t p = 0; p < pairs; ++p) {
+      const int64_t src = in_row[p], dst = out_row[p];
+      if (dst < 0 || src < 0) continue;
+      const float *f = features + src * ci;
+      float *o = features_out + dst * co;
+      for (int64_t c = 0; c < ci; ++c) {
+        const float a = f[c];
+        const float *wr = wk + c * co;
+        for (int64_t n = 0; n < co; ++n) o[n] += a * wr[n];
+      }
+    }
+  }
+  return 0;
+}
+
 /* ------------------------------------------------------------------ */
 /* float -> half bits (tools.cpp:460-505): round to nearest even in    */
 /* the normal range, saturate finite overflow to 0x7bff, round-half-up */

@@ -116,6 +116,58 @@ class ClockSampler:
 D2H_CHUNK_BYTES = int(os.environ.get("BENCH_D2H_CHUNK", 4 << 20))
 
 
+def gpu_cpu_affinity(gpu_index):
+    """CPU ids the driver reports as local to this GPU (`nvidia-smi topo -m`, column "CPU Affinity"), or None."""
+    try:
+        out = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=20).stdout
+    except (OSError, subprocess.SubprocessError):
+        return None
+    header = None
+    for line in out.splitlines():
+        cols = [c.strip() for c in line.split("\t") if c.strip()]
+        if not cols:
+            continue
+        if header is None and any(c.startswith("CPU Affinity") for c in cols):
+            header = cols
+            continue
+        if header is not None and cols[0] == "GPU%d" % gpu_index:
+            # data rows have one more leading column (the row label) than the header
+            at = [i for i, c in enumerate(header) if c.startswith("CPU Affinity")][0] + 1
+            if at >= len(cols):
+                return None
+            cpus = set()
+            for part in cols[at].split(","):
+                lo, _, hi = part.partition("-")
+                if lo.isdigit():
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+            return sorted(cpus) or None
+    return None
+
+
+def pin_rank_to_cores(local_rank, local_world, gpu_index):
+    """Binds this process to its share of the cores that are local to its GPU (falling back to an
+    even split of all cores), before any pinned host buffer is allocated, so that the buffers
+    land on that socket's memory.  Returns the description that goes into the JSON line."""
+    try:
+        allowed = sorted(os.sched_getaffinity(0))
+    except AttributeError:
+        return None
+    local = gpu_cpu_affinity(gpu_index)
+    local = [c for c in (local or []) if c in allowed]
+    if local:
+        # ranks whose GPUs share a socket share its cores: slice by position among them
+        share = max(1, len(local) // max(1, (local_world + 1) // 2))
+        first = (local_rank % max(1, len(local) // share)) * share
+        mine, how = local[first:first + share], "cores local to the GPU"
+    else:
+        share = max(1, len(allowed) // local_world)
+        mine, how = allowed[local_rank * share:(local_rank + 1) * share], "even split of all cores"
+    if not mine:
+        return None
+    os.sched_setaffinity(0, mine)
+    return "%s: %d-%d (%d)" % (how, mine[0], mine[-1], len(mine))
+
+
 def read_trace(ops):
     """Parses the library's kernel trace into {name: (launches, total_ms, bytes, flops)}."""
     lib = ops.lib()
@@ -143,6 +195,11 @@ def run_b200(args):
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path for the product)"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    pinned = None
+    if world > 1 and not args.no_pin_cores:
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        gpu_index = int(visible.split(",")[local_rank]) if visible else local_rank
+        pinned = pin_rank_to_cores(local_rank, int(os.environ.get("LOCAL_WORLD_SIZE", world)), gpu_index)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -232,14 +289,21 @@ def run_b200(args):
     out_pending = []
     e2e_state = {"i": 0}
 
+    copy_events = None  # e2e breakdown: [(kind, start event, end event)]
+
     def prefetch(slot):
         if buf_free[slot] is not None:
             s_in.wait_event(buf_free[slot])  # the step that last read this half has finished
         with torch.cuda.stream(s_in):
+            if copy_events is not None:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e0.record(s_in)
             d_in[slot][0].copy_(h_idx, non_blocking=True)
             d_in[slot][1].copy_(h_feat, non_blocking=True)
-            ev = torch.cuda.Event()
+            ev = torch.cuda.Event(enable_timing=copy_events is not None)
             ev.record(s_in)
+            if copy_events is not None:
+                copy_events.append(("h2d", e0, ev))
         in_ready[slot] = ev
 
     def read_back():
@@ -251,12 +315,19 @@ def run_b200(args):
                                  torch.empty(out_idx.shape, dtype=out_idx.dtype).pin_memory())
             s_out.wait_event(done)
             with torch.cuda.stream(s_out):
+                if copy_events is not None:
+                    e0 = torch.cuda.Event(enable_timing=True)
+                    e0.record(s_out)
                 # in pieces: the step's own small device -> host reads (rulebook counts) share the
                 # copy engine with this transfer and would otherwise wait for all of it
                 rows = max(1, D2H_CHUNK_BYTES // (out.shape[1] * elem))
                 for r0 in range(0, out.shape[0], rows):
                     host_out[key][0][r0:r0 + rows].copy_(out[r0:r0 + rows], non_blocking=True)
                 host_out[key][1].copy_(out_idx, non_blocking=True)
+                if copy_events is not None:
+                    e1 = torch.cuda.Event(enable_timing=True)
+                    e1.record(s_out)
+                    copy_events.append(("d2h", e0, e1))
             out.record_stream(s_out)
             out_idx.record_stream(s_out)
 
@@ -334,6 +405,61 @@ def run_b200(args):
         d2h[0] = nbytes
     e2e_ms = timed(e2e_once, args.steps)
     clocks = sampler.stop(t_begin, time.time()) if rank == 0 else None
+
+    if args.e2e_breakdown:
+        # Where an end-to-end step spends its time on this rank: host seconds per phase
+        # (perf_counter around the calls) and device time of the copies (events on their streams).
+        copy_events = []
+        net.timers = {}
+        host = {"prefetch_and_readback_enqueue_s": 0.0, "forward_s": 0.0, "gather_finish_s": 0.0, "step_s": 0.0}
+
+        def step_instrumented():
+            slot = e2e_state["i"] % 2
+            e2e_state["i"] += 1
+            t0 = time.perf_counter()
+            if in_ready[slot] is None:
+                prefetch(slot)
+            prefetch(1 - slot)
+            read_back()
+            stream.wait_event(in_ready[slot])
+            in_ready[slot] = None
+            idx_in, feat_in = d_in[slot]
+            t1 = time.perf_counter()
+            if args.no_gather:
+                out, out_idx, _ = net.forward(idx_in, feat_in)
+                t2 = t3 = time.perf_counter()
+            else:
+                out, out_idx, _ = net.forward(idx_in, feat_in, on_final_indices=gather.begin)
+                t2 = time.perf_counter()
+                gather.finish(out, wait=True)
+                t3 = time.perf_counter()
+            done = torch.cuda.Event()
+            done.record(stream)
+            buf_free[slot] = done
+            out_pending.append((out, out_idx, done, slot))
+            host["prefetch_and_readback_enqueue_s"] += t1 - t0
+            host["forward_s"] += t2 - t1
+            host["gather_finish_s"] += t3 - t2
+            host["step_s"] += time.perf_counter() - t0
+
+        region_ms = timed(step_instrumented, args.steps)
+        torch.cuda.synchronize()
+        sums = {"h2d": [], "d2h": []}
+        for kind, e0, e1 in copy_events:
+            sums[kind].append(e0.elapsed_time(e1))
+        n = args.steps
+        report = {"rank": rank, "world": world, "pinned": pinned, "steps": n, "e2e_ms_per_step": round(region_ms / n, 4),
+                  "host_ms_per_step": {k: round(v / n * 1e3, 4) for k, v in host.items()},
+                  "rulebook_wait_ms_per_step": round(net.timers.get("rulebook_wait_s", 0.0) / n * 1e3, 4),
+                  "h2d_ms": {"mean": round(sum(sums["h2d"]) / max(1, len(sums["h2d"])), 4),
+                             "max": round(max(sums["h2d"] or [0]), 4), "bytes": int(h_idx.numel() * 4 + h_feat.numel() * elem)},
+                  "d2h_ms": {"mean": round(sum(sums["d2h"]) / max(1, len(sums["d2h"])), 4),
+                             "max": round(max(sums["d2h"] or [0]), 4), "bytes": int(d2h[0])}}
+        net.timers = None
+        copy_events = None
+        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+        with open(os.path.join(ROOT, "gpurun_out", "e2e_breakdown_rank%d_of_%d.json" % (rank, world)), "w") as f:
+            json.dump(report, f)
 
     # traced pass: per-kernel durations (CUDA events around every launch) and launch counts
     ops.lib().mluOpTraceKernelReset()
@@ -439,7 +565,7 @@ def run_b200(args):
                 "h2d_bytes_per_step": int(h_idx.numel() * 4 + h_feat.numel() * elem) * world,
                 "d2h_bytes_per_step": int(d2h[0]), "ms_per_step": round(total_e2e / args.steps, 4)},
         "gpu_launches": int(gpu_launches),
-        "ranks_ms_per_step": ranks_ms, "host_cores": os.cpu_count(),
+        "ranks_ms_per_step": ranks_ms, "host_cores": os.cpu_count(), "rank0_cores": pinned,
         "clocks": clocks,
         "roofline": roofline,
         "roofline_whole_step": whole,
@@ -935,6 +1061,11 @@ def main():
                          "\"voxelization\" object to the JSON line")
     ap.add_argument("--serial-rulebooks", action="store_true",
                     help="run the rulebooks on the same stream as the convolutions instead of a second one")
+    ap.add_argument("--no-pin-cores", action="store_true",
+                    help="N>1: do not bind each rank to the cores local to its GPU")
+    ap.add_argument("--e2e-breakdown", action="store_true",
+                    help="also write gpurun_out/e2e_breakdown_rank<r>.json: where each rank's end-to-end step spends "
+                         "its host time (rulebook waits, library calls, copies) and how long its copies take")
     ap.add_argument("--no-gather", action="store_true",
                     help="diagnostic for N>1: skip the NCCL gather (independent replicas) to separate its cost "
                          "from host-side contention between the ranks' processes")

@@ -14,6 +14,7 @@ GPU.
 import contextlib
 import ctypes
 import sys
+import time
 
 import torch
 
@@ -110,6 +111,8 @@ class SparseNetwork:
         self.n_act = ctypes.c_int(0)
         self.size = ctypes.c_size_t(0)
         self.tables = {}  # neighbour tables of the current step's rulebooks (reuse_tables)
+        # {"rulebook_wait_s": host seconds spent waiting for rulebook counts, "steps": n}, or None (no timing)
+        self.timers = None
 
     def close(self):
         for d in [self.d_idx, self.d_pairs, self.d_out_idx, self.d_num, self.d_feat, self.d_fout] + self.d_filt:
@@ -188,7 +191,12 @@ class SparseNetwork:
                     # The convolution API takes indice_num as a host array, so the rulebook writes it
                     # straight into pinned host memory (device-accessible under unified addressing):
                     # no copy is queued on the copy engines, only the rulebook's stream has to drain.
+                    if self.timers is not None:
+                        t_wait = time.perf_counter()
                     torch.cuda.current_stream().synchronize()
+                    if self.timers is not None:
+                        self.timers["rulebook_wait_s"] = self.timers.get("rulebook_wait_s", 0.0) + \
+                            time.perf_counter() - t_wait
                 if second:
                     # allocated on the rulebook stream, read by the convolutions on the other one
                     pairs.record_stream(compute)

@@ -1,0 +1,35 @@
+"""The hardware fact the convolution kernel's roofline rests on (tests/microbench/umma_rate.cu):
+a tcgen05.mma with both operands in shared memory costs max(math, operand bytes / 128 B per
+clock), so M128 x N64 x K16 takes about 48 clocks (6 KB of operands) rather than the 32 of its
+flops, and only N = 256 is bound by the math.  The test compiles the microbenchmark, runs it
+(bounded waits, a few milliseconds of GPU time) and checks the measured clocks per MMA."""
+import os
+import re
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_mma_cost_follows_the_shared_memory_operand_bytes(tmp_path):
+    exe = str(tmp_path / "umma_rate")
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-o", exe,
+                           os.path.join(HERE, "microbench", "umma_rate.cu")])
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=300).stdout
+    rows = {}
+    for line in out.splitlines():
+        m = re.match(r"N=(\d+) ctas_per_sm=(\d+) clk_per_mma=([\d.]+) sm_clk_per_mma=([\d.]+) tflops=([\d.]+) err=(\d)", line)
+        assert m, line
+        assert m.group(6) == "0", line
+        rows[(int(m.group(1)), int(m.group(2)))] = (float(m.group(3)), float(m.group(4)), float(m.group(5)))
+    assert len(rows) == 14, out
+    one = {n: rows[(n, 1)][0] for n in (16, 32, 64, 128, 256)}
+    assert 44 <= one[64] <= 54, one       # 4 KB of A + 2 KB of B at 128 B per clock = 48, not the 32 of the math
+    assert 60 <= one[128] <= 70, one      # 8 KB of operands = 64 clocks = its math
+    assert 120 <= one[256] <= 136, one    # math-bound: 128 clocks
+    assert one[16] >= 40 and one[32] >= 40, one  # the A tile alone costs 32 clocks: small N buys nothing
+    # more resident CTAs do not raise an SM's rate at N = 64
+    assert rows[(64, 4)][1] >= 0.9 * rows[(64, 1)][1], rows

@@ -228,6 +228,16 @@ def run_b200(args):
     if not args.serial_rulebooks:
         rb_stream = torch.cuda.Stream(dev)
         rb_handle = ops.Handle(rb_stream.cuda_stream)
+    if args.config_only:
+        # one configuration alone (profiling captures of a small case): its object, nothing else
+        hbm_gbs, tensor_tflops, _ = measured_peaks()
+        env = dict(torch=torch, dist=dist, ops=ops, workloads=workloads, backbone=backbone, sharding=sharding,
+                   dev=dev, rank=rank, world=world, flush=torch.empty((256 << 20,), dtype=torch.uint8, device=dev),
+                   stream=stream, handle=handle, rb_handle=rb_handle, rb_stream=rb_stream, flush_at=0,
+                   pipelined=not args.no_pipeline and rb_handle is not None, hbm_gbs=hbm_gbs,
+                   tensor_tflops=tensor_tflops, fp32_tflops=64.0, batch_override=args.config_batch)
+        print(json.dumps({args.config_only: time_config(args.config_only, args.steps, env)}))
+        return
     net = backbone.SparseNetwork(handle, layers, weights, grid, batch, rulebook_handle=rb_handle,
                                  rulebook_stream=rb_stream)
 
@@ -268,8 +278,27 @@ def run_b200(args):
             gather.begin(out_idx, ready=done)
             gather.finish(out, wait=False, ready=done)
 
+    # A stream of batches is software-pipelined one level further (unless --no-pipeline): rulebooks
+    # depend only on coordinates, so the rulebooks of batch i+1 (their kernels on the second stream
+    # and the host waits for their counts) run while the convolutions of batch i, already enqueued,
+    # keep the first stream busy.  Every step still does one batch's rulebooks and one batch's
+    # convolutions inside the timed region; they just belong to neighbouring batches.
+    pipelined = not args.no_pipeline and rb_handle is not None
+    next_plan = {}
+
     def step_resident():
         """One step of a stream of batches."""
+        if pipelined:
+            plan = next_plan.pop("resident", None) or net.plan_rulebooks(d_idx)
+            if world > 1 and not args.no_gather:
+                flush_pending()  # rows of the step before: their convolutions have long been enqueued
+            out, out_idx, records = net.run_convolutions(plan, d_feat)
+            if world > 1 and not args.no_gather:
+                done = torch.cuda.Event()
+                done.record(stream)
+                pending.append((out, out_idx, done))
+            next_plan["resident"] = net.plan_rulebooks(d_idx)
+            return records
         if args.no_gather or world == 1:  # --no-gather: diagnostic, nothing crosses NVLink
             return net.forward(d_idx, d_feat)[2]
         out, out_idx, records = net.forward(d_idx, d_feat, on_host_idle=flush_pending)
@@ -349,18 +378,31 @@ def run_b200(args):
             prefetch(slot)      # very first step: nothing was prefetched yet
         prefetch(1 - slot)      # inputs of the next step
         read_back()             # results of the previous step
-        stream.wait_event(in_ready[slot])
-        in_ready[slot] = None
         idx_in, feat_in = d_in[slot]
-        if args.no_gather:
-            out, out_idx, records = net.forward(idx_in, feat_in)
+        if pipelined:
+            plan = next_plan.pop(("e2e", slot), None) or net.plan_rulebooks(idx_in, ready=in_ready[slot])
+            stream.wait_event(in_ready[slot])
+            in_ready[slot] = None
+            if not args.no_gather:
+                gather.begin(plan.out_indices, ready=plan.done)  # the coordinates can leave before the convolutions
+            out, out_idx, records = net.run_convolutions(plan, feat_in)
+            if not args.no_gather:
+                gather.finish(out, wait=True)
         else:
-            out, out_idx, records = net.forward(idx_in, feat_in, on_final_indices=gather.begin)
-            gather.finish(out, wait=True)
+            stream.wait_event(in_ready[slot])
+            in_ready[slot] = None
+            if args.no_gather:
+                out, out_idx, records = net.forward(idx_in, feat_in)
+            else:
+                out, out_idx, records = net.forward(idx_in, feat_in, on_final_indices=gather.begin)
+                gather.finish(out, wait=True)
         done = torch.cuda.Event()
         done.record(stream)
         buf_free[slot] = done
         out_pending.append((out, out_idx, done, slot))
+        if pipelined:
+            # rulebooks of the next batch (its inputs are on their way since the start of this step)
+            next_plan[("e2e", 1 - slot)] = net.plan_rulebooks(d_in[1 - slot][0], ready=in_ready[1 - slot])
         return records, (out.shape[0] * out.shape[1] * elem + out_idx.shape[0] * 16)
 
     def timed(step, steps):
@@ -481,7 +523,7 @@ def run_b200(args):
         fp32_tflops = measure_fp32_fma_peak(torch, dev) if world == 1 else None
         env = dict(torch=torch, dist=dist, ops=ops, workloads=workloads, backbone=backbone, sharding=sharding,
                    dev=dev, rank=rank, world=world, flush=flush, stream=stream, handle=handle, rb_handle=rb_handle,
-                   rb_stream=rb_stream, flush_at=flush_at, hbm_gbs=hbm_gbs, tensor_tflops=tensor_tflops,
+                   rb_stream=rb_stream, flush_at=flush_at, pipelined=pipelined, hbm_gbs=hbm_gbs, tensor_tflops=tensor_tflops,
                    fp32_tflops=fp32_tflops)
         extra["c4"] = time_config("c4", max(5, args.steps // 2), env)
         if world == 1:
@@ -557,7 +599,9 @@ def run_b200(args):
                                (args.workload, batch, cfg["per_sample"], *grid),
                    "voxels_per_gpu": L, "l2": "flushed after every step (256 MiB write, inside the timed region)",
                    "rulebooks": "same stream as the convolutions" if args.serial_rulebooks else
-                                "second handle on a second stream, overlapping the convolutions of earlier layers",
+                                ("second handle on a second stream; the rulebooks of batch i+1 run during the "
+                                 "convolutions of batch i (every step holds one batch of each)" if pipelined else
+                                 "second handle on a second stream, overlapping the convolutions of earlier layers"),
                    "e2e_pipeline": "inputs of step i+1 and results of step i-1 are copied on two more streams while "
                                    "step i computes; every step's copies are inside the timed region",
                    "parallelism": ("batch samples per rank, NO gather (diagnostic)" if args.no_gather else "batch samples per rank; NCCL gather of final rows to rank 0 on a second stream, overlapping the next step") if world > 1 else "1 GPU"},
@@ -585,12 +629,19 @@ def run_b200(args):
                                          tensor_tflops)
     if world == 1 and args.fast_path:
         def step_fast():
-            net.forward(d_idx, d_feat, reuse_tables=True)
+            if pipelined:
+                plan = next_plan.pop("fast", None) or net.plan_rulebooks(d_idx, reuse_tables=True)
+                net.run_convolutions(plan, d_feat)
+                next_plan["fast"] = net.plan_rulebooks(d_idx, reuse_tables=True)
+            else:
+                net.forward(d_idx, d_feat, reuse_tables=True, defer_counts=True)
         for _ in range(3):
             step_fast()
         fast_ms = timed(step_fast, args.steps) / args.steps
         line["fast_path"] = {"ms_per_step": round(fast_ms, 4), "value": round(L / (fast_ms * 1e-3), 1), "unit": UNIT,
-                             "what": "one neighbour table per rulebook instead of one per convolution call"}
+                             "what": "one neighbour table per rulebook instead of one per convolution call; "
+                                     "submanifold rulebooks emit their table themselves and are not waited for "
+                                     "on the host"}
     if world == 1 and args.voxelization:
         line["voxelization"] = voxelization_step(args, ops, handle, flush, hbm_gbs)
     if world == 1 and not args.no_cpu_baseline:
@@ -649,7 +700,9 @@ def time_config(name, steps, env):
         # the shards of one fixed 16-sample job: rank r draws samples [r*batch, (r+1)*batch)
         idx_np, feat_np, layers, weights_np = workloads.make_inputs(name, batch=batch, first_sample=rank * batch)
     else:
-        idx_np, feat_np, layers, weights_np = workloads.make_inputs(name)
+        if env.get("batch_override"):
+            batch = int(env["batch_override"])
+        idx_np, feat_np, layers, weights_np = workloads.make_inputs(name, batch=batch)
     L = idx_np.shape[0]
     elem = feat_np.dtype.itemsize
     weights = [torch.from_numpy(w).to(dev) for w in weights_np]
@@ -665,7 +718,20 @@ def time_config(name, steps, env):
             gather.begin(out_idx, ready=done)
             gather.finish(out, wait=False, ready=done)
 
+    next_plan = {}
+
     def step():
+        if env["pipelined"]:  # rulebooks of the next batch during this batch's convolutions, as in the headline
+            plan = next_plan.pop("plan", None) or net.plan_rulebooks(d_idx)
+            if gather is not None:
+                flush_pending()
+            out, out_idx, records = net.run_convolutions(plan, d_feat)
+            if gather is not None:
+                done = torch.cuda.Event()
+                done.record(stream)
+                pending.append((out, out_idx, done))
+            next_plan["plan"] = net.plan_rulebooks(d_idx)
+            return records
         if gather is None:
             return net.forward(d_idx, d_feat)[2]
         out, out_idx, records = net.forward(d_idx, d_feat, on_host_idle=flush_pending)
@@ -719,6 +785,8 @@ def time_config(name, steps, env):
             times.append(t0.elapsed_time(t1))
         ms = sum(times) / len(times)
         timing = "mean of %d steps, each between its own events, L2 flushed between steps" % steps
+    if env["pipelined"]:
+        timing += "; rulebooks of batch i+1 during the convolutions of batch i"
 
     ops.lib().mluOpTraceKernelReset()
     ops.lib().mluOpTraceKernelEnable(1)
@@ -746,7 +814,7 @@ def time_config(name, steps, env):
     achieved = top_bytes / (top_ms * 1e-3) / 1e9
     return {
         "workload": "%s: batch %d x %d voxels%s, %s" % (
-            name, cfg["batch"], cfg["per_sample"], " split over %d ranks" % world if sharded and world > 1 else "",
+            name, batch * (world if sharded else 1), cfg["per_sample"], " split over %d ranks" % world if sharded and world > 1 else "",
             "12-layer backbone" if len(layers) > 1 else "one %s convolution %d -> %d, %s" % (
                 "submanifold" if layers[0].sub_m else "strided", layers[0].ci, layers[0].co, cfg["dtype"])),
         "value": round(L * world / (ms * 1e-3), 1) if sharded else round(L / (ms * 1e-3), 1), "unit": UNIT,
@@ -1045,6 +1113,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--config-only", default=None, choices=["c0", "c1", "c3", "c4"],
+                    help="time this configuration alone and print its object (profiling captures of a small case)")
+    ap.add_argument("--config-batch", type=int, default=None,
+                    help="with --config-only c0/c1/c3: number of samples instead of the configuration's own")
     ap.add_argument("--no-reference-code", action="store_true",
                     help="--impl reference: skip the one-pass timing of the reference's own single-threaded code")
     ap.add_argument("--headline-only", action="store_true",
@@ -1066,6 +1138,9 @@ def main():
     ap.add_argument("--e2e-breakdown", action="store_true",
                     help="also write gpurun_out/e2e_breakdown_rank<r>.json: where each rank's end-to-end step spends "
                          "its host time (rulebook waits, library calls, copies) and how long its copies take")
+    ap.add_argument("--no-pipeline", action="store_true",
+                    help="generate each batch's rulebooks inside its own step instead of during the convolutions of "
+                         "the batch before")
     ap.add_argument("--no-gather", action="store_true",
                     help="diagnostic for N>1: skip the NCCL gather (independent replicas) to separate its cost "
                          "from host-side contention between the ranks' processes")

@@ -45,6 +45,21 @@ class LayerRecord:
                  "features_out", "new_rulebook", "in_space", "out_space", "weights")
 
 
+class Rulebook:
+    """Outputs of one mluOpGetIndicePairs call as the driver keeps them."""
+    __slots__ = ("pairs", "out_indices", "indice_num", "n_out", "table", "in_space", "out_space", "in_indices")
+
+
+class RulebookPlan:
+    """All rulebooks of one batch (plan_rulebooks) for run_convolutions."""
+
+    def __init__(self):
+        self.rulebooks = {}
+        self.out_indices = None
+        self.reuse_tables = False
+        self.done = None
+
+
 class _Desc:
     """A tensor descriptor that lives as long as the driver; dims are re-set per call."""
 
@@ -106,11 +121,13 @@ class SparseNetwork:
             if not ly.sub_m:
                 space = self.geometry[ly.rulebook][2]
         max_k = max(ly.kernel_volume for ly in layers)
-        self.num_host = torch.empty((max_k,), dtype=torch.int32).pin_memory()
+        # one pinned row of counts per rulebook, so that a count that is read late is still there
+        self.num_slot = {name: i for i, name in enumerate(self.geometry)}
+        self.num_host = torch.empty((len(self.geometry), max_k), dtype=torch.int32).pin_memory()
+        self.zero_i64 = (ctypes.c_int64 * max_k)()
         self.num_i64 = (ctypes.c_int64 * max_k)()
         self.n_act = ctypes.c_int(0)
         self.size = ctypes.c_size_t(0)
-        self.tables = {}  # neighbour tables of the current step's rulebooks (reuse_tables)
         # {"rulebook_wait_s": host seconds spent waiting for rulebook counts, "steps": n}, or None (no timing)
         self.timers = None
 
@@ -120,7 +137,8 @@ class SparseNetwork:
         for conv, _, _ in self.geometry.values():
             conv.destroy()
 
-    def forward(self, indices, features, keep=False, on_final_indices=None, on_host_idle=None, reuse_tables=False):
+    def forward(self, indices, features, keep=False, on_final_indices=None, on_host_idle=None, reuse_tables=False,
+                defer_counts=False):
         """indices [L,4] int32, features [L,Cin] on the GPU.
         Returns (features_out, out_indices, records).
 
@@ -138,14 +156,18 @@ class SparseNetwork:
         reuse_tables: build the neighbour table of a rulebook once
         (mluOpBuildIndiceNeighbourTable) and run its convolutions through
         mluOpIndiceConvolutionForwardFromTable, instead of the reference-shaped
-        mluOpIndiceConvolutionForward that rebuilds the table in every call."""
-        lib, h = self.lib, self.handle.ptr
+        mluOpIndiceConvolutionForward that rebuilds the table in every call.
+
+        defer_counts (with reuse_tables): a submanifold rulebook that emits its own table needs
+        nothing from the host before its convolutions can be enqueued (the active outputs are the
+        inputs, the table is on the device), so the host does not wait for it: the convolutions
+        are ordered after it on the device, its records carry indice_num = None, and
+        resolve_counts(records) fills them in after the step."""
         second = self.rulebook_handle is not None
         compute = torch.cuda.current_stream()
         if second:
             # the coordinates are ready where the caller's stream is now
             self.rulebook_stream.wait_stream(compute)
-        hr = self.rulebook_handle.ptr if second else h
         final_rulebook = self.layers[-1].rulebook
         ready = None
         rulebooks = {}
@@ -153,117 +175,204 @@ class SparseNetwork:
         cur_idx, cur_feat = indices, features
         for li, (ly, w) in enumerate(zip(self.layers, self.weights)):
             new_rb = ly.rulebook not in rulebooks
-            conv, in_space, out_space = self.geometry[ly.rulebook]
-            K = ly.kernel_volume
             if new_rb:
-                L = cur_idx.shape[0]
-                out_rows = L if ly.sub_m else ops.max_active_outputs(L, self.batch, out_space, ly.filter_space,
-                                                                     ly.stride, ly.dilation)
-                d_in, d_pairs = self.d_idx.set(L, 4), self.d_pairs.set(K, 2, L)
-                d_out, d_num = self.d_out_idx.set(out_rows, 4), self.d_num.set(K)
                 if on_host_idle is not None:
                     on_host_idle(li)
-                table = None
-                with (torch.cuda.stream(self.rulebook_stream) if second else contextlib.nullcontext()):
-                    pairs = torch.empty((K, 2, L), dtype=torch.int32, device=self.device)
-                    out_idx = torch.empty((out_rows, 4), dtype=torch.int32, device=self.device)
-                    ops.check("mluOpGetIndicePairsWorkspaceSize",
-                              lib.mluOpGetIndicePairsWorkspaceSize(hr, conv.ptr, d_in, d_pairs, d_out, d_num,
-                                                                   ctypes.byref(self.size)))
-                    ws_bytes = self.size.value
-                    ws = (self.rulebook_workspace if second else self.workspace).get(ws_bytes)
-                    args = [hr, conv.ptr, d_in, _vp(cur_idx.data_ptr()), _vp(ws.data_ptr()), ws_bytes, d_pairs,
-                            _vp(pairs.data_ptr()), d_out, _vp(out_idx.data_ptr()), d_num,
-                            _vp(self.num_host.data_ptr())]
-                    st = ops.STATUS_NOT_SUPPORTED
-                    if reuse_tables and ly.sub_m:
-                        # submanifold rulebooks leave their neighbour table behind themselves
-                        ops.check("mluOpGetIndiceNeighbourTableSize",
-                                  lib.mluOpGetIndiceNeighbourTableSize(hr, d_pairs, L, ctypes.byref(self.size)))
-                        table = torch.empty((max(self.size.value, 16),), dtype=torch.uint8, device=self.device)
-                        st = lib.mluOpGetIndicePairsWithNeighbourTable(*args, _vp(table.data_ptr()), table.numel())
-                        if st == ops.STATUS_NOT_SUPPORTED:
-                            table = None
-                        else:
-                            ops.check("mluOpGetIndicePairsWithNeighbourTable", st)
-                    if table is None:
-                        ops.check("mluOpGetIndicePairs", lib.mluOpGetIndicePairs(*args))
-                    # The convolution API takes indice_num as a host array, so the rulebook writes it
-                    # straight into pinned host memory (device-accessible under unified addressing):
-                    # no copy is queued on the copy engines, only the rulebook's stream has to drain.
-                    if self.timers is not None:
-                        t_wait = time.perf_counter()
-                    torch.cuda.current_stream().synchronize()
-                    if self.timers is not None:
-                        self.timers["rulebook_wait_s"] = self.timers.get("rulebook_wait_s", 0.0) + \
-                            time.perf_counter() - t_wait
-                if second:
-                    # allocated on the rulebook stream, read by the convolutions on the other one
-                    pairs.record_stream(compute)
-                    out_idx.record_stream(compute)
-                    if table is not None:
-                        table.record_stream(compute)
-                lib.mluOpGetSparseConvolutionNumActOut(conv.ptr, ctypes.byref(self.n_act))
-                num_list = self.num_host[:K].tolist()
-                if reuse_tables and table is None:
-                    for i, v in enumerate(num_list):
-                        self.num_i64[i] = v
-                    d_p = self.d_pairs.set(K, 2, L)
-                    ops.check("mluOpGetIndiceNeighbourTableSize",
-                              lib.mluOpGetIndiceNeighbourTableSize(h, d_p, self.n_act.value, ctypes.byref(self.size)))
-                    table = torch.empty((max(self.size.value, 16),), dtype=torch.uint8, device=self.device)
-                    ops.check("mluOpBuildIndiceNeighbourTable",
-                              lib.mluOpBuildIndiceNeighbourTable(h, d_p, _vp(pairs.data_ptr()), self.num_i64,
-                                                                 self.n_act.value, _vp(table.data_ptr()),
-                                                                 table.numel()))
-                self.tables[ly.rulebook] = table
-                rulebooks[ly.rulebook] = (pairs, out_idx, num_list, self.n_act.value)
+                rulebooks[ly.rulebook] = self._generate_rulebook(ly, cur_idx, compute, reuse_tables, defer_counts)
                 if on_final_indices is not None and ly.rulebook == final_rulebook:
                     ready = torch.cuda.Event()
                     ready.record(self.rulebook_stream if second else compute)
-            pairs, out_idx, num_list, n_out = rulebooks[ly.rulebook]
-            L = cur_feat.shape[0]
-            for i, v in enumerate(num_list):
-                self.num_i64[i] = v
-            out = torch.empty((n_out, ly.co), dtype=cur_feat.dtype, device=self.device)
-            d_f, d_p, d_o = self.d_feat.set(L, ly.ci), self.d_pairs.set(K, 2, L), self.d_fout.set(n_out, ly.co)
-            d_w = self.d_filt[li].ptr
-            table = self.tables.get(ly.rulebook) if reuse_tables else None
-            if table is not None:
-                ops.check("mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize",
-                          lib.mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize(
-                              h, d_f, d_w, d_p, d_o, self.num_i64, n_out, 0, ly.sub_m, ctypes.byref(self.size)))
-                ws = self.workspace.get(self.size.value)
-                ops.check("mluOpIndiceConvolutionForwardFromTable",
-                          lib.mluOpIndiceConvolutionForwardFromTable(
-                              h, d_f, _vp(cur_feat.data_ptr()), d_w, _vp(w.data_ptr()), d_p, _vp(table.data_ptr()),
-                              table.numel(), self.num_i64, n_out, 0, ly.sub_m, _vp(ws.data_ptr()), self.size.value,
-                              d_o, _vp(out.data_ptr())))
-            else:
-                ops.check("mluOpGetIndiceConvolutionForwardWorkspaceSize",
-                          lib.mluOpGetIndiceConvolutionForwardWorkspaceSize(h, d_f, d_w, d_p, d_o, self.num_i64,
-                                                                            n_out, 0, ly.sub_m,
-                                                                            ctypes.byref(self.size)))
-                ws = self.workspace.get(self.size.value)
-                ops.check("mluOpIndiceConvolutionForward",
-                          lib.mluOpIndiceConvolutionForward(h, d_f, _vp(cur_feat.data_ptr()), d_w, _vp(w.data_ptr()),
-                                                            d_p, _vp(pairs.data_ptr()), self.num_i64, n_out, 0,
-                                                            ly.sub_m, _vp(ws.data_ptr()), self.size.value, d_o,
-                                                            _vp(out.data_ptr())))
-            rec = LayerRecord()
-            rec.layer, rec.n_in, rec.n_out, rec.indice_num, rec.new_rulebook = ly, L, n_out, num_list, new_rb
-            if keep:
-                rec.pairs, rec.in_indices, rec.out_indices = pairs, cur_idx, out_idx[:n_out]
-                rec.features_in, rec.features_out = cur_feat, out
-                rec.in_space, rec.out_space = list(in_space), list(out_space)
-            records.append(rec)
+            rb = rulebooks[ly.rulebook]
+            out = self._convolve(li, ly, w, cur_feat, rb, reuse_tables)
+            records.append(self._record(ly, cur_feat, out, cur_idx, rb, new_rb, keep))
             cur_feat = out
             if not ly.sub_m:
-                cur_idx = out_idx[:n_out]
+                cur_idx = rb.out_indices[:rb.n_out]
             if ready is not None:
                 on_final_indices(cur_idx, ready)
                 ready = None
         return cur_feat, cur_idx, records
+
+    def plan_rulebooks(self, indices, ready=None, reuse_tables=False):
+        """Every rulebook of the layer list from the input coordinates alone (rulebooks never
+        depend on features), on the rulebook stream when the driver has one; the host waits
+        there for the counts the API hands back.  `ready` (a CUDA event, optional) marks the
+        point after which `indices` is valid; without it the caller guarantees that it already
+        is.  Returns a plan for run_convolutions().  A serving loop calls this for batch i+1
+        right after it has enqueued run_convolutions() of batch i, so that the rulebook
+        kernels and the host waits of one batch overlap the convolutions of the one before."""
+        second = self.rulebook_handle is not None
+        compute = torch.cuda.current_stream()
+        if ready is not None:
+            (self.rulebook_stream if second else compute).wait_event(ready)
+        plan = RulebookPlan()
+        cur_idx = indices
+        for ly in self.layers:
+            if ly.rulebook not in plan.rulebooks:
+                rb = self._generate_rulebook(ly, cur_idx, compute, reuse_tables, False, record_for=None)
+                rb.in_indices = cur_idx
+                plan.rulebooks[ly.rulebook] = rb
+            if not ly.sub_m:
+                rb = plan.rulebooks[ly.rulebook]
+                cur_idx = rb.out_indices[:rb.n_out]
+        plan.out_indices = cur_idx
+        plan.reuse_tables = reuse_tables
+        plan.done = torch.cuda.Event()
+        plan.done.record(self.rulebook_stream if second else compute)
+        return plan
+
+    def run_convolutions(self, plan, features, keep=False):
+        """The convolutions of the layer list on the current stream, from a plan of
+        plan_rulebooks(); nothing here waits on the host.  Returns (features_out, out_indices,
+        records)."""
+        compute = torch.cuda.current_stream()
+        compute.wait_event(plan.done)
+        records, seen = [], set()
+        cur_feat = features
+        for li, (ly, w) in enumerate(zip(self.layers, self.weights)):
+            rb = plan.rulebooks[ly.rulebook]
+            for t in (rb.pairs, rb.out_indices, rb.table):
+                if t is not None and self.rulebook_handle is not None:
+                    t.record_stream(compute)
+            out = self._convolve(li, ly, w, cur_feat, rb, plan.reuse_tables)
+            records.append(self._record(ly, cur_feat, out, rb.in_indices, rb, ly.rulebook not in seen, keep))
+            seen.add(ly.rulebook)
+            cur_feat = out
+        return cur_feat, plan.out_indices, records
+
+    def _generate_rulebook(self, ly, cur_idx, compute, reuse_tables, defer_counts, record_for="compute"):
+        """One mluOpGetIndicePairs call (or its table-emitting extension) and the host read of
+        its counts.  record_for="compute": the outputs, allocated on the rulebook stream, are
+        marked as used by `compute` right away (forward()); None: the caller does that."""
+        lib, h = self.lib, self.handle.ptr
+        second = self.rulebook_handle is not None
+        hr = self.rulebook_handle.ptr if second else h
+        conv, in_space, out_space = self.geometry[ly.rulebook]
+        K = ly.kernel_volume
+        L = cur_idx.shape[0]
+        out_rows = L if ly.sub_m else ops.max_active_outputs(L, self.batch, out_space, ly.filter_space, ly.stride,
+                                                             ly.dilation)
+        d_in, d_pairs = self.d_idx.set(L, 4), self.d_pairs.set(K, 2, L)
+        d_out, d_num = self.d_out_idx.set(out_rows, 4), self.d_num.set(K)
+        table = None
+        slot = self.num_host[self.num_slot[ly.rulebook]]
+        with (torch.cuda.stream(self.rulebook_stream) if second else contextlib.nullcontext()):
+            pairs = torch.empty((K, 2, L), dtype=torch.int32, device=self.device)
+            out_idx = torch.empty((out_rows, 4), dtype=torch.int32, device=self.device)
+            ops.check("mluOpGetIndicePairsWorkspaceSize",
+                      lib.mluOpGetIndicePairsWorkspaceSize(hr, conv.ptr, d_in, d_pairs, d_out, d_num,
+                                                           ctypes.byref(self.size)))
+            ws_bytes = self.size.value
+            ws = (self.rulebook_workspace if second else self.workspace).get(ws_bytes)
+            args = [hr, conv.ptr, d_in, _vp(cur_idx.data_ptr()), _vp(ws.data_ptr()), ws_bytes, d_pairs,
+                    _vp(pairs.data_ptr()), d_out, _vp(out_idx.data_ptr()), d_num, _vp(slot.data_ptr())]
+            if reuse_tables and ly.sub_m:
+                # submanifold rulebooks leave their neighbour table behind themselves
+                ops.check("mluOpGetIndiceNeighbourTableSize",
+                          lib.mluOpGetIndiceNeighbourTableSize(hr, d_pairs, L, ctypes.byref(self.size)))
+                table = torch.empty((max(self.size.value, 16),), dtype=torch.uint8, device=self.device)
+                st = lib.mluOpGetIndicePairsWithNeighbourTable(*args, _vp(table.data_ptr()), table.numel())
+                if st == ops.STATUS_NOT_SUPPORTED:
+                    table = None
+                else:
+                    ops.check("mluOpGetIndicePairsWithNeighbourTable", st)
+            if table is None:
+                ops.check("mluOpGetIndicePairs", lib.mluOpGetIndicePairs(*args))
+            deferred = defer_counts and table is not None
+            if deferred:
+                if second:  # order the convolutions after the rulebook on the device
+                    done = torch.cuda.Event()
+                    done.record(self.rulebook_stream)
+                    compute.wait_event(done)
+            else:
+                # The convolution API takes indice_num as a host array, so the rulebook writes it
+                # straight into pinned host memory (device-accessible under unified addressing):
+                # no copy is queued on the copy engines, only the rulebook's stream has to drain.
+                if self.timers is not None:
+                    t_wait = time.perf_counter()
+                torch.cuda.current_stream().synchronize()
+                if self.timers is not None:
+                    self.timers["rulebook_wait_s"] = self.timers.get("rulebook_wait_s", 0.0) + \
+                        time.perf_counter() - t_wait
+        lib.mluOpGetSparseConvolutionNumActOut(conv.ptr, ctypes.byref(self.n_act))
+        n_out = self.n_act.value
+        num_list = None if deferred else slot[:K].tolist()
+        if reuse_tables and table is None:
+            # (built on the convolutions' stream, where the rulebook is complete: the host has waited for it)
+            for i, v in enumerate(num_list):
+                self.num_i64[i] = v
+            with (torch.cuda.stream(self.rulebook_stream) if second and record_for is None
+                  else contextlib.nullcontext()):
+                ops.check("mluOpGetIndiceNeighbourTableSize",
+                          lib.mluOpGetIndiceNeighbourTableSize(h, d_pairs, n_out, ctypes.byref(self.size)))
+                table = torch.empty((max(self.size.value, 16),), dtype=torch.uint8, device=self.device)
+                ops.check("mluOpBuildIndiceNeighbourTable",
+                          lib.mluOpBuildIndiceNeighbourTable(hr if second and record_for is None else h, d_pairs,
+                                                             _vp(pairs.data_ptr()), self.num_i64, n_out,
+                                                             _vp(table.data_ptr()), table.numel()))
+        if second and record_for == "compute":
+            # allocated on the rulebook stream, read by the convolutions on the other one
+            for t in (pairs, out_idx, table):
+                if t is not None:
+                    t.record_stream(compute)
+        rb = Rulebook()
+        rb.pairs, rb.out_indices, rb.indice_num, rb.n_out, rb.table = pairs, out_idx, num_list, n_out, table
+        rb.in_space, rb.out_space, rb.in_indices = list(in_space), list(out_space), cur_idx
+        return rb
+
+    def _convolve(self, li, ly, w, cur_feat, rb, reuse_tables):
+        """One mluOpIndiceConvolutionForward call (or its from-table extension) on the current stream."""
+        lib, h = self.lib, self.handle.ptr
+        K, L, n_out = ly.kernel_volume, cur_feat.shape[0], rb.n_out
+        # (a convolution from a table reads the pairs from the table: the counts it is handed
+        # only size its trace accounting, so a rulebook that was not waited for passes zeros)
+        for i, v in enumerate(rb.indice_num if rb.indice_num is not None else self.zero_i64[:K]):
+            self.num_i64[i] = v
+        out = torch.empty((n_out, ly.co), dtype=cur_feat.dtype, device=self.device)
+        d_f, d_p, d_o = self.d_feat.set(L, ly.ci), self.d_pairs.set(K, 2, L), self.d_fout.set(n_out, ly.co)
+        d_w = self.d_filt[li].ptr
+        table = rb.table if reuse_tables else None
+        if table is not None:
+            ops.check("mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize",
+                      lib.mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize(
+                          h, d_f, d_w, d_p, d_o, self.num_i64, n_out, 0, ly.sub_m, ctypes.byref(self.size)))
+            ws = self.workspace.get(self.size.value)
+            ops.check("mluOpIndiceConvolutionForwardFromTable",
+                      lib.mluOpIndiceConvolutionForwardFromTable(
+                          h, d_f, _vp(cur_feat.data_ptr()), d_w, _vp(w.data_ptr()), d_p, _vp(table.data_ptr()),
+                          table.numel(), self.num_i64, n_out, 0, ly.sub_m, _vp(ws.data_ptr()), self.size.value,
+                          d_o, _vp(out.data_ptr())))
+        else:
+            ops.check("mluOpGetIndiceConvolutionForwardWorkspaceSize",
+                      lib.mluOpGetIndiceConvolutionForwardWorkspaceSize(h, d_f, d_w, d_p, d_o, self.num_i64, n_out, 0,
+                                                                        ly.sub_m, ctypes.byref(self.size)))
+            ws = self.workspace.get(self.size.value)
+            ops.check("mluOpIndiceConvolutionForward",
+                      lib.mluOpIndiceConvolutionForward(h, d_f, _vp(cur_feat.data_ptr()), d_w, _vp(w.data_ptr()), d_p,
+                                                        _vp(rb.pairs.data_ptr()), self.num_i64, n_out, 0, ly.sub_m,
+                                                        _vp(ws.data_ptr()), self.size.value, d_o,
+                                                        _vp(out.data_ptr())))
+        return out
+
+    def _record(self, ly, features_in, features_out, in_indices, rb, new_rb, keep):
+        rec = LayerRecord()
+        rec.layer, rec.n_in, rec.n_out = ly, features_in.shape[0], rb.n_out
+        rec.indice_num, rec.new_rulebook = rb.indice_num, new_rb
+        if keep:
+            rec.pairs, rec.in_indices, rec.out_indices = rb.pairs, in_indices, rb.out_indices[:rb.n_out]
+            rec.features_in, rec.features_out = features_in, features_out
+            rec.in_space, rec.out_space = list(rb.in_space), list(rb.out_space)
+        return rec
+
+    def resolve_counts(self, records):
+        """Fills in the pair counts of records whose rulebook was not waited for (defer_counts);
+        waits for the device first."""
+        torch.cuda.synchronize(self.device)
+        for rec in records:
+            if rec.indice_num is None:
+                K = rec.layer.kernel_volume
+                rec.indice_num = self.num_host[self.num_slot[rec.layer.rulebook], :K].tolist()
+        return records
 
     def backward(self, records, grad_out):
         """Gradients of the layer stack, last layer first, from the records of

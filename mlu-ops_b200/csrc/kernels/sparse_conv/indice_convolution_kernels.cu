@@ -55,29 +55,34 @@ struct PairCounts {
 
 // ------------------------------------------------------------ preparation
 
+// dst is [K][n_dst][c_dst]: n the produced channel, c the contracted channel of this
+// direction (forward: n = Co, c = Ci; input gradient, `swap`: n = Ci, c = Co), zero where
+// n >= n_real or c >= c_real (channel counts padded for the tensor-core kernel).
 template <typename T>
 __global__ void __launch_bounds__(256)
-repackFilterKernel(const T *__restrict__ src, T *__restrict__ dst, int K, int ci, int co, int layout,
-                   int co_innermost) {
-  // dst is [K][Co][Ci], or [K][Ci][Co] when co_innermost is set
-  const int64_t total = (int64_t)K * ci * co;
-  const int inner = co_innermost ? co : ci, mid = co_innermost ? ci : co;
+repackFilterKernel(const T *__restrict__ src, T *__restrict__ dst, int K, int ci, int co, int layout, int swap,
+                   int n_dst, int c_dst) {
+  const int64_t total = (int64_t)K * n_dst * c_dst;
+  const int n_real = swap ? ci : co, c_real = swap ? co : ci;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
-    const int a = (int)(i % inner);
-    const int b = (int)((i / inner) % mid);
-    const int c = co_innermost ? b : a;
-    const int o = co_innermost ? a : b;
-    const int k = (int)(i / ((int64_t)ci * co));
-    int64_t s;
-    if (layout == kFilterArray) {
-      s = ((int64_t)k * ci + c) * co + o;  // [K][Ci][Co]
-    } else if (layout == kFilterNDHWC) {
-      s = ((int64_t)o * K + k) * ci + c;  // [Co][K][Ci]
-    } else {
-      s = ((int64_t)o * ci + c) * K + k;  // [Co][Ci][K]
+    const int c = (int)(i % c_dst);
+    const int n = (int)((i / c_dst) % n_dst);
+    const int k = (int)(i / ((int64_t)n_dst * c_dst));
+    T v = T(0.f);
+    if (n < n_real && c < c_real) {
+      const int in_ch = swap ? n : c, out_ch = swap ? c : n;  // the caller's Ci and Co indices
+      int64_t s;
+      if (layout == kFilterArray) {
+        s = ((int64_t)k * ci + in_ch) * co + out_ch;  // [K][Ci][Co]
+      } else if (layout == kFilterNDHWC) {
+        s = ((int64_t)out_ch * K + k) * ci + in_ch;  // [Co][K][Ci]
+      } else {
+        s = ((int64_t)out_ch * ci + in_ch) * K + k;  // [Co][Ci][K]
+      }
+      v = src[s];
     }
-    dst[i] = src[s];
+    dst[i] = v;
   }
 }
 
@@ -455,7 +460,10 @@ ConvWorkspacePlan planConvWorkspace(const ConvProblem &p, bool external_table) {
   plan.status = off;
   off = alignUp(off + 64 * sizeof(int32_t), 256);
   plan.filter = off;
-  off = alignUp(off + (size_t)p.K * p.ci * p.co * elem, 256);
+  // room for the channel counts the tensor-core kernel pads to
+  const size_t ci_room = p.is_half && tcgen05PaddedChannels(p.ci) ? tcgen05PaddedChannels(p.ci) : p.ci;
+  const size_t co_room = p.is_half && tcgen05PaddedChannels(p.co) ? tcgen05PaddedChannels(p.co) : p.co;
+  off = alignUp(off + (size_t)p.K * ci_room * co_room * elem, 256);
   plan.neighbour = off;
   if (!external_table) off = alignUp(off + (size_t)p.K * plan.n_pad * sizeof(int32_t), 256);
   plan.counts = off;
@@ -513,19 +521,31 @@ cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWo
   const double conv_bytes = pairs_total * ((p.ci + p.co) * elem + 8.0);
   const double conv_flops = 2.0 * pairs_total * p.ci * p.co;
 
-  // 1. filter -> [K][Co][Ci]
+  // Half with channel counts that are multiples of 8 up to 128 runs on the tcgen05 tensor
+  // cores (odd counts at the next of 16/32/64/128, zero padded); MLUOP_B200_CONV_KERNEL=mma
+  // selects the mma.sync variant instead (kept for cross-checking), =fma the plain FMA kernels.
+  static const char *forced = std::getenv("MLUOP_B200_CONV_KERNEL");
+  const bool force_mma = forced && std::strcmp(forced, "mma") == 0;
+  const bool force_fma = forced && std::strcmp(forced, "fma") == 0;
+  const bool use_tc = do_conv && !force_mma && !force_fma && tcgen05Eligible(p, features, features_out);
+
+  // 1. filter -> [K][Co][Ci] (channel counts padded for the tensor-core kernel)
   if (do_conv) {
-    const int64_t total = (int64_t)p.K * p.ci * p.co;
+    const int n_dst = use_tc ? tcgen05PaddedChannels(p.co) : p.co;
+    const int c_dst = use_tc ? tcgen05PaddedChannels(p.ci) : p.ci;
+    const int64_t total = (int64_t)p.K * n_dst * c_dst;
     const unsigned blocks = (unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
     trace::Scope t("repackFilterKernel", stream, 2.0 * total * elem);
     if (p.is_half) {
       repackFilterKernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half *>(filters),
                                                              static_cast<__half *>(filter_packed), p.K,
-                                                             caller.ci, caller.co, p.filter_layout, swap);
+                                                             caller.ci, caller.co, p.filter_layout, swap, n_dst,
+                                                             c_dst);
     } else {
       repackFilterKernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float *>(filters),
                                                             static_cast<float *>(filter_packed), p.K,
-                                                            caller.ci, caller.co, p.filter_layout, swap);
+                                                            caller.ci, caller.co, p.filter_layout, swap, n_dst,
+                                                            c_dst);
     }
   }
 
@@ -561,13 +581,8 @@ cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWo
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
   if (!do_conv) return cudaSuccess;
 
-  // 3. convolution.  Half with channel counts 16/32/64/128 runs on the tcgen05
-  // tensor cores; MLUOP_B200_CONV_KERNEL=mma selects the mma.sync variant instead
-  // (kept for cross-checking), =fma the plain FMA kernels.
-  static const char *forced = std::getenv("MLUOP_B200_CONV_KERNEL");
-  const bool force_mma = forced && std::strcmp(forced, "mma") == 0;
-  const bool force_fma = forced && std::strcmp(forced, "fma") == 0;
-  if (!force_mma && !force_fma && tcgen05Eligible(p, features, features_out)) {
+  // 3. convolution
+  if (use_tc) {
     return launchConvTcgen05(p, plan, static_cast<const __half *>(features),
                              static_cast<const __half *>(filter_packed), nbr,
                              static_cast<__half *>(features_out), status, conv_bytes, conv_flops, stream);

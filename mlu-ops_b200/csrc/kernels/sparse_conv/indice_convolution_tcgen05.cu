@@ -44,7 +44,8 @@ namespace {
 constexpr int kTile = kConvTileRows;      // 128 output rows = 128 TMEM lanes
 constexpr int kProducerThreads = 128;     // warps 0-3: gather, then epilogue
 constexpr int kThreads = 160;             // + warp 4: TMEM allocation and MMA issue
-constexpr int kMaxOffsets = 32;
+constexpr int kMaxOffsets = 128;           // kernel volumes up to 5x5x5
+constexpr int kMaskWords = kMaxOffsets / 32;
 constexpr long long kWaitCycles = 2000000000ll;  // a wait gives up after about one second
 
 __device__ __forceinline__ unsigned smemAddr(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -186,15 +187,18 @@ __device__ __forceinline__ unsigned long long makeDesc(unsigned smem_byte_addr) 
 
 // Work items of a block: (offset k ascending, tile t ascending) for which the
 // tile has at least one live row at k.  The list is built once per block in
-// shared memory, one byte per item: bit 7 = first item of its offset, bits 2..6
-// = k, bits 0..1 = t.  Producers and the MMA issuer walk the same list.
-constexpr int kMaxItems = 4 * kMaxOffsets;
+// shared memory, two bytes per item: bit 15 = first item of its offset, bits
+// 2..14 = k, bits 0..1 = t.  Producers and the MMA issuer walk the same list.
+constexpr int kMaxItems = 2 * kMaxOffsets;
+constexpr unsigned kItemFirst = 0x8000u;
+__device__ __forceinline__ int itemOffset(unsigned code) { return (int)((code >> 2) & 0x1FFFu); }
+__device__ __forceinline__ int itemTile(unsigned code) { return (int)(code & 3u); }
 
 template <int CI, int CO>
 __global__ void __launch_bounds__(kThreads)
 convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict__ filter_kcoci,
-                  const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, __half *__restrict__ out,
-                  int32_t *status_word, int32_t *sticky) {
+                  const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, int ci_real, int co_real,
+                  __half *__restrict__ out, int32_t *status_word, int32_t *sticky) {
   using Cfg = TcConfig<CI, CO>;
   constexpr int S = Cfg::kAStages, NB = Cfg::kBBuffers, T = Cfg::kTiles;
   constexpr int CPR = Cfg::kChunksPerRow;  // 16-byte chunks per feature row
@@ -204,8 +208,9 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   unsigned char *b_ring = a_ring + (size_t)S * Cfg::kAStageBytes;
   __shared__ unsigned long long a_full[S], a_empty[S], b_empty[NB], accum_bar;
   __shared__ unsigned tmem_base_s;
-  __shared__ unsigned masks_s[T];
-  __shared__ unsigned char items_s[kMaxItems];
+  static_assert(T <= 2, "kMaxItems holds two tiles per offset");
+  __shared__ unsigned masks_s[T][kMaskWords];
+  __shared__ unsigned short items_s[kMaxItems];
   __shared__ int n_items_s;
   __shared__ int abort_s;
 
@@ -222,7 +227,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (tid < T) masks_s[tid] = 0u;
+  if (tid < T * kMaskWords) masks_s[tid / kMaskWords][tid % kMaskWords] = 0u;
   if (warp == 4) tmemAlloc(&tmem_base_s, Cfg::kTmemCols);
   tcFenceBefore();
   __syncthreads();
@@ -234,16 +239,16 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     const int k = e / T, t = e % T;
     const int4 v = __ldg(reinterpret_cast<const int4 *>(nbr + (size_t)k * n_pad + row0 + t * kTile) + lane);
     const unsigned any = __ballot_sync(0xffffffffu, (v.x & v.y & v.z & v.w) >= 0);
-    if (lane == 0 && any) atomicOr(&masks_s[t], 1u << k);
+    if (lane == 0 && any) atomicOr(&masks_s[t][k >> 5], 1u << (k & 31));
   }
   __syncthreads();
   if (tid == 0) {
     int n = 0;
     for (int k = 0; k < K; ++k) {
-      unsigned first = 0x80u;
+      unsigned first = kItemFirst;
       for (int t = 0; t < T; ++t) {
-        if ((masks_s[t] >> k) & 1u) {
-          items_s[n++] = (unsigned char)(first | (unsigned)(k << 2) | (unsigned)t);
+        if ((masks_s[t][k >> 5] >> (k & 31)) & 1u) {
+          items_s[n++] = (unsigned short)(first | (unsigned)(k << 2) | (unsigned)t);
           first = 0u;
         }
       }
@@ -281,6 +286,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     }
     const unsigned a_ring_addr = smemAddr(a_ring);
     const __half *feat_chunk = features + chunk * 8;
+    const bool chunk_in_row = chunk * 8 < ci_real;  // channels past ci_real are zero fill (padded Ci)
     const int32_t *nbr_rows = nbr + row0 + tid;
 
     int s = 0, b = -1;
@@ -288,20 +294,20 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     int idx_next = -1;
     if (n_items > 0) {
       const unsigned c0 = items_s[0];
-      idx_next = __ldg(nbr_rows + (size_t)((c0 >> 2) & 31u) * n_pad + (c0 & 3u) * kTile);
+      idx_next = __ldg(nbr_rows + (size_t)itemOffset(c0) * n_pad + itemTile(c0) * kTile);
     }
     for (int it = 0; it < n_items; ++it) {
       const unsigned code = items_s[it];
       const int idx = idx_next;
       if (it + 1 < n_items) {
         const unsigned c1 = items_s[it + 1];
-        idx_next = __ldg(nbr_rows + (size_t)((c1 >> 2) & 31u) * n_pad + (c1 & 3u) * kTile);
+        idx_next = __ldg(nbr_rows + (size_t)itemOffset(c1) * n_pad + itemTile(c1) * kTile);
       }
       if (it >= S) {
         if (!mbarWait(&a_empty[s], a_parity ^ 1u, abort_flag, status, 1)) break;
       }
-      if (code & 0x80u) {
-        const int k = (code >> 2) & 31u;
+      if (code & kItemFirst) {
+        const int k = itemOffset(code);
         if (++b == NB) b = 0;
         if (b_uses >= (unsigned)NB) {
           if (!mbarWait(&b_empty[b], ((b_uses / NB) - 1u) & 1u, abort_flag, status, 8)) break;
@@ -321,8 +327,8 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
 #pragma unroll
       for (int i = 0; i < CPR; ++i) {
         const int src_row = __shfl_sync(0xffffffffu, idx, rr0 + i * kRowsPerInstr);
-        const bool valid = src_row >= 0;
-        cpAsync16(stage_addr + a_off[i], feat_chunk + (valid ? (size_t)src_row * CI : 0), valid);
+        const bool valid = src_row >= 0 && chunk_in_row;
+        cpAsync16(stage_addr + a_off[i], feat_chunk + (valid ? (size_t)src_row * ci_real : 0), valid);
       }
       cpAsyncArriveOn(&a_full[s]);
       if (++s == S) {
@@ -340,8 +346,11 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
 #pragma unroll 1
       for (int t = 0; t < T; ++t) {
         const int64_t r = row0 + t * kTile + tid;
-        const bool tile_has_acc = have_acc && masks_s[t] != 0;
-        __half *dst = out + (size_t)r * CO;
+        unsigned live = 0u;
+#pragma unroll
+        for (int w = 0; w < kMaskWords; ++w) live |= masks_s[t][w];
+        const bool tile_has_acc = have_acc && live != 0u;
+        __half *dst = out + (size_t)r * co_real;
 #pragma unroll
         for (int c0 = 0; c0 < CO; c0 += 16) {
           unsigned v[16];
@@ -357,8 +366,9 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               h[i] = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-            *reinterpret_cast<uint4 *>(dst + c0) = *reinterpret_cast<uint4 *>(&h[0]);
-            *reinterpret_cast<uint4 *>(dst + c0 + 8) = *reinterpret_cast<uint4 *>(&h[4]);
+            // columns past co_real belong to the padding of Co
+            if (c0 + 8 <= co_real) *reinterpret_cast<uint4 *>(dst + c0) = *reinterpret_cast<uint4 *>(&h[0]);
+            if (c0 + 16 <= co_real) *reinterpret_cast<uint4 *>(dst + c0 + 8) = *reinterpret_cast<uint4 *>(&h[4]);
           }
         }
       }
@@ -375,8 +385,8 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
       int it = 0;
       for (; it < n_items; ++it) {
         const unsigned code = items_s[it];
-        const int t = code & 3u;
-        if (code & 0x80u) {
+        const int t = itemTile(code);
+        if (code & kItemFirst) {
           if (++b == NB) b = 0;
         }
         if (!mbarWait(&a_full[s], a_parity, abort_flag, status, 2)) break;
@@ -397,7 +407,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
         started |= 1u << t;
         ummaCommit(&a_empty[s]);  // the stage may be refilled once these MMAs have read it
         // last item of offset k: its filter slice is free once these MMAs are done
-        if (it + 1 == n_items || (items_s[it + 1] & 0x80u)) ummaCommit(&b_empty[b]);
+        if (it + 1 == n_items || (items_s[it + 1] & kItemFirst)) ummaCommit(&b_empty[b]);
         if (++s == S) {
           s = 0;
           a_parity ^= 1u;
@@ -429,7 +439,7 @@ cudaError_t launchTc(const ConvProblem &p, const ConvWorkspacePlan &plan, const 
   static const std::string name = "convTcgen05Kernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
   static const std::string name_dgrad = name + ":input_grad";
   trace::Scope t(p.backward_data ? name_dgrad.c_str() : name.c_str(), stream, algo_bytes, algo_flops);
-  kernel<<<blocks, kThreads, smem, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K, out, status,
+  kernel<<<blocks, kThreads, smem, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K, p.ci, p.co, out, status,
                                              p.sticky_status);
   return cudaGetLastError();
 }
@@ -438,7 +448,7 @@ template <int CI>
 cudaError_t dispatchCo(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
                        const __half *filter, const int32_t *nbr, __half *out, int32_t *status, double algo_bytes,
                        double algo_flops, cudaStream_t stream) {
-  switch (p.co) {
+  switch (tcgen05PaddedChannels(p.co)) {
     case 16: return launchTc<CI, 16>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
     case 32: return launchTc<CI, 32>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
     case 64: return launchTc<CI, 64>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
@@ -449,16 +459,20 @@ cudaError_t dispatchCo(const ConvProblem &p, const ConvWorkspacePlan &plan, cons
 
 }  // namespace
 
+int tcgen05PaddedChannels(int c) {
+  if (c < 8 || c > 128 || c % 8) return 0;
+  return c <= 16 ? 16 : (c <= 32 ? 32 : (c <= 64 ? 64 : 128));
+}
+
 bool tcgen05Eligible(const ConvProblem &p, const void *features, const void *out) {
-  auto ok = [](int c) { return c == 16 || c == 32 || c == 64 || c == 128; };
-  return p.is_half && p.K <= kMaxOffsets && ok(p.ci) && ok(p.co) &&
+  return p.is_half && p.K <= kMaxOffsets && tcgen05PaddedChannels(p.ci) && tcgen05PaddedChannels(p.co) &&
          (reinterpret_cast<size_t>(features) % 16 == 0) && (reinterpret_cast<size_t>(out) % 16 == 0);
 }
 
 cudaError_t launchConvTcgen05(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
                               const __half *filter_kcoci, const int32_t *nbr, __half *out, int32_t *status,
                               double algo_bytes, double algo_flops, cudaStream_t stream) {
-  switch (p.ci) {
+  switch (tcgen05PaddedChannels(p.ci)) {
     case 16: return dispatchCo<16>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);
     case 32: return dispatchCo<32>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);
     case 64: return dispatchCo<64>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);

@@ -1,5 +1,6 @@
-// tcgen05 / tensor-memory variant of the convolution kernel (half, channel
-// counts 16/32/64/128, kernel volume up to 32).
+// tcgen05 / tensor-memory variant of the convolution kernel: half, channel
+// counts that are multiples of 8 up to 128 (run at the next of 16 / 32 / 64 / 128
+// with zero padding on chip), kernel volume up to 128.
 #ifndef MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_TCGEN05_H_
 #define MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_TCGEN05_H_
 
@@ -12,6 +13,9 @@ namespace mluop {
 namespace sparse_conv {
 
 bool tcgen05Eligible(const ConvProblem &p, const void *features, const void *out);
+// The channel count the kernel runs a count of c at (16, 32, 64 or 128), 0 if unsupported.
+// The repacked filter the kernel reads is [K][padded Co][padded Ci], zero in the padding.
+int tcgen05PaddedChannels(int c);
 
 // status: one int32 of device memory, zero before the launch; a non-zero value
 // afterwards means a bounded wait inside the kernel gave up (bit 0 producer on a gather stage,

@@ -78,10 +78,14 @@ def test_neighbour_table_fast_path_is_bit_identical(ops, workloads, backbone, gp
     grid = list(workloads.CONFIGS["c2"]["grid"])
     net = backbone.SparseNetwork(gpu_handle, layers, [torch.from_numpy(w).cuda() for w in weights], grid, 1)
     d_idx, d_feat = torch.from_numpy(idx).cuda(), torch.from_numpy(feat).cuda()
-    a, ia, _ = net.forward(d_idx, d_feat)
+    a, ia, ra = net.forward(d_idx, d_feat)
     b, ib, _ = net.forward(d_idx, d_feat, reuse_tables=True)
+    c, ic, rc = net.forward(d_idx, d_feat, reuse_tables=True, defer_counts=True)
     torch.cuda.synchronize()
-    assert torch.equal(a, b) and torch.equal(ia, ib)
+    assert torch.equal(a, b) and torch.equal(ia, ib) and torch.equal(a, c) and torch.equal(ia, ic)
+    assert any(r.indice_num is None for r in rc)
+    net.resolve_counts(rc)
+    assert [r.indice_num for r in rc] == [r.indice_num for r in ra]
     net.close()
 
 
@@ -100,7 +104,7 @@ def test_rulebooks_on_a_second_stream_are_bit_identical(ops, workloads, backbone
     net = backbone.SparseNetwork(gpu_handle, layers, d_w, grid, 1, rulebook_handle=second, rulebook_stream=stream)
     for _ in range(3):
         b, ib, _ = net.forward(d_idx, d_feat)
-        c, ic, _ = net.forward(d_idx, d_feat, reuse_tables=True)
+        c, ic, _ = net.forward(d_idx, d_feat, reuse_tables=True, defer_counts=True)
         torch.cuda.synchronize()
         assert torch.equal(a, b) and torch.equal(ia, ib) and torch.equal(a, c) and torch.equal(ia, ic)
     net.close()

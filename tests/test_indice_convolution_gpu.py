@@ -60,13 +60,14 @@ def make_case(oracle, rng, batch, space, n, ks, stride, pad, sub_m, ci, co, dtyp
 
 
 CHANNELS = [(4, 16), (16, 16), (16, 32), (32, 32), (32, 64), (64, 64), (64, 128), (128, 128), (3, 5), (20, 48),
-            (128, 16), (130, 140)]
+            (128, 16), (130, 140), (8, 8), (24, 48), (48, 96), (96, 80), (72, 120), (120, 8)]
 
 
 @pytest.mark.parametrize("ci,co", CHANNELS)
 @pytest.mark.parametrize("dtype", [np.float16, np.float32])
 def test_channel_sweep(ops, oracle, gpu_handle, ci, co, dtype):
-    """Every kernel variant: tensor-core tiles for half with power-of-two channels, FMA otherwise."""
+    """Every kernel variant: tensor-core tiles for half with channel counts that are multiples of 8
+    up to 128 (odd counts run zero-padded at the next power of two), FMA otherwise."""
     rng = np.random.default_rng(ci * 1000 + co)
     is_half = dtype == np.float16
     for sub_m, stride in ((1, [1] * 3), (0, [2] * 3)):
@@ -75,6 +76,19 @@ def test_channel_sweep(ops, oracle, gpu_handle, ci, co, dtype):
         ref = oracle_conv(oracle, feat, w, "ARRAY", [3] * 3, pairs, num, n_out, co, is_half)
         got = gpu_conv(ops, gpu_handle, feat, w, "ARRAY", [3] * 3, pairs, num, n_out, sub_m)
         assert_close(oracle, got, ref, is_half)
+
+
+@pytest.mark.parametrize("ks,stride,pad,sub_m", [([5, 5, 5], [1] * 3, [2] * 3, 1), ([5, 3, 5], [1] * 3, [2, 1, 2], 1),
+                                                 ([4, 4, 4], [2] * 3, [1] * 3, 0)])
+def test_large_kernel_volumes_on_tensor_cores(ops, oracle, gpu_handle, ks, stride, pad, sub_m):
+    """Kernel volumes above 32 (up to 5x5x5 = 125 offsets) take the tensor-core kernel too."""
+    rng = np.random.default_rng(int(np.prod(ks)))
+    for ci, co in ((16, 32), (64, 64), (48, 24)):
+        pairs, num, n_out, feat, w = make_case(oracle, rng, 2, [9, 12, 13], 900, ks, stride, pad, sub_m, ci, co,
+                                               np.float16)
+        ref = oracle_conv(oracle, feat, w, "ARRAY", ks, pairs, num, n_out, co, True)
+        got = gpu_conv(ops, gpu_handle, feat, w, "ARRAY", ks, pairs, num, n_out, sub_m)
+        assert_close(oracle, got, ref, True)
 
 
 def test_output_rows_without_pairs_are_zero(ops, oracle, gpu_handle):

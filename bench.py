@@ -234,7 +234,7 @@ def run_b200(args):
         env = dict(torch=torch, dist=dist, ops=ops, workloads=workloads, backbone=backbone, sharding=sharding,
                    dev=dev, rank=rank, world=world, flush=torch.empty((256 << 20,), dtype=torch.uint8, device=dev),
                    stream=stream, handle=handle, rb_handle=rb_handle, rb_stream=rb_stream, flush_at=0,
-                   pipelined=not args.no_pipeline and rb_handle is not None, hbm_gbs=hbm_gbs,
+                   pipelined=args.pipeline and rb_handle is not None, hbm_gbs=hbm_gbs,
                    tensor_tflops=tensor_tflops, fp32_tflops=64.0, batch_override=args.config_batch)
         print(json.dumps({args.config_only: time_config(args.config_only, args.steps, env)}))
         return
@@ -278,12 +278,12 @@ def run_b200(args):
             gather.begin(out_idx, ready=done)
             gather.finish(out, wait=False, ready=done)
 
-    # A stream of batches is software-pipelined one level further (unless --no-pipeline): rulebooks
+    # With --pipeline a stream of batches is software-pipelined one level further: rulebooks
     # depend only on coordinates, so the rulebooks of batch i+1 (their kernels on the second stream
     # and the host waits for their counts) run while the convolutions of batch i, already enqueued,
     # keep the first stream busy.  Every step still does one batch's rulebooks and one batch's
     # convolutions inside the timed region; they just belong to neighbouring batches.
-    pipelined = not args.no_pipeline and rb_handle is not None
+    pipelined = args.pipeline and rb_handle is not None
     next_plan = {}
 
     def step_resident():
@@ -1138,9 +1138,10 @@ def main():
     ap.add_argument("--e2e-breakdown", action="store_true",
                     help="also write gpurun_out/e2e_breakdown_rank<r>.json: where each rank's end-to-end step spends "
                          "its host time (rulebook waits, library calls, copies) and how long its copies take")
-    ap.add_argument("--no-pipeline", action="store_true",
-                    help="generate each batch's rulebooks inside its own step instead of during the convolutions of "
-                         "the batch before")
+    ap.add_argument("--pipeline", action="store_true",
+                    help="generate the rulebooks of batch i+1 during the convolutions of batch i instead of inside "
+                         "their own step (measured: no gain on one GPU, where the two kinds of kernels already share "
+                         "the SMs through the second stream and the step is bound by their total kernel time)")
     ap.add_argument("--no-gather", action="store_true",
                     help="diagnostic for N>1: skip the NCCL gather (independent replicas) to separate its cost "
                          "from host-side contention between the ranks' processes")

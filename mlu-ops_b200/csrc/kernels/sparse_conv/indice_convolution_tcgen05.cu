@@ -228,6 +228,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   __shared__ int n_items_s;
   __shared__ int abort_s;
   __shared__ int tile_entry_s[T], tile_first_pair_s[T];  // pair mode: sparse offset and first pair of each tile
+  __shared__ short sparse_k_s[kMaxOffsets];               // the sparse offsets, for the epilogue
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t row0 = (int64_t)blockIdx.x * (T * kTile);
@@ -243,6 +244,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (tid < T * kMaskWords) masks_s[tid / kMaskWords][tid % kMaskWords] = 0u;
+  if (!PAIRS && tid < sp.count) sparse_k_s[tid] = sp.k[tid];
   if (warp == 4) tmemAlloc(&tmem_base_s, Cfg::kTmemCols);
   tcFenceBefore();
   __syncthreads();
@@ -417,16 +419,21 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
           continue;
         }
         const int64_t r = row0 + t * kTile + tid;
-        // partial rows of this output row from the sparse offsets, ascending offset
+        // partial rows of this output row from the sparse offsets, ascending offset; the table
+        // entries are fetched eight at a time before any is examined (independent loads)
         int hit[kEpilogueHits];
         int n_hits = 0;
-        if (sp.count > 0 && r < n_out) {
-          for (int i = 0; i < sp.count; ++i) {
-            const int row = __ldg(nbr + (size_t)sp.k[i] * n_pad + r);
-            if (row >= 0) {
+        for (int i0 = 0; i0 < sp.count; i0 += 8) {
+          int rows[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            rows[u] = i0 + u < sp.count ? __ldg(nbr + (size_t)sparse_k_s[i0 + u] * n_pad + r) : -1;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (rows[u] >= 0) {
 #pragma unroll
               for (int q = 0; q < kEpilogueHits; ++q)
-                if (n_hits == q) hit[q] = row;
+                if (n_hits == q) hit[q] = rows[u];
               ++n_hits;
             }
           }
@@ -464,7 +471,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
               if (n_hits > kEpilogueHits) {  // rare: the rows past the first few, found again by a second scan
                 int seen = 0;
                 for (int i = 0; i < sp.count; ++i) {
-                  const int row = __ldg(nbr + (size_t)sp.k[i] * n_pad + r);
+                  const int row = __ldg(nbr + (size_t)sparse_k_s[i] * n_pad + r);
                   if (row >= 0 && seen++ >= kEpilogueHits) add_row(row);
                 }
               }

@@ -245,7 +245,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionBackwardDataWorkspaceSize(
   if (st != MLUOP_STATUS_SUCCESS) return st;
   if (is_zero) return MLUOP_STATUS_SUCCESS;
   const ConvProblem p = makeProblem(handle, output_grad_desc, filters_desc, input_grad_desc);
-  *workspace_size = mluop::sparse_conv::planConvWorkspace(p, false, indice_num).total;
+  *workspace_size = mluop::sparse_conv::planConvWorkspace(p).total;
   return MLUOP_STATUS_SUCCESS;
 }
 
@@ -269,7 +269,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardData(
     PARAM_CHECK(api, workspace != nullptr);
   }
   const ConvProblem p = makeProblem(handle, output_grad_desc, filters_desc, input_grad_desc);
-  const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p, false, indice_num);
+  const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p);
   if (workspace_size < plan.total || workspace == nullptr) {
     LOG(ERROR) << api << " workspace of " << workspace_size << " bytes is smaller than the " << plan.total
                << " bytes mluOpGetIndiceConvolutionBackwardDataWorkspaceSize reports.";

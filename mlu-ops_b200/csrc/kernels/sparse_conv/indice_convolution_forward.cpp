@@ -165,7 +165,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionForwardWorkspaceSize(
   }
   PARAM_CHECK(api, size != nullptr);
   const ConvProblem p = makeProblem(handle, features_desc, filters_desc, num_act_out);
-  *size = mluop::sparse_conv::planConvWorkspace(p, false, indice_num).total;
+  *size = mluop::sparse_conv::planConvWorkspace(p).total;
   return MLUOP_STATUS_SUCCESS;
 }
 
@@ -191,7 +191,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForward(
     PARAM_CHECK(api, workspace != nullptr);
   }
   const ConvProblem p = makeProblem(handle, features_desc, filters_desc, num_act_out);
-  const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p, false, indice_num);
+  const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p);
   if (workspace_size < plan.total || workspace == nullptr) {
     LOG(ERROR) << api << " workspace of " << workspace_size << " bytes is smaller than the " << plan.total
                << " bytes mluOpGetIndiceConvolutionForwardWorkspaceSize reports.";

@@ -92,32 +92,29 @@ constexpr int kBuildPairsPerThread = 4;
 template <bool BY_VALUE>
 __global__ void __launch_bounds__(256)
 buildNeighbourKernel(const int32_t *__restrict__ pairs, int64_t pair_stride, int swap, int64_t L,
-                     int64_t n_out, int64_t n_pad, PairCounts counts, PairCounts partial_base,
+                     int64_t n_out, int64_t n_pad, PairCounts counts,
                      const int32_t *__restrict__ counts_dev, int32_t *__restrict__ nbr) {
   // pairs is [K][2][pair_stride]; row 0 of an offset holds the ids of the rows that
   // are gathered (L of them) and row 1 the ids of the rows that are produced (n_out),
   // the other way round when swap is set.
   const int k = blockIdx.y;
   const int64_t pk = BY_VALUE ? counts.n[k] : counts_dev[k];
-  // an offset on the pair-list route stores the pair's row in the partial buffer, not the gathered row
-  const int32_t base = BY_VALUE ? partial_base.n[k] : -1;
   const int32_t *in_row = pairs + (size_t)k * 2 * pair_stride + (swap ? pair_stride : 0);
   const int32_t *out_row = pairs + (size_t)k * 2 * pair_stride + (swap ? 0 : pair_stride);
   int32_t *table = nbr + (size_t)k * n_pad;
   const int64_t span = (int64_t)blockDim.x * kBuildPairsPerThread;
-  for (int64_t base_pos = (int64_t)blockIdx.x * span; base_pos < pk; base_pos += (int64_t)gridDim.x * span) {
+  for (int64_t base = (int64_t)blockIdx.x * span; base < pk; base += (int64_t)gridDim.x * span) {
     int32_t src[kBuildPairsPerThread], dst[kBuildPairsPerThread];
 #pragma unroll
     for (int i = 0; i < kBuildPairsPerThread; ++i) {
-      const int64_t p = base_pos + i * blockDim.x + threadIdx.x;
+      const int64_t p = base + i * blockDim.x + threadIdx.x;
       src[i] = p < pk ? in_row[p] : -1;
       dst[i] = p < pk ? out_row[p] : -1;
     }
     // A rulebook holds one pair per (k, output row), so plain stores never collide.
 #pragma unroll
     for (int i = 0; i < kBuildPairsPerThread; ++i)
-      if (src[i] >= 0 && src[i] < L && dst[i] >= 0 && dst[i] < n_out)
-        table[dst[i]] = base < 0 ? src[i] : base + (int32_t)(base_pos + i * blockDim.x + threadIdx.x);
+      if (src[i] >= 0 && src[i] < L && dst[i] >= 0 && dst[i] < n_out) table[dst[i]] = src[i];
   }
 }
 
@@ -448,67 +445,13 @@ bool mmaEligible(const ConvProblem &p, const void *features, const void *out) {
 
 }  // namespace
 
-namespace {
-
-// Which offsets take the pair-list route of the tensor-core kernel: those with fewer
-// pairs than a twelfth of the produced rows (a 128-row tile then holds about ten live rows
-// or fewer at that offset, and walking it tile by tile would move and multiply mostly zero
-// fill).  Only for half on the tensor-core path, kernel volumes the kernel-argument path
-// covers, and while the partial products stay below 1 GiB.  Returns the number of pairs on
-// that route and fills `sparse` (except its pointers) when given.
-constexpr int64_t kSparseDensityDivisor = 12;
-constexpr int64_t kSparseMinPairs = 2048;
-constexpr size_t kSparsePartialLimit = (size_t)1 << 30;
-
-int64_t classifySparseOffsets(const ConvProblem &p, const int64_t *indice_num, SparseOffsets *sparse) {
-  if (sparse) {
-    std::memset(sparse, 0, sizeof(*sparse));
-  }
-  // MLUOP_B200_CONV_SPARSE_OFFSETS=0 switches the route off (every offset is walked tile by
-  // tile); MLUOP_B200_CONV_SPARSE_MIN_PAIRS=<n> lowers the minimum so that small test cases take it.
-  static const char *route_env = std::getenv("MLUOP_B200_CONV_SPARSE_OFFSETS");
-  static const char *min_env = std::getenv("MLUOP_B200_CONV_SPARSE_MIN_PAIRS");
-  static const int64_t min_pairs = min_env ? std::atoll(min_env) : kSparseMinPairs;
-  if (route_env && route_env[0] == '0') return 0;
-  if (indice_num == nullptr || !p.is_half || p.K > kMaxCountsByValue || p.K > kTcMaxOffsets) return 0;
-  const int co_pad = tcgen05PaddedChannels(p.backward_data ? p.ci : p.co);
-  const int ci_pad = tcgen05PaddedChannels(p.backward_data ? p.co : p.ci);
-  if (!co_pad || !ci_pad) return 0;
-  const int64_t rows_out = p.backward_data ? p.L : p.n_out;
-  int64_t pairs = 0;
-  for (int k = 0; k < p.K; ++k)
-    if (indice_num[k] > 0 && indice_num[k] * kSparseDensityDivisor < rows_out) pairs += indice_num[k];
-  if (pairs < min_pairs || pairs < 1 || (size_t)pairs * co_pad * sizeof(float) > kSparsePartialLimit ||
-      pairs + p.K * (int64_t)kConvTileRows >= ((int64_t)1 << 31))
-    return 0;
-  if (sparse) {
-    int n = 0, tiles = 0, rows = 0;
-    for (int k = 0; k < p.K; ++k) {
-      if (!(indice_num[k] > 0 && indice_num[k] * kSparseDensityDivisor < rows_out)) continue;
-      sparse->mask[k >> 5] |= 1u << (k & 31);
-      sparse->k[n] = (short)k;
-      sparse->tile_start[n] = tiles;
-      sparse->row_start[n] = rows;
-      tiles += (int)((indice_num[k] + kConvTileRows - 1) / kConvTileRows);
-      rows += (int)indice_num[k];
-      ++n;
-    }
-    sparse->count = n;
-    sparse->tile_start[n] = tiles;
-    sparse->row_start[n] = rows;
-  }
-  return pairs;
-}
-
-}  // namespace
-
 size_t neighbourTableBytes(const ConvProblem &p) {
   const int64_t rows_out = p.backward_data ? p.L : p.n_out;
   const int64_t n_pad = (rows_out + kConvPadRows - 1) / kConvPadRows * kConvPadRows;
   return (size_t)p.K * n_pad * sizeof(int32_t);
 }
 
-ConvWorkspacePlan planConvWorkspace(const ConvProblem &p, bool external_table, const int64_t *indice_num) {
+ConvWorkspacePlan planConvWorkspace(const ConvProblem &p, bool external_table) {
   ConvWorkspacePlan plan{};
   const size_t elem = p.is_half ? 2 : 4;
   const int64_t rows_out = p.backward_data ? p.L : p.n_out;
@@ -525,12 +468,6 @@ ConvWorkspacePlan planConvWorkspace(const ConvProblem &p, bool external_table, c
   if (!external_table) off = alignUp(off + (size_t)p.K * plan.n_pad * sizeof(int32_t), 256);
   plan.counts = off;
   off = alignUp(off + (size_t)p.K * sizeof(int32_t), 256);
-  plan.partial = off;
-  plan.sparse_pairs = external_table ? 0 : classifySparseOffsets(p, indice_num, nullptr);
-  if (plan.sparse_pairs > 0) {
-    const int co_pad = tcgen05PaddedChannels(p.backward_data ? p.ci : p.co);
-    off = alignUp(off + (size_t)plan.sparse_pairs * co_pad * sizeof(float), 256);
-  }
   plan.total = off + 256;
   return plan;
 }
@@ -612,22 +549,6 @@ cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWo
     }
   }
 
-  // Offsets on the pair-list route (tensor-core path with its own table only: a caller's
-  // table holds gathered rows for every offset).
-  SparseOffsets sparse;
-  std::memset(&sparse, 0, sizeof(sparse));
-  PairCounts partial_base;
-  for (int k = 0; k < kMaxCountsByValue; ++k) partial_base.n[k] = -1;
-  if (use_tc && do_build && external_table == nullptr && plan.sparse_pairs > 0 &&
-      classifySparseOffsets(caller, indice_num, &sparse) == plan.sparse_pairs) {
-    sparse.partial = reinterpret_cast<float *>(base + plan.partial);
-    sparse.gather_ids = indice_pairs + (swap ? pair_stride : 0);
-    sparse.offset_stride = 2 * pair_stride;
-    for (int i = 0; i < sparse.count; ++i) partial_base.n[sparse.k[i]] = sparse.row_start[i];
-  } else {
-    sparse.count = 0;
-  }
-
   // 2. neighbour table
   if (do_build) {
     trace::Scope t("memset:neighbour_table", stream, 4.0 * p.K * plan.n_pad);
@@ -644,7 +565,7 @@ cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWo
       PairCounts counts{};
       for (int k = 0; k < p.K; ++k) counts.n[k] = (int32_t)indice_num[k];
       buildNeighbourKernel<true><<<grid, 256, 0, stream>>>(indice_pairs, pair_stride, swap, p.L, p.n_out,
-                                                           plan.n_pad, counts, partial_base, nullptr, nbr);
+                                                           plan.n_pad, counts, nullptr, nbr);
     } else {
       // Large kernel volumes: counts travel through device memory.  The copy
       // from pageable host memory is staged by the runtime before it returns.
@@ -654,7 +575,7 @@ cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWo
       delete[] tmp;
       if (err != cudaSuccess) return err;
       buildNeighbourKernel<false><<<grid, 256, 0, stream>>>(indice_pairs, pair_stride, swap, p.L, p.n_out,
-                                                            plan.n_pad, PairCounts{}, PairCounts{}, counts_dev, nbr);
+                                                            plan.n_pad, PairCounts{}, counts_dev, nbr);
     }
   }
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
@@ -664,7 +585,7 @@ cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWo
   if (use_tc) {
     return launchConvTcgen05(p, plan, static_cast<const __half *>(features),
                              static_cast<const __half *>(filter_packed), nbr,
-                             static_cast<__half *>(features_out), status, sparse, conv_bytes, conv_flops, stream);
+                             static_cast<__half *>(features_out), status, conv_bytes, conv_flops, stream);
   }
   if (!force_fma && mmaEligible(p, features, features_out)) {
     const __half *f = static_cast<const __half *>(features);

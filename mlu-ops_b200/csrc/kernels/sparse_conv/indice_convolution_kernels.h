@@ -44,18 +44,13 @@ struct ConvWorkspacePlan {
                      // (input gradient: T[K][Ci][Co])
   size_t neighbour;  // int32[K][n_pad]: source row feeding (k, destination row), -1 if none
   size_t counts;     // int32[K]: pair counts, only used when K is too large for kernel arguments
-  size_t partial;    // float[sparse pairs][padded Co]: products of the offsets that take the pair-list route
   size_t total;
   int64_t n_pad;
-  int64_t sparse_pairs;  // pairs of those offsets (0: every offset is walked tile by tile)
 };
 
 // external_table: the neighbour table lives in a buffer of the caller (see
-// launchIndiceConvolutionSteps), the workspace holds the rest.  indice_num (the
-// caller's host array, optional) lets the plan set room aside for the partial
-// products of sparse offsets; the same array must be given to the launch.
-ConvWorkspacePlan planConvWorkspace(const ConvProblem &p, bool external_table = false,
-                                    const int64_t *indice_num = nullptr);
+// launchIndiceConvolutionSteps), the workspace holds the rest.
+ConvWorkspacePlan planConvWorkspace(const ConvProblem &p, bool external_table = false);
 
 // Bytes of a neighbour table int32[K][n_pad] for this problem and direction.
 size_t neighbourTableBytes(const ConvProblem &p);

@@ -22,17 +22,6 @@
 // once.  The reduction over offsets happens in TMEM in a fixed order, so the
 // result is deterministic.
 //
-// Offsets with few pairs ("sparse": fewer pairs than a twelfth of the output
-// rows) would cost a whole 128-row item per tile for a handful of live rows.
-// They take a second route, still deterministic and without atomics:
-//   1. the same kernel in pair mode (PAIRS) walks the pair lists of the sparse
-//      offsets, 128 pairs per tile: the gathered rows are dense, one filter slice
-//      per tile, and the fp32 products go to a partial buffer, one row per pair;
-//   2. the neighbour table holds, for a sparse offset, the pair's row in that
-//      buffer instead of the input row, and the epilogue of the ordinary pass
-//      adds an output row's partial rows in ascending offset order to what the
-//      dense offsets left in TMEM.
-//
 // Every mbarrier wait is bounded: after about one second the waiter records an
 // error in the status word, raises a block-wide abort flag and every role
 // falls through to the common exit, where outstanding cp.async groups are
@@ -55,7 +44,7 @@ namespace {
 constexpr int kTile = kConvTileRows;      // 128 output rows = 128 TMEM lanes
 constexpr int kProducerThreads = 128;     // warps 0-3: gather, then epilogue
 constexpr int kThreads = 160;             // + warp 4: TMEM allocation and MMA issue
-constexpr int kMaxOffsets = kTcMaxOffsets;  // kernel volumes up to 5x5x5
+constexpr int kMaxOffsets = 128;           // kernel volumes up to 5x5x5
 constexpr int kMaskWords = kMaxOffsets / 32;
 constexpr long long kWaitCycles = 2000000000ll;  // a wait gives up after about one second
 
@@ -205,14 +194,11 @@ constexpr unsigned kItemFirst = 0x8000u;
 __device__ __forceinline__ int itemOffset(unsigned code) { return (int)((code >> 2) & 0x1FFFu); }
 __device__ __forceinline__ int itemTile(unsigned code) { return (int)(code & 3u); }
 
-constexpr int kEpilogueHits = 4;  // partial rows of one output row kept in registers; more take a second scan
-
-template <int CI, int CO, bool PAIRS>
+template <int CI, int CO>
 __global__ void __launch_bounds__(kThreads)
 convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict__ filter_kcoci,
                   const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, int ci_real, int co_real,
-                  __half *__restrict__ out, int32_t *status_word, int32_t *sticky,
-                  const __grid_constant__ SparseOffsets sp) {
+                  __half *__restrict__ out, int32_t *status_word, int32_t *sticky) {
   using Cfg = TcConfig<CI, CO>;
   constexpr int S = Cfg::kAStages, NB = Cfg::kBBuffers, T = Cfg::kTiles;
   constexpr int CPR = Cfg::kChunksPerRow;  // 16-byte chunks per feature row
@@ -227,8 +213,6 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   __shared__ unsigned short items_s[kMaxItems];
   __shared__ int n_items_s;
   __shared__ int abort_s;
-  __shared__ int tile_entry_s[T], tile_first_pair_s[T];  // pair mode: sparse offset and first pair of each tile
-  __shared__ short sparse_k_s[kMaxOffsets];               // the sparse offsets, for the epilogue
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t row0 = (int64_t)blockIdx.x * (T * kTile);
@@ -244,56 +228,32 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (tid < T * kMaskWords) masks_s[tid / kMaskWords][tid % kMaskWords] = 0u;
-  if (!PAIRS && tid < sp.count) sparse_k_s[tid] = sp.k[tid];
   if (warp == 4) tmemAlloc(&tmem_base_s, Cfg::kTmemCols);
   tcFenceBefore();
   __syncthreads();
   tcFenceAfter();
-  if (PAIRS) {
-    // Pair mode: tile t of the block is the 128-pair tile number blockIdx.x*T + t of the
-    // concatenated pair lists of the sparse offsets; one item per tile.
-    if (tid == 0) {
-      int n = 0, previous_k = -1;
+  // Live masks: bit k of masks_s[t] is set when some row of tile t has a
+  // neighbour at offset k.  Each warp scans (offset, tile) slices of the table,
+  // four rows per lane.
+  for (int e = warp; e < K * T; e += kThreads / 32) {
+    const int k = e / T, t = e % T;
+    const int4 v = __ldg(reinterpret_cast<const int4 *>(nbr + (size_t)k * n_pad + row0 + t * kTile) + lane);
+    const unsigned any = __ballot_sync(0xffffffffu, (v.x & v.y & v.z & v.w) >= 0);
+    if (lane == 0 && any) atomicOr(&masks_s[t][k >> 5], 1u << (k & 31));
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int n = 0;
+    for (int k = 0; k < K; ++k) {
+      unsigned first = kItemFirst;
       for (int t = 0; t < T; ++t) {
-        const int tile = blockIdx.x * T + t;
-        tile_entry_s[t] = -1;
-        if (tile >= sp.tile_start[sp.count]) continue;
-        int i = 0;
-        while (sp.tile_start[i + 1] <= tile) ++i;
-        tile_entry_s[t] = i;
-        tile_first_pair_s[t] = (tile - sp.tile_start[i]) * kTile;
-        const int k = sp.k[i];
-        items_s[n++] = (unsigned short)((k != previous_k ? kItemFirst : 0u) | (unsigned)(k << 2) | (unsigned)t);
-        previous_k = k;
-        masks_s[t][0] = 1u;
-      }
-      n_items_s = n;
-    }
-  } else {
-    // Live masks: bit k of masks_s[t] is set when some row of tile t has a
-    // neighbour at offset k.  Each warp scans (offset, tile) slices of the table,
-    // four rows per lane.  Sparse offsets are not walked here.
-    for (int e = warp; e < K * T; e += kThreads / 32) {
-      const int k = e / T, t = e % T;
-      if ((sp.mask[k >> 5] >> (k & 31)) & 1u) continue;
-      const int4 v = __ldg(reinterpret_cast<const int4 *>(nbr + (size_t)k * n_pad + row0 + t * kTile) + lane);
-      const unsigned any = __ballot_sync(0xffffffffu, (v.x & v.y & v.z & v.w) >= 0);
-      if (lane == 0 && any) atomicOr(&masks_s[t][k >> 5], 1u << (k & 31));
-    }
-    __syncthreads();
-    if (tid == 0) {
-      int n = 0;
-      for (int k = 0; k < K; ++k) {
-        unsigned first = kItemFirst;
-        for (int t = 0; t < T; ++t) {
-          if ((masks_s[t][k >> 5] >> (k & 31)) & 1u) {
-            items_s[n++] = (unsigned short)(first | (unsigned)(k << 2) | (unsigned)t);
-            first = 0u;
-          }
+        if ((masks_s[t][k >> 5] >> (k & 31)) & 1u) {
+          items_s[n++] = (unsigned short)(first | (unsigned)(k << 2) | (unsigned)t);
+          first = 0u;
         }
       }
-      n_items_s = n;
     }
+    n_items_s = n;
   }
   __syncthreads();
   const int n_items = n_items_s;
@@ -328,28 +288,20 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     const __half *feat_chunk = features + chunk * 8;
     const bool chunk_in_row = chunk * 8 < ci_real;  // channels past ci_real are zero fill (padded Ci)
     const int32_t *nbr_rows = nbr + row0 + tid;
-    // the id of the row this thread's output row gathers for an item
-    auto gather_id = [&](unsigned code) -> int {
-      if (PAIRS) {
-        const int t = itemTile(code), i = tile_entry_s[t];
-        const int p = tile_first_pair_s[t] + tid;
-        if (p >= sp.row_start[i + 1] - sp.row_start[i]) return -1;
-        return __ldg(sp.gather_ids + (size_t)itemOffset(code) * sp.offset_stride + p);
-      }
-      return __ldg(nbr_rows + (size_t)itemOffset(code) * n_pad + itemTile(code) * kTile);
-    };
 
     int s = 0, b = -1;
     unsigned a_parity = 0, b_uses = 0;  // a_parity: parity of the current pass over the stage ring
     int idx_next = -1;
     if (n_items > 0) {
-      idx_next = gather_id(items_s[0]);
+      const unsigned c0 = items_s[0];
+      idx_next = __ldg(nbr_rows + (size_t)itemOffset(c0) * n_pad + itemTile(c0) * kTile);
     }
     for (int it = 0; it < n_items; ++it) {
       const unsigned code = items_s[it];
       const int idx = idx_next;
       if (it + 1 < n_items) {
-        idx_next = gather_id(items_s[it + 1]);
+        const unsigned c1 = items_s[it + 1];
+        idx_next = __ldg(nbr_rows + (size_t)itemOffset(c1) * n_pad + itemTile(c1) * kTile);
       }
       if (it >= S) {
         if (!mbarWait(&a_empty[s], a_parity ^ 1u, abort_flag, status, 1)) break;
@@ -393,51 +345,11 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     if (!*abort_flag) {
 #pragma unroll 1
       for (int t = 0; t < T; ++t) {
+        const int64_t r = row0 + t * kTile + tid;
         unsigned live = 0u;
 #pragma unroll
         for (int w = 0; w < kMaskWords; ++w) live |= masks_s[t][w];
         const bool tile_has_acc = have_acc && live != 0u;
-        if (PAIRS) {
-          // fp32 products of this tile's pairs -> their rows of the partial buffer
-          const int i = tile_entry_s[t];
-          const int p = tile_first_pair_s[t] + tid;
-          const bool store = i >= 0 && tile_has_acc && p < sp.row_start[i + 1] - sp.row_start[i];
-          float *dst = sp.partial + (store ? (size_t)(sp.row_start[i] + p) * CO : 0);
-#pragma unroll
-          for (int c0 = 0; c0 < CO; c0 += 16) {
-            unsigned v[16];
-            if (tile_has_acc) {  // same decision in every thread of the warp
-              tmemLoad16(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(t * CO + c0), v);
-              tmemLoadWait();
-            }
-            if (store) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                *reinterpret_cast<uint4 *>(dst + c0 + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            }
-          }
-          continue;
-        }
-        const int64_t r = row0 + t * kTile + tid;
-        // partial rows of this output row from the sparse offsets, ascending offset; the table
-        // entries are fetched eight at a time before any is examined (independent loads)
-        int hit[kEpilogueHits];
-        int n_hits = 0;
-        for (int i0 = 0; i0 < sp.count; i0 += 8) {
-          int rows[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            rows[u] = i0 + u < sp.count ? __ldg(nbr + (size_t)sparse_k_s[i0 + u] * n_pad + r) : -1;
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            if (rows[u] >= 0) {
-#pragma unroll
-              for (int q = 0; q < kEpilogueHits; ++q)
-                if (n_hits == q) hit[q] = rows[u];
-              ++n_hits;
-            }
-          }
-        }
         __half *dst = out + (size_t)r * co_real;
 #pragma unroll
         for (int c0 = 0; c0 < CO; c0 += 16) {
@@ -450,34 +362,6 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
             for (int i = 0; i < 16; ++i) v[i] = 0u;
           }
           if (r < n_out) {
-            if (n_hits > 0) {
-              float acc[16];
-#pragma unroll
-              for (int i = 0; i < 16; ++i) acc[i] = __uint_as_float(v[i]);
-              auto add_row = [&](int row) {
-                const float4 *src = reinterpret_cast<const float4 *>(sp.partial + (size_t)row * CO + c0);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const float4 f = __ldg(src + q);
-                  acc[4 * q] += f.x;
-                  acc[4 * q + 1] += f.y;
-                  acc[4 * q + 2] += f.z;
-                  acc[4 * q + 3] += f.w;
-                }
-              };
-#pragma unroll
-              for (int q = 0; q < kEpilogueHits; ++q)
-                if (q < n_hits) add_row(hit[q]);
-              if (n_hits > kEpilogueHits) {  // rare: the rows past the first few, found again by a second scan
-                int seen = 0;
-                for (int i = 0; i < sp.count; ++i) {
-                  const int row = __ldg(nbr + (size_t)sparse_k_s[i] * n_pad + r);
-                  if (row >= 0 && seen++ >= kEpilogueHits) add_row(row);
-                }
-              }
-#pragma unroll
-              for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(acc[i]);
-            }
             __half2 h[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i)
@@ -543,44 +427,32 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
 
 template <int CI, int CO>
 cudaError_t launchTc(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
-                     const __half *filter, const int32_t *nbr, __half *out, int32_t *status,
-                     const SparseOffsets &sparse, double algo_bytes, double algo_flops, cudaStream_t stream) {
+                     const __half *filter, const int32_t *nbr, __half *out, int32_t *status, double algo_bytes,
+                     double algo_flops, cudaStream_t stream) {
   using Cfg = TcConfig<CI, CO>;
+  auto kernel = convTcgen05Kernel<CI, CO>;
   const size_t smem = Cfg::smemBytes();
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) return err;
+  const unsigned blocks = (unsigned)(plan.n_pad / (Cfg::kTiles * kTile));
   // the input gradient runs the same kernel; its launches are listed apart in the trace
   static const std::string name = "convTcgen05Kernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
   static const std::string name_dgrad = name + ":input_grad";
-  static const std::string name_pairs = name + ":sparse_offsets";
-  cudaError_t err;
-  if (sparse.count > 0) {
-    auto pair_kernel = convTcgen05Kernel<CI, CO, true>;
-    if ((err = cudaFuncSetAttribute(pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
-      return err;
-    const int tiles = sparse.tile_start[sparse.count];
-    const double rows = sparse.row_start[sparse.count];
-    trace::Scope t(name_pairs.c_str(), stream, rows * (p.ci * 2.0 + CO * 4.0 + 4.0), 2.0 * rows * p.ci * p.co);
-    pair_kernel<<<(unsigned)((tiles + Cfg::kTiles - 1) / Cfg::kTiles), kThreads, smem, stream>>>(
-        features, filter, nbr, p.n_out, plan.n_pad, p.K, p.ci, p.co, out, status, p.sticky_status, sparse);
-    if ((err = cudaGetLastError()) != cudaSuccess) return err;
-  }
-  auto kernel = convTcgen05Kernel<CI, CO, false>;
-  if ((err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return err;
-  const unsigned blocks = (unsigned)(plan.n_pad / (Cfg::kTiles * kTile));
   trace::Scope t(p.backward_data ? name_dgrad.c_str() : name.c_str(), stream, algo_bytes, algo_flops);
   kernel<<<blocks, kThreads, smem, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K, p.ci, p.co, out, status,
-                                             p.sticky_status, sparse);
+                                             p.sticky_status);
   return cudaGetLastError();
 }
 
 template <int CI>
 cudaError_t dispatchCo(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
-                       const __half *filter, const int32_t *nbr, __half *out, int32_t *status,
-                       const SparseOffsets &sparse, double algo_bytes, double algo_flops, cudaStream_t stream) {
+                       const __half *filter, const int32_t *nbr, __half *out, int32_t *status, double algo_bytes,
+                       double algo_flops, cudaStream_t stream) {
   switch (tcgen05PaddedChannels(p.co)) {
-    case 16: return launchTc<CI, 16>(p, plan, features, filter, nbr, out, status, sparse, algo_bytes, algo_flops, stream);
-    case 32: return launchTc<CI, 32>(p, plan, features, filter, nbr, out, status, sparse, algo_bytes, algo_flops, stream);
-    case 64: return launchTc<CI, 64>(p, plan, features, filter, nbr, out, status, sparse, algo_bytes, algo_flops, stream);
-    case 128: return launchTc<CI, 128>(p, plan, features, filter, nbr, out, status, sparse, algo_bytes, algo_flops, stream);
+    case 16: return launchTc<CI, 16>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 32: return launchTc<CI, 32>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 64: return launchTc<CI, 64>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 128: return launchTc<CI, 128>(p, plan, features, filter, nbr, out, status, algo_bytes, algo_flops, stream);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -599,13 +471,12 @@ bool tcgen05Eligible(const ConvProblem &p, const void *features, const void *out
 
 cudaError_t launchConvTcgen05(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
                               const __half *filter_kcoci, const int32_t *nbr, __half *out, int32_t *status,
-                              const SparseOffsets &sparse, double algo_bytes, double algo_flops,
-                              cudaStream_t stream) {
+                              double algo_bytes, double algo_flops, cudaStream_t stream) {
   switch (tcgen05PaddedChannels(p.ci)) {
-    case 16: return dispatchCo<16>(p, plan, features, filter_kcoci, nbr, out, status, sparse, algo_bytes, algo_flops, stream);
-    case 32: return dispatchCo<32>(p, plan, features, filter_kcoci, nbr, out, status, sparse, algo_bytes, algo_flops, stream);
-    case 64: return dispatchCo<64>(p, plan, features, filter_kcoci, nbr, out, status, sparse, algo_bytes, algo_flops, stream);
-    case 128: return dispatchCo<128>(p, plan, features, filter_kcoci, nbr, out, status, sparse, algo_bytes, algo_flops, stream);
+    case 16: return dispatchCo<16>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 32: return dispatchCo<32>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 64: return dispatchCo<64>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 128: return dispatchCo<128>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -12,22 +12,6 @@
 namespace mluop {
 namespace sparse_conv {
 
-// Kernel volumes the tensor-core kernel accepts.
-constexpr int kTcMaxOffsets = 128;
-
-// The offsets of a launch that take the pair-list route (see the kernel's header
-// comment), and where their partial products live.  count == 0: none.
-struct SparseOffsets {
-  int count;                           // sparse offsets
-  unsigned mask[kTcMaxOffsets / 32];   // bit k set: offset k is sparse
-  short k[kTcMaxOffsets];              // the i-th sparse offset, ascending
-  int tile_start[kTcMaxOffsets + 1];   // first 128-pair tile of the i-th sparse offset; [count] = all tiles
-  int row_start[kTcMaxOffsets + 1];    // first partial row of the i-th sparse offset; [count] = all rows
-  float *partial;                      // [rows][padded Co] fp32 products, one row per pair
-  const int32_t *gather_ids;           // ids of the gathered rows: row 0 (or 1) of offset 0 of indice_pairs
-  int64_t offset_stride;               // entries between the lists of consecutive offsets (2 * pair stride)
-};
-
 bool tcgen05Eligible(const ConvProblem &p, const void *features, const void *out);
 // The channel count the kernel runs a count of c at (16, 32, 64 or 128), 0 if unsupported.
 // The repacked filter the kernel reads is [K][padded Co][padded Ci], zero in the padding.
@@ -38,8 +22,7 @@ int tcgen05PaddedChannels(int c);
 // bit 1 MMA issuer, bit 2 epilogue, bit 3 producer on a filter buffer).
 cudaError_t launchConvTcgen05(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
                               const __half *filter_kcoci, const int32_t *nbr, __half *out, int32_t *status,
-                              const SparseOffsets &sparse, double algo_bytes, double algo_flops,
-                              cudaStream_t stream);
+                              double algo_bytes, double algo_flops, cudaStream_t stream);
 
 }  // namespace sparse_conv
 }  // namespace mluop

@@ -71,22 +71,9 @@ def test_sample_sharding_reproduces_the_unsharded_run(ops, workloads, backbone, 
     net.close()
 
 
-def _same_rows(a, b):
-    """Equal up to the rounding of the last half bit: the reference-shaped entry point sums the
-    offsets with few pairs per pair (fp32 partial rows added after the dense offsets), a
-    convolution from a table sums every offset in offset order; both orders are fixed, so each
-    path is reproducible, but their fp32 sums may differ in the last place."""
-    if a.shape != b.shape:
-        return False
-    fa, fb = a.float(), b.float()
-    close = torch.isclose(fa, fb, rtol=2e-3, atol=2e-4)
-    return bool(close.all()) and float((a != b).float().mean()) < 0.02
-
-
-def test_neighbour_table_fast_path_matches(ops, workloads, backbone, gpu_handle):
-    """One table per rulebook (mluOpBuildIndiceNeighbourTable / mluOpGetIndicePairsWithNeighbourTable +
-    ...ForwardFromTable) gives the features the reference-shaped entry point gives, and the same
-    coordinates bit for bit."""
+def test_neighbour_table_fast_path_is_bit_identical(ops, workloads, backbone, gpu_handle):
+    """One table per rulebook (mluOpBuildIndiceNeighbourTable + ...ForwardFromTable) gives exactly the
+    features the reference-shaped entry point gives."""
     idx, feat, layers, weights = workloads.make_inputs("c2", batch=1)
     grid = list(workloads.CONFIGS["c2"]["grid"])
     net = backbone.SparseNetwork(gpu_handle, layers, [torch.from_numpy(w).cuda() for w in weights], grid, 1)
@@ -95,7 +82,7 @@ def test_neighbour_table_fast_path_matches(ops, workloads, backbone, gpu_handle)
     b, ib, _ = net.forward(d_idx, d_feat, reuse_tables=True)
     c, ic, rc = net.forward(d_idx, d_feat, reuse_tables=True, defer_counts=True)
     torch.cuda.synchronize()
-    assert _same_rows(a, b) and torch.equal(ia, ib) and torch.equal(b, c) and torch.equal(ia, ic)
+    assert torch.equal(a, b) and torch.equal(ia, ib) and torch.equal(a, c) and torch.equal(ia, ic)
     assert any(r.indice_num is None for r in rc)
     net.resolve_counts(rc)
     assert [r.indice_num for r in rc] == [r.indice_num for r in ra]
@@ -119,7 +106,7 @@ def test_rulebooks_on_a_second_stream_are_bit_identical(ops, workloads, backbone
         b, ib, _ = net.forward(d_idx, d_feat)
         c, ic, _ = net.forward(d_idx, d_feat, reuse_tables=True, defer_counts=True)
         torch.cuda.synchronize()
-        assert torch.equal(a, b) and torch.equal(ia, ib) and _same_rows(a, c) and torch.equal(ia, ic)
+        assert torch.equal(a, b) and torch.equal(ia, ib) and torch.equal(a, c) and torch.equal(ia, ic)
     net.close()
     plain.close()
     second.destroy()

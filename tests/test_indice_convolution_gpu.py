@@ -183,23 +183,6 @@ def test_linearity_at_full_size(ops, oracle, workloads, gpu_handle):
     conv.destroy()
 
 
-@pytest.mark.parametrize("env", [{"MLUOP_B200_CONV_SPARSE_MIN_PAIRS": "1"}, {"MLUOP_B200_CONV_SPARSE_OFFSETS": "0"}])
-def test_sparse_offset_route_on_and_off(env):
-    """Offsets with few pairs take the pair-list route of the tensor-core kernel (products per
-    pair into a partial buffer, summed per output row in the epilogue).  With the minimum lowered
-    the small parity cases take it too, with the route switched off none does: both must pass
-    (the choice is per process, hence the child)."""
-    import os
-    import subprocess
-    import sys
-    here = os.path.dirname(os.path.abspath(__file__))
-    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_indice_convolution_gpu.py"),
-                        os.path.join(here, "test_indice_convolution_backward_gpu.py"), "-m", "gpu", "-x", "-q", "-k",
-                        "channel_sweep or large_kernel_volumes or config1_full or without_pairs or golden_input or adjoint"],
-                       env=dict(os.environ, **env), capture_output=True, text=True)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
-
-
 @pytest.mark.parametrize("variant", ["mma", "fma"])
 def test_other_kernel_variants(variant):
     """The mma.sync and plain-FMA variants of the convolution pass the same parity

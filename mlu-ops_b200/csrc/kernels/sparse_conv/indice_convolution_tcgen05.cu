@@ -157,9 +157,11 @@ struct TcConfig {
   static constexpr int kTiles = 2;                              // tiles per block
   static constexpr int kTmemCols = kTiles * CO < 32 ? 32 : kTiles * CO;  // 64, 128 or 256
   static constexpr int kBlocksPerSmByTmem = 512 / kTmemCols;
-  static constexpr int kBBuffers = 2;  // filter slices in flight
-  // gathered tiles in flight; sized so that as many blocks share an SM as tensor memory allows
-  static constexpr int kAStages = CI >= 128 ? 3 : 2;
+  // filter slices and gathered tiles in flight; sized so that as many blocks share an SM as
+  // tensor memory allows (128 input channels: 2 x 32 KB tiles + one 32 KB slice = two blocks
+  // per SM, which hides more latency than a third stage and a second slice in one block)
+  static constexpr int kBBuffers = CI >= 128 ? 1 : 2;
+  static constexpr int kAStages = 2;
   static constexpr int kChunksPerRow = CI / 8;  // 16-byte chunks of one feature row
   // instruction descriptor: D fp32, A and B fp16, both K-major, N = CO, M = 128
   static constexpr unsigned kIdesc = (1u << 4) | ((unsigned)(CO >> 3) << 17) | ((unsigned)(kTile >> 4) << 24);

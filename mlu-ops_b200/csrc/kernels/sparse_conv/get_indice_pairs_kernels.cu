@@ -202,10 +202,10 @@ __device__ __forceinline__ int hashLookup(const unsigned long long *__restrict__
 
 // ------------------------------------------------------- occupancy-bit table
 
+// A reduction: nothing is returned, so the thread does not wait for it (reading the
+// word first to spare the atomic made every bit a dependent round trip).
 __device__ __forceinline__ void setBit(uint2 *rank_table, uint32_t lin) {
-  const uint32_t bit = 1u << (lin & 31);
-  uint32_t *word = &rank_table[lin >> 5].x;
-  if (!(*(volatile uint32_t *)word & bit)) atomicOr(word, bit);
+  atomicOr(&rank_table[lin >> 5].x, 1u << (lin & 31));
 }
 
 // default mode: the occupancy bit of every valid output cell

@@ -299,6 +299,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardData(
       return MLUOP_STATUS_EXECUTION_FAILED;
     }
     if (word != 0) {
+      handle->host_words[mluOpContext::kStickyWord] = 0;  // reported here; not again by the next call
       LOG(ERROR) << api << " device reported error bits " << word << " (a bounded wait gave up).";
       return MLUOP_STATUS_EXECUTION_FAILED;
     }

@@ -30,6 +30,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <string>
 
 #include "core/trace.h"
@@ -46,7 +47,7 @@ constexpr int kProducerThreads = 128;     // warps 0-3: gather, then epilogue
 constexpr int kThreads = 160;             // + warp 4: TMEM allocation and MMA issue
 constexpr int kMaxOffsets = 128;           // kernel volumes up to 5x5x5
 constexpr int kMaskWords = kMaxOffsets / 32;
-constexpr long long kWaitCycles = 2000000000ll;  // a wait gives up after about one second
+constexpr long long kWaitCycles = 2000000000ll;  // a wait gives up after about one second (default)
 
 __device__ __forceinline__ unsigned smemAddr(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -64,30 +65,60 @@ __device__ __forceinline__ bool mbarTryWait(unsigned long long *bar, unsigned pa
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and raises the abort flag) when the phase did
-// not complete within kWaitCycles clock cycles or another waiter already gave up.
 struct ErrorSink {
   int32_t *status;  // status word in the workspace
   int32_t *sticky;  // device-visible host word of the handle, or null
 };
+__device__ __forceinline__ void raiseWaitError(const ErrorSink &sink, int code) {
+  atomicOr(sink.status, code);
+  if (sink.sticky) {
+    *reinterpret_cast<volatile int32_t *>(sink.sticky) = code << 8;
+    __threadfence_system();
+  }
+}
+// Bounded wait of ONE thread (the MMA issuer).  Returns false (and raises the abort
+// flag) when the phase did not complete within `limit` clock cycles or another
+// waiter already gave up.
 __device__ __forceinline__ bool mbarWait(unsigned long long *bar, unsigned parity, volatile int *abort_flag,
-                                         const ErrorSink &sink, int code) {
+                                         const ErrorSink &sink, int code, long long limit) {
   if (mbarTryWait(bar, parity)) return true;
   const long long t0 = clock64();
   for (unsigned spin = 1;; ++spin) {
     if (mbarTryWait(bar, parity)) return true;
     if ((spin & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) break;
+      if (clock64() - t0 > limit) break;
     }
   }
   *abort_flag = 1;
-  atomicOr(sink.status, code);
-  if (sink.sticky) {
-    *reinterpret_cast<volatile int32_t *>(sink.sticky) = code << 8;
-    __threadfence_system();
-  }
+  raiseWaitError(sink, code);
   return false;
+}
+// The same wait for a whole warp, called by all 32 lanes at the same point of the
+// program.  The lanes poll on their own, but they leave together: the result is a
+// vote, so a lane that gave up (or saw the abort flag) takes the whole warp to the
+// exit and no lane goes on to a warp-wide shuffle without the others.
+__device__ __forceinline__ bool mbarWaitWarp(unsigned long long *bar, unsigned parity, volatile int *abort_flag,
+                                             const ErrorSink &sink, int code, long long limit) {
+  bool ok = mbarTryWait(bar, parity);
+  if (!ok) {
+    const long long t0 = clock64();
+    for (unsigned spin = 1;; ++spin) {
+      if (mbarTryWait(bar, parity)) {
+        ok = true;
+        break;
+      }
+      if ((spin & 63u) == 0u) {
+        if (*abort_flag) break;
+        if (clock64() - t0 > limit) {
+          *abort_flag = 1;
+          raiseWaitError(sink, code);
+          break;
+        }
+      }
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
 }
 
 __device__ __forceinline__ void cpAsync16(unsigned smem, const void *gmem, bool valid) {
@@ -200,7 +231,8 @@ template <int CI, int CO>
 __global__ void __launch_bounds__(kThreads)
 convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict__ filter_kcoci,
                   const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, int ci_real, int co_real,
-                  __half *__restrict__ out, int32_t *status_word, int32_t *sticky) {
+                  __half *__restrict__ out, int32_t *status_word, int32_t *sticky, long long wait_limit,
+                  int test_drop_release) {
   using Cfg = TcConfig<CI, CO>;
   constexpr int S = Cfg::kAStages, NB = Cfg::kBBuffers, T = Cfg::kTiles;
   constexpr int CPR = Cfg::kChunksPerRow;  // 16-byte chunks per feature row
@@ -208,7 +240,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   // operand blocks must sit on 1024-byte boundaries (swizzle atoms)
   unsigned char *a_ring = reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
   unsigned char *b_ring = a_ring + (size_t)S * Cfg::kAStageBytes;
-  __shared__ unsigned long long a_full[S], a_empty[S], b_empty[NB], accum_bar;
+  __shared__ unsigned long long a_full[S], a_empty[S], b_empty[NB], accum_bar, drain_bar;
   __shared__ unsigned tmem_base_s;
   static_assert(T <= 2, "kMaxItems holds two tiles per offset");
   __shared__ unsigned masks_s[T][kMaskWords];
@@ -226,6 +258,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     }
     for (int b = 0; b < NB; ++b) mbarInit(&b_empty[b], 1);
     mbarInit(&accum_bar, 1);
+    mbarInit(&drain_bar, 1);
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -306,13 +339,13 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
         idx_next = __ldg(nbr_rows + (size_t)itemOffset(c1) * n_pad + itemTile(c1) * kTile);
       }
       if (it >= S) {
-        if (!mbarWait(&a_empty[s], a_parity ^ 1u, abort_flag, status, 1)) break;
+        if (!mbarWaitWarp(&a_empty[s], a_parity ^ 1u, abort_flag, status, 1, wait_limit)) break;
       }
       if (code & kItemFirst) {
         const int k = itemOffset(code);
         if (++b == NB) b = 0;
         if (b_uses >= (unsigned)NB) {
-          if (!mbarWait(&b_empty[b], ((b_uses / NB) - 1u) & 1u, abort_flag, status, 8)) break;
+          if (!mbarWaitWarp(&b_empty[b], ((b_uses / NB) - 1u) & 1u, abort_flag, status, 8, wait_limit)) break;
         }
         ++b_uses;
         unsigned char *b_buf = b_ring + (size_t)b * Cfg::kBBufBytes;
@@ -342,7 +375,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
 
     // ------------------------------------------------------------- epilogue
     bool have_acc = n_items > 0;
-    if (have_acc) have_acc = mbarWait(&accum_bar, 0, abort_flag, status, 4);
+    if (have_acc) have_acc = mbarWaitWarp(&accum_bar, 0, abort_flag, status, 4, wait_limit);
     tcFenceAfter();
     if (!*abort_flag) {
 #pragma unroll 1
@@ -391,7 +424,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
         if (code & kItemFirst) {
           if (++b == NB) b = 0;
         }
-        if (!mbarWait(&a_full[s], a_parity, abort_flag, status, 2)) break;
+        if (!mbarWait(&a_full[s], a_parity, abort_flag, status, 2, wait_limit)) break;
         fenceProxyAsync();
         tcFenceAfter();
         // only the start-address field (16-byte units) differs between stages and K steps
@@ -407,7 +440,9 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
                (((started >> t) & 1u) || j > 0) ? 1u : 0u);
         }
         started |= 1u << t;
-        ummaCommit(&a_empty[s]);  // the stage may be refilled once these MMAs have read it
+        // the stage may be refilled once these MMAs have read it (test hook: the first release of a
+        // block is withheld, so that the producers' wait for that stage runs out)
+        if (!(test_drop_release && it == 0)) ummaCommit(&a_empty[s]);
         // last item of offset k: its filter slice is free once these MMAs are done
         if (it + 1 == n_items || (items_s[it + 1] & kItemFirst)) ummaCommit(&b_empty[b]);
         if (++s == S) {
@@ -415,7 +450,17 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
           a_parity ^= 1u;
         }
       }
-      if (it == n_items && n_items > 0 && !*abort_flag) ummaCommit(&accum_bar);
+      if (it == n_items && n_items > 0 && !*abort_flag) {
+        ummaCommit(&accum_bar);
+      } else if (it > 0) {
+        // Leaving early: the MMAs issued so far may still be running, and tensor memory must not
+        // be freed under them (the next block could be given the same columns).  One more
+        // commit and one more bounded wait, whose outcome changes nothing, see them out.
+        ummaCommit(&drain_bar);
+        const long long t0 = clock64();
+        while (!mbarTryWait(&drain_bar, 0) && clock64() - t0 <= wait_limit) {
+        }
+      }
     }
     __syncwarp();
     tcFenceBefore();
@@ -441,8 +486,21 @@ cudaError_t launchTc(const ConvProblem &p, const ConvWorkspacePlan &plan, const 
   static const std::string name = "convTcgen05Kernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
   static const std::string name_dgrad = name + ":input_grad";
   trace::Scope t(p.backward_data ? name_dgrad.c_str() : name.c_str(), stream, algo_bytes, algo_flops);
+  // Test hook: MLUOP_B200_TEST_CONV_WAIT=<cycles> gives every wait that limit and withholds the
+  // first stage release of every block, so that the producers' bounded wait runs out: the kernel
+  // must record the error, leave through its common exit (copies drained, tensor memory freed) and
+  // return.  Nothing faults or spins on.
+  long long wait_limit = kWaitCycles;
+  int test_drop_release = 0;
+  if (const char *hook = std::getenv("MLUOP_B200_TEST_CONV_WAIT")) {
+    const long long cycles = std::atoll(hook);
+    if (cycles > 0) {
+      wait_limit = cycles;
+      test_drop_release = 1;
+    }
+  }
   kernel<<<blocks, kThreads, smem, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K, p.ci, p.co, out, status,
-                                             p.sticky_status);
+                                             p.sticky_status, wait_limit, test_drop_release);
   return cudaGetLastError();
 }
 

@@ -183,6 +183,28 @@ def test_linearity_at_full_size(ops, oracle, workloads, gpu_handle):
     conv.destroy()
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives(ops, oracle, gpu_handle, monkeypatch):
+    """Failure detection on the device without a fault: the test hook gives the tensor-core kernel's
+    waits a limit of about a millisecond and withholds one stage release per block, so the producers'
+    wait for that stage runs out.  The kernel must record the error, leave through its common exit
+    (copies drained, MMAs seen out, tensor memory freed) and return: the call reports
+    MLUOP_STATUS_EXECUTION_FAILED, and the same call without the hook then gives the right answer on
+    the same context."""
+    rng = np.random.default_rng(12)
+    space = [6, 10, 10]
+    n = 2 * 6 * 10 * 10  # fully occupied: every tile is live at (almost) every offset
+    pairs, num, n_out, feat, w = make_case(oracle, rng, 2, space, n, [3] * 3, [1] * 3, [1] * 3, 1, 64, 64, np.float16)
+    monkeypatch.setenv("MLUOP_B200_TEST_CONV_WAIT", "2000000")
+    with pytest.raises(ops.MluOpError) as err:
+        gpu_conv(ops, gpu_handle, feat, w, "ARRAY", [3] * 3, pairs, num, n_out, 1)
+    assert err.value.status == ops.STATUS_EXECUTION_FAILED
+    monkeypatch.delenv("MLUOP_B200_TEST_CONV_WAIT")
+    ref = oracle_conv(oracle, feat, w, "ARRAY", [3] * 3, pairs, num, n_out, 64, True)
+    for _ in range(2):  # tensor memory was freed: later launches get their columns and compute correctly
+        got = gpu_conv(ops, gpu_handle, feat, w, "ARRAY", [3] * 3, pairs, num, n_out, 1)
+        assert_close(oracle, got, ref, True)
+
+
 @pytest.mark.parametrize("variant", ["mma", "fma"])
 def test_other_kernel_variants(variant):
     """The mma.sync and plain-FMA variants of the convolution pass the same parity

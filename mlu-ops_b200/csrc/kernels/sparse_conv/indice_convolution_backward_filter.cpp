@@ -190,7 +190,8 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilter(
   if (workspace_size > 0) {
     PARAM_CHECK(api, workspace != nullptr);
   }
-  const FilterGradProblem p = makeProblem(features_desc, output_grad_desc, indice_pairs_desc);
+  FilterGradProblem p = makeProblem(features_desc, output_grad_desc, indice_pairs_desc);
+  p.sticky_status = handle->host_only ? nullptr : handle->host_words + mluOpContext::kStickyWord;
   const FilterGradWorkspacePlan plan =
       mluop::sparse_conv::planFilterGradWorkspace(p, indice_num, handle->sm_count);
   if (workspace_size < plan.total || workspace == nullptr) {
@@ -205,7 +206,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilter(
   if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
   cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionBackwardFilter(
       p, plan, features, output_grad, static_cast<const int32_t *>(indice_pairs), indice_num, workspace,
-      filters_grad, handle->queue);
+      filters_grad, handle->sm_count, handle->queue);
   if (err != cudaSuccess) {
     LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
     return MLUOP_STATUS_EXECUTION_FAILED;

@@ -28,6 +28,7 @@
 #include <string>
 
 #include "core/trace.h"
+#include "kernels/sparse_conv/indice_convolution_backward_filter_tcgen05.h"
 
 namespace mluop {
 namespace sparse_conv {
@@ -469,6 +470,20 @@ FilterGradWorkspacePlan planFilterGradWorkspace(const FilterGradProblem &p, cons
   off = alignUp(off + (size_t)p.K * sizeof(int32_t), 256);
   plan.partial = off;
   off = alignUp(off + (size_t)p.K * plan.max_segments * p.ci * p.co * sizeof(float), 256);
+  // The tensor-memory kernel is chosen by shape; should the pointers of the call
+  // turn out misaligned the pair-list kernels run in the same workspace.
+  plan.use_tc = filterGradTcShapeEligible(p) ? 1 : 0;
+  if (plan.use_tc) {
+    const FilterGradTcPlan tc = planFilterGradTc(p, sm_count);
+    size_t tc_off = plan.partial;
+    plan.tc_status = tc_off;
+    tc_off = alignUp(tc_off + 64 * sizeof(int32_t), 256);
+    plan.tc_table = tc_off;
+    tc_off = alignUp(tc_off + tc.table_bytes, 256);
+    plan.tc_partial = tc_off;
+    tc_off = alignUp(tc_off + tc.partial_bytes, 256);
+    if (tc_off > off) off = tc_off;
+  }
   plan.total = off + 256;
   return plan;
 }
@@ -478,7 +493,7 @@ cudaError_t launchIndiceConvolutionBackwardFilter(const FilterGradProblem &p,
                                                   const void *features, const void *output_grad,
                                                   const int32_t *indice_pairs,
                                                   const int64_t *indice_num, void *workspace,
-                                                  void *filters_grad, cudaStream_t stream) {
+                                                  void *filters_grad, int sm_count, cudaStream_t stream) {
   char *base = reinterpret_cast<char *>(alignUp(reinterpret_cast<size_t>(workspace), 256));
   int32_t *counts = reinterpret_cast<int32_t *>(base + plan.counts);
   float *partial = reinterpret_cast<float *>(base + plan.partial);
@@ -503,6 +518,13 @@ cudaError_t launchIndiceConvolutionBackwardFilter(const FilterGradProblem &p,
   const double bytes = pairs_total * ((p.ci + p.co) * elem + 8.0) + (double)p.K * p.ci * p.co * elem;
   const double flops = 2.0 * pairs_total * p.ci * p.co;
 
+  if (plan.use_tc && reinterpret_cast<size_t>(features) % 16 == 0 && reinterpret_cast<size_t>(output_grad) % 16 == 0) {
+    return launchFilterGradTcgen05(p, planFilterGradTc(p, sm_count), features, output_grad, indice_pairs, indice_num,
+                                   reinterpret_cast<int32_t *>(base + plan.tc_table),
+                                   reinterpret_cast<float *>(base + plan.tc_partial),
+                                   reinterpret_cast<int32_t *>(base + plan.tc_status), filters_grad, sm_count, bytes,
+                                   flops, stream);
+  }
   if (gradMmaEligible(p, features, output_grad)) {
     const __half *f = static_cast<const __half *>(features);
     const __half *g = static_cast<const __half *>(output_grad);

@@ -18,6 +18,9 @@ struct FilterGradProblem {
   int32_t K;      // kernel volume
   int32_t ci, co;
   int32_t is_half;
+  // Device-visible host word (or null) that a kernel's error path stores its error
+  // bits into, so that the next entry point on the handle can report them.
+  int32_t *sticky_status;
 };
 
 // The pair list of every kernel offset is cut into segments of seg_pairs pairs;
@@ -27,6 +30,11 @@ struct FilterGradProblem {
 struct FilterGradWorkspacePlan {
   size_t counts;   // int32[K]: pair counts
   size_t partial;  // float[K][max_segments][Ci][Co]
+  // tensor-memory kernel (half, 64 input channels): its own scratch, laid over `partial`
+  int32_t use_tc;
+  size_t tc_status;   // int32: error bits of the kernel's bounded waits
+  size_t tc_table;    // int32[K][n_pad]: the forward convolution's neighbour table
+  size_t tc_partial;  // float[blocks][pairs][128][Co]
   size_t total;
   int32_t seg_pairs;
   int32_t max_segments;  // segments of the longest pair list
@@ -41,7 +49,7 @@ cudaError_t launchIndiceConvolutionBackwardFilter(const FilterGradProblem &p,
                                                   const void *features, const void *output_grad,
                                                   const int32_t *indice_pairs,
                                                   const int64_t *indice_num, void *workspace,
-                                                  void *filters_grad, cudaStream_t stream);
+                                                  void *filters_grad, int sm_count, cudaStream_t stream);
 
 }  // namespace sparse_conv
 }  // namespace mluop

@@ -80,3 +80,27 @@ def guard_bands(ops):
     poisoned bands that are checked when the test ends (ops.Guards)."""
     with ops.guarded() as guards:
         yield guards
+
+
+@pytest.fixture
+def trace_kernels(ops):
+    """trace_kernels() is a context manager that yields a list filled, on exit, with the names
+    of the library kernels launched inside it (include/mlu_op_trace.h)."""
+    import contextlib
+    import ctypes
+
+    @contextlib.contextmanager
+    def tracing():
+        lib = ops.lib()
+        names = []
+        lib.mluOpTraceKernelReset()
+        lib.mluOpTraceKernelEnable(1)
+        try:
+            yield names
+        finally:
+            lib.mluOpTraceKernelEnable(0)
+            buf = ctypes.create_string_buffer(1 << 16)
+            assert lib.mluOpTraceKernelReport(buf, len(buf), None) == 0
+            names.extend(line.rsplit(",", 4)[0] for line in buf.value.decode().splitlines()[1:])
+
+    return tracing

@@ -183,3 +183,32 @@ def test_kernel_volumes_outside_the_tensor_core_range(ops, oracle, gpu_handle, k
     ref = r(oracle.indice_convolution_backward_filter(f32(feat), f32(og), ks, pairs, num))
     got = gpu_backward_filter(ops, gpu_handle, feat, og, ks, pairs, num, 1)
     assert_close(oracle, got.reshape(ref.shape), ref, is_half)
+
+
+@pytest.mark.parametrize("co", [64, 128])
+@pytest.mark.parametrize("ks,n,space", [([3, 3, 3], 30000, [20, 40, 40]), ([1, 1, 1], 5000, [10, 30, 30]),
+                                        ([5, 5, 5], 3000, [8, 16, 16]), ([3, 1, 2], 1000, [9, 10, 10])])
+def test_filter_gradient_in_tensor_memory(ops, oracle, gpu_handle, trace_kernels, monkeypatch, co, ks, n, space):
+    """Half with 64 input channels runs filterGradTcgen05Kernel (sums of all offsets of a
+    group kept in tensor memory, tiles of output rows streamed past them): several tiles
+    per block, a ragged last tile, odd kernel volumes (a pair with one offset) and more
+    groups than one.  Checked against the oracle, against the pair-list kernel
+    (MLUOP_B200_FILTER_GRAD_KERNEL=mma) and for bit-identical repeats."""
+    rng = np.random.default_rng(co + sum(ks) + n)
+    pad = [(k - 1) // 2 for k in ks]
+    for sub_m, stride in ((1, [1] * 3), (0, [2] * 3)):
+        pairs, num, n_out, feat, og, w = make_case(oracle, rng, 2, space, n, ks, stride, pad, sub_m, 64, co, np.float16)
+        ref = oracle.round_through_half(oracle.indice_convolution_backward_filter(
+            feat.astype(np.float32), og.astype(np.float32), ks, pairs, num))
+        with trace_kernels() as names:
+            got = gpu_backward_filter(ops, gpu_handle, feat, og, ks, pairs, num, sub_m)
+        assert any(nm.startswith("filterGradTcgen05Kernel") for nm in names), names
+        assert_close(oracle, got.reshape(ref.shape), ref, True)
+        again = gpu_backward_filter(ops, gpu_handle, feat, og, ks, pairs, num, sub_m)
+        assert np.array_equal(got, again)
+        monkeypatch.setenv("MLUOP_B200_FILTER_GRAD_KERNEL", "mma")
+        with trace_kernels() as names:
+            other = gpu_backward_filter(ops, gpu_handle, feat, og, ks, pairs, num, sub_m)
+        monkeypatch.delenv("MLUOP_B200_FILTER_GRAD_KERNEL")
+        assert not any(nm.startswith("filterGradTcgen05Kernel") for nm in names), names
+        assert_close(oracle, got, other, True)

@@ -116,13 +116,14 @@ class ClockSampler:
 D2H_CHUNK_BYTES = int(os.environ.get("BENCH_D2H_CHUNK", 4 << 20))
 
 
-def gpu_cpu_affinity(gpu_index):
-    """CPU ids the driver reports as local to this GPU (`nvidia-smi topo -m`, column "CPU Affinity"), or None."""
+def gpu_cpu_affinities():
+    """{gpu index: CPU ids the driver reports as local to it} from `nvidia-smi topo -m` (column
+    "CPU Affinity"); empty when the tool or the column is missing."""
     try:
         out = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=20).stdout
     except (OSError, subprocess.SubprocessError):
-        return None
-    header = None
+        return {}
+    header, found = None, {}
     for line in out.splitlines():
         cols = [c.strip() for c in line.split("\t") if c.strip()]
         if not cols:
@@ -130,34 +131,40 @@ def gpu_cpu_affinity(gpu_index):
         if header is None and any(c.startswith("CPU Affinity") for c in cols):
             header = cols
             continue
-        if header is not None and cols[0] == "GPU%d" % gpu_index:
+        if header is not None and cols[0].startswith("GPU") and cols[0][3:].isdigit():
             # data rows have one more leading column (the row label) than the header
             at = [i for i, c in enumerate(header) if c.startswith("CPU Affinity")][0] + 1
             if at >= len(cols):
-                return None
+                continue
             cpus = set()
             for part in cols[at].split(","):
                 lo, _, hi = part.partition("-")
                 if lo.isdigit():
                     cpus.update(range(int(lo), int(hi or lo) + 1))
-            return sorted(cpus) or None
-    return None
+            if cpus:
+                found[int(cols[0][3:])] = sorted(cpus)
+    return found
 
 
-def pin_rank_to_cores(local_rank, local_world, gpu_index):
+def pin_rank_to_cores(local_rank, local_world, gpu_index, gpu_indices=None):
     """Binds this process to its share of the cores that are local to its GPU (falling back to an
     even split of all cores), before any pinned host buffer is allocated, so that the buffers
-    land on that socket's memory.  Returns the description that goes into the JSON line."""
+    land on that socket's memory.  Ranks whose GPUs report the same set of local cores divide
+    that set among themselves by their position in the group.  `gpu_indices`: the GPU of every
+    local rank (default: rank r uses GPU r).  Returns the description that goes into the JSON line."""
     try:
         allowed = sorted(os.sched_getaffinity(0))
     except AttributeError:
         return None
-    local = gpu_cpu_affinity(gpu_index)
-    local = [c for c in (local or []) if c in allowed]
+    affinities = gpu_cpu_affinities()
+    local = [c for c in affinities.get(gpu_index, []) if c in allowed]
     if local:
-        # ranks whose GPUs share a socket share its cores: slice by position among them
-        share = max(1, len(local) // max(1, (local_world + 1) // 2))
-        first = (local_rank % max(1, len(local) // share)) * share
+        gpus = list(gpu_indices) if gpu_indices is not None else list(range(local_world))
+        same = [r for r, g in enumerate(gpus) if affinities.get(g) == affinities.get(gpu_index)]
+        if local_rank not in same:
+            same = sorted(same + [local_rank])
+        share = max(1, len(local) // len(same))
+        first = same.index(local_rank) * share
         mine, how = local[first:first + share], "cores local to the GPU"
     else:
         share = max(1, len(allowed) // local_world)
@@ -198,8 +205,10 @@ def run_b200(args):
     pinned = None
     if world > 1 and not args.no_pin_cores:
         visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-        gpu_index = int(visible.split(",")[local_rank]) if visible else local_rank
-        pinned = pin_rank_to_cores(local_rank, int(os.environ.get("LOCAL_WORLD_SIZE", world)), gpu_index)
+        local_world = int(os.environ.get("LOCAL_WORLD_SIZE", world))
+        ids = [int(v) for v in visible.split(",")] if visible and all(v.strip().isdigit() for v in visible.split(",")) else []
+        gpus = ids[:local_world] if len(ids) >= local_world else list(range(local_world))
+        pinned = pin_rank_to_cores(local_rank, local_world, gpus[local_rank], gpus)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -391,14 +400,20 @@ def run_b200(args):
         else:
             stream.wait_event(in_ready[slot])
             in_ready[slot] = None
-            if args.no_gather:
+            if args.no_gather or world == 1:
                 out, out_idx, records = net.forward(idx_in, feat_in)
             else:
-                out, out_idx, records = net.forward(idx_in, feat_in, on_final_indices=gather.begin)
-                gather.finish(out, wait=True)
+                # like the resident steps: the rows of the step before leave for rank 0 at the point of
+                # this step where the host would otherwise sit waiting for a rulebook, so neither the
+                # collectives' host cost nor their NVLink traffic holds up a step; the last step's
+                # gather is waited for before the region's closing event (drain)
+                out, out_idx, records = net.forward(idx_in, feat_in, on_host_idle=flush_pending)
+                flush_pending()
         done = torch.cuda.Event()
         done.record(stream)
         buf_free[slot] = done
+        if world > 1 and not args.no_gather and not pipelined:
+            pending.append((out, out_idx, done))
         out_pending.append((out, out_idx, done, slot))
         if pipelined:
             # rulebooks of the next batch (its inputs are on their way since the start of this step)

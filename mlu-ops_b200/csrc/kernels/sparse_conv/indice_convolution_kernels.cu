@@ -58,14 +58,28 @@ struct PairCounts {
 // dst is [K][n_dst][c_dst]: n the produced channel, c the contracted channel of this
 // direction (forward: n = Co, c = Ci; input gradient, `swap`: n = Ci, c = Co), zero where
 // n >= n_real or c >= c_real (channel counts padded for the tensor-core kernel).
+// Blocks [0, repack_blocks) of the grid repack; any further blocks fill `table` (table_vec
+// 16-byte words, null when there is nothing to fill) with -1, so that a call that also builds
+// its neighbour table needs one launch for both preparations.  Block 0 also clears the
+// workspace's status words.
 template <typename T>
 __global__ void __launch_bounds__(256)
 repackFilterKernel(const T *__restrict__ src, T *__restrict__ dst, int K, int ci, int co, int layout, int swap,
-                   int n_dst, int c_dst) {
+                   int n_dst, int c_dst, unsigned repack_blocks, int4 *__restrict__ table, int64_t table_vec,
+                   int32_t *__restrict__ status_words) {
+  // the 64 status words of the workspace start at zero for the kernels that follow
+  if (blockIdx.x == 0 && threadIdx.x < 64) status_words[threadIdx.x] = 0;
+  if (blockIdx.x >= repack_blocks) {
+    const int4 none = make_int4(-1, -1, -1, -1);
+    const int64_t stride = (int64_t)(gridDim.x - repack_blocks) * blockDim.x;
+    for (int64_t i = (int64_t)(blockIdx.x - repack_blocks) * blockDim.x + threadIdx.x; i < table_vec; i += stride)
+      table[i] = none;
+    return;
+  }
   const int64_t total = (int64_t)K * n_dst * c_dst;
   const int n_real = swap ? ci : co, c_real = swap ? co : ci;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
+       i += (int64_t)repack_blocks * blockDim.x) {
     const int c = (int)(i % c_dst);
     const int n = (int)((i / c_dst) % n_dst);
     const int k = (int)(i / ((int64_t)n_dst * c_dst));
@@ -507,7 +521,6 @@ cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWo
   int32_t *counts_dev = workspace ? reinterpret_cast<int32_t *>(base + plan.counts) : nullptr;
   int32_t *status = workspace ? reinterpret_cast<int32_t *>(base + plan.status) : nullptr;
   cudaError_t err;
-  if (do_conv && (err = cudaMemsetAsync(status, 0, 64 * sizeof(int32_t), stream)) != cudaSuccess) return err;
 
   double pairs_total = 0;
   int64_t max_pairs = 0;
@@ -529,31 +542,33 @@ cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWo
   const bool force_fma = forced && std::strcmp(forced, "fma") == 0;
   const bool use_tc = do_conv && !force_mma && !force_fma && tcgen05Eligible(p, features, features_out);
 
-  // 1. filter -> [K][Co][Ci] (channel counts padded for the tensor-core kernel)
+  // 1. filter -> [K][Co][Ci] (channel counts padded for the tensor-core kernel) and
+  // 2. the neighbour table filled with -1; one launch does both when the call needs both
+  const size_t table_bytes = (size_t)p.K * plan.n_pad * sizeof(int32_t);  // n_pad is a multiple of 512 rows
   if (do_conv) {
     const int n_dst = use_tc ? tcgen05PaddedChannels(p.co) : p.co;
     const int c_dst = use_tc ? tcgen05PaddedChannels(p.ci) : p.ci;
     const int64_t total = (int64_t)p.K * n_dst * c_dst;
     const unsigned blocks = (unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
-    trace::Scope t("repackFilterKernel", stream, 2.0 * total * elem);
+    const int64_t table_vec = do_build ? (int64_t)(table_bytes / sizeof(int4)) : 0;
+    // fill: 16 stores of 16 bytes per thread, at most 32 blocks per SM
+    int64_t fill_blocks = (table_vec + 256 * 16 - 1) / (256 * 16);
+    const int64_t fill_cap = (int64_t)(sm_count > 0 ? sm_count : 148) * 32;
+    if (fill_blocks > fill_cap) fill_blocks = fill_cap;
+    trace::Scope t(do_build ? "repackFilterKernel+fill" : "repackFilterKernel", stream,
+                   2.0 * total * elem + (double)(do_build ? table_bytes : 0));
     if (p.is_half) {
-      repackFilterKernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half *>(filters),
-                                                             static_cast<__half *>(filter_packed), p.K,
-                                                             caller.ci, caller.co, p.filter_layout, swap, n_dst,
-                                                             c_dst);
+      repackFilterKernel<__half><<<blocks + (unsigned)fill_blocks, 256, 0, stream>>>(
+          static_cast<const __half *>(filters), static_cast<__half *>(filter_packed), p.K, caller.ci, caller.co,
+          p.filter_layout, swap, n_dst, c_dst, blocks, reinterpret_cast<int4 *>(nbr), table_vec, status);
     } else {
-      repackFilterKernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float *>(filters),
-                                                            static_cast<float *>(filter_packed), p.K,
-                                                            caller.ci, caller.co, p.filter_layout, swap, n_dst,
-                                                            c_dst);
+      repackFilterKernel<float><<<blocks + (unsigned)fill_blocks, 256, 0, stream>>>(
+          static_cast<const float *>(filters), static_cast<float *>(filter_packed), p.K, caller.ci, caller.co,
+          p.filter_layout, swap, n_dst, c_dst, blocks, reinterpret_cast<int4 *>(nbr), table_vec, status);
     }
-  }
-
-  // 2. neighbour table
-  if (do_build) {
-    trace::Scope t("memset:neighbour_table", stream, 4.0 * p.K * plan.n_pad);
-    if ((err = cudaMemsetAsync(nbr, 0xFF, (size_t)p.K * plan.n_pad * sizeof(int32_t), stream)) != cudaSuccess)
-      return err;
+  } else if (do_build) {
+    trace::Scope t("memset:neighbour_table", stream, (double)table_bytes);
+    if ((err = cudaMemsetAsync(nbr, 0xFF, table_bytes, stream)) != cudaSuccess) return err;
   }
   if (do_build && max_pairs > 0) {
     int64_t bx = (max_pairs + 256 * kBuildPairsPerThread - 1) / (256 * kBuildPairsPerThread);

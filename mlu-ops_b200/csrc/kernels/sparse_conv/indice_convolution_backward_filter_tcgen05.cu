@@ -17,7 +17,7 @@
 // are cut into groups of that many pairs and a block serves one group.  The
 // blocks of a group (one per SM) take the tiles of 128 output rows round-robin.
 //
-// Per tile the four producer warps copy the tile's output_grad rows to shared
+// Per tile the eight producer warps copy the tile's output_grad rows to shared
 // memory once (contiguous rows, cp.async) and, for every pair with at least one
 // live row in the tile, gather the feature rows of its two offsets into a stage
 // of the ring (rows without a neighbour are zero-filled, nothing is fetched).
@@ -62,8 +62,10 @@ using namespace tc;
 
 constexpr int kTile = kConvTileRows;  // 128 output rows per tile
 constexpr int kCi = 64;               // input channels (one 128-byte swizzle atom per row)
-constexpr int kProducerThreads = 128;
-constexpr int kThreads = 160;
+constexpr int kProducerWarps = 8;      // warps 0-7: gather; warps 0-3 also read the sums back
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kIssuerWarp = kProducerWarps;  // tensor-memory allocation and MMA issue
+constexpr int kThreads = kProducerThreads + 32;
 constexpr int kSubTileBytes = kTile * kCi * 2;  // [128 rows][64 halfs], rows 128 bytes apart
 constexpr int kTmemCols = 512;
 constexpr long long kWaitCycles = 2000000000ll;  // a wait gives up after about one second
@@ -161,7 +163,7 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 4) tmemAlloc(&tmem_base_s, kTmemCols);
+  if (warp == kIssuerWarp) tmemAlloc(&tmem_base_s, kTmemCols);
   tcFenceBefore();
   __syncthreads();
   tcFenceAfter();
@@ -169,17 +171,21 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
   volatile int *abort_flag = &abort_s;
   const ErrorSink status{status_word, sticky};
 
-  if (warp < 4) {
+  if (warp < kProducerWarps) {
     // ------------------------------------------------------------ producers
-    // Lane l of warp w holds the table entries of row 32w+l and hands them to the
-    // lanes that fetch that row by shuffle; consecutive lanes fetch consecutive
-    // 16-byte chunks of a feature row (8 per row), so one warp instruction
-    // touches four rows.
+    // Eight warps, so that every scheduler of the SM has two to hide instruction latency
+    // with (four warps, one per scheduler, ran at a fifth of the issue rate and the kernel
+    // was bound by that, not by the copies or the MMAs).  Warp w gathers rows 16w..16w+15 of
+    // both offsets of a pair: lane l holds the table entry of row 16w + (l & 15) for offset
+    // 2q + (l >> 4) and hands it to the lanes that fetch that row by shuffle; consecutive
+    // lanes fetch consecutive 16-byte chunks of a feature row (8 per row), so one warp
+    // instruction touches four rows.
     const int rr0 = lane >> 3, chunk = lane & 7;
-    unsigned a_off[8];
+    const int my_row = warp * 16 + (lane & 15), my_half = lane >> 4;
+    unsigned a_off[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int row = warp * 32 + rr0 + i * 4;
+    for (int i = 0; i < 4; ++i) {
+      const int row = warp * 16 + rr0 + i * 4;
       unsigned off = (unsigned)(row * 128 + chunk * 16);
       off ^= ((off >> 7) & 7u) << 4;
       a_off[i] = off;
@@ -191,26 +197,13 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
     unsigned a_parity = 0, items = 0, ever_live = 0u;
     bool ok = true;
     int64_t n_mine = 0;
-    // table entries of the next tile: the whole tile's for the vote, this thread's row for the gather
+    // table entries of the next tile, for the vote
     int4 vote_next[OPG];
-    int idx_next[OPG];
     loadTileEntries<OPG>(nbr, n_pad, member, n_tiles, k0, k_end, lane, vote_next);
-#pragma unroll
-    for (int j = 0; j < OPG; ++j)
-      idx_next[j] = (k0 + j < k_end && member < n_tiles) ? __ldg(nbr + (size_t)(k0 + j) * n_pad + (int64_t)member * kTile + tid) : -1;
     for (int64_t tile = member; tile < n_tiles && ok; tile += blocks_per_group, ++n_mine) {
       const int64_t row0 = tile * kTile;
       const unsigned live = voteTileLive<OPG>(vote_next);
-      int idx[OPG];
-#pragma unroll
-      for (int j = 0; j < OPG; ++j) idx[j] = idx_next[j];
-      {
-        const int64_t next = tile + blocks_per_group;
-        loadTileEntries<OPG>(nbr, n_pad, next, n_tiles, k0, k_end, lane, vote_next);
-#pragma unroll
-        for (int j = 0; j < OPG; ++j)
-          idx_next[j] = (k0 + j < k_end && next < n_tiles) ? __ldg(nbr + (size_t)(k0 + j) * n_pad + next * kTile + tid) : -1;
-      }
+      loadTileEntries<OPG>(nbr, n_pad, tile + blocks_per_group, n_tiles, k0, k_end, lane, vote_next);
       ever_live |= live;
       // this tile's rows of output_grad
       const int g = (int)(n_mine % NG);
@@ -224,7 +217,7 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
       if (live) {
         const unsigned g_addr = g_ring_addr + (unsigned)g * Cfg::kGradBufBytes;
 #pragma unroll
-        for (int i = 0; i < kGradChunks; ++i) {
+        for (int i = 0; i < kGradChunks * kTile / kProducerThreads; ++i) {
           const int e = tid + i * kProducerThreads;
           const int row = e / kGradChunks, c = e % kGradChunks;
           unsigned off = (unsigned)(row * 128 + (c & 7) * 16);
@@ -236,9 +229,15 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
       }
       cpAsyncArriveOn(&g_full[g]);
       // the gathered feature rows of every live pair
-#pragma unroll
-      for (int q = 0; q < PPG; ++q) {
-        if (!ok || !((live >> (2 * q)) & 3u)) continue;
+      // (a real loop: unrolled over the pairs its body no longer fits the instruction cache)
+      unsigned todo = (live | (live >> 1)) & 0x55555555u;  // bit 2q: pair q has a live offset
+#pragma unroll 1
+      while (todo && ok) {
+        const int q = (__ffs(todo) - 1) >> 1;
+        todo &= todo - 1u;
+        // this lane's table entry: row 16w + (l & 15) of offset 2q + (l >> 4); the line is in L1 since the vote
+        const int k = k0 + 2 * q + my_half;
+        const int idx = k < k_end ? __ldg(nbr + (size_t)k * n_pad + row0 + my_row) : -1;
         if (items >= (unsigned)S) {
           if (!mbarWaitWarp(&a_empty[s], a_parity ^ 1u, abort_flag, status, kErrProducerStage, wait_limit)) {
             ok = false;
@@ -249,8 +248,8 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int src_row = __shfl_sync(0xffffffffu, idx[2 * q + h], rr0 + i * 4);
+          for (int i = 0; i < 4; ++i) {
+            const int src_row = __shfl_sync(0xffffffffu, idx, h * 16 + rr0 + i * 4);
             const bool valid = src_row >= 0;
             cpAsync16(stage_addr + (unsigned)h * kSubTileBytes + a_off[i], feat_chunk + (valid ? (size_t)src_row * kCi : 0),
                       valid);
@@ -270,7 +269,7 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
     bool have_acc = ok && items > 0;
     if (have_acc) have_acc = mbarWaitWarp(&accum_bar, 0, abort_flag, status, kErrAccum, wait_limit);
     tcFenceAfter();
-    if (ok && !*abort_flag) {
+    if (ok && !*abort_flag && warp < 4) {
       float *dst_block = partial + (size_t)blockIdx.x * pairs_per_group * kTile * CO;
 #pragma unroll 1
       for (int q = 0; q < pairs_per_group; ++q) {
@@ -356,7 +355,7 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
     tcFenceBefore();
   }
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kIssuerWarp) {
     tcFenceAfter();
     tmemDealloc(tmem_base, kTmemCols);
   }

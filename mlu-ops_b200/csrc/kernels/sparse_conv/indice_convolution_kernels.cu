@@ -66,7 +66,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 repackFilterKernel(const T *__restrict__ src, T *__restrict__ dst, int K, int ci, int co, int layout, int swap,
                    int n_dst, int c_dst, unsigned repack_blocks, int4 *__restrict__ table, int64_t table_vec,
-                   int32_t *__restrict__ status_words) {
+                   int32_t *__restrict__ status_words, int image_row_bytes, int image_block_stride,
+                   int image_bytes_per_offset) {
   // the 64 status words of the workspace start at zero for the kernels that follow
   if (blockIdx.x == 0 && threadIdx.x < 64) status_words[threadIdx.x] = 0;
   if (blockIdx.x >= repack_blocks) {
@@ -96,7 +97,17 @@ repackFilterKernel(const T *__restrict__ src, T *__restrict__ dst, int K, int ci
       }
       v = src[s];
     }
-    dst[i] = v;
+    if (image_row_bytes == 0) {
+      dst[i] = v;
+    } else {
+      // the tensor-core kernel's shared-memory image of this offset (see Tcgen05FilterImage)
+      const int block_k = image_row_bytes / (int)sizeof(T);
+      unsigned off = (unsigned)(n * image_row_bytes + (c % block_k) * (int)sizeof(T));
+      off ^= ((off >> 7) & (unsigned)(image_row_bytes / 16 - 1)) << 4;
+      char *at = reinterpret_cast<char *>(dst) + (size_t)k * image_bytes_per_offset +
+                 (size_t)(c / block_k) * image_block_stride + off;
+      *reinterpret_cast<T *>(at) = v;
+    }
   }
 }
 
@@ -477,7 +488,17 @@ ConvWorkspacePlan planConvWorkspace(const ConvProblem &p, bool external_table) {
   // room for the channel counts the tensor-core kernel pads to
   const size_t ci_room = p.is_half && tcgen05PaddedChannels(p.ci) ? tcgen05PaddedChannels(p.ci) : p.ci;
   const size_t co_room = p.is_half && tcgen05PaddedChannels(p.co) ? tcgen05PaddedChannels(p.co) : p.co;
-  off = alignUp(off + (size_t)p.K * ci_room * co_room * elem, 256);
+  size_t filter_bytes = (size_t)p.K * ci_room * co_room * elem;
+  if (p.is_half && tcgen05PaddedChannels(p.ci) && tcgen05PaddedChannels(p.co)) {
+    // the tensor-core kernel's filter image (blocks padded to 1 KiB); the contracted channel is
+    // Ci forward and Co in the input gradient, the image is as large either way round only when
+    // both are taken into account
+    const size_t fwd = (size_t)tcgen05FilterImage((int)ci_room, (int)co_room).bytes_per_offset;
+    const size_t bwd = (size_t)tcgen05FilterImage((int)co_room, (int)ci_room).bytes_per_offset;
+    const size_t image = (size_t)p.K * (fwd > bwd ? fwd : bwd);
+    if (image > filter_bytes) filter_bytes = image;
+  }
+  off = alignUp(off + filter_bytes, 256);
   plan.neighbour = off;
   if (!external_table) off = alignUp(off + (size_t)p.K * plan.n_pad * sizeof(int32_t), 256);
   plan.counts = off;
@@ -555,16 +576,20 @@ cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWo
     int64_t fill_blocks = (table_vec + 256 * 16 - 1) / (256 * 16);
     const int64_t fill_cap = (int64_t)(sm_count > 0 ? sm_count : 148) * 32;
     if (fill_blocks > fill_cap) fill_blocks = fill_cap;
+    Tcgen05FilterImage image{0, 0, 0};
+    if (use_tc) image = tcgen05FilterImage(c_dst, n_dst);
     trace::Scope t(do_build ? "repackFilterKernel+fill" : "repackFilterKernel", stream,
                    2.0 * total * elem + (double)(do_build ? table_bytes : 0));
     if (p.is_half) {
       repackFilterKernel<__half><<<blocks + (unsigned)fill_blocks, 256, 0, stream>>>(
           static_cast<const __half *>(filters), static_cast<__half *>(filter_packed), p.K, caller.ci, caller.co,
-          p.filter_layout, swap, n_dst, c_dst, blocks, reinterpret_cast<int4 *>(nbr), table_vec, status);
+          p.filter_layout, swap, n_dst, c_dst, blocks, reinterpret_cast<int4 *>(nbr), table_vec, status,
+          image.row_bytes, image.block_stride, image.bytes_per_offset);
     } else {
       repackFilterKernel<float><<<blocks + (unsigned)fill_blocks, 256, 0, stream>>>(
           static_cast<const float *>(filters), static_cast<float *>(filter_packed), p.K, caller.ci, caller.co,
-          p.filter_layout, swap, n_dst, c_dst, blocks, reinterpret_cast<int4 *>(nbr), table_vec, status);
+          p.filter_layout, swap, n_dst, c_dst, blocks, reinterpret_cast<int4 *>(nbr), table_vec, status,
+          image.row_bytes, image.block_stride, image.bytes_per_offset);
     }
   } else if (do_build) {
     trace::Scope t("memset:neighbour_table", stream, (double)table_bytes);

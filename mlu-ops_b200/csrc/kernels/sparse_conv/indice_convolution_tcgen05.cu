@@ -4,7 +4,8 @@
 // One thread block owns a few consecutive tiles of 128 output rows and keeps
 // one [128 x Co] fp32 accumulator per tile in TMEM for the whole kernel.  It
 // walks the kernel offsets in ascending order; for each offset k the filter
-// slice W_k ([Co x Ci], Ci contiguous) is copied to shared memory once and
+// slice W_k ([Co x Ci], Ci contiguous) arrives in shared memory by ONE bulk copy
+// (the repacked filter is the byte image of the operand, swizzle included) and is
 // reused by all tiles of the block, and for every tile with at least one live
 // row at k (a per-tile bit mask the block derives from the neighbour table)
 //   * four producer warps (one thread per output row) gather the input rows
@@ -112,7 +113,7 @@ __device__ __forceinline__ int itemTile(unsigned code) { return (int)(code & 3u)
 
 template <int CI, int CO>
 __global__ void __launch_bounds__(kThreads)
-convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict__ filter_kcoci,
+convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict__ filter_image,
                   const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, int ci_real, int co_real,
                   __half *__restrict__ out, int32_t *status_word, int32_t *sticky, long long wait_limit,
                   int test_drop_release) {
@@ -123,7 +124,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   // operand blocks must sit on 1024-byte boundaries (swizzle atoms)
   unsigned char *a_ring = reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
   unsigned char *b_ring = a_ring + (size_t)S * Cfg::kAStageBytes;
-  __shared__ unsigned long long a_full[S], a_empty[S], b_empty[NB], accum_bar, drain_bar;
+  __shared__ unsigned long long a_full[S], a_empty[S], b_full[NB], b_empty[NB], accum_bar, drain_bar;
   __shared__ unsigned tmem_base_s;
   static_assert(T <= 2, "kMaxItems holds two tiles per offset");
   __shared__ unsigned masks_s[T][kMaskWords];
@@ -139,7 +140,10 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
       mbarInit(&a_full[s], kProducerThreads);
       mbarInit(&a_empty[s], 1);
     }
-    for (int b = 0; b < NB; ++b) mbarInit(&b_empty[b], 1);
+    for (int b = 0; b < NB; ++b) {
+      mbarInit(&b_full[b], 1);
+      mbarInit(&b_empty[b], 1);
+    }
     mbarInit(&accum_bar, 1);
     mbarInit(&drain_bar, 1);
     abort_s = 0;
@@ -153,11 +157,22 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
   // Live masks: bit k of masks_s[t] is set when some row of tile t has a
   // neighbour at offset k.  Each warp scans (offset, tile) slices of the table,
   // four rows per lane.
-  for (int e = warp; e < K * T; e += kThreads / 32) {
-    const int k = e / T, t = e % T;
-    const int4 v = __ldg(reinterpret_cast<const int4 *>(nbr + (size_t)k * n_pad + row0 + t * kTile) + lane);
-    const unsigned any = __ballot_sync(0xffffffffu, (v.x & v.y & v.z & v.w) >= 0);
-    if (lane == 0 && any) atomicOr(&masks_s[t][k >> 5], 1u << (k & 31));
+  // (eight slices' loads are issued before the first vote, so a warp pays the memory latency
+  // once per eight slices, not once per slice)
+  for (int e0 = warp; e0 < K * T; e0 += 8 * (kThreads / 32)) {
+    int4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = e0 + u * (kThreads / 32);
+      v[u] = make_int4(-1, -1, -1, -1);
+      if (e < K * T) v[u] = __ldg(reinterpret_cast<const int4 *>(nbr + (size_t)(e / T) * n_pad + row0 + (e % T) * kTile) + lane);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = e0 + u * (kThreads / 32);
+      const unsigned any = __ballot_sync(0xffffffffu, (v[u].x & v[u].y & v[u].z & v[u].w) >= 0);
+      if (lane == 0 && any && e < K * T) atomicOr(&masks_s[e % T][(e / T) >> 5], 1u << ((e / T) & 31));
+    }
   }
   __syncthreads();
   if (tid == 0) {
@@ -188,8 +203,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     // cp.async (zero fill for rows without a neighbour: nothing is read), and
     // each thread lets the stage's mbarrier collect one arrival when its own
     // copies have landed, so producers never wait for data: as many gathers are
-    // in flight as there are stages.  The filter slice of offset k travels with
-    // the first item of k.
+    // in flight as there are stages.
     constexpr int kRowsPerInstr = 32 / CPR > 0 ? 32 / CPR : 1;  // rows one warp instruction covers (CPR <= 32)
     const int rr0 = lane / CPR;         // row (within the instruction's rows) this lane fetches
     const int chunk = lane % CPR;       // its 16-byte chunk of the row
@@ -225,21 +239,23 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
         if (!mbarWaitWarp(&a_empty[s], a_parity ^ 1u, abort_flag, status, 1, wait_limit)) break;
       }
       if (code & kItemFirst) {
-        const int k = itemOffset(code);
+        // The filter slice of offset k: one bulk copy of its shared-memory image, issued by one
+        // thread of warp 0 once the MMAs that read the buffer's previous slice are done; its
+        // bytes are counted by b_full[b], which the issuer waits for.
         if (++b == NB) b = 0;
-        if (b_uses >= (unsigned)NB) {
-          if (!mbarWaitWarp(&b_empty[b], ((b_uses / NB) - 1u) & 1u, abort_flag, status, 8, wait_limit)) break;
+        if (warp == 0) {
+          if (b_uses >= (unsigned)NB) {
+            if (!mbarWaitWarp(&b_empty[b], ((b_uses / NB) - 1u) & 1u, abort_flag, status, 8, wait_limit)) break;
+          }
+          if (lane == 0) {
+            mbarArriveExpectTx(&b_full[b], (unsigned)Cfg::kBBufBytes);
+            bulkCopyToShared(smemAddr(b_ring + (size_t)b * Cfg::kBBufBytes),
+                             reinterpret_cast<const unsigned char *>(filter_image) + (size_t)itemOffset(code) * Cfg::kBBufBytes,
+                             (unsigned)Cfg::kBBufBytes, &b_full[b]);
+          }
+          __syncwarp();
         }
         ++b_uses;
-        unsigned char *b_buf = b_ring + (size_t)b * Cfg::kBBufBytes;
-        const __half *wk = filter_kcoci + (size_t)k * CO * CI;
-        for (int e = tid; e < CO * CPR; e += kProducerThreads) {
-          const int n = e / CPR, c = e % CPR;
-          const int kb = c / (Cfg::kRowBytes / 16), cc = c % (Cfg::kRowBytes / 16);
-          unsigned off = (unsigned)(n * Cfg::kRowBytes + cc * 16);
-          off ^= ((off >> 7) & Cfg::kSwizzleMask) << 4;
-          cpAsync16(smemAddr(b_buf + kb * Cfg::kBBlockStride + off), wk + (size_t)n * CI + c * 8, true);
-        }
       }
       const unsigned stage_addr = a_ring_addr + (unsigned)s * Cfg::kAStageBytes;
 #pragma unroll
@@ -255,6 +271,15 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
       }
     }
     cpAsyncWaitAll();
+    if (tid == 0 && *abort_flag) {
+      // leaving early: a bulk copy may still be writing a filter buffer; see it out (bounded)
+      for (int i = 0; i < NB && (unsigned)i < b_uses; ++i) {
+        const unsigned use = b_uses - 1u - (unsigned)i;  // the i-th last slice sent
+        const long long t0 = clock64();
+        while (!mbarTryWait(&b_full[use % NB], (use / NB) & 1u) && clock64() - t0 <= wait_limit) {
+        }
+      }
+    }
 
     // ------------------------------------------------------------- epilogue
     bool have_acc = n_items > 0;
@@ -298,6 +323,7 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
       const unsigned long long a_desc0 = makeDesc<Cfg>(smemAddr(a_ring));
       const unsigned long long b_desc0 = makeDesc<Cfg>(smemAddr(b_ring));
       unsigned started = 0;  // tiles whose accumulator has been written
+      unsigned b_firsts = 0;  // offsets begun so far
       int s = 0, b = -1;
       unsigned a_parity = 0;
       int it = 0;
@@ -306,6 +332,8 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
         const int t = itemTile(code);
         if (code & kItemFirst) {
           if (++b == NB) b = 0;
+          if (!mbarWait(&b_full[b], (b_firsts / NB) & 1u, abort_flag, status, 16, wait_limit)) break;
+          ++b_firsts;
         }
         if (!mbarWait(&a_full[s], a_parity, abort_flag, status, 2, wait_limit)) break;
         fenceProxyAsync();
@@ -413,13 +441,13 @@ bool tcgen05Eligible(const ConvProblem &p, const void *features, const void *out
 }
 
 cudaError_t launchConvTcgen05(const ConvProblem &p, const ConvWorkspacePlan &plan, const __half *features,
-                              const __half *filter_kcoci, const int32_t *nbr, __half *out, int32_t *status,
+                              const __half *filter_image, const int32_t *nbr, __half *out, int32_t *status,
                               double algo_bytes, double algo_flops, cudaStream_t stream) {
   switch (tcgen05PaddedChannels(p.ci)) {
-    case 16: return dispatchCo<16>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);
-    case 32: return dispatchCo<32>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);
-    case 64: return dispatchCo<64>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);
-    case 128: return dispatchCo<128>(p, plan, features, filter_kcoci, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 16: return dispatchCo<16>(p, plan, features, filter_image, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 32: return dispatchCo<32>(p, plan, features, filter_image, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 64: return dispatchCo<64>(p, plan, features, filter_image, nbr, out, status, algo_bytes, algo_flops, stream);
+    case 128: return dispatchCo<128>(p, plan, features, filter_image, nbr, out, status, algo_bytes, algo_flops, stream);
     default: return cudaErrorInvalidValue;
   }
 }

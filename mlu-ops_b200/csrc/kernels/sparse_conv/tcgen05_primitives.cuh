@@ -98,6 +98,20 @@ __device__ __forceinline__ void cpAsync16(unsigned smem, const void *gmem, bool 
 __device__ __forceinline__ void cpAsyncArriveOn(unsigned long long *bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smemAddr(bar)) : "memory");
 }
+// One arrival on an mbarrier of this block that also announces `bytes` of bulk-copy data: the
+// barrier's phase completes when the arrivals are in and that many bytes have landed.
+__device__ __forceinline__ void mbarArriveExpectTx(unsigned long long *bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smemAddr(bar)), "r"(bytes) : "memory");
+}
+// Bulk copy (the TMA engine, no tensor map) of `bytes` contiguous bytes from global to this
+// block's shared memory; both addresses 16-byte aligned, bytes a multiple of 16.  Completion is
+// reported to the mbarrier as transferred bytes.  No multicast.
+__device__ __forceinline__ void bulkCopyToShared(unsigned smem_dst, const void *gmem_src, unsigned bytes,
+                                                 unsigned long long *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_dst),
+               "l"(gmem_src), "r"(bytes), "r"(smemAddr(bar))
+               : "memory");
+}
 __device__ __forceinline__ void cpAsyncWaitAll() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 __device__ __forceinline__ void fenceProxyAsync() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }

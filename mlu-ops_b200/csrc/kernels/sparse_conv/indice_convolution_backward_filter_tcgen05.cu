@@ -1,6 +1,6 @@
 // Filter gradient of the sparse convolution on the 5th-generation tensor cores
-// (tcgen05) of sm_100a: half inputs with 64 input channels, fp32 accumulation in
-// tensor memory.
+// (tcgen05) of sm_100a: half inputs with 32 or 64 input channels, fp32 accumulation
+// in tensor memory.
 //
 //   filters_grad[k,c,n] = sum_j features[nbr[k][j], c] * output_grad[j, n]
 //
@@ -11,21 +11,22 @@
 // offsets in tensor memory for the whole kernel and streams tiles of 128 output
 // rows past them.
 //
-// Work split.  Two offsets share one accumulator of 128 lanes (lanes 0-63: the 64
-// input channels of offset 2q, lanes 64-127: those of offset 2q+1) and Co
-// columns; 512 columns of tensor memory hold 512/Co such pairs, so the offsets
-// are cut into groups of that many pairs and a block serves one group.  The
-// blocks of a group (one per SM) take the tiles of 128 output rows round-robin.
+// Work split.  128 / Ci offsets (a "bundle": two at 64 channels, four at 32) share
+// one accumulator of 128 lanes (lanes h*Ci .. h*Ci+Ci-1: the input channels of the
+// bundle's h-th offset) and Co columns.  Tensor memory holds 512/Co such bundles
+// (and the kernel keeps at most 16 offsets' table entries in registers), so the
+// offsets are cut into groups and a block serves one group.  The blocks of a group
+// (one per SM) take the tiles of 128 output rows round-robin.
 //
 // Per tile the eight producer warps copy the tile's output_grad rows to shared
-// memory once (contiguous rows, cp.async) and, for every pair with at least one
-// live row in the tile, gather the feature rows of its two offsets into a stage
+// memory once (contiguous rows, cp.async) and, for every bundle with at least one
+// live row in the tile, gather the feature rows of its offsets into a stage
 // of the ring (rows without a neighbour are zero-filled, nothing is fetched).
 // Both operands lie row-major in shared memory - the contracted axis (rows) is
 // the slow one - which tcgen05.mma reads as "MN-major" operands: one elected
-// thread issues 8 MMAs (M=128, N=Co, K=16 rows each) per pair and tile and
+// thread issues 8 MMAs (M=128, N=Co, K=16 rows each) per bundle and tile and
 // releases the stage with tcgen05.commit.  Producers, issuer and epilogue each
-// derive which pairs are live from the table itself (a warp reads the tile's
+// derive which bundles are live from the table itself (a warp reads the tile's
 // 128 entries of an offset with one 16-byte load per lane and votes), so no
 // flags travel between them.
 //
@@ -61,42 +62,63 @@ namespace {
 using namespace tc;
 
 constexpr int kTile = kConvTileRows;  // 128 output rows per tile
-constexpr int kCi = 64;               // input channels (one 128-byte swizzle atom per row)
 constexpr int kProducerWarps = 8;      // warps 0-7: gather; warps 0-3 also read the sums back
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kIssuerWarp = kProducerWarps;  // tensor-memory allocation and MMA issue
 constexpr int kThreads = kProducerThreads + 32;
-constexpr int kSubTileBytes = kTile * kCi * 2;  // [128 rows][64 halfs], rows 128 bytes apart
-constexpr int kTmemCols = 512;
+constexpr int kMaxGroupOffsets = 16;  // offsets whose table entries a thread keeps in registers
 constexpr long long kWaitCycles = 2000000000ll;  // a wait gives up after about one second
 constexpr int kErrProducerStage = 1, kErrIssuerStage = 2, kErrAccum = 4, kErrGradTile = 8, kErrIssuerGrad = 16;
 
-template <int CO>
+// An operand tile in shared memory: 128 rows (the contracted axis) of up to 64 halfs,
+// `row_bytes` apart, 16-byte chunks XOR-swizzled over `row_bytes`; wider rows are split
+// into 64-half atoms `kTileBytes` apart.
+template <int CHANNELS>
+struct OperandTile {
+  static constexpr int kAtomChannels = CHANNELS < 64 ? CHANNELS : 64;
+  static constexpr int kAtoms = CHANNELS / kAtomChannels;
+  static constexpr int kRowBytes = kAtomChannels * 2;              // 64 or 128
+  static constexpr unsigned kSwizzleMask = kRowBytes / 16 - 1;     // 3 or 7
+  static constexpr unsigned long long kLayoutType = kRowBytes == 128 ? 2 : 4;  // 128-byte / 64-byte swizzle
+  static constexpr int kTileBytes = kTile * kRowBytes;             // one atom: 8 or 16 KB
+  static constexpr int kBytes = kAtoms * kTileBytes;
+  static constexpr int kGroupStride = 8 * kRowBytes;               // between groups of 8 rows
+  static constexpr int kStepBytes = 16 * kRowBytes;                // 16 rows of the contracted axis (one MMA)
+};
+
+template <int CI, int CO>
 struct GradTcConfig {
-  static constexpr int kPairsPerGroup = kTmemCols / CO;  // accumulators of 128 lanes x CO columns
-  static constexpr int kOffsetsPerGroup = 2 * kPairsPerGroup;
-  // as many stages as shared memory holds: the gathers are latency-bound, what counts is bytes in flight
-  static constexpr int kAStages = CO == 64 ? 6 : 5;
-  static constexpr int kAStageBytes = 2 * kSubTileBytes;         // the gathered rows of two offsets
-  static constexpr int kGradBufBytes = (CO / 64) * kSubTileBytes;  // one tile of output_grad rows
+  using A = OperandTile<CI>;   // the gathered rows of ONE offset
+  using G = OperandTile<CO>;   // a tile of output_grad rows
+  static constexpr int kOffsetsPerBundle = kTile / CI;  // 2 or 4: together 128 accumulator lanes
+  static constexpr int kBundlesByTmem = 512 / CO;
+  static constexpr int kBundlesByRegs = kMaxGroupOffsets / kOffsetsPerBundle;
+  static constexpr int kBundlesPerGroup = kBundlesByTmem < kBundlesByRegs ? kBundlesByTmem : kBundlesByRegs;
+  static constexpr int kOffsetsPerGroup = kBundlesPerGroup * kOffsetsPerBundle;
+  static constexpr int kTmemCols = kBundlesPerGroup * CO;  // 128, 256 or 512 (a power of two)
+  static constexpr int kAStageBytes = kOffsetsPerBundle * A::kBytes;  // 32 KB: the gathered rows of a bundle
+  static constexpr int kGradBufBytes = G::kBytes;
   static constexpr int kGradBufs = 2;
+  // as many stages as shared memory holds: the gathers are latency-bound, what counts is bytes in flight
+  static constexpr int kAStages = (227 * 1024 - 2048 - kGradBufs * kGradBufBytes) / kAStageBytes;
   static constexpr size_t kSmemBytes = 1024 + (size_t)kAStages * kAStageBytes + (size_t)kGradBufs * kGradBufBytes;
   // D fp32, A and B fp16, both MN-major (bits 15 and 16), N = CO, M = 128
   static constexpr unsigned kIdesc =
       (1u << 4) | (1u << 15) | (1u << 16) | ((unsigned)(CO >> 3) << 17) | ((unsigned)(kTile >> 4) << 24);
 };
 
-// Descriptor of an MN-major operand with the 128-byte swizzle: 64 elements of the
-// M (or N) axis are contiguous (one 128-byte row per step of the contracted axis),
-// groups of 8 such rows are 1024 bytes apart (stride byte offset) and the next 64
-// elements of the M/N axis start `atom_stride` bytes further (leading byte offset).
+// Descriptor of an MN-major operand tile: the elements of an atom's M (or N) axis are
+// contiguous (one row per step of the contracted axis), groups of 8 rows are
+// kGroupStride bytes apart (stride byte offset) and the next atom of the M/N axis starts
+// `atom_stride` bytes further (leading byte offset).
+template <typename Tile>
 __device__ __forceinline__ unsigned long long makeDescMn(unsigned smem_byte_addr, unsigned atom_stride) {
   unsigned long long d = 0;
   d |= (unsigned long long)((smem_byte_addr & 0x3FFFFu) >> 4);
   d |= (unsigned long long)(atom_stride >> 4) << 16;
-  d |= (unsigned long long)(1024u >> 4) << 32;
+  d |= (unsigned long long)((unsigned)Tile::kGroupStride >> 4) << 32;
   d |= 1ull << 46;
-  d |= 2ull << 61;
+  d |= Tile::kLayoutType << 61;
   return d;
 }
 
@@ -127,13 +149,16 @@ __device__ __forceinline__ unsigned voteTileLive(const int4 (&v)[OFFSETS]) {
   return mask;
 }
 
-template <int CO>
+template <int CI, int CO>
 __global__ void __launch_bounds__(kThreads, 1)
 filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict__ output_grad,
-                        const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, int pairs_per_group,
+                        const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, int bundles_per_group,
                         int blocks_per_group, float *__restrict__ partial, int32_t *status_word, int32_t *sticky, long long wait_limit) {
-  using Cfg = GradTcConfig<CO>;
-  constexpr int S = Cfg::kAStages, NG = Cfg::kGradBufs, PPG = Cfg::kPairsPerGroup, OPG = Cfg::kOffsetsPerGroup;
+  using Cfg = GradTcConfig<CI, CO>;
+  using ATile = typename Cfg::A;
+  using GTile = typename Cfg::G;
+  constexpr int S = Cfg::kAStages, NG = Cfg::kGradBufs, OPB = Cfg::kOffsetsPerBundle, OPG = Cfg::kOffsetsPerGroup;
+  constexpr int kTmemCols = Cfg::kTmemCols;
   constexpr int kGradChunks = CO / 8;  // 16-byte chunks of one output_grad row
   extern __shared__ unsigned char smem_raw[];
   unsigned char *a_ring = reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
@@ -144,9 +169,9 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = blockIdx.x / blocks_per_group, member = blockIdx.x % blocks_per_group;
-  // the group's offsets: pairs_per_group (<= PPG) pairs from offset k0 on
-  const int k0 = group * 2 * pairs_per_group;
-  const int k_end = K < k0 + 2 * pairs_per_group ? K : k0 + 2 * pairs_per_group;
+  // the group's offsets: bundles_per_group (<= kBundlesPerGroup) bundles from offset k0 on
+  const int k0 = group * OPB * bundles_per_group;
+  const int k_end = K < k0 + OPB * bundles_per_group ? K : k0 + OPB * bundles_per_group;
   const int64_t n_tiles = (n_out + kTile - 1) / kTile;
 
   if (tid == 0) {
@@ -174,20 +199,23 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
   if (warp < kProducerWarps) {
     // ------------------------------------------------------------ producers
     // Eight warps, so that every scheduler of the SM has two to hide instruction latency
-    // with (four warps, one per scheduler, ran at a fifth of the issue rate and the kernel
-    // was bound by that, not by the copies or the MMAs).  Warp w gathers rows 16w..16w+15 of
-    // both offsets of a pair: lane l holds the table entry of row 16w + (l & 15) for offset
-    // 2q + (l >> 4) and hands it to the lanes that fetch that row by shuffle; consecutive
-    // lanes fetch consecutive 16-byte chunks of a feature row (8 per row), so one warp
-    // instruction touches four rows.
-    const int rr0 = lane >> 3, chunk = lane & 7;
+    // with (four warps, one per scheduler, ran at a fifth of the issue rate).  Warp w
+    // gathers rows 16w..16w+15 of every offset of a bundle.  A lane holds table entries of
+    // row 16w + (l & 15): register j for offset 2j + (l >> 4) of the bundle, and hands them
+    // to the lanes that fetch that row by shuffle; consecutive lanes fetch consecutive
+    // 16-byte chunks of a feature row (CPR per row), so one warp instruction touches
+    // 32 / CPR rows.
+    constexpr int CPR = CI / 8;                 // 16-byte chunks per feature row: 4 or 8
+    constexpr int kRowsPerInstr = 32 / CPR;     // 8 or 4
+    constexpr int kInstrPerOffset = 16 / kRowsPerInstr;  // 2 or 4
+    const int rr0 = lane / CPR, chunk = lane % CPR;
     const int my_row = warp * 16 + (lane & 15), my_half = lane >> 4;
-    unsigned a_off[4];
+    unsigned a_off[kInstrPerOffset];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int row = warp * 16 + rr0 + i * 4;
-      unsigned off = (unsigned)(row * 128 + chunk * 16);
-      off ^= ((off >> 7) & 7u) << 4;
+    for (int i = 0; i < kInstrPerOffset; ++i) {
+      const int row = warp * 16 + rr0 + i * kRowsPerInstr;
+      unsigned off = (unsigned)(row * ATile::kRowBytes + chunk * 16);
+      off ^= ((off >> 7) & ATile::kSwizzleMask) << 4;
       a_off[i] = off;
     }
     const unsigned a_ring_addr = smemAddr(a_ring), g_ring_addr = smemAddr(g_ring);
@@ -220,24 +248,32 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
         for (int i = 0; i < kGradChunks * kTile / kProducerThreads; ++i) {
           const int e = tid + i * kProducerThreads;
           const int row = e / kGradChunks, c = e % kGradChunks;
-          unsigned off = (unsigned)(row * 128 + (c & 7) * 16);
-          off ^= ((off >> 7) & 7u) << 4;
+          constexpr int kAtomChunks = GTile::kRowBytes / 16;
+          unsigned off = (unsigned)(row * GTile::kRowBytes + (c % kAtomChunks) * 16);
+          off ^= ((off >> 7) & GTile::kSwizzleMask) << 4;
           const bool valid = row0 + row < n_out;
-          cpAsync16(g_addr + (unsigned)(c >> 3) * kSubTileBytes + off,
+          cpAsync16(g_addr + (unsigned)(c / kAtomChunks) * GTile::kTileBytes + off,
                     output_grad + (valid ? (size_t)(row0 + row) * CO + c * 8 : 0), valid);
         }
       }
       cpAsyncArriveOn(&g_full[g]);
       // the gathered feature rows of every live pair
       // (a real loop: unrolled over the pairs its body no longer fits the instruction cache)
-      unsigned todo = (live | (live >> 1)) & 0x55555555u;  // bit 2q: pair q has a live offset
+      unsigned todo = 0u;  // bit q: bundle q has a live offset
+#pragma unroll
+      for (int q = 0; q < Cfg::kBundlesPerGroup; ++q)
+        if ((live >> (q * OPB)) & ((1u << OPB) - 1u)) todo |= 1u << q;
 #pragma unroll 1
       while (todo && ok) {
-        const int q = (__ffs(todo) - 1) >> 1;
+        const int q = __ffs(todo) - 1;
         todo &= todo - 1u;
-        // this lane's table entry: row 16w + (l & 15) of offset 2q + (l >> 4); the line is in L1 since the vote
-        const int k = k0 + 2 * q + my_half;
-        const int idx = k < k_end ? __ldg(nbr + (size_t)k * n_pad + row0 + my_row) : -1;
+        // this lane's table entries (row 16w + (l & 15)); the lines are in L1 since the vote
+        int idx[OPB / 2];
+#pragma unroll
+        for (int j = 0; j < OPB / 2; ++j) {
+          const int k = k0 + q * OPB + 2 * j + my_half;
+          idx[j] = k < k_end ? __ldg(nbr + (size_t)k * n_pad + row0 + my_row) : -1;
+        }
         if (items >= (unsigned)S) {
           if (!mbarWaitWarp(&a_empty[s], a_parity ^ 1u, abort_flag, status, kErrProducerStage, wait_limit)) {
             ok = false;
@@ -246,12 +282,12 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
         }
         const unsigned stage_addr = a_ring_addr + (unsigned)s * Cfg::kAStageBytes;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < OPB; ++h) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int src_row = __shfl_sync(0xffffffffu, idx, h * 16 + rr0 + i * 4);
+          for (int i = 0; i < kInstrPerOffset; ++i) {
+            const int src_row = __shfl_sync(0xffffffffu, idx[h >> 1], (h & 1) * 16 + rr0 + i * kRowsPerInstr);
             const bool valid = src_row >= 0;
-            cpAsync16(stage_addr + (unsigned)h * kSubTileBytes + a_off[i], feat_chunk + (valid ? (size_t)src_row * kCi : 0),
+            cpAsync16(stage_addr + (unsigned)h * ATile::kBytes + a_off[i], feat_chunk + (valid ? (size_t)src_row * CI : 0),
                       valid);
           }
         }
@@ -270,10 +306,10 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
     if (have_acc) have_acc = mbarWaitWarp(&accum_bar, 0, abort_flag, status, kErrAccum, wait_limit);
     tcFenceAfter();
     if (ok && !*abort_flag && warp < 4) {
-      float *dst_block = partial + (size_t)blockIdx.x * pairs_per_group * kTile * CO;
+      float *dst_block = partial + (size_t)blockIdx.x * bundles_per_group * kTile * CO;
 #pragma unroll 1
-      for (int q = 0; q < pairs_per_group; ++q) {
-        const bool touched = have_acc && ((ever_live >> (2 * q)) & 3u);
+      for (int q = 0; q < bundles_per_group; ++q) {
+        const bool touched = have_acc && ((ever_live >> (q * OPB)) & ((1u << OPB) - 1u));
         float *dst = dst_block + ((size_t)q * kTile + tid) * CO;
 #pragma unroll
         for (int c0 = 0; c0 < CO; c0 += 16) {
@@ -294,10 +330,10 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
     tcFenceBefore();
   } else {
     // ------------------------------------------------------------ MMA issuer
-    // The whole warp derives the live pairs of a tile; lane 0 issues.
-    const unsigned long long a_desc0 = makeDescMn(smemAddr(a_ring), kSubTileBytes);
-    const unsigned long long g_desc0 = makeDescMn(smemAddr(g_ring), kSubTileBytes);
-    unsigned started = 0u;  // pairs whose accumulator has been written
+    // The whole warp derives the live bundles of a tile; lane 0 issues.
+    const unsigned long long a_desc0 = makeDescMn<ATile>(smemAddr(a_ring), ATile::kBytes);
+    const unsigned long long g_desc0 = makeDescMn<GTile>(smemAddr(g_ring), GTile::kTileBytes);
+    unsigned started = 0u;  // bundles whose accumulator has been written
     int s = 0;
     unsigned a_parity = 0, items = 0;
     bool ok = true;
@@ -311,8 +347,8 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
       if (lane == 0) {
         ok = mbarWait(&g_full[g], (unsigned)(n_mine / NG) & 1u, abort_flag, status, kErrIssuerGrad, wait_limit);
         const unsigned long long g_desc = g_desc0 + (unsigned long long)((g * Cfg::kGradBufBytes) >> 4);
-        for (int q = 0; q < PPG && ok; ++q) {
-          if (!((live >> (2 * q)) & 3u)) continue;
+        for (int q = 0; q < Cfg::kBundlesPerGroup && ok; ++q) {
+          if (!((live >> (q * OPB)) & ((1u << OPB) - 1u))) continue;
           if (!mbarWait(&a_full[s], a_parity, abort_flag, status, kErrIssuerStage, wait_limit)) {
             ok = false;
             break;
@@ -323,9 +359,10 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
           const unsigned d_addr = tmem_base + (unsigned)(q * CO);
 #pragma unroll
           for (int j = 0; j < kTile / 16; ++j) {
-            // 16 rows of the contracted axis per MMA: 2048 bytes further in both operands
-            umma(d_addr, a_desc + (unsigned long long)((j * 2048) >> 4), g_desc + (unsigned long long)((j * 2048) >> 4),
-                 Cfg::kIdesc, (((started >> q) & 1u) || j > 0) ? 1u : 0u);
+            // 16 rows of the contracted axis per MMA: 16 rows further in both operands
+            umma(d_addr, a_desc + (unsigned long long)((j * ATile::kStepBytes) >> 4),
+                 g_desc + (unsigned long long)((j * GTile::kStepBytes) >> 4), Cfg::kIdesc,
+                 (((started >> q) & 1u) || j > 0) ? 1u : 0u);
           }
           started |= 1u << q;
           ummaCommit(&a_empty[s]);
@@ -362,59 +399,72 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
 }
 
 // filters_grad[k][c][n] = sum over the blocks of k's group, in ascending block
-// order, of partial[block][pair of k][lane (k & 1) * 64 + c][n].
+// order, of partial[block][bundle of k][lane (k % offsets per bundle) * Ci + c][n].
 __global__ void __launch_bounds__(256)
-reduceFilterGradTcKernel(const float *__restrict__ partial, int K, int co, int pairs_per_group, int blocks_per_group,
-                         __half *__restrict__ filters_grad) {
-  const int64_t total = (int64_t)K * kCi * co;
+reduceFilterGradTcKernel(const float *__restrict__ partial, int K, int ci, int co, int bundles_per_group,
+                         int blocks_per_group, __half *__restrict__ filters_grad) {
+  const int64_t total = (int64_t)K * ci * co;
+  const int offsets_per_bundle = kTile / ci;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int n = (int)(i % co);
-    const int c = (int)((i / co) % kCi);
-    const int k = (int)(i / ((int64_t)co * kCi));
-    const int pair = k >> 1, group = pair / pairs_per_group, q = pair % pairs_per_group;
-    const size_t block_stride = (size_t)pairs_per_group * kTile * co;
+    const int c = (int)((i / co) % ci);
+    const int k = (int)(i / ((int64_t)co * ci));
+    const int bundle = k / offsets_per_bundle, group = bundle / bundles_per_group, q = bundle % bundles_per_group;
+    const size_t block_stride = (size_t)bundles_per_group * kTile * co;
     const float *src = partial + (size_t)group * blocks_per_group * block_stride +
-                       ((size_t)q * kTile + (size_t)(k & 1) * kCi + c) * co + n;
+                       ((size_t)q * kTile + (size_t)(k % offsets_per_bundle) * ci + c) * co + n;
     float v = 0.0f;
     for (int b = 0; b < blocks_per_group; ++b) v += src[(size_t)b * block_stride];
     filters_grad[i] = __float2half_rn(v);
   }
 }
 
-template <int CO>
+template <int CI, int CO>
 cudaError_t launchGradTc(const FilterGradProblem &p, const FilterGradTcPlan &plan, const __half *features,
                          const __half *output_grad, const int32_t *nbr, float *partial, int32_t *status,
                          double bytes, double flops, cudaStream_t stream) {
-  using Cfg = GradTcConfig<CO>;
-  auto kernel = filterGradTcgen05Kernel<CO>;
+  using Cfg = GradTcConfig<CI, CO>;
+  auto kernel = filterGradTcgen05Kernel<CI, CO>;
   cudaError_t err =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes);
   if (err != cudaSuccess) return err;
-  static const std::string name = "filterGradTcgen05Kernel<64," + std::to_string(CO) + ">";
+  static const std::string name = "filterGradTcgen05Kernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
   trace::Scope t(name.c_str(), stream, bytes, flops);
   kernel<<<(unsigned)(plan.groups * plan.blocks_per_group), kThreads, Cfg::kSmemBytes, stream>>>(
-      features, output_grad, nbr, p.n_out, plan.n_pad, p.K, plan.pairs_per_group, plan.blocks_per_group, partial, status, p.sticky_status,
-      kWaitCycles);
+      features, output_grad, nbr, p.n_out, plan.n_pad, p.K, plan.bundles_per_group, plan.blocks_per_group, partial,
+      status, p.sticky_status, kWaitCycles);
   return cudaGetLastError();
+}
+
+// bundles a group may hold for this shape (tensor-memory columns, table entries in registers)
+int maxBundlesPerGroup(int ci, int co) {
+  const int by_tmem = 512 / co, by_regs = kMaxGroupOffsets / (kTile / ci);
+  return by_tmem < by_regs ? by_tmem : by_regs;
 }
 
 }  // namespace
 
 bool filterGradTcShapeEligible(const FilterGradProblem &p) {
   const char *forced = std::getenv("MLUOP_B200_FILTER_GRAD_KERNEL");  // read per call: tests switch it
-  if (forced && std::string(forced) == "mma") return false;
-  return p.is_half && p.ci == kCi && (p.co == 64 || p.co == 128) && p.K >= 1 && p.K <= 128 && p.n_out >= 1 &&
-         neighbourTableCountsFit(p.K);
+  const std::string choice = forced ? forced : "";
+  if (choice == "mma") return false;
+  // 32 input channels run correctly but slower than the pair-list kernel (0.79 vs 0.56 ms for the two
+  // 32->32 layers of the c2 backbone: an item costs the same hand-offs for half the arithmetic), so they
+  // take this kernel only on request.
+  const bool wide = p.ci == 64 && (p.co == 64 || p.co == 128);
+  const bool narrow = p.ci == 32 && (p.co == 32 || p.co == 64) && choice == "tcgen05";
+  return p.is_half && (wide || narrow) && p.K >= 1 && p.K <= 128 && p.n_out >= 1 && neighbourTableCountsFit(p.K);
 }
 
 FilterGradTcPlan planFilterGradTc(const FilterGradProblem &p, int sm_count) {
   FilterGradTcPlan plan{};
   const int sms = sm_count > 0 ? sm_count : 148;
-  // as few groups as tensor memory allows, the pairs spread evenly over them
-  const int max_pairs_per_group = kTmemCols / p.co;
-  const int pairs = (p.K + 1) / 2;
-  plan.groups = (pairs + max_pairs_per_group - 1) / max_pairs_per_group;
-  plan.pairs_per_group = (pairs + plan.groups - 1) / plan.groups;
+  // as few groups as the kernel allows, the bundles spread evenly over them
+  const int offsets_per_bundle = kTile / p.ci;
+  const int bundles = (p.K + offsets_per_bundle - 1) / offsets_per_bundle;
+  const int max_per_group = maxBundlesPerGroup(p.ci, p.co);
+  plan.groups = (bundles + max_per_group - 1) / max_per_group;
+  plan.bundles_per_group = (bundles + plan.groups - 1) / plan.groups;
   const int64_t tiles = (p.n_out + kTile - 1) / kTile;
   int64_t per_group = sms / plan.groups;
   if (per_group < 1) per_group = 1;
@@ -423,7 +473,7 @@ FilterGradTcPlan planFilterGradTc(const FilterGradProblem &p, int sm_count) {
   plan.n_pad = (p.n_out + kConvPadRows - 1) / kConvPadRows * kConvPadRows;
   plan.table_bytes = (size_t)p.K * plan.n_pad * sizeof(int32_t);
   plan.partial_bytes =
-      (size_t)plan.groups * plan.blocks_per_group * plan.pairs_per_group * kTile * p.co * sizeof(float);
+      (size_t)plan.groups * plan.blocks_per_group * plan.bundles_per_group * kTile * p.co * sizeof(float);
   return plan;
 }
 
@@ -449,17 +499,21 @@ cudaError_t launchFilterGradTcgen05(const FilterGradProblem &p, const FilterGrad
   // 2. partial sums of every block
   const __half *f = static_cast<const __half *>(features);
   const __half *g = static_cast<const __half *>(output_grad);
-  if (p.co == 64) {
-    err = launchGradTc<64>(p, plan, f, g, table, partial, status, bytes, flops, stream);
+  if (p.ci == 64 && p.co == 64) {
+    err = launchGradTc<64, 64>(p, plan, f, g, table, partial, status, bytes, flops, stream);
+  } else if (p.ci == 64) {
+    err = launchGradTc<64, 128>(p, plan, f, g, table, partial, status, bytes, flops, stream);
+  } else if (p.co == 32) {
+    err = launchGradTc<32, 32>(p, plan, f, g, table, partial, status, bytes, flops, stream);
   } else {
-    err = launchGradTc<128>(p, plan, f, g, table, partial, status, bytes, flops, stream);
+    err = launchGradTc<32, 64>(p, plan, f, g, table, partial, status, bytes, flops, stream);
   }
   if (err != cudaSuccess) return err;
   // 3. blocks of a group added in a fixed order
   const int64_t total = (int64_t)p.K * p.ci * p.co;
   const unsigned blocks = (unsigned)((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048);
   trace::Scope t("reduceFilterGradTcKernel", stream, (double)plan.partial_bytes + 2.0 * (double)total);
-  reduceFilterGradTcKernel<<<blocks, 256, 0, stream>>>(partial, p.K, p.co, plan.pairs_per_group,
+  reduceFilterGradTcKernel<<<blocks, 256, 0, stream>>>(partial, p.K, p.ci, p.co, plan.bundles_per_group,
                                                        plan.blocks_per_group, static_cast<__half *>(filters_grad));
   return cudaGetLastError();
 }

@@ -1,5 +1,5 @@
 // Filter gradient of the sparse convolution on the tcgen05 tensor cores: plan
-// and launch (half, 64 input channels, 64 or 128 output channels).
+// and launch (half; 64 input channels with 64 or 128 output channels, 32 with 32 or 64).
 #ifndef MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_BACKWARD_FILTER_TCGEN05_H_
 #define MLUOP_B200_KERNELS_SPARSE_CONV_INDICE_CONVOLUTION_BACKWARD_FILTER_TCGEN05_H_
 
@@ -15,15 +15,17 @@ namespace sparse_conv {
 
 struct FilterGradTcPlan {
   int32_t groups;            // groups of kernel offsets; a block serves one group
-  int32_t pairs_per_group;   // pairs of offsets whose sums fit tensor memory (512 / Co)
+  int32_t bundles_per_group;  // bundles of 128 / Ci offsets (one accumulator each) a block keeps in tensor memory
   int32_t blocks_per_group;  // blocks that share a group's tiles of 128 output rows
   int64_t n_pad;             // rows of the neighbour table (n_out padded)
   size_t table_bytes;        // int32[K][n_pad]
-  size_t partial_bytes;      // float[groups * blocks_per_group][pairs_per_group][128][Co]
+  size_t partial_bytes;      // float[groups * blocks_per_group][bundles_per_group][128][Co]
 };
 
 // Decided from the shape alone, so that the workspace query and the call agree;
-// MLUOP_B200_FILTER_GRAD_KERNEL=mma turns the tensor-memory kernel off.
+// MLUOP_B200_FILTER_GRAD_KERNEL=mma turns the tensor-memory kernel off, =tcgen05 also
+// sends 32 input channels to it (slower there than the pair-list kernel; kept selectable
+// and tested).
 bool filterGradTcShapeEligible(const FilterGradProblem &p);
 
 FilterGradTcPlan planFilterGradTc(const FilterGradProblem &p, int sm_count);

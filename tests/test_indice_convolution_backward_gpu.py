@@ -185,21 +185,23 @@ def test_kernel_volumes_outside_the_tensor_core_range(ops, oracle, gpu_handle, k
     assert_close(oracle, got.reshape(ref.shape), ref, is_half)
 
 
-@pytest.mark.parametrize("co", [64, 128])
+@pytest.mark.parametrize("ci,co", [(64, 64), (64, 128), (32, 32), (32, 64)])
 @pytest.mark.parametrize("ks,n,space", [([3, 3, 3], 30000, [20, 40, 40]), ([1, 1, 1], 5000, [10, 30, 30]),
                                         ([5, 5, 5], 3000, [8, 16, 16]), ([3, 1, 2], 1000, [9, 10, 10])])
-def test_filter_gradient_in_tensor_memory(ops, oracle, gpu_handle, trace_kernels, monkeypatch, co, ks, n, space):
-    """Half with 64 input channels runs filterGradTcgen05Kernel (sums of all offsets of a
+def test_filter_gradient_in_tensor_memory(ops, oracle, gpu_handle, trace_kernels, monkeypatch, ci, co, ks, n, space):
+    """Half with 32 or 64 input channels runs filterGradTcgen05Kernel (sums of all offsets of a
     group kept in tensor memory, tiles of output rows streamed past them): several tiles
-    per block, a ragged last tile, odd kernel volumes (a pair with one offset) and more
+    per block, a ragged last tile, kernel volumes that leave a bundle of offsets part empty and more
     groups than one.  Checked against the oracle, against the pair-list kernel
     (MLUOP_B200_FILTER_GRAD_KERNEL=mma) and for bit-identical repeats."""
-    rng = np.random.default_rng(co + sum(ks) + n)
+    rng = np.random.default_rng(ci * 7 + co + sum(ks) + n)
     pad = [(k - 1) // 2 for k in ks]
     for sub_m, stride in ((1, [1] * 3), (0, [2] * 3)):
-        pairs, num, n_out, feat, og, w = make_case(oracle, rng, 2, space, n, ks, stride, pad, sub_m, 64, co, np.float16)
+        pairs, num, n_out, feat, og, w = make_case(oracle, rng, 2, space, n, ks, stride, pad, sub_m, ci, co, np.float16)
         ref = oracle.round_through_half(oracle.indice_convolution_backward_filter(
             feat.astype(np.float32), og.astype(np.float32), ks, pairs, num))
+        if ci == 32:  # 32 input channels take this kernel on request only
+            monkeypatch.setenv("MLUOP_B200_FILTER_GRAD_KERNEL", "tcgen05")
         with trace_kernels() as names:
             got = gpu_backward_filter(ops, gpu_handle, feat, og, ks, pairs, num, sub_m)
         assert any(nm.startswith("filterGradTcgen05Kernel") for nm in names), names

@@ -267,7 +267,9 @@ def run_b200(args):
     # Final features and out_indices of every rank -> rank 0 over NCCL (exact sizes): the row
     # counts and the coordinate rows leave on a second stream as soon as the last rulebook
     # exists, the feature rows after the last convolution.
-    gather = sharding.RowGather(first_sample, rank, world, device=dev)
+    # the ranks' row counts travel host to host (a gloo group beside the NCCL one)
+    host_group = dist.new_group(backend="gloo") if world > 1 else None
+    gather = sharding.RowGather(first_sample, rank, world, device=dev, host_group=host_group)
 
     # The gather of step i is enqueued during step i+1, at the point of the layer loop where
     # the host would otherwise wait with the most convolution work queued on the GPU: its
@@ -379,7 +381,7 @@ def run_b200(args):
         stream.wait_stream(s_out)
         stream.wait_stream(s_in)  # a prefetch for a step that never came must not outlive the region
 
-    def step_e2e():
+    def step_e2e(host=None):
         """Host buffers in, host buffers out: pinned-host -> device copies of this rank's
         indices and features, the layer stack, the NCCL gather, and the device -> host read
         of this rank's final features and out_indices (every rank reads its own rows back
@@ -388,8 +390,25 @@ def run_b200(args):
         e2e_state["i"] += 1
         if in_ready[slot] is None:
             prefetch(slot)      # very first step: nothing was prefetched yet
-        prefetch(1 - slot)      # inputs of the next step
-        read_back()             # results of the previous step
+        copies = {"done": False}
+
+        def enqueue_copies(li=None):
+            """Inputs of the next step in, results of the previous step out: enqueued where the host
+            would otherwise sit waiting for a rulebook with the most convolution work queued (a third
+            of a millisecond of copy launches that, done before the step, left the GPU idle)."""
+            t_a = time.perf_counter()
+            if not copies["done"] and (li is None or li == flush_at):
+                copies["done"] = True
+                prefetch(1 - slot)
+                read_back()
+            t_b = time.perf_counter()
+            if world > 1 and not args.no_gather and not pipelined:
+                flush_pending(li)
+            if host is not None:
+                host["prefetch_and_readback_enqueue_s"] += t_b - t_a
+                host["gather_enqueue_s"] += time.perf_counter() - t_b
+        if pipelined:
+            enqueue_copies()
         idx_in, feat_in = d_in[slot]
         if pipelined:
             plan = next_plan.pop(("e2e", slot), None) or net.plan_rulebooks(idx_in, ready=in_ready[slot])
@@ -403,15 +422,15 @@ def run_b200(args):
         else:
             stream.wait_event(in_ready[slot])
             in_ready[slot] = None
-            if args.no_gather or world == 1:
-                out, out_idx, records = net.forward(idx_in, feat_in)
-            else:
-                # like the resident steps: the rows of the step before leave for rank 0 at the point of
-                # this step where the host would otherwise sit waiting for a rulebook, so neither the
-                # collectives' host cost nor their NVLink traffic holds up a step; the last step's
-                # gather is waited for before the region's closing event (drain)
-                out, out_idx, records = net.forward(idx_in, feat_in, on_host_idle=flush_pending)
-                flush_pending()
+            # like the resident steps: the rows of the step before leave for rank 0 at the point of
+            # this step where the host would otherwise sit waiting for a rulebook, so neither the
+            # collectives' host cost nor their NVLink traffic holds up a step; the last step's
+            # gather is waited for before the region's closing event (drain)
+            t_f = time.perf_counter()
+            out, out_idx, records = net.forward(idx_in, feat_in, on_host_idle=enqueue_copies)
+            enqueue_copies()  # only when the layer list has no such point
+            if host is not None:
+                host["forward_s"] += time.perf_counter() - t_f  # includes the two enqueue phases
         done = torch.cuda.Event()
         done.record(stream)
         buf_free[slot] = done
@@ -471,35 +490,11 @@ def run_b200(args):
         # (perf_counter around the calls) and device time of the copies (events on their streams).
         copy_events = []
         net.timers = {}
-        host = {"prefetch_and_readback_enqueue_s": 0.0, "forward_s": 0.0, "gather_finish_s": 0.0, "step_s": 0.0}
+        host = {"prefetch_and_readback_enqueue_s": 0.0, "gather_enqueue_s": 0.0, "forward_s": 0.0, "step_s": 0.0}
 
         def step_instrumented():
-            slot = e2e_state["i"] % 2
-            e2e_state["i"] += 1
             t0 = time.perf_counter()
-            if in_ready[slot] is None:
-                prefetch(slot)
-            prefetch(1 - slot)
-            read_back()
-            stream.wait_event(in_ready[slot])
-            in_ready[slot] = None
-            idx_in, feat_in = d_in[slot]
-            t1 = time.perf_counter()
-            if args.no_gather:
-                out, out_idx, _ = net.forward(idx_in, feat_in)
-                t2 = t3 = time.perf_counter()
-            else:
-                out, out_idx, _ = net.forward(idx_in, feat_in, on_final_indices=gather.begin)
-                t2 = time.perf_counter()
-                gather.finish(out, wait=True)
-                t3 = time.perf_counter()
-            done = torch.cuda.Event()
-            done.record(stream)
-            buf_free[slot] = done
-            out_pending.append((out, out_idx, done, slot))
-            host["prefetch_and_readback_enqueue_s"] += t1 - t0
-            host["forward_s"] += t2 - t1
-            host["gather_finish_s"] += t3 - t2
+            step_e2e(host)
             host["step_s"] += time.perf_counter() - t0
 
         region_ms = timed(step_instrumented, args.steps)
@@ -542,7 +537,7 @@ def run_b200(args):
         env = dict(torch=torch, dist=dist, ops=ops, workloads=workloads, backbone=backbone, sharding=sharding,
                    dev=dev, rank=rank, world=world, flush=flush, stream=stream, handle=handle, rb_handle=rb_handle,
                    rb_stream=rb_stream, flush_at=flush_at, pipelined=pipelined, hbm_gbs=hbm_gbs, tensor_tflops=tensor_tflops,
-                   fp32_tflops=fp32_tflops)
+                   fp32_tflops=fp32_tflops, host_group=host_group)
         extra["c4"] = time_config("c4", max(5, args.steps // 2), env)
         if world == 1:
             extra["per_config"] = {name: time_config(name, max(5, args.steps // 2), env) for name in ("c0", "c1", "c3")}
@@ -727,7 +722,7 @@ def time_config(name, steps, env):
     net = backbone.SparseNetwork(env["handle"], layers, weights, list(cfg["grid"]), batch,
                                  rulebook_handle=env["rb_handle"], rulebook_stream=env["rb_stream"])
     d_idx, d_feat = torch.from_numpy(idx_np).to(dev), torch.from_numpy(feat_np).to(dev)
-    gather = sharding.RowGather(rank * batch, rank, world, device=dev) if sharded and world > 1 else None
+    gather = sharding.RowGather(rank * batch, rank, world, device=dev, host_group=env.get("host_group")) if sharded and world > 1 else None
     pending = []
 
     def flush_pending(li=None):

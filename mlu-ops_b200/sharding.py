@@ -50,8 +50,13 @@ class RowGather:
     it (call it before reading the gathered rows, and once at the end).
     """
 
-    def __init__(self, first_sample, rank, world, dst=0, device=None):
+    def __init__(self, first_sample, rank, world, dst=0, device=None, host_group=None):
+        """host_group: a process group on CPU tensors (gloo).  With it the ranks' row counts -
+        numbers every rank already has on the host - are exchanged over that group; without it
+        they travel through the device and the host has to wait for the stream to read them,
+        which costs a rank whatever lead its host had over its GPU."""
         self.first_sample, self.rank, self.world, self.dst = int(first_sample), rank, world, dst
+        self.host_group = host_group
         self.cuda = device is not None and torch.device(device).type == "cuda"
         self.comm = torch.cuda.Stream(device) if self.cuda and world > 1 else None
         self.counts = None
@@ -77,10 +82,16 @@ class RowGather:
             if self.world == 1:
                 return
             n = out_indices.shape[0]
-            rows = torch.tensor([n], dtype=torch.int64, device=out_indices.device)
-            all_rows = torch.empty((self.world,), dtype=torch.int64, device=out_indices.device)
-            dist.all_gather_into_tensor(all_rows, rows)
-            self.counts = all_rows.tolist()  # one host read for all ranks' row counts
+            if self.host_group is not None:
+                mine = torch.tensor([n], dtype=torch.int64)
+                every = [torch.empty((1,), dtype=torch.int64) for _ in range(self.world)]
+                dist.all_gather(every, mine, group=self.host_group)  # host to host: no stream is waited for
+                self.counts = [int(t.item()) for t in every]
+            else:
+                rows = torch.tensor([n], dtype=torch.int64, device=out_indices.device)
+                all_rows = torch.empty((self.world,), dtype=torch.int64, device=out_indices.device)
+                dist.all_gather_into_tensor(all_rows, rows)
+                self.counts = all_rows.tolist()  # one host read for all ranks' row counts
             total = sum(self.counts) if self.rank == self.dst else 0
             self.idxs = torch.empty((total, 4), dtype=out_indices.dtype, device=out_indices.device)
             dist.all_to_all_single(self.idxs, shifted, self._recv_rows(), self._send_rows(n))

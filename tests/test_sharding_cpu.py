@@ -31,13 +31,15 @@ def _rank_main(rank, world, port, queue):
     out, out_idx, _ = backbone_cpu.run_layers(l_idx.numpy(), l_feat.numpy(), layers, weights, grid, l_batch)
     feats, idxs = sharding.gather_rows(torch.from_numpy(out), torch.from_numpy(out_idx), b0, rank, world)
     # the two-phase form the benchmark uses: coordinates first, features later, twice in a row on one object
-    two_phase = sharding.RowGather(b0, rank, world)
     same_again = True
-    for _ in range(2):
-        two_phase.begin(torch.from_numpy(out_idx))
-        f2, i2 = two_phase.finish(torch.from_numpy(out), wait=False)
-        two_phase.wait()
-        same_again = same_again and torch.equal(f2, feats) and torch.equal(i2, idxs)
+    # the ranks' row counts through the tensors' own group, then through a separate host group
+    for host_group in (None, dist.new_group(backend="gloo")):
+        two_phase = sharding.RowGather(b0, rank, world, host_group=host_group)
+        for _ in range(2):
+            two_phase.begin(torch.from_numpy(out_idx))
+            f2, i2 = two_phase.finish(torch.from_numpy(out), wait=False)
+            two_phase.wait()
+            same_again = same_again and torch.equal(f2, feats) and torch.equal(i2, idxs)
     if rank == 0:
         ref_out, ref_idx, _ = backbone_cpu.run_layers(idx, feat, layers, weights, grid, batch)
         queue.put((bool(np.array_equal(feats.numpy(), ref_out)) and same_again,

@@ -187,7 +187,8 @@ def test_kernel_volumes_outside_the_tensor_core_range(ops, oracle, gpu_handle, k
 
 @pytest.mark.parametrize("ci,co", [(64, 64), (64, 128), (32, 32), (32, 64)])
 @pytest.mark.parametrize("ks,n,space", [([3, 3, 3], 30000, [20, 40, 40]), ([1, 1, 1], 5000, [10, 30, 30]),
-                                        ([5, 5, 5], 3000, [8, 16, 16]), ([3, 1, 2], 1000, [9, 10, 10])])
+                                        ([5, 5, 5], 3000, [8, 16, 16]), ([3, 1, 2], 1000, [9, 10, 10]),
+                                        ([4, 4, 8], 600, [8, 8, 16])])  # 128 offsets: the largest volume it takes
 def test_filter_gradient_in_tensor_memory(ops, oracle, gpu_handle, trace_kernels, monkeypatch, ci, co, ks, n, space):
     """Half with 32 or 64 input channels runs filterGradTcgen05Kernel (sums of all offsets of a
     group kept in tensor memory, tiles of output rows streamed past them): several tiles

@@ -215,3 +215,35 @@ def test_filter_gradient_in_tensor_memory(ops, oracle, gpu_handle, trace_kernels
         monkeypatch.delenv("MLUOP_B200_FILTER_GRAD_KERNEL")
         assert not any(nm.startswith("filterGradTcgen05Kernel") for nm in names), names
         assert_close(oracle, got, other, True)
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_rows_that_start_one_element_off_an_aligned_address(ops, oracle, gpu_handle, dtype):
+    """The tensor-core kernels move rows as 16-byte vectors and are chosen only for 16-byte
+    aligned row arrays; a view that starts one element into a buffer (a caller's slice)
+    must take the scalar kernels and give the same results, not fault."""
+    rng = np.random.default_rng(31)
+    is_half = dtype == np.float16
+    ks = [3] * 3
+    pairs, num, n_out, feat, og, w = make_case(oracle, rng, 2, [8, 12, 12], 900, ks, [1] * 3, [1] * 3, 1, 64, 64, dtype)
+    f32 = lambda a: a.astype(np.float32)  # noqa: E731
+    r = (lambda a: oracle.round_through_half(a)) if is_half else (lambda a: a)
+
+    def off_by_one(a):
+        buf = torch.empty((a.size + 1,), dtype=torch.from_numpy(a).dtype, device="cuda")
+        view = buf[1:].view(a.shape)
+        view.copy_(torch.from_numpy(a))
+        assert view.data_ptr() % 16 != 0
+        return view
+
+    d_pairs, nums = torch.from_numpy(pairs).cuda(), [int(v) for v in num]
+    d_w = torch.from_numpy(w).cuda()
+    got = ops.indice_convolution_forward(gpu_handle, off_by_one(feat), d_w, "ARRAY", ks, d_pairs, nums, n_out, 1)
+    ref = r(oracle.indice_convolution_forward(f32(feat), f32(w), "ARRAY", ks, pairs, num, n_out, 64))
+    assert_close(oracle, got.float().cpu().numpy(), ref, is_half)
+    got = ops.indice_convolution_backward_data(gpu_handle, off_by_one(og), d_w, "ARRAY", d_pairs, nums, 1)
+    ref = r(oracle.indice_convolution_backward_data(f32(og), f32(w), "ARRAY", ks, pairs, num, 64, is_half))
+    assert_close(oracle, got.float().cpu().numpy(), ref, is_half)
+    got = ops.indice_convolution_backward_filter(gpu_handle, off_by_one(feat), off_by_one(og), ks, d_pairs, nums, 1)
+    ref = r(oracle.indice_convolution_backward_filter(f32(feat), f32(og), ks, pairs, num))
+    assert_close(oracle, got.float().cpu().numpy().reshape(ref.shape), ref, is_half)

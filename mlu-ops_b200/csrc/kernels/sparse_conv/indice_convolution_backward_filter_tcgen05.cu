@@ -64,8 +64,13 @@ using namespace tc;
 constexpr int kTile = kConvTileRows;  // 128 output rows per tile
 constexpr int kProducerWarps = 8;      // warps 0-7: gather; warps 0-3 also read the sums back
 constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kIssuerWarp = kProducerWarps;  // tensor-memory allocation and MMA issue
-constexpr int kThreads = kProducerThreads + 32;
+constexpr int kIssuerWarp = kProducerWarps;  // first MMA-issuing warp; it also owns the tensor-memory allocation
+// Two issuing threads (one per warp): a single thread's wait / issue / release loop handles an item
+// in no less than about 300 clocks plus the time its MMAs are accepted in, and was the slowest
+// part of the chain.  Accumulator q belongs to issuer q % kIssuers, so every sum still sees its
+// tiles in one fixed order.
+constexpr int kIssuers = 2;
+constexpr int kThreads = kProducerThreads + 32 * kIssuers;
 constexpr int kMaxGroupOffsets = 16;  // offsets whose table entries a thread keeps in registers
 constexpr long long kWaitCycles = 2000000000ll;  // a wait gives up after about one second
 constexpr int kErrProducerStage = 1, kErrIssuerStage = 2, kErrAccum = 4, kErrGradTile = 8, kErrIssuerGrad = 16;
@@ -163,7 +168,7 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
   extern __shared__ unsigned char smem_raw[];
   unsigned char *a_ring = reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
   unsigned char *g_ring = a_ring + (size_t)S * Cfg::kAStageBytes;
-  __shared__ unsigned long long a_full[S], a_empty[S], g_full[NG], g_empty[NG], accum_bar, drain_bar;
+  __shared__ unsigned long long a_full[S], a_empty[S], g_full[NG], g_empty[NG], accum_bar, drain_bar[kIssuers];
   __shared__ unsigned tmem_base_s;
   __shared__ int abort_s;
 
@@ -181,10 +186,10 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
     }
     for (int g = 0; g < NG; ++g) {
       mbarInit(&g_full[g], kProducerThreads);
-      mbarInit(&g_empty[g], 1);
+      mbarInit(&g_empty[g], kIssuers);
     }
-    mbarInit(&accum_bar, 1);
-    mbarInit(&drain_bar, 1);
+    mbarInit(&accum_bar, kIssuers);
+    for (int i = 0; i < kIssuers; ++i) mbarInit(&drain_bar[i], 1);
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -329,13 +334,14 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
     }
     tcFenceBefore();
   } else {
-    // ------------------------------------------------------------ MMA issuer
-    // The whole warp derives the live bundles of a tile; lane 0 issues.
+    // ------------------------------------------------------------ MMA issuers
+    // The whole warp derives the live bundles of a tile; lane 0 issues those of its accumulators.
+    const int me = warp - kIssuerWarp;
     const unsigned long long a_desc0 = makeDescMn<ATile>(smemAddr(a_ring), ATile::kBytes);
     const unsigned long long g_desc0 = makeDescMn<GTile>(smemAddr(g_ring), GTile::kTileBytes);
     unsigned started = 0u;  // bundles whose accumulator has been written
     int s = 0;
-    unsigned a_parity = 0, items = 0;
+    unsigned a_parity = 0, items = 0, my_items = 0;  // items: all of the block's, my_items: this issuer's
     bool ok = true;
     int64_t n_mine = 0;
     int4 vote_next[OPG];
@@ -349,30 +355,33 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
         const unsigned long long g_desc = g_desc0 + (unsigned long long)((g * Cfg::kGradBufBytes) >> 4);
         for (int q = 0; q < Cfg::kBundlesPerGroup && ok; ++q) {
           if (!((live >> (q * OPB)) & ((1u << OPB) - 1u))) continue;
-          if (!mbarWait(&a_full[s], a_parity, abort_flag, status, kErrIssuerStage, wait_limit)) {
-            ok = false;
-            break;
-          }
-          fenceProxyAsync();
-          tcFenceAfter();
-          const unsigned long long a_desc = a_desc0 + (unsigned long long)((s * Cfg::kAStageBytes) >> 4);
-          const unsigned d_addr = tmem_base + (unsigned)(q * CO);
+          if (q % kIssuers == me) {
+            if (!mbarWait(&a_full[s], a_parity, abort_flag, status, kErrIssuerStage, wait_limit)) {
+              ok = false;
+              break;
+            }
+            fenceProxyAsync();
+            tcFenceAfter();
+            const unsigned long long a_desc = a_desc0 + (unsigned long long)((s * Cfg::kAStageBytes) >> 4);
+            const unsigned d_addr = tmem_base + (unsigned)(q * CO);
 #pragma unroll
-          for (int j = 0; j < kTile / 16; ++j) {
-            // 16 rows of the contracted axis per MMA: 16 rows further in both operands
-            umma(d_addr, a_desc + (unsigned long long)((j * ATile::kStepBytes) >> 4),
-                 g_desc + (unsigned long long)((j * GTile::kStepBytes) >> 4), Cfg::kIdesc,
-                 (((started >> q) & 1u) || j > 0) ? 1u : 0u);
+            for (int j = 0; j < kTile / 16; ++j) {
+              // 16 rows of the contracted axis per MMA: 16 rows further in both operands
+              umma(d_addr, a_desc + (unsigned long long)((j * ATile::kStepBytes) >> 4),
+                   g_desc + (unsigned long long)((j * GTile::kStepBytes) >> 4), Cfg::kIdesc,
+                   (((started >> q) & 1u) || j > 0) ? 1u : 0u);
+            }
+            started |= 1u << q;
+            ummaCommit(&a_empty[s]);
+            ++my_items;
           }
-          started |= 1u << q;
-          ummaCommit(&a_empty[s]);
           ++items;
           if (++s == S) {
             s = 0;
             a_parity ^= 1u;
           }
         }
-        // the tile's output_grad rows are free once the MMAs issued so far are done
+        // the tile's output_grad rows are free once both issuers' MMAs issued so far are done
         if (ok) ummaCommit(&g_empty[g]);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -380,11 +389,11 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
     if (lane == 0) {
       if (ok && items > 0 && !*abort_flag) {
         ummaCommit(&accum_bar);
-      } else if (items > 0) {
+      } else if (my_items > 0) {
         // leaving early: see the outstanding MMAs out before tensor memory is freed
-        ummaCommit(&drain_bar);
+        ummaCommit(&drain_bar[me]);
         const long long t0 = clock64();
-        while (!mbarTryWait(&drain_bar, 0) && clock64() - t0 <= wait_limit) {
+        while (!mbarTryWait(&drain_bar[me], 0) && clock64() - t0 <= wait_limit) {
         }
       }
     }

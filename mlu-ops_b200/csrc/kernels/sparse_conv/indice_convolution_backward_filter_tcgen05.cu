@@ -23,9 +23,10 @@
 // live row in the tile, gather the feature rows of its offsets into a stage
 // of the ring (rows without a neighbour are zero-filled, nothing is fetched).
 // Both operands lie row-major in shared memory - the contracted axis (rows) is
-// the slow one - which tcgen05.mma reads as "MN-major" operands: one elected
-// thread issues 8 MMAs (M=128, N=Co, K=16 rows each) per bundle and tile and
-// releases the stage with tcgen05.commit.  Producers, issuer and epilogue each
+// the slow one - which tcgen05.mma reads as "MN-major" operands: an issuing
+// thread (there are two, each owning every other accumulator) issues 8 MMAs
+// (M=128, N=Co, K=16 rows each) per bundle and tile and releases the stage with
+// tcgen05.commit.  Producers, issuer and epilogue each
 // derive which bundles are live from the table itself (a warp reads the tile's
 // 128 entries of an offset with one 16-byte load per lane and votes), so no
 // flags travel between them.

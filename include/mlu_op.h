@@ -378,6 +378,53 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionForwardFromTable(
     const size_t workspace_size, const mluOpTensorDescriptor_t features_out_desc,
     void *features_out);
 
+/* The same for the gradients (no counterpart in the reference either).
+ *
+ * Input gradient: mluOpIndiceConvolutionBackwardData works from the table of the
+ * opposite direction (int32 [K][L padded to 512]: the OUTPUT row an input row
+ * feeds at a kernel offset, -1 if none) and builds it from indice_pairs on every
+ * call.  mluOpGetIndiceInputNeighbourTableSize / mluOpBuildIndiceInputNeighbourTable
+ * build it once per rulebook; mluOpIndiceConvolutionBackwardDataFromTable is
+ * mluOpIndiceConvolutionBackwardData with (table, table_size) in place of the
+ * indice_pairs pointer, its workspace the size
+ * mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize reports.  Bit-identical
+ * to the reference-shaped call.
+ *
+ * Filter gradient: the tensor-memory kernel (half, 64 input channels, 64 or 128 output
+ * channels, 16-byte aligned rows) works from the FORWARD table (the one
+ * mluOpBuildIndiceNeighbourTable builds or mluOpGetIndicePairsWithNeighbourTable emits).
+ * mluOpIndiceConvolutionBackwardFilterFromTable is mluOpIndiceConvolutionBackwardFilter
+ * with (table, table_size) in place of the indice_pairs pointer and the workspace
+ * mluOpGetIndiceConvolutionBackwardFilterWorkspaceSize reports; other shapes return
+ * MLUOP_STATUS_NOT_SUPPORTED before anything is enqueued (the caller uses the
+ * reference-shaped call).  Bit-identical to the reference-shaped call. */
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceInputNeighbourTableSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t indice_pairs_desc, size_t *table_size);
+
+mluOpStatus_t MLUOP_WIN_API mluOpBuildIndiceInputNeighbourTable(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t indice_pairs_desc, const void *indice_pairs,
+    const int64_t indice_num[], const int64_t num_act_out, void *table, const size_t table_size);
+
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t output_grad_desc,
+    const mluOpTensorDescriptor_t filters_desc, const mluOpTensorDescriptor_t indice_pairs_desc,
+    const mluOpTensorDescriptor_t input_grad_desc, const int64_t indice_num[], const int64_t inverse,
+    size_t *workspace_size);
+
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardDataFromTable(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t output_grad_desc, const void *output_grad,
+    const mluOpTensorDescriptor_t filters_desc, const void *filters,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *table, const size_t table_size,
+    const int64_t indice_num[], const int64_t inverse, const int64_t sub_m, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t input_grad_desc, void *input_grad);
+
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilterFromTable(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc, const void *features,
+    const mluOpTensorDescriptor_t output_grad_desc, const void *output_grad,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *table, const size_t table_size,
+    const int64_t indice_num[], const int64_t inverse, const int64_t sub_m, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t filters_grad_desc, void *filters_grad);
+
 /* ------------------------------------------------ the step before the path */
 
 /* reference mlu_op.h:5942, kernels/voxelization/voxelization.cpp:178.  Bytes of

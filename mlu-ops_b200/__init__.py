@@ -87,6 +87,14 @@ SIGNATURES = {
                                                                      _i64, ctypes.POINTER(_szt)]),
     "mluOpIndiceConvolutionForwardFromTable": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _szt, _i64p, _i64, _i64,
                                                      _i64, _vp, _szt, _vp, _vp]),
+    "mluOpGetIndiceInputNeighbourTableSize": (_int, [_vp, _vp, ctypes.POINTER(_szt)]),
+    "mluOpBuildIndiceInputNeighbourTable": (_int, [_vp, _vp, _vp, _i64p, _i64, _vp, _szt]),
+    "mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, _vp, _i64p, _i64,
+                                                                          ctypes.POINTER(_szt)]),
+    "mluOpIndiceConvolutionBackwardDataFromTable": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _szt, _i64p, _i64,
+                                                          _i64, _vp, _szt, _vp, _vp]),
+    "mluOpIndiceConvolutionBackwardFilterFromTable": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _szt, _i64p, _i64,
+                                                            _i64, _vp, _szt, _vp, _vp]),
     "mluOpGetVoxelizationWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32,
                                                 ctypes.c_int32, ctypes.c_bool, _vp, _vp, _vp, _vp,
                                                 ctypes.POINTER(_szt)]),
@@ -395,6 +403,26 @@ def build_neighbour_table(handle, indice_pairs, indice_num, num_act_out):
     return table
 
 
+def build_input_neighbour_table(handle, indice_pairs, indice_num, num_act_out):
+    """The table the input gradient works from (mluOpBuildIndiceInputNeighbourTable): for every
+    kernel offset and input row the output row it feeds, int32 [K, L padded to 512]."""
+    import torch
+    K, _, L = indice_pairs.shape
+    d_pairs = TensorDesc(LAYOUT_ARRAY, DTYPE_INT32, (K, 2, L))
+    size = _szt(0)
+    try:
+        check("mluOpGetIndiceInputNeighbourTableSize",
+              lib().mluOpGetIndiceInputNeighbourTableSize(handle.ptr, d_pairs.ptr, ctypes.byref(size)))
+        table = _alloc((K, size.value // (4 * K)), torch.int32, indice_pairs.device)
+        check("mluOpBuildIndiceInputNeighbourTable",
+              lib().mluOpBuildIndiceInputNeighbourTable(handle.ptr, d_pairs.ptr, _ptr(indice_pairs),
+                                                        i64_array([int(v) for v in indice_num]), num_act_out,
+                                                        _ptr(table), size.value))
+    finally:
+        d_pairs.destroy()
+    return table
+
+
 FILTER_LAYOUTS = {"ARRAY": LAYOUT_ARRAY, "NDHWC": LAYOUT_NDHWC, "NCDHW": LAYOUT_NCDHW,
                   "HWCN": LAYOUT_HWCN, "NHWC": LAYOUT_NHWC, "NCHW": LAYOUT_NCHW}
 
@@ -449,12 +477,14 @@ def indice_convolution_forward(handle, features, filters, filter_layout, filter_
 
 
 def indice_convolution_backward_data(handle, output_grad, filters, filter_layout, indice_pairs,
-                                     indice_num_host, sub_m, workspace=None, out=None):
+                                     indice_num_host, sub_m, workspace=None, out=None, table=None):
     """input_grad [L, Ci] through mluOpIndiceConvolutionBackwardData.
 
     output_grad [N_out,Co] and filters (4-D or 5-D, in `filter_layout`: ARRAY, HWCN,
     NDHWC, NCDHW, NHWC, NCHW) are CUDA tensors of the same dtype; L is indice_pairs'
-    last dimension; indice_num_host is a sequence of K ints.
+    last dimension; indice_num_host is a sequence of K ints.  table: the rulebook's input
+    neighbour table (build_input_neighbour_table); with it the call is
+    mluOpIndiceConvolutionBackwardDataFromTable and indice_pairs only gives the shapes.
     """
     import torch
     n_out, co = output_grad.shape
@@ -476,6 +506,20 @@ def indice_convolution_backward_data(handle, output_grad, filters, filter_layout
     d_o = TensorDesc(LAYOUT_ARRAY, dt, (L, ci))
     num = i64_array(indice_num_host)
     size = _szt(0)
+    if table is not None:
+        check("mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize",
+              lib().mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize(handle.ptr, d_g.ptr, d_w.ptr, d_p.ptr,
+                                                                                d_o.ptr, num, 0, ctypes.byref(size)))
+        if workspace is None or workspace.numel() < size.value:
+            workspace = _alloc((max(size.value, 1),), torch.uint8, dev)
+        check("mluOpIndiceConvolutionBackwardDataFromTable",
+              lib().mluOpIndiceConvolutionBackwardDataFromTable(handle.ptr, d_g.ptr, _ptr(output_grad), d_w.ptr,
+                                                                _ptr(filters), d_p.ptr, _ptr(table),
+                                                                table.numel() * 4, num, 0, int(bool(sub_m)),
+                                                                _ptr(workspace), size.value, d_o.ptr, _ptr(out)))
+        for d in (d_g, d_w, d_p, d_o):
+            d.destroy()
+        return out
     check("mluOpGetIndiceConvolutionBackwardDataWorkspaceSize",
           lib().mluOpGetIndiceConvolutionBackwardDataWorkspaceSize(handle.ptr, d_g.ptr, d_w.ptr, d_p.ptr, d_o.ptr,
                                                                    num, 0, ctypes.byref(size)))
@@ -491,11 +535,13 @@ def indice_convolution_backward_data(handle, output_grad, filters, filter_layout
 
 
 def indice_convolution_backward_filter(handle, features, output_grad, filter_space, indice_pairs,
-                                       indice_num_host, sub_m, workspace=None, out=None):
+                                       indice_num_host, sub_m, workspace=None, out=None, table=None):
     """filters_grad [kd,kh,kw,Ci,Co] through mluOpIndiceConvolutionBackwardFilter.
 
     features [L,Ci] and output_grad [N_out,Co] are CUDA tensors of the same dtype;
-    indice_num_host is a sequence of K = kd*kh*kw ints.
+    indice_num_host is a sequence of K = kd*kh*kw ints.  table: the rulebook's FORWARD
+    neighbour table; with it the call is mluOpIndiceConvolutionBackwardFilterFromTable where the
+    shapes allow it (STATUS_NOT_SUPPORTED falls back to the reference-shaped call).
     """
     import torch
     L, ci = features.shape
@@ -518,11 +564,20 @@ def indice_convolution_backward_filter(handle, features, output_grad, filter_spa
                                                                      ctypes.byref(size)))
     if workspace is None or workspace.numel() < size.value:
         workspace = _alloc((max(size.value, 1),), torch.uint8, dev)
-    check("mluOpIndiceConvolutionBackwardFilter",
-          lib().mluOpIndiceConvolutionBackwardFilter(handle.ptr, d_f.ptr, _ptr(features), d_g.ptr,
-                                                     _ptr(output_grad), d_p.ptr, _ptr(indice_pairs), num, 0,
-                                                     int(bool(sub_m)), _ptr(workspace), size.value, d_w.ptr,
-                                                     _ptr(out)))
+    st = STATUS_NOT_SUPPORTED
+    if table is not None:
+        st = lib().mluOpIndiceConvolutionBackwardFilterFromTable(handle.ptr, d_f.ptr, _ptr(features), d_g.ptr,
+                                                                 _ptr(output_grad), d_p.ptr, _ptr(table),
+                                                                 table.numel() * 4, num, 0, int(bool(sub_m)),
+                                                                 _ptr(workspace), size.value, d_w.ptr, _ptr(out))
+        if st != STATUS_NOT_SUPPORTED:
+            check("mluOpIndiceConvolutionBackwardFilterFromTable", st)
+    if st == STATUS_NOT_SUPPORTED:
+        check("mluOpIndiceConvolutionBackwardFilter",
+              lib().mluOpIndiceConvolutionBackwardFilter(handle.ptr, d_f.ptr, _ptr(features), d_g.ptr,
+                                                         _ptr(output_grad), d_p.ptr, _ptr(indice_pairs), num, 0,
+                                                         int(bool(sub_m)), _ptr(workspace), size.value, d_w.ptr,
+                                                         _ptr(out)))
     for d in (d_f, d_g, d_p, d_w):
         d.destroy()
     return out

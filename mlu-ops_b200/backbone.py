@@ -42,12 +42,13 @@ class Workspace:
 class LayerRecord:
     """What one layer consumed and produced (kept for parity checks and roofline accounting)."""
     __slots__ = ("layer", "n_in", "n_out", "indice_num", "pairs", "in_indices", "out_indices", "features_in",
-                 "features_out", "new_rulebook", "in_space", "out_space", "weights")
+                 "features_out", "new_rulebook", "in_space", "out_space", "weights", "rulebook")
 
 
 class Rulebook:
     """Outputs of one mluOpGetIndicePairs call as the driver keeps them."""
-    __slots__ = ("pairs", "out_indices", "indice_num", "n_out", "table", "in_space", "out_space", "in_indices")
+    __slots__ = ("pairs", "out_indices", "indice_num", "n_out", "table", "in_space", "out_space", "in_indices",
+                 "input_table")
 
 
 class RulebookPlan:
@@ -359,6 +360,7 @@ class SparseNetwork:
         rec.layer, rec.n_in, rec.n_out = ly, features_in.shape[0], rb.n_out
         rec.indice_num, rec.new_rulebook = rb.indice_num, new_rb
         if keep:
+            rec.rulebook = rb
             rec.pairs, rec.in_indices, rec.out_indices = rb.pairs, in_indices, rb.out_indices[:rb.n_out]
             rec.features_in, rec.features_out = features_in, features_out
             rec.in_space, rec.out_space = list(rb.in_space), list(rb.out_space)
@@ -374,12 +376,16 @@ class SparseNetwork:
                 rec.indice_num = self.num_host[self.num_slot[rec.layer.rulebook], :K].tolist()
         return records
 
-    def backward(self, records, grad_out):
+    def backward(self, records, grad_out, reuse_tables=False):
         """Gradients of the layer stack, last layer first, from the records of
         forward(keep=True) and the gradient of its final features.  Per layer one
         mluOpIndiceConvolutionBackwardFilter and one mluOpIndiceConvolutionBackwardData
-        call on the rulebook the forward pass generated.  Returns (input_grad of the
-        first layer, [filters_grad per layer])."""
+        call on the rulebook the forward pass generated.  reuse_tables: one input
+        neighbour table per rulebook (mluOpBuildIndiceInputNeighbourTable) feeds the input
+        gradients of all its layers (...BackwardDataFromTable), and the filter gradients take
+        the forward table the rulebook kept (forward(reuse_tables=True)) where their kernel
+        works from one (...BackwardFilterFromTable).  Returns (input_grad of the first layer,
+        [filters_grad per layer])."""
         lib, h = self.lib, self.handle.ptr
         grad = grad_out
         filter_grads = [None] * len(records)
@@ -396,13 +402,45 @@ class SparseNetwork:
                       lib.mluOpGetIndiceConvolutionBackwardFilterWorkspaceSize(h, d_f, d_g, d_p, d_w, self.num_i64, 0,
                                                                                ly.sub_m, ctypes.byref(self.size)))
             ws = self.workspace.get(self.size.value)
-            ops.check("mluOpIndiceConvolutionBackwardFilter",
-                      lib.mluOpIndiceConvolutionBackwardFilter(h, d_f, _vp(rec.features_in.data_ptr()), d_g,
-                                                               _vp(grad.data_ptr()), d_p, _vp(rec.pairs.data_ptr()),
-                                                               self.num_i64, 0, ly.sub_m, _vp(ws.data_ptr()),
-                                                               self.size.value, d_w, _vp(dw.data_ptr())))
+            rb = rec.rulebook
+            st = ops.STATUS_NOT_SUPPORTED
+            if reuse_tables and getattr(rb, "table", None) is not None:
+                st = lib.mluOpIndiceConvolutionBackwardFilterFromTable(
+                    h, d_f, _vp(rec.features_in.data_ptr()), d_g, _vp(grad.data_ptr()), d_p, _vp(rb.table.data_ptr()),
+                    rb.table.numel() * 4, self.num_i64, 0, ly.sub_m, _vp(ws.data_ptr()), self.size.value, d_w,
+                    _vp(dw.data_ptr()))
+                if st != ops.STATUS_NOT_SUPPORTED:
+                    ops.check("mluOpIndiceConvolutionBackwardFilterFromTable", st)
+            if st == ops.STATUS_NOT_SUPPORTED:
+                ops.check("mluOpIndiceConvolutionBackwardFilter",
+                          lib.mluOpIndiceConvolutionBackwardFilter(h, d_f, _vp(rec.features_in.data_ptr()), d_g,
+                                                                   _vp(grad.data_ptr()), d_p,
+                                                                   _vp(rec.pairs.data_ptr()), self.num_i64, 0,
+                                                                   ly.sub_m, _vp(ws.data_ptr()), self.size.value,
+                                                                   d_w, _vp(dw.data_ptr())))
             filter_grads[li] = dw
             dx = torch.empty((L, ly.ci), dtype=grad.dtype, device=self.device)
+            if reuse_tables and K <= 128:
+                if getattr(rb, "input_table", None) is None:
+                    size = ctypes.c_size_t(0)
+                    ops.check("mluOpGetIndiceInputNeighbourTableSize",
+                              lib.mluOpGetIndiceInputNeighbourTableSize(h, d_p, ctypes.byref(size)))
+                    rb.input_table = torch.empty((size.value // 4,), dtype=torch.int32, device=self.device)
+                    ops.check("mluOpBuildIndiceInputNeighbourTable",
+                              lib.mluOpBuildIndiceInputNeighbourTable(h, d_p, _vp(rec.pairs.data_ptr()), self.num_i64,
+                                                                      n_out, _vp(rb.input_table.data_ptr()),
+                                                                      size.value))
+                ops.check("mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize",
+                          lib.mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize(
+                              h, d_g, d_w, d_p, d_f, self.num_i64, 0, ctypes.byref(self.size)))
+                ws = self.workspace.get(self.size.value)
+                ops.check("mluOpIndiceConvolutionBackwardDataFromTable",
+                          lib.mluOpIndiceConvolutionBackwardDataFromTable(
+                              h, d_g, _vp(grad.data_ptr()), d_w, _vp(w.data_ptr()), d_p,
+                              _vp(rb.input_table.data_ptr()), rb.input_table.numel() * 4, self.num_i64, 0, ly.sub_m,
+                              _vp(ws.data_ptr()), self.size.value, d_f, _vp(dx.data_ptr())))
+                grad = dx
+                continue
             ops.check("mluOpGetIndiceConvolutionBackwardDataWorkspaceSize",
                       lib.mluOpGetIndiceConvolutionBackwardDataWorkspaceSize(h, d_g, d_w, d_p, d_f, self.num_i64, 0,
                                                                              ctypes.byref(self.size)))

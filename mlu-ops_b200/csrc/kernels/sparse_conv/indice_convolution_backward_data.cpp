@@ -307,4 +307,145 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardData(
   return MLUOP_STATUS_SUCCESS;
 }
 
+// ---- neighbour-table fast path (no counterpart in the reference) -------------
+//
+// mluOpIndiceConvolutionBackwardData turns indice_pairs into its table (for every
+// kernel offset and INPUT row the output row it feeds) on every call.  Layers that
+// share a rulebook can build that table once and run each input gradient from it.
+
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceInputNeighbourTableSize(mluOpHandle_t handle,
+                                                                  const mluOpTensorDescriptor_t indice_pairs_desc,
+                                                                  size_t *table_size) {
+  const std::string api = "[mluOpGetIndiceInputNeighbourTableSize]";
+  PARAM_CHECK(api, handle != nullptr);
+  PARAM_CHECK(api, indice_pairs_desc != nullptr);
+  PARAM_CHECK(api, table_size != nullptr);
+  PARAM_CHECK(api, indice_pairs_desc->getDim() == 3 && indice_pairs_desc->getDimIndex(1) == 2);
+  PARAM_CHECK(api, indice_pairs_desc->getDtype() == MLUOP_DTYPE_INT32);
+  ConvProblem p{};
+  p.L = indice_pairs_desc->getDimIndex(2);
+  p.K = (int32_t)indice_pairs_desc->getDimIndex(0);
+  p.backward_data = 1;
+  *table_size = mluop::sparse_conv::neighbourTableBytes(p);
+  return MLUOP_STATUS_SUCCESS;
+}
+
+mluOpStatus_t MLUOP_WIN_API mluOpBuildIndiceInputNeighbourTable(mluOpHandle_t handle,
+                                                                const mluOpTensorDescriptor_t indice_pairs_desc,
+                                                                const void *indice_pairs, const int64_t indice_num[],
+                                                                const int64_t num_act_out, void *table,
+                                                                const size_t table_size) {
+  const std::string api = "[mluOpBuildIndiceInputNeighbourTable]";
+  PARAM_CHECK(api, handle != nullptr);
+  PARAM_CHECK(api, indice_pairs_desc != nullptr);
+  PARAM_CHECK(api, indice_num != nullptr);
+  PARAM_CHECK(api, indice_pairs_desc->getDim() == 3 && indice_pairs_desc->getDimIndex(1) == 2);
+  PARAM_CHECK(api, indice_pairs_desc->getDtype() == MLUOP_DTYPE_INT32);
+  PARAM_CHECK(api, num_act_out >= 0);
+  STRIDE_TENSOR_CHECK(api + ":", indice_pairs_desc, "indice_pairs_desc must be contiguous");
+  if (mluOpGetTensorElementNum(indice_pairs_desc) >= LARGE_TENSOR_NUM) {
+    LOG(ERROR) << api << " Max tensor number overflow. Tensors must have fewer than 2^31 elements.";
+    return MLUOP_STATUS_NOT_SUPPORTED;
+  }
+  ConvProblem p{};
+  p.L = indice_pairs_desc->getDimIndex(2);
+  p.n_out = num_act_out;
+  p.K = (int32_t)indice_pairs_desc->getDimIndex(0);
+  p.backward_data = 1;
+  for (int32_t k = 0; k < p.K; ++k) {
+    PARAM_CHECK(api, indice_num[k] >= 0 && indice_num[k] <= p.L);
+  }
+  if (!mluop::sparse_conv::neighbourTableCountsFit(p.K)) {
+    LOG(ERROR) << api << " kernel volumes above 128 are not supported by the table path.";
+    return MLUOP_STATUS_NOT_SUPPORTED;
+  }
+  const size_t need = mluop::sparse_conv::neighbourTableBytes(p);
+  if (need == 0 || p.L == 0) return MLUOP_STATUS_SUCCESS;
+  PARAM_CHECK(api, indice_pairs != nullptr);
+  PARAM_CHECK(api, table != nullptr);
+  PARAM_CHECK(api, reinterpret_cast<size_t>(table) % 16 == 0);
+  if (table_size < need) {
+    LOG(ERROR) << api << " table of " << table_size << " bytes is smaller than the " << need
+               << " bytes mluOpGetIndiceInputNeighbourTableSize reports.";
+    return MLUOP_STATUS_BAD_PARAM;
+  }
+  if (handle->host_only) {
+    LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
+  const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p, true);
+  cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionSteps(
+      p, plan, nullptr, nullptr, static_cast<const int32_t *>(indice_pairs), indice_num, nullptr, nullptr,
+      handle->sm_count, handle->queue, static_cast<int32_t *>(table), mluop::sparse_conv::kTableBuildOnly);
+  if (err != cudaSuccess) {
+    LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  return MLUOP_STATUS_SUCCESS;
+}
+
+mluOpStatus_t MLUOP_WIN_API mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t output_grad_desc,
+    const mluOpTensorDescriptor_t filters_desc, const mluOpTensorDescriptor_t indice_pairs_desc,
+    const mluOpTensorDescriptor_t input_grad_desc, const int64_t indice_num[], const int64_t inverse,
+    size_t *workspace_size) {
+  const std::string api = "[mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize]";
+  PARAM_CHECK(api, workspace_size != nullptr);
+  bool is_zero = false;
+  mluOpStatus_t st = foolCheckNoPtr(api, handle, output_grad_desc, filters_desc, indice_pairs_desc, indice_num,
+                                    inverse, 0, input_grad_desc, &is_zero);
+  if (st != MLUOP_STATUS_SUCCESS) return st;
+  *workspace_size = 0;
+  if (is_zero) return MLUOP_STATUS_SUCCESS;
+  const ConvProblem p = makeProblem(handle, output_grad_desc, filters_desc, input_grad_desc);
+  *workspace_size = mluop::sparse_conv::planConvWorkspace(p, true).total;
+  return MLUOP_STATUS_SUCCESS;
+}
+
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardDataFromTable(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t output_grad_desc, const void *output_grad,
+    const mluOpTensorDescriptor_t filters_desc, const void *filters,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *table, const size_t table_size,
+    const int64_t indice_num[], const int64_t inverse, const int64_t sub_m, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t input_grad_desc, void *input_grad) {
+  const std::string api = "[mluOpIndiceConvolutionBackwardDataFromTable]";
+  bool is_zero = false;
+  mluOpStatus_t st = foolCheckNoPtr(api, handle, output_grad_desc, filters_desc, indice_pairs_desc, indice_num,
+                                    inverse, sub_m, input_grad_desc, &is_zero);
+  if (st != MLUOP_STATUS_SUCCESS) return st;
+  if (is_zero) return MLUOP_STATUS_SUCCESS;
+  PARAM_CHECK(api, output_grad != nullptr);
+  PARAM_CHECK(api, filters != nullptr);
+  PARAM_CHECK(api, table != nullptr);
+  PARAM_CHECK(api, input_grad != nullptr);
+  PARAM_CHECK(api, workspace != nullptr);
+  PARAM_CHECK(api, reinterpret_cast<size_t>(table) % 16 == 0);  // read 16 bytes at a time
+  const ConvProblem p = makeProblem(handle, output_grad_desc, filters_desc, input_grad_desc);
+  if (!mluop::sparse_conv::neighbourTableCountsFit(p.K)) {
+    LOG(ERROR) << api << " kernel volumes above 128 are not supported by the table path.";
+    return MLUOP_STATUS_NOT_SUPPORTED;
+  }
+  const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p, true);
+  const size_t need = mluop::sparse_conv::neighbourTableBytes(p);
+  if (workspace_size < plan.total || table_size < need) {
+    LOG(ERROR) << api << " workspace (" << workspace_size << " of " << plan.total << " bytes) or table ("
+               << table_size << " of " << need << " bytes) is smaller than the size queries report.";
+    return MLUOP_STATUS_BAD_PARAM;
+  }
+  if (handle->host_only) {
+    LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
+  cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionSteps(
+      p, plan, output_grad, filters, nullptr, indice_num, workspace, input_grad, handle->sm_count, handle->queue,
+      const_cast<int32_t *>(static_cast<const int32_t *>(table)), mluop::sparse_conv::kTableConvolveOnly);
+  if (err != cudaSuccess) {
+    LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  return MLUOP_STATUS_SUCCESS;
+}
+
 }  // extern "C"

@@ -22,6 +22,7 @@
 #include "core/logging.h"
 #include "core/tensor.h"
 #include "kernels/sparse_conv/indice_convolution_backward_filter_kernels.h"
+#include "kernels/sparse_conv/indice_convolution_kernels.h"
 
 using mluop::sparse_conv::FilterGradProblem;
 using mluop::sparse_conv::FilterGradWorkspacePlan;
@@ -207,6 +208,74 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilter(
   cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionBackwardFilter(
       p, plan, features, output_grad, static_cast<const int32_t *>(indice_pairs), indice_num, workspace,
       filters_grad, handle->sm_count, handle->queue);
+  if (err != cudaSuccess) {
+    LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  return MLUOP_STATUS_SUCCESS;
+}
+
+// ---- neighbour-table fast path (no counterpart in the reference) -------------
+//
+// The tensor-memory kernel works from the FORWARD convolution's neighbour table
+// (mluOpBuildIndiceNeighbourTable, or the one mluOpGetIndicePairsWithNeighbourTable
+// emitted) and builds it from indice_pairs on every call; a caller that kept the
+// table hands it over instead.  Shapes the kernel does not take (anything but half
+// with 64 input and 64 or 128 output channels) are MLUOP_STATUS_NOT_SUPPORTED: the
+// caller uses mluOpIndiceConvolutionBackwardFilter.  The workspace is the one
+// mluOpGetIndiceConvolutionBackwardFilterWorkspaceSize reports.
+
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilterFromTable(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc, const void *features,
+    const mluOpTensorDescriptor_t output_grad_desc, const void *output_grad,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *table, const size_t table_size,
+    const int64_t indice_num[], const int64_t inverse, const int64_t sub_m, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t filters_grad_desc, void *filters_grad) {
+  const std::string api = "[mluOpIndiceConvolutionBackwardFilterFromTable]";
+  (void)sub_m;
+  mluOpStatus_t st = baseParamCheck(api, handle, features_desc, output_grad_desc, indice_pairs_desc,
+                                    filters_grad_desc, indice_num, inverse);
+  if (st != MLUOP_STATUS_SUCCESS) return st;
+  if (anyZeroElement(features_desc, output_grad_desc, indice_pairs_desc, filters_grad_desc)) {
+    VLOG(5) << api << " Skip zero element tensor.";
+    return MLUOP_STATUS_SUCCESS;
+  }
+  st = pairCountCheck(api, indice_pairs_desc, indice_num);
+  if (st != MLUOP_STATUS_SUCCESS) return st;
+  PARAM_CHECK(api, features != nullptr);
+  PARAM_CHECK(api, output_grad != nullptr);
+  PARAM_CHECK(api, table != nullptr);
+  PARAM_CHECK(api, filters_grad != nullptr);
+  PARAM_CHECK(api, workspace != nullptr);
+  PARAM_CHECK(api, reinterpret_cast<size_t>(table) % 16 == 0);  // read 16 bytes at a time
+  FilterGradProblem p = makeProblem(features_desc, output_grad_desc, indice_pairs_desc);
+  p.sticky_status = handle->host_only ? nullptr : handle->host_words + mluOpContext::kStickyWord;
+  const FilterGradWorkspacePlan plan =
+      mluop::sparse_conv::planFilterGradWorkspace(p, indice_num, handle->sm_count);
+  if (!mluop::sparse_conv::filterGradRunsFromTable(p, plan, features, output_grad)) {
+    // an answer, not an error: callers try this entry point first
+    VLOG(5) << api << " only half tensors with 64 input and 64 or 128 output channels (16-byte aligned) run "
+            << "from a neighbour table; use mluOpIndiceConvolutionBackwardFilter.";
+    return MLUOP_STATUS_NOT_SUPPORTED;
+  }
+  mluop::sparse_conv::ConvProblem cp{};
+  cp.L = p.L;
+  cp.n_out = p.n_out;
+  cp.K = p.K;
+  const size_t need = mluop::sparse_conv::neighbourTableBytes(cp);
+  if (workspace_size < plan.total || table_size < need) {
+    LOG(ERROR) << api << " workspace (" << workspace_size << " of " << plan.total << " bytes) or table ("
+               << table_size << " of " << need << " bytes) is smaller than the size queries report.";
+    return MLUOP_STATUS_BAD_PARAM;
+  }
+  if (handle->host_only) {
+    LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
+  cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionBackwardFilter(
+      p, plan, features, output_grad, nullptr, indice_num, workspace, filters_grad, handle->sm_count, handle->queue,
+      static_cast<const int32_t *>(table));
   if (err != cudaSuccess) {
     LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
     return MLUOP_STATUS_EXECUTION_FAILED;

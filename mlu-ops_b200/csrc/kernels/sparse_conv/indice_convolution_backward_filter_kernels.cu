@@ -488,12 +488,19 @@ FilterGradWorkspacePlan planFilterGradWorkspace(const FilterGradProblem &p, cons
   return plan;
 }
 
+bool filterGradRunsFromTable(const FilterGradProblem &p, const FilterGradWorkspacePlan &plan, const void *features,
+                             const void *output_grad) {
+  (void)p;
+  return plan.use_tc && reinterpret_cast<size_t>(features) % 16 == 0 && reinterpret_cast<size_t>(output_grad) % 16 == 0;
+}
+
 cudaError_t launchIndiceConvolutionBackwardFilter(const FilterGradProblem &p,
                                                   const FilterGradWorkspacePlan &plan,
                                                   const void *features, const void *output_grad,
                                                   const int32_t *indice_pairs,
                                                   const int64_t *indice_num, void *workspace,
-                                                  void *filters_grad, int sm_count, cudaStream_t stream) {
+                                                  void *filters_grad, int sm_count, cudaStream_t stream,
+                                                  const int32_t *forward_table) {
   char *base = reinterpret_cast<char *>(alignUp(reinterpret_cast<size_t>(workspace), 256));
   int32_t *counts = reinterpret_cast<int32_t *>(base + plan.counts);
   float *partial = reinterpret_cast<float *>(base + plan.partial);
@@ -518,13 +525,14 @@ cudaError_t launchIndiceConvolutionBackwardFilter(const FilterGradProblem &p,
   const double bytes = pairs_total * ((p.ci + p.co) * elem + 8.0) + (double)p.K * p.ci * p.co * elem;
   const double flops = 2.0 * pairs_total * p.ci * p.co;
 
-  if (plan.use_tc && reinterpret_cast<size_t>(features) % 16 == 0 && reinterpret_cast<size_t>(output_grad) % 16 == 0) {
+  if (filterGradRunsFromTable(p, plan, features, output_grad)) {
     return launchFilterGradTcgen05(p, planFilterGradTc(p, sm_count), features, output_grad, indice_pairs, indice_num,
                                    reinterpret_cast<int32_t *>(base + plan.tc_table),
                                    reinterpret_cast<float *>(base + plan.tc_partial),
                                    reinterpret_cast<int32_t *>(base + plan.tc_status), filters_grad, sm_count, bytes,
-                                   flops, stream);
+                                   flops, stream, forward_table);
   }
+  if (forward_table != nullptr) return cudaErrorNotSupported;  // the pair-list kernels have no use for a table
   if (gradMmaEligible(p, features, output_grad)) {
     const __half *f = static_cast<const __half *>(features);
     const __half *g = static_cast<const __half *>(output_grad);

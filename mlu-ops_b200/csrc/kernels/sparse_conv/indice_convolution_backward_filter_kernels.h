@@ -49,7 +49,13 @@ cudaError_t launchIndiceConvolutionBackwardFilter(const FilterGradProblem &p,
                                                   const void *features, const void *output_grad,
                                                   const int32_t *indice_pairs,
                                                   const int64_t *indice_num, void *workspace,
-                                                  void *filters_grad, int sm_count, cudaStream_t stream);
+                                                  void *filters_grad, int sm_count, cudaStream_t stream,
+                                                  const int32_t *forward_table = nullptr);
+
+// Whether a call with these shapes and pointers runs from the forward convolution's neighbour
+// table (the tensor-memory kernel) and can therefore take the caller's copy of it.
+bool filterGradRunsFromTable(const FilterGradProblem &p, const FilterGradWorkspacePlan &plan, const void *features,
+                             const void *output_grad);
 
 }  // namespace sparse_conv
 }  // namespace mluop

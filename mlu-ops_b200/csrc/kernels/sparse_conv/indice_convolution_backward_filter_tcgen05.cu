@@ -491,20 +491,25 @@ cudaError_t launchFilterGradTcgen05(const FilterGradProblem &p, const FilterGrad
                                     const void *output_grad, const int32_t *indice_pairs,
                                     const int64_t *indice_num, int32_t *table, float *partial, int32_t *status,
                                     void *filters_grad, int sm_count, double bytes, double flops,
-                                    cudaStream_t stream) {
-  // 1. the forward convolution's neighbour table, from the pair lists
-  ConvProblem cp{};
-  cp.L = p.L;
-  cp.n_out = p.n_out;
-  cp.K = p.K;
-  cp.ci = p.ci;
-  cp.co = p.co;
-  cp.is_half = 1;
-  cp.sticky_status = p.sticky_status;
-  const ConvWorkspacePlan conv_plan = planConvWorkspace(cp, /*external_table=*/true);
-  cudaError_t err = launchIndiceConvolutionSteps(cp, conv_plan, nullptr, nullptr, indice_pairs, indice_num, nullptr,
-                                                 nullptr, sm_count, stream, table, kTableBuildOnly);
-  if (err != cudaSuccess) return err;
+                                    cudaStream_t stream, const int32_t *external_table) {
+  // 1. the forward convolution's neighbour table: the caller's, or built from the pair lists
+  cudaError_t err = cudaSuccess;
+  if (external_table != nullptr) {
+    table = const_cast<int32_t *>(external_table);
+  } else {
+    ConvProblem cp{};
+    cp.L = p.L;
+    cp.n_out = p.n_out;
+    cp.K = p.K;
+    cp.ci = p.ci;
+    cp.co = p.co;
+    cp.is_half = 1;
+    cp.sticky_status = p.sticky_status;
+    const ConvWorkspacePlan conv_plan = planConvWorkspace(cp, /*external_table=*/true);
+    err = launchIndiceConvolutionSteps(cp, conv_plan, nullptr, nullptr, indice_pairs, indice_num, nullptr, nullptr,
+                                       sm_count, stream, table, kTableBuildOnly);
+    if (err != cudaSuccess) return err;
+  }
   if ((err = cudaMemsetAsync(status, 0, sizeof(int32_t), stream)) != cudaSuccess) return err;
   // 2. partial sums of every block
   const __half *f = static_cast<const __half *>(features);

@@ -32,12 +32,13 @@ FilterGradTcPlan planFilterGradTc(const FilterGradProblem &p, int sm_count);
 
 // table, partial and status (one int32 of error bits) are 256-byte aligned
 // device buffers of the sizes the plan gives; filters_grad is written as half
-// [K][Ci][Co].
+// [K][Ci][Co].  external_table: the forward convolution's neighbour table if the
+// caller has it (then `table` is unused and nothing is built), else null.
 cudaError_t launchFilterGradTcgen05(const FilterGradProblem &p, const FilterGradTcPlan &plan, const void *features,
                                     const void *output_grad, const int32_t *indice_pairs,
                                     const int64_t *indice_num, int32_t *table, float *partial, int32_t *status,
                                     void *filters_grad, int sm_count, double bytes, double flops,
-                                    cudaStream_t stream);
+                                    cudaStream_t stream, const int32_t *external_table = nullptr);
 
 }  // namespace sparse_conv
 }  // namespace mluop

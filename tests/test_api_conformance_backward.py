@@ -255,3 +255,84 @@ def test_bf_null_sweep(ops, handle):
         assert lib.mluOpIndiceConvolutionBackwardFilter(*a) == ops.STATUS_BAD_PARAM, i
     for d in descs:
         d.destroy()
+
+
+# ------------------------------------------------- neighbour-table fast path of the gradients (extensions)
+
+def test_gradient_table_entry_points_argument_checks(ops, handle):
+    lib = ops.lib()
+    keep = (ctypes.c_char * 65536)()
+    p = VP((ctypes.addressof(keep) + 15) // 16 * 16)
+    # the input table: [K][L padded to 512] int32
+    d_p = ops.TensorDesc(ARRAY, I32, (9, 2, 10))
+    size = ctypes.c_size_t(0)
+    assert lib.mluOpGetIndiceInputNeighbourTableSize(handle.ptr, d_p.ptr, ctypes.byref(size)) == 0
+    assert size.value == 9 * 512 * 4
+    for a in ([None, d_p.ptr, ctypes.byref(size)], [handle.ptr, None, ctypes.byref(size)], [handle.ptr, d_p.ptr, None]):
+        assert lib.mluOpGetIndiceInputNeighbourTableSize(*a) == ops.STATUS_BAD_PARAM
+    num = ops.i64_array([10] * 9)
+    build = [handle.ptr, d_p.ptr, p, num, 10, p, size.value]
+    assert lib.mluOpBuildIndiceInputNeighbourTable(*build) == ops.STATUS_EXECUTION_FAILED  # checks pass; host-only handle
+    for i in (0, 1, 2, 3, 5):
+        a = list(build)
+        a[i] = None
+        assert lib.mluOpBuildIndiceInputNeighbourTable(*a) == ops.STATUS_BAD_PARAM, i
+    assert lib.mluOpBuildIndiceInputNeighbourTable(handle.ptr, d_p.ptr, p, num, 10, p, 100) == ops.STATUS_BAD_PARAM
+    assert lib.mluOpBuildIndiceInputNeighbourTable(handle.ptr, d_p.ptr, p, num, 10, VP(p.value + 4),
+                                                   size.value) == ops.STATUS_BAD_PARAM
+    assert lib.mluOpBuildIndiceInputNeighbourTable(handle.ptr, d_p.ptr, p, ops.i64_array([11] + [10] * 8), 10, p,
+                                                   size.value) == ops.STATUS_BAD_PARAM
+    # the input gradient from it: the reference-shaped entry point's checks, plus table and workspace sizes
+    descs = [ops.TensorDesc(*BD_GOOD[k]) for k in ("output_grad", "filters", "pairs", "input_grad")]
+    d_g, d_w, d_pp, d_i = (d.ptr for d in descs)
+    ws = ctypes.c_size_t(0)
+    assert lib.mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize(handle.ptr, d_g, d_w, d_pp, d_i, num, 0,
+                                                                           ctypes.byref(ws)) == 0
+    full = ctypes.c_size_t(0)
+    assert lib.mluOpGetIndiceConvolutionBackwardDataWorkspaceSize(handle.ptr, d_g, d_w, d_pp, d_i, num, 0,
+                                                                  ctypes.byref(full)) == 0
+    assert 0 < ws.value < full.value  # the table no longer lives in the workspace
+    args = [handle.ptr, d_g, p, d_w, p, d_pp, p, size.value, num, 0, 0, p, ws.value, d_i, p]
+    assert lib.mluOpIndiceConvolutionBackwardDataFromTable(*args) == ops.STATUS_EXECUTION_FAILED
+    for i in (0, 1, 2, 3, 4, 5, 6, 8, 11, 13, 14):
+        a = list(args)
+        a[i] = None
+        assert lib.mluOpIndiceConvolutionBackwardDataFromTable(*a) == ops.STATUS_BAD_PARAM, i
+    odd = list(args)
+    odd[6] = VP(p.value + 4)  # the table is read 16 bytes at a time
+    assert lib.mluOpIndiceConvolutionBackwardDataFromTable(*odd) == ops.STATUS_BAD_PARAM
+    small = list(args)
+    small[7] = 100
+    assert lib.mluOpIndiceConvolutionBackwardDataFromTable(*small) == ops.STATUS_BAD_PARAM
+    inv = list(args)
+    inv[9] = 1
+    assert lib.mluOpIndiceConvolutionBackwardDataFromTable(*inv) == ops.STATUS_NOT_SUPPORTED
+    # the filter gradient from the forward table: float tensors are not the kernel's, half 64 -> 64 are
+    fdescs = [ops.TensorDesc(*BF_GOOD[k]) for k in ("features", "output_grad", "pairs", "filters_grad")]
+    d_f, d_og, d_fp, d_fw = (d.ptr for d in fdescs)
+    fnum = ops.i64_array(BF_GOOD["indice_num"])
+    fargs = [handle.ptr, d_f, p, d_og, p, d_fp, p, 9 * 512 * 4, fnum, 0, 0, p, 1 << 16, d_fw, p]
+    assert lib.mluOpIndiceConvolutionBackwardFilterFromTable(*fargs) == ops.STATUS_NOT_SUPPORTED
+    for i in (0, 1, 2, 3, 4, 5, 6, 8, 11, 13, 14):
+        a = list(fargs)
+        a[i] = None
+        assert lib.mluOpIndiceConvolutionBackwardFilterFromTable(*a) == ops.STATUS_BAD_PARAM, i
+    hdescs = [ops.TensorDesc(ARRAY, F16, (3, 64)), ops.TensorDesc(ARRAY, F16, (3, 64)),
+              ops.TensorDesc(ARRAY, I32, (9, 2, 3)), ops.TensorDesc(ARRAY, F16, (3, 3, 64, 64))]
+    hsize = ctypes.c_size_t(0)
+    assert lib.mluOpGetIndiceConvolutionBackwardFilterWorkspaceSize(handle.ptr, hdescs[0].ptr, hdescs[1].ptr,
+                                                                    hdescs[2].ptr, hdescs[3].ptr, fnum, 0, 0,
+                                                                    ctypes.byref(hsize)) == 0
+    big = (ctypes.c_char * (hsize.value + 64))()
+    wp = VP((ctypes.addressof(big) + 15) // 16 * 16)
+    hargs = [handle.ptr, hdescs[0].ptr, p, hdescs[1].ptr, p, hdescs[2].ptr, p, 9 * 512 * 4, fnum, 0, 0, wp,
+             hsize.value, hdescs[3].ptr, p]
+    assert lib.mluOpIndiceConvolutionBackwardFilterFromTable(*hargs) == ops.STATUS_EXECUTION_FAILED  # host-only handle
+    hsmall = list(hargs)
+    hsmall[7] = 100
+    assert lib.mluOpIndiceConvolutionBackwardFilterFromTable(*hsmall) == ops.STATUS_BAD_PARAM
+    hodd = list(hargs)
+    hodd[6] = VP(p.value + 4)
+    assert lib.mluOpIndiceConvolutionBackwardFilterFromTable(*hodd) == ops.STATUS_BAD_PARAM
+    for d in [d_p] + descs + fdescs + hdescs:
+        d.destroy()

@@ -89,6 +89,36 @@ def test_neighbour_table_fast_path_is_bit_identical(ops, workloads, backbone, gp
     net.close()
 
 
+def test_gradient_table_fast_path_is_bit_identical(ops, workloads, backbone, gpu_handle):
+    """One input neighbour table per rulebook (mluOpBuildIndiceInputNeighbourTable +
+    ...BackwardDataFromTable) and the forward table handed to the filter gradient
+    (...BackwardFilterFromTable) give exactly the gradients of the reference-shaped entry points."""
+    idx, feat, layers, weights = workloads.make_inputs("c2", batch=1)
+    grid = list(workloads.CONFIGS["c2"]["grid"])
+    net = backbone.SparseNetwork(gpu_handle, layers, [torch.from_numpy(w).cuda() for w in weights], grid, 1)
+    d_idx, d_feat = torch.from_numpy(idx).cuda(), torch.from_numpy(feat).cuda()
+    out, _, records = net.forward(d_idx, d_feat, keep=True, reuse_tables=True)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    grad = torch.randn(out.shape, generator=gen, device="cuda").half()
+    dx_ref, dw_ref = net.backward(records, grad)
+    lib = ops.lib()
+    lib.mluOpTraceKernelReset()
+    lib.mluOpTraceKernelEnable(1)
+    dx, dw = net.backward(records, grad, reuse_tables=True)
+    torch.cuda.synchronize()
+    lib.mluOpTraceKernelEnable(0)
+    import ctypes
+    buf = ctypes.create_string_buffer(1 << 16)
+    assert lib.mluOpTraceKernelReport(buf, len(buf), None) == 0
+    launches = {line.rsplit(",", 4)[0]: int(line.rsplit(",", 4)[1]) for line in buf.value.decode().splitlines()[1:]}
+    # one table build per rulebook for the input gradients, none for the 64-channel filter gradients
+    assert launches["buildNeighbourKernel"] == len({ly.rulebook for ly in layers}) + sum(
+        1 for ly in layers if ly.ci == 64 and ly.co not in (64, 128)), launches
+    assert torch.equal(dx, dx_ref)
+    assert all(torch.equal(a, b) for a, b in zip(dw, dw_ref))
+    net.close()
+
+
 def test_rulebooks_on_a_second_stream_are_bit_identical(ops, workloads, backbone, gpu_handle):
     """mluOpGetIndicePairs through a second handle on a second stream, overlapping the
     convolutions of earlier layers, gives exactly the single-stream results, repeatedly."""

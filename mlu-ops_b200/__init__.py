@@ -439,11 +439,13 @@ def filter_dims(layout, filter_space, ci, co):
 
 
 def indice_convolution_forward(handle, features, filters, filter_layout, filter_space, indice_pairs,
-                               indice_num_host, num_act_out, sub_m, workspace=None, out=None):
+                               indice_num_host, num_act_out, sub_m, workspace=None, out=None, table=None):
     """features_out [num_act_out, Co] through mluOpIndiceConvolutionForward.
 
     features [L,Ci] and filters (5-D, in `filter_layout`) are CUDA tensors of the
-    same dtype (float16 or float32); indice_num_host is a sequence of K ints.
+    same dtype (float16 or float32); indice_num_host is a sequence of K ints.  table: the
+    rulebook's neighbour table (build_neighbour_table); with it the call is
+    mluOpIndiceConvolutionForwardFromTable and indice_pairs only gives the shapes.
     """
     import torch
     L, ci = features.shape
@@ -460,6 +462,21 @@ def indice_convolution_forward(handle, features, filters, filter_layout, filter_
     d_o = TensorDesc(LAYOUT_ARRAY, dt, (num_act_out, co))
     num = i64_array(indice_num_host)
     size = _szt(0)
+    if table is not None:
+        check("mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize",
+              lib().mluOpGetIndiceConvolutionForwardFromTableWorkspaceSize(handle.ptr, d_f.ptr, d_w.ptr, d_p.ptr,
+                                                                           d_o.ptr, num, num_act_out, 0,
+                                                                           int(bool(sub_m)), ctypes.byref(size)))
+        if workspace is None or workspace.numel() < size.value:
+            workspace = _alloc((max(size.value, 1),), torch.uint8, dev)
+        check("mluOpIndiceConvolutionForwardFromTable",
+              lib().mluOpIndiceConvolutionForwardFromTable(handle.ptr, d_f.ptr, _ptr(features), d_w.ptr,
+                                                           _ptr(filters), d_p.ptr, _ptr(table), table.numel() * 4,
+                                                           num, num_act_out, 0, int(bool(sub_m)), _ptr(workspace),
+                                                           size.value, d_o.ptr, _ptr(out)))
+        for d in (d_f, d_w, d_p, d_o):
+            d.destroy()
+        return out
     check("mluOpGetIndiceConvolutionForwardWorkspaceSize",
           lib().mluOpGetIndiceConvolutionForwardWorkspaceSize(handle.ptr, d_f.ptr, d_w.ptr, d_p.ptr, d_o.ptr,
                                                               num, num_act_out, 0, int(bool(sub_m)),

@@ -47,7 +47,27 @@ def _triple(v):
 
 class Rulebook:
     """What mluOpGetIndicePairs produced for one geometry (shared through indice_key)."""
-    __slots__ = ("indice_pairs", "out_indices", "indice_num", "num_act_out", "out_space", "filter_space", "sub_m")
+    __slots__ = ("indice_pairs", "out_indices", "indice_num", "num_act_out", "out_space", "filter_space", "sub_m",
+                 "shared", "table", "input_table")
+
+    def forward_table(self, handle):
+        """The neighbour table of a rulebook that several layers share (an indice_key), built at its
+        first use and kept: those layers then run from it instead of each rebuilding it from the
+        pair lists.  None for a rulebook of one layer or a kernel volume above 128."""
+        if not getattr(self, "shared", False) or len(self.indice_num) > 128:
+            return None
+        if getattr(self, "table", None) is None:
+            self.table = ops.build_neighbour_table(handle, self.indice_pairs, self.indice_num, self.num_act_out)
+        return self.table
+
+    def backward_table(self, handle):
+        """The same for the input gradients (for every offset and input row the output row it feeds)."""
+        if not getattr(self, "shared", False) or len(self.indice_num) > 128:
+            return None
+        if getattr(self, "input_table", None) is None:
+            self.input_table = ops.build_input_neighbour_table(handle, self.indice_pairs, self.indice_num,
+                                                               self.num_act_out)
+        return self.input_table
 
 
 class SparseConvTensor:
@@ -80,7 +100,7 @@ class _IndiceConvFunction(torch.autograd.Function):
         h = _handle(features.device)
         out = ops.indice_convolution_forward(h, features, weight, "ARRAY", rulebook.filter_space,
                                              rulebook.indice_pairs, rulebook.indice_num, rulebook.num_act_out,
-                                             rulebook.sub_m)
+                                             rulebook.sub_m, table=rulebook.forward_table(h))
         ctx.save_for_backward(features, weight)
         ctx.rulebook = rulebook
         return out
@@ -94,10 +114,12 @@ class _IndiceConvFunction(torch.autograd.Function):
         grad_features = grad_weight = None
         if ctx.needs_input_grad[1]:
             grad_weight = ops.indice_convolution_backward_filter(h, features, grad_out, rb.filter_space,
-                                                                 rb.indice_pairs, rb.indice_num, rb.sub_m)
+                                                                 rb.indice_pairs, rb.indice_num, rb.sub_m,
+                                                                 table=rb.forward_table(h))
         if ctx.needs_input_grad[0]:
             grad_features = ops.indice_convolution_backward_data(h, grad_out, weight, "ARRAY", rb.indice_pairs,
-                                                                 rb.indice_num, rb.sub_m)
+                                                                 rb.indice_num, rb.sub_m,
+                                                                 table=rb.backward_table(h))
         return grad_features, grad_weight, None
 
 
@@ -147,6 +169,7 @@ class SparseConvolution(nn.Module):
         rb.indice_num = num.cpu().tolist()  # the convolution API takes the counts as a host array
         rb.num_act_out, rb.out_space = n_out, out_space
         rb.filter_space, rb.sub_m = list(self.kernel_size), int(self.subm)
+        rb.shared = self.indice_key is not None  # other layers will come for it: worth keeping its tables
         if self.indice_key is not None:
             x.indice_dict[self.indice_key] = rb
         return rb

@@ -150,3 +150,28 @@ def test_dynamic_scatter_autograd(sp, oracle):
                                                                                             ref[2], m))
     mean, _, _ = sp.dynamic_scatter(d_feats, torch.from_numpy(coors).cuda(), "mean")
     assert np.array_equal(mean.cpu().numpy(), oracle.dynamic_point_to_voxel_forward(feats, coors, "mean")[0][:m])
+
+
+def test_layers_that_share_a_rulebook_run_from_its_tables_bit_identically(sp):
+    """Layers under one indice_key run from the rulebook's neighbour tables (built once, kept on
+    the rulebook: forward, input gradient and, at 64 channels, filter gradient from a table);
+    the same weights without a key rebuild the tables per call.  Same bits either way."""
+    rng = np.random.default_rng(41)
+    batch, space, n = 2, [8, 16, 16], 1500
+    _, _, d_idx, d_feat = make_input(rng, batch, space, n, 64, torch.float16)
+    results = []
+    for key in ("k", None):
+        torch.manual_seed(5)
+        l1 = sp.SubMConv3d(64, 64, 3, bias=False, indice_key=key, dtype=torch.float16).cuda()
+        l2 = sp.SubMConv3d(64, 64, 3, bias=False, indice_key=key, dtype=torch.float16).cuda()
+        feat = d_feat.clone().requires_grad_(True)
+        x = sp.SparseConvTensor(feat, d_idx, space, batch)
+        y = l2(l1(x))
+        gen = torch.Generator(device="cuda").manual_seed(6)
+        y.features.backward(torch.randn(y.features.shape, generator=gen, device="cuda").half())
+        if key is not None:
+            rb = x.indice_dict[key]
+            assert rb.table is not None and rb.input_table is not None
+        results.append((y.features.detach(), feat.grad, l1.weight.grad, l2.weight.grad))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)

@@ -418,6 +418,22 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardDataFromTable(
     const int64_t indice_num[], const int64_t inverse, const int64_t sub_m, void *workspace,
     const size_t workspace_size, const mluOpTensorDescriptor_t input_grad_desc, void *input_grad);
 
+/* The input gradient of a SUBMANIFOLD layer with centred padding (stride 1, dilation 1, odd
+ * kernel extents, pad = extent / 2) straight from the rulebook's FORWARD table: such a rulebook is
+ * symmetric, so the kernel reads the forward table with the offsets mirrored and no input table
+ * is built at all.  The caller vouches for the geometry; sub_m must be 1 and input_grad has as
+ * many rows as output_grad.  Only the tensor-memory kernel reads a table this way (half, channel
+ * counts that are multiples of 8 up to 128, 16-byte aligned rows): anything else returns
+ * MLUOP_STATUS_NOT_SUPPORTED before anything is enqueued and the caller uses
+ * mluOpIndiceConvolutionBackwardDataFromTable.  Workspace as for that entry point.  Bit-identical
+ * to the reference-shaped call.  No counterpart in the reference. */
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardDataFromForwardTable(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t output_grad_desc, const void *output_grad,
+    const mluOpTensorDescriptor_t filters_desc, const void *filters,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *table, const size_t table_size,
+    const int64_t indice_num[], const int64_t inverse, const int64_t sub_m, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t input_grad_desc, void *input_grad);
+
 mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilterFromTable(
     mluOpHandle_t handle, const mluOpTensorDescriptor_t features_desc, const void *features,
     const mluOpTensorDescriptor_t output_grad_desc, const void *output_grad,

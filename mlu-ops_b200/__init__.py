@@ -93,6 +93,8 @@ SIGNATURES = {
                                                                           ctypes.POINTER(_szt)]),
     "mluOpIndiceConvolutionBackwardDataFromTable": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _szt, _i64p, _i64,
                                                           _i64, _vp, _szt, _vp, _vp]),
+    "mluOpIndiceConvolutionBackwardDataFromForwardTable": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _szt, _i64p,
+                                                                 _i64, _i64, _vp, _szt, _vp, _vp]),
     "mluOpIndiceConvolutionBackwardFilterFromTable": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _szt, _i64p, _i64,
                                                             _i64, _vp, _szt, _vp, _vp]),
     "mluOpGetVoxelizationWorkspaceSize": (_int, [_vp, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32,

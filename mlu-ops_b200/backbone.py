@@ -420,6 +420,23 @@ class SparseNetwork:
                                                                    d_w, _vp(dw.data_ptr())))
             filter_grads[li] = dw
             dx = torch.empty((L, ly.ci), dtype=grad.dtype, device=self.device)
+            centred = ly.sub_m and all(s == 1 for s in ly.stride) and all(d == 1 for d in ly.dilation) and all(
+                k % 2 == 1 and p == k // 2 for k, p in zip(ly.filter_space, ly.pad))
+            if reuse_tables and K <= 128 and centred and getattr(rb, "table", None) is not None:
+                # a centred submanifold rulebook is symmetric: its forward table, offsets mirrored, is its
+                # input table (where the tensor-memory kernel runs; NOT_SUPPORTED otherwise)
+                ops.check("mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize",
+                          lib.mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize(
+                              h, d_g, d_w, d_p, d_f, self.num_i64, 0, ctypes.byref(self.size)))
+                ws = self.workspace.get(self.size.value)
+                st = lib.mluOpIndiceConvolutionBackwardDataFromForwardTable(
+                    h, d_g, _vp(grad.data_ptr()), d_w, _vp(w.data_ptr()), d_p, _vp(rb.table.data_ptr()),
+                    rb.table.numel() * 4, self.num_i64, 0, ly.sub_m, _vp(ws.data_ptr()), self.size.value, d_f,
+                    _vp(dx.data_ptr()))
+                if st != ops.STATUS_NOT_SUPPORTED:
+                    ops.check("mluOpIndiceConvolutionBackwardDataFromForwardTable", st)
+                    grad = dx
+                    continue
             if reuse_tables and K <= 128:
                 if getattr(rb, "input_table", None) is None:
                     size = ctypes.c_size_t(0)

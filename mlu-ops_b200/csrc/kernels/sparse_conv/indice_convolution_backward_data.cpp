@@ -448,4 +448,64 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardDataFromTable(
   return MLUOP_STATUS_SUCCESS;
 }
 
+// The input gradient of a SUBMANIFOLD layer with centred padding straight from the rulebook's
+// FORWARD table (the one the forward convolutions run from): its pairs are symmetric, (i, o) at
+// offset k goes with (o, i) at offset K-1-k, so the kernel reads the forward table with the
+// offsets mirrored and no table of the opposite direction is ever built.  The caller vouches
+// for the geometry (stride 1, dilation 1, odd kernel extents, pad = extent / 2: what
+// mluOpGetIndicePairsWithNeighbourTable accepts).  Only the tensor-memory kernel reads a table
+// this way: other shapes are MLUOP_STATUS_NOT_SUPPORTED before anything is enqueued, and the
+// caller uses mluOpIndiceConvolutionBackwardDataFromTable with an input table.  Workspace as for
+// that entry point.
+mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardDataFromForwardTable(
+    mluOpHandle_t handle, const mluOpTensorDescriptor_t output_grad_desc, const void *output_grad,
+    const mluOpTensorDescriptor_t filters_desc, const void *filters,
+    const mluOpTensorDescriptor_t indice_pairs_desc, const void *table, const size_t table_size,
+    const int64_t indice_num[], const int64_t inverse, const int64_t sub_m, void *workspace,
+    const size_t workspace_size, const mluOpTensorDescriptor_t input_grad_desc, void *input_grad) {
+  const std::string api = "[mluOpIndiceConvolutionBackwardDataFromForwardTable]";
+  bool is_zero = false;
+  mluOpStatus_t st = foolCheckNoPtr(api, handle, output_grad_desc, filters_desc, indice_pairs_desc, indice_num,
+                                    inverse, sub_m, input_grad_desc, &is_zero);
+  if (st != MLUOP_STATUS_SUCCESS) return st;
+  if (is_zero) return MLUOP_STATUS_SUCCESS;
+  PARAM_CHECK(api, output_grad != nullptr);
+  PARAM_CHECK(api, filters != nullptr);
+  PARAM_CHECK(api, table != nullptr);
+  PARAM_CHECK(api, input_grad != nullptr);
+  PARAM_CHECK(api, workspace != nullptr);
+  PARAM_CHECK(api, reinterpret_cast<size_t>(table) % 16 == 0);  // read 16 bytes at a time
+  PARAM_CHECK(api, sub_m == 1);  // only a submanifold rulebook is symmetric
+  ConvProblem p = makeProblem(handle, output_grad_desc, filters_desc, input_grad_desc);
+  PARAM_CHECK(api, p.L == p.n_out);
+  p.mirror_table = 1;
+  if (!mluop::sparse_conv::neighbourTableCountsFit(p.K) ||
+      !mluop::sparse_conv::convRunsOnTensorMemory(p, output_grad, input_grad)) {
+    // an answer, not an error: callers try this entry point first
+    VLOG(5) << api << " only the tensor-memory kernel (half, channel counts that are multiples of 8 up to 128, "
+            << "16-byte aligned rows, kernel volume up to 128) reads a mirrored table.";
+    return MLUOP_STATUS_NOT_SUPPORTED;
+  }
+  const ConvWorkspacePlan plan = mluop::sparse_conv::planConvWorkspace(p, true);
+  const size_t need = mluop::sparse_conv::neighbourTableBytes(p);
+  if (workspace_size < plan.total || table_size < need) {
+    LOG(ERROR) << api << " workspace (" << workspace_size << " of " << plan.total << " bytes) or table ("
+               << table_size << " of " << need << " bytes) is smaller than the size queries report.";
+    return MLUOP_STATUS_BAD_PARAM;
+  }
+  if (handle->host_only) {
+    LOG(ERROR) << api << " this handle was created without a CUDA device; nothing can be launched.";
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  if (mluop::takeStickyDeviceError(handle, std::string(api).c_str())) return MLUOP_STATUS_EXECUTION_FAILED;
+  cudaError_t err = mluop::sparse_conv::launchIndiceConvolutionSteps(
+      p, plan, output_grad, filters, nullptr, indice_num, workspace, input_grad, handle->sm_count, handle->queue,
+      const_cast<int32_t *>(static_cast<const int32_t *>(table)), mluop::sparse_conv::kTableConvolveOnly);
+  if (err != cudaSuccess) {
+    LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  return MLUOP_STATUS_SUCCESS;
+}
+
 }  // extern "C"

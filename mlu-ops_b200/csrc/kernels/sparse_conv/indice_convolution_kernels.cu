@@ -470,6 +470,19 @@ bool mmaEligible(const ConvProblem &p, const void *features, const void *out) {
 
 }  // namespace
 
+bool convRunsOnTensorMemory(const ConvProblem &caller, const void *rows_in, const void *rows_out) {
+  static const char *forced = std::getenv("MLUOP_B200_CONV_KERNEL");
+  if (forced && (std::strcmp(forced, "mma") == 0 || std::strcmp(forced, "fma") == 0)) return false;
+  ConvProblem p = caller;
+  if (caller.backward_data) {  // the rows that are gathered / produced, whichever direction runs
+    p.L = caller.n_out;
+    p.n_out = caller.L;
+    p.ci = caller.co;
+    p.co = caller.ci;
+  }
+  return tcgen05Eligible(p, rows_in, rows_out);
+}
+
 size_t neighbourTableBytes(const ConvProblem &p) {
   const int64_t rows_out = p.backward_data ? p.L : p.n_out;
   const int64_t n_pad = (rows_out + kConvPadRows - 1) / kConvPadRows * kConvPadRows;
@@ -558,10 +571,10 @@ cudaError_t launchIndiceConvolutionSteps(const ConvProblem &caller, const ConvWo
   // Half with channel counts that are multiples of 8 up to 128 runs on the tcgen05 tensor
   // cores (odd counts at the next of 16/32/64/128, zero padded); MLUOP_B200_CONV_KERNEL=mma
   // selects the mma.sync variant instead (kept for cross-checking), =fma the plain FMA kernels.
+  const bool use_tc = do_conv && convRunsOnTensorMemory(caller, features, features_out);
   static const char *forced = std::getenv("MLUOP_B200_CONV_KERNEL");
-  const bool force_mma = forced && std::strcmp(forced, "mma") == 0;
   const bool force_fma = forced && std::strcmp(forced, "fma") == 0;
-  const bool use_tc = do_conv && !force_mma && !force_fma && tcgen05Eligible(p, features, features_out);
+  if (do_conv && caller.mirror_table && !use_tc) return cudaErrorNotSupported;
 
   // 1. filter -> [K][Co][Ci] (channel counts padded for the tensor-core kernel) and
   // 2. the neighbour table filled with -1; one launch does both when the call needs both

@@ -33,6 +33,11 @@ struct ConvProblem {
   //    computation with the two row sets, the two ids of a pair and the two
   //    channel axes of the filter exchanged.
   int32_t backward_data;
+  // 1 (input gradient from a caller's table only): the table is the FORWARD table of a submanifold
+  // rulebook with centred padding, whose pairs are symmetric - (i, o) at offset k goes with (o, i)
+  // at offset K-1-k - so the output row input row i feeds through offset k stands in forward table
+  // row K-1-k at column i.  Only the tensor-memory kernel reads a table this way.
+  int32_t mirror_table;
   // Device-visible host word (or null) that a kernel's error path stores its error
   // bits into, so that the next entry point on the handle can report them.
   int32_t *sticky_status;
@@ -51,6 +56,10 @@ struct ConvWorkspacePlan {
 // external_table: the neighbour table lives in a buffer of the caller (see
 // launchIndiceConvolutionSteps), the workspace holds the rest.
 ConvWorkspacePlan planConvWorkspace(const ConvProblem &p, bool external_table = false);
+
+// Whether the convolution of this problem (either direction) and these row arrays runs on the
+// tensor-memory kernel (the only one that reads a mirrored table).
+bool convRunsOnTensorMemory(const ConvProblem &p, const void *rows_in, const void *rows_out);
 
 // Bytes of a neighbour table int32[K][n_pad] for this problem and direction.
 size_t neighbourTableBytes(const ConvProblem &p);

@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(kThreads)
 convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict__ filter_image,
                   const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, int ci_real, int co_real,
                   __half *__restrict__ out, int32_t *status_word, int32_t *sticky, long long wait_limit,
-                  int test_drop_release) {
+                  int test_drop_release, int mirror) {
   using Cfg = TcConfig<CI, CO>;
   constexpr int S = Cfg::kAStages, NB = Cfg::kBBuffers, T = Cfg::kTiles;
   constexpr int CPR = Cfg::kChunksPerRow;  // 16-byte chunks per feature row
@@ -165,7 +165,11 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     for (int u = 0; u < 8; ++u) {
       const int e = e0 + u * (kThreads / 32);
       v[u] = make_int4(-1, -1, -1, -1);
-      if (e < K * T) v[u] = __ldg(reinterpret_cast<const int4 *>(nbr + (size_t)(e / T) * n_pad + row0 + (e % T) * kTile) + lane);
+      // (mirror: offset k reads table row K-1-k, see launchConvTcgen05)
+      if (e < K * T) {
+        const int row_k = mirror ? K - 1 - e / T : e / T;
+        v[u] = __ldg(reinterpret_cast<const int4 *>(nbr + (size_t)row_k * n_pad + row0 + (e % T) * kTile) + lane);
+      }
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -226,14 +230,14 @@ convTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict_
     int idx_next = -1;
     if (n_items > 0) {
       const unsigned c0 = items_s[0];
-      idx_next = __ldg(nbr_rows + (size_t)itemOffset(c0) * n_pad + itemTile(c0) * kTile);
+      idx_next = __ldg(nbr_rows + (size_t)(mirror ? K - 1 - itemOffset(c0) : itemOffset(c0)) * n_pad + itemTile(c0) * kTile);
     }
     for (int it = 0; it < n_items; ++it) {
       const unsigned code = items_s[it];
       const int idx = idx_next;
       if (it + 1 < n_items) {
         const unsigned c1 = items_s[it + 1];
-        idx_next = __ldg(nbr_rows + (size_t)itemOffset(c1) * n_pad + itemTile(c1) * kTile);
+        idx_next = __ldg(nbr_rows + (size_t)(mirror ? K - 1 - itemOffset(c1) : itemOffset(c1)) * n_pad + itemTile(c1) * kTile);
       }
       if (it >= S) {
         if (!mbarWaitWarp(&a_empty[s], a_parity ^ 1u, abort_flag, status, 1, wait_limit)) break;
@@ -411,7 +415,7 @@ cudaError_t launchTc(const ConvProblem &p, const ConvWorkspacePlan &plan, const 
     }
   }
   kernel<<<blocks, kThreads, smem, stream>>>(features, filter, nbr, p.n_out, plan.n_pad, p.K, p.ci, p.co, out, status,
-                                             p.sticky_status, wait_limit, test_drop_release);
+                                             p.sticky_status, wait_limit, test_drop_release, p.mirror_table);
   return cudaGetLastError();
 }
 

@@ -307,6 +307,31 @@ def test_gradient_table_entry_points_argument_checks(ops, handle):
     inv = list(args)
     inv[9] = 1
     assert lib.mluOpIndiceConvolutionBackwardDataFromTable(*inv) == ops.STATUS_NOT_SUPPORTED
+    # the input gradient of a centred submanifold layer from its FORWARD table, offsets mirrored
+    assert lib.mluOpIndiceConvolutionBackwardDataFromForwardTable(*args) == ops.STATUS_BAD_PARAM  # sub_m must be 1
+    sub = list(args)
+    sub[10] = 1
+    # float tensors are not the tensor-memory kernel's: an answer, the caller uses the input table
+    assert lib.mluOpIndiceConvolutionBackwardDataFromForwardTable(*sub) == ops.STATUS_NOT_SUPPORTED
+    for i in (0, 1, 2, 3, 4, 5, 6, 8, 11, 13, 14):
+        a = list(sub)
+        a[i] = None
+        assert lib.mluOpIndiceConvolutionBackwardDataFromForwardTable(*a) == ops.STATUS_BAD_PARAM, i
+    hd = [ops.TensorDesc(ARRAY, F16, (10, 16)), ops.TensorDesc(HWCN, F16, (3, 3, 24, 16)),
+          ops.TensorDesc(ARRAY, I32, (9, 2, 10)), ops.TensorDesc(ARRAY, F16, (10, 24))]
+    hws = ctypes.c_size_t(0)
+    assert lib.mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize(handle.ptr, hd[0].ptr, hd[1].ptr, hd[2].ptr,
+                                                                           hd[3].ptr, num, 0, ctypes.byref(hws)) == 0
+    hbuf = (ctypes.c_char * (hws.value + 64))()
+    hwp = VP((ctypes.addressof(hbuf) + 15) // 16 * 16)
+    half = [handle.ptr, hd[0].ptr, p, hd[1].ptr, p, hd[2].ptr, p, size.value, num, 0, 1, hwp, hws.value, hd[3].ptr, p]
+    assert lib.mluOpIndiceConvolutionBackwardDataFromForwardTable(*half) == ops.STATUS_EXECUTION_FAILED  # host-only
+    rows = list(half)
+    bad_rows = ops.TensorDesc(ARRAY, F16, (11, 16))  # a submanifold layer has as many output as input rows
+    rows[1] = bad_rows.ptr
+    assert lib.mluOpIndiceConvolutionBackwardDataFromForwardTable(*rows) == ops.STATUS_BAD_PARAM
+    for d in hd + [bad_rows]:
+        d.destroy()
     # the filter gradient from the forward table: float tensors are not the kernel's, half 64 -> 64 are
     fdescs = [ops.TensorDesc(*BF_GOOD[k]) for k in ("features", "output_grad", "pairs", "filters_grad")]
     d_f, d_og, d_fp, d_fw = (d.ptr for d in fdescs)

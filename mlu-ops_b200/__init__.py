@@ -496,7 +496,8 @@ def indice_convolution_forward(handle, features, filters, filter_layout, filter_
 
 
 def indice_convolution_backward_data(handle, output_grad, filters, filter_layout, indice_pairs,
-                                     indice_num_host, sub_m, workspace=None, out=None, table=None):
+                                     indice_num_host, sub_m, workspace=None, out=None, table=None,
+                                     forward_table=None):
     """input_grad [L, Ci] through mluOpIndiceConvolutionBackwardData.
 
     output_grad [N_out,Co] and filters (4-D or 5-D, in `filter_layout`: ARRAY, HWCN,
@@ -504,6 +505,9 @@ def indice_convolution_backward_data(handle, output_grad, filters, filter_layout
     last dimension; indice_num_host is a sequence of K ints.  table: the rulebook's input
     neighbour table (build_input_neighbour_table); with it the call is
     mluOpIndiceConvolutionBackwardDataFromTable and indice_pairs only gives the shapes.
+    forward_table: the FORWARD table of a submanifold rulebook with centred padding; tried first
+    (mluOpIndiceConvolutionBackwardDataFromForwardTable), NOT_SUPPORTED falls through to the rest;
+    a callable is called for `table` only then.
     """
     import torch
     n_out, co = output_grad.shape
@@ -525,6 +529,22 @@ def indice_convolution_backward_data(handle, output_grad, filters, filter_layout
     d_o = TensorDesc(LAYOUT_ARRAY, dt, (L, ci))
     num = i64_array(indice_num_host)
     size = _szt(0)
+    if forward_table is not None and sub_m:
+        check("mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize",
+              lib().mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize(handle.ptr, d_g.ptr, d_w.ptr, d_p.ptr,
+                                                                                d_o.ptr, num, 0, ctypes.byref(size)))
+        if workspace is None or workspace.numel() < size.value:
+            workspace = _alloc((max(size.value, 1),), torch.uint8, dev)
+        st = lib().mluOpIndiceConvolutionBackwardDataFromForwardTable(
+            handle.ptr, d_g.ptr, _ptr(output_grad), d_w.ptr, _ptr(filters), d_p.ptr, _ptr(forward_table),
+            forward_table.numel() * 4, num, 0, 1, _ptr(workspace), size.value, d_o.ptr, _ptr(out))
+        if st != STATUS_NOT_SUPPORTED:
+            check("mluOpIndiceConvolutionBackwardDataFromForwardTable", st)
+            for d in (d_g, d_w, d_p, d_o):
+                d.destroy()
+            return out
+    if callable(table):
+        table = table()
     if table is not None:
         check("mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize",
               lib().mluOpGetIndiceConvolutionBackwardDataFromTableWorkspaceSize(handle.ptr, d_g.ptr, d_w.ptr, d_p.ptr,
@@ -554,7 +574,8 @@ def indice_convolution_backward_data(handle, output_grad, filters, filter_layout
 
 
 def indice_convolution_backward_filter(handle, features, output_grad, filter_space, indice_pairs,
-                                       indice_num_host, sub_m, workspace=None, out=None, table=None):
+                                       indice_num_host, sub_m, workspace=None, out=None, table=None,
+                                     forward_table=None):
     """filters_grad [kd,kh,kw,Ci,Co] through mluOpIndiceConvolutionBackwardFilter.
 
     features [L,Ci] and output_grad [N_out,Co] are CUDA tensors of the same dtype;

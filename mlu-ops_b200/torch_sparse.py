@@ -119,7 +119,8 @@ class _IndiceConvFunction(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             grad_features = ops.indice_convolution_backward_data(h, grad_out, weight, "ARRAY", rb.indice_pairs,
                                                                  rb.indice_num, rb.sub_m,
-                                                                 table=rb.backward_table(h))
+                                                                 table=lambda: rb.backward_table(h),
+                                                                 forward_table=rb.forward_table(h) if rb.sub_m else None)
         return grad_features, grad_weight, None
 
 

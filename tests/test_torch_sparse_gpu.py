@@ -171,7 +171,8 @@ def test_layers_that_share_a_rulebook_run_from_its_tables_bit_identically(sp):
         y.features.backward(torch.randn(y.features.shape, generator=gen, device="cuda").half())
         if key is not None:
             rb = x.indice_dict[key]
-            assert rb.table is not None and rb.input_table is not None
+            # forward table kept; the input gradients read it mirrored, so no input table was ever built
+            assert rb.table is not None and getattr(rb, "input_table", None) is None
         results.append((y.features.detach(), feat.grad, l1.weight.grad, l2.weight.grad))
     for a, b in zip(*results):
         assert torch.equal(a, b)

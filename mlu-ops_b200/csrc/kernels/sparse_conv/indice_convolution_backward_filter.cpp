@@ -141,6 +141,32 @@ FilterGradProblem makeProblem(const mluOpTensorDescriptor_t features_desc,
   return p;
 }
 
+// The tensor-memory kernel records a bounded wait that gave up in a status word of the workspace
+// (and in the handle's sticky word).  MLUOP_B200_CHECK_STATUS=1 makes the call wait for the
+// stream and report it itself (debugging and tests).
+mluOpStatus_t reportKernelStatus(const std::string &api, mluOpHandle_t handle, const FilterGradProblem &p,
+                                 const FilterGradWorkspacePlan &plan, const void *features, const void *output_grad,
+                                 const void *workspace) {
+  if (!mluop::checkStatusRequested() ||
+      !mluop::sparse_conv::filterGradRunsFromTable(p, plan, features, output_grad)) {
+    return MLUOP_STATUS_SUCCESS;
+  }
+  int32_t word = 0;
+  const char *base = reinterpret_cast<const char *>((reinterpret_cast<size_t>(workspace) + 255) / 256 * 256);
+  cudaError_t err = cudaMemcpyAsync(&word, base + plan.tc_status, sizeof(word), cudaMemcpyDeviceToHost, handle->queue);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(handle->queue);
+  if (err != cudaSuccess) {
+    LOG(ERROR) << api << " execution failed: " << cudaGetErrorString(err);
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  if (word != 0) {
+    handle->host_words[mluOpContext::kStickyWord] = 0;  // reported here; not again by the next call
+    LOG(ERROR) << api << " device reported error bits " << word << " (a bounded wait gave up).";
+    return MLUOP_STATUS_EXECUTION_FAILED;
+  }
+  return MLUOP_STATUS_SUCCESS;
+}
+
 }  // namespace
 
 extern "C" {
@@ -212,7 +238,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilter(
     LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
-  return MLUOP_STATUS_SUCCESS;
+  return reportKernelStatus(api, handle, p, plan, features, output_grad, workspace);
 }
 
 // ---- neighbour-table fast path (no counterpart in the reference) -------------
@@ -280,7 +306,7 @@ mluOpStatus_t MLUOP_WIN_API mluOpIndiceConvolutionBackwardFilterFromTable(
     LOG(ERROR) << api << " launch failed: " << cudaGetErrorString(err);
     return MLUOP_STATUS_EXECUTION_FAILED;
   }
-  return MLUOP_STATUS_SUCCESS;
+  return reportKernelStatus(api, handle, p, plan, features, output_grad, workspace);
 }
 
 }  // extern "C"

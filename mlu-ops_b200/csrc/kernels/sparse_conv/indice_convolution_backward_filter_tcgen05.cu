@@ -159,7 +159,8 @@ template <int CI, int CO>
 __global__ void __launch_bounds__(kThreads, 1)
 filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__restrict__ output_grad,
                         const int32_t *__restrict__ nbr, int64_t n_out, int64_t n_pad, int K, int bundles_per_group,
-                        int blocks_per_group, float *__restrict__ partial, int32_t *status_word, int32_t *sticky, long long wait_limit) {
+                        int blocks_per_group, float *__restrict__ partial, int32_t *status_word, int32_t *sticky, long long wait_limit,
+                        int test_drop_release) {
   using Cfg = GradTcConfig<CI, CO>;
   using ATile = typename Cfg::A;
   using GTile = typename Cfg::G;
@@ -373,7 +374,9 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
                    (((started >> q) & 1u) || j > 0) ? 1u : 0u);
             }
             started |= 1u << q;
-            ummaCommit(&a_empty[s]);
+            // the stage may be refilled once these MMAs have read it (test hook: the first issuer's first
+            // release is withheld, so that the producers' wait for that stage runs out)
+            if (!(test_drop_release && me == 0 && my_items == 0)) ummaCommit(&a_empty[s]);
             ++my_items;
           }
           ++items;
@@ -440,9 +443,22 @@ cudaError_t launchGradTc(const FilterGradProblem &p, const FilterGradTcPlan &pla
   if (err != cudaSuccess) return err;
   static const std::string name = "filterGradTcgen05Kernel<" + std::to_string(CI) + "," + std::to_string(CO) + ">";
   trace::Scope t(name.c_str(), stream, bytes, flops);
+  // Test hook: MLUOP_B200_TEST_FILTER_GRAD_WAIT=<cycles> gives every wait that limit and withholds one
+  // stage release per block, so that the producers' bounded wait runs out: the kernel must record the
+  // error, leave through its common exit (copies drained, MMAs seen out, tensor memory freed) and
+  // return.  Nothing faults or spins on.
+  long long wait_limit = kWaitCycles;
+  int test_drop_release = 0;
+  if (const char *hook = std::getenv("MLUOP_B200_TEST_FILTER_GRAD_WAIT")) {
+    const long long cycles = std::atoll(hook);
+    if (cycles > 0) {
+      wait_limit = cycles;
+      test_drop_release = 1;
+    }
+  }
   kernel<<<(unsigned)(plan.groups * plan.blocks_per_group), kThreads, Cfg::kSmemBytes, stream>>>(
       features, output_grad, nbr, p.n_out, plan.n_pad, p.K, plan.bundles_per_group, plan.blocks_per_group, partial,
-      status, p.sticky_status, kWaitCycles);
+      status, p.sticky_status, wait_limit, test_drop_release);
   return cudaGetLastError();
 }
 

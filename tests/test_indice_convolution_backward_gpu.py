@@ -247,3 +247,27 @@ def test_rows_that_start_one_element_off_an_aligned_address(ops, oracle, gpu_han
     got = ops.indice_convolution_backward_filter(gpu_handle, off_by_one(feat), off_by_one(og), ks, d_pairs, nums, 1)
     ref = r(oracle.indice_convolution_backward_filter(f32(feat), f32(og), ks, pairs, num))
     assert_close(oracle, got.float().cpu().numpy().reshape(ref.shape), ref, is_half)
+
+
+def test_a_filter_gradient_wait_that_runs_out_is_reported_and_the_context_survives(ops, oracle, gpu_handle, monkeypatch):
+    """Failure detection on the device without a fault, for the tensor-memory filter gradient: the test
+    hook gives its waits a limit of about a millisecond and withholds one stage release per block, so
+    the producers' wait for that stage runs out.  The kernel must record the error, leave through its
+    common exit (copies drained, MMAs seen out, tensor memory freed) and return: the call reports
+    MLUOP_STATUS_EXECUTION_FAILED, and the same call without the hook then gives the right answer on
+    the same context."""
+    rng = np.random.default_rng(13)
+    space = [6, 10, 10]
+    n = 2 * 6 * 10 * 10  # fully occupied: every tile is live at every offset, more items than ring stages
+    pairs, num, n_out, feat, og, w = make_case(oracle, rng, 2, space, n, [3] * 3, [1] * 3, [1] * 3, 1, 64, 64,
+                                               np.float16)
+    monkeypatch.setenv("MLUOP_B200_TEST_FILTER_GRAD_WAIT", "2000000")
+    with pytest.raises(ops.MluOpError) as err:
+        gpu_backward_filter(ops, gpu_handle, feat, og, [3] * 3, pairs, num, 1)
+    assert err.value.status == ops.STATUS_EXECUTION_FAILED
+    monkeypatch.delenv("MLUOP_B200_TEST_FILTER_GRAD_WAIT")
+    ref = oracle.round_through_half(oracle.indice_convolution_backward_filter(
+        feat.astype(np.float32), og.astype(np.float32), [3] * 3, pairs, num))
+    for _ in range(2):  # tensor memory was freed: later launches get their columns and compute correctly
+        got = gpu_backward_filter(ops, gpu_handle, feat, og, [3] * 3, pairs, num, 1)
+        assert_close(oracle, got.reshape(ref.shape), ref, True)

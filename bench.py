@@ -112,6 +112,9 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
 
 
+# Folder (under the repository root) for the files a diagnostic run writes.
+OUT_DIR = os.environ.get("BENCH_OUT_DIR", "gpurun_out")
+
 # Size of the pieces in which the end-to-end steps copy their results to the host.  The rulebook
 # counts the host waits for reach it as stores of a kernel over the same PCIe link, behind whatever
 # piece is on its way: 1 MiB keeps that delay at 20-60 us (measured: 4.37 ms per step with 4 MiB
@@ -512,8 +515,8 @@ def run_b200(args):
                              "max": round(max(sums["d2h"] or [0]), 4), "bytes": int(d2h[0])}}
         net.timers = None
         copy_events = None
-        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-        with open(os.path.join(ROOT, "gpurun_out", "e2e_breakdown_rank%d_of_%d.json" % (rank, world)), "w") as f:
+        os.makedirs(os.path.join(ROOT, OUT_DIR), exist_ok=True)
+        with open(os.path.join(ROOT, OUT_DIR, "e2e_breakdown_rank%d_of_%d.json" % (rank, world)), "w") as f:
             json.dump(report, f)
 
     # traced pass: per-kernel durations (CUDA events around every launch) and launch counts
@@ -1158,7 +1161,8 @@ def main():
     ap.add_argument("--no-pin-cores", action="store_true",
                     help="N>1: do not bind each rank to the cores local to its GPU")
     ap.add_argument("--e2e-breakdown", action="store_true",
-                    help="also write gpurun_out/e2e_breakdown_rank<r>.json: where each rank's end-to-end step spends "
+                    help="also write e2e_breakdown_rank<r>_of_<n>.json into the output folder (BENCH_OUT_DIR): where "
+                         "each rank's end-to-end step spends "
                          "its host time (rulebook waits, library calls, copies) and how long its copies take")
     ap.add_argument("--pipeline", action="store_true",
                     help="generate the rulebooks of batch i+1 during the convolutions of batch i instead of inside "

@@ -170,7 +170,11 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
   extern __shared__ unsigned char smem_raw[];
   unsigned char *a_ring = reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
   unsigned char *g_ring = a_ring + (size_t)S * Cfg::kAStageBytes;
-  __shared__ unsigned long long a_full[S], a_empty[S], g_full[NG], g_empty[NG], accum_bar, drain_bar[kIssuers];
+  // a_full: one set of barriers per issuer.  An mbarrier wait names a phase by its parity only, so a
+  // waiter must see every phase of a barrier: an issuer that waited on a stage only when the item in it
+  // is its own would skip phases and take a stage that is still being filled for one that is ready.
+  // The producers arrive on the barrier of the issuer that owns the item.
+  __shared__ unsigned long long a_full[kIssuers][S], a_empty[S], g_full[NG], g_empty[NG], accum_bar, drain_bar[kIssuers];
   __shared__ unsigned tmem_base_s;
   __shared__ int abort_s;
 
@@ -183,7 +187,7 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
-      mbarInit(&a_full[s], kProducerThreads);
+      for (int i = 0; i < kIssuers; ++i) mbarInit(&a_full[i][s], kProducerThreads);
       mbarInit(&a_empty[s], 1);
     }
     for (int g = 0; g < NG; ++g) {
@@ -298,7 +302,7 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
                       valid);
           }
         }
-        cpAsyncArriveOn(&a_full[s]);
+        cpAsyncArriveOn(&a_full[q % kIssuers][s]);
         ++items;
         if (++s == S) {
           s = 0;
@@ -343,7 +347,8 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
     const unsigned long long g_desc0 = makeDescMn<GTile>(smemAddr(g_ring), GTile::kTileBytes);
     unsigned started = 0u;  // bundles whose accumulator has been written
     int s = 0;
-    unsigned a_parity = 0, items = 0, my_items = 0;  // items: all of the block's, my_items: this issuer's
+    unsigned items = 0, my_items = 0;  // items: all of the block's, my_items: this issuer's
+    unsigned my_phase = 0u;  // bit s: parity of the next phase of a_full[me][s]
     bool ok = true;
     int64_t n_mine = 0;
     int4 vote_next[OPG];
@@ -358,7 +363,8 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
         for (int q = 0; q < Cfg::kBundlesPerGroup && ok; ++q) {
           if (!((live >> (q * OPB)) & ((1u << OPB) - 1u))) continue;
           if (q % kIssuers == me) {
-            if (!mbarWait(&a_full[s], a_parity, abort_flag, status, kErrIssuerStage, wait_limit)) {
+            // the phase of MY barrier of this stage: it advances only when an item of mine uses the stage
+            if (!mbarWait(&a_full[me][s], (my_phase >> s) & 1u, abort_flag, status, kErrIssuerStage, wait_limit)) {
               ok = false;
               break;
             }
@@ -374,16 +380,14 @@ filterGradTcgen05Kernel(const __half *__restrict__ features, const __half *__res
                    (((started >> q) & 1u) || j > 0) ? 1u : 0u);
             }
             started |= 1u << q;
+            my_phase ^= 1u << s;
             // the stage may be refilled once these MMAs have read it (test hook: the first issuer's first
             // release is withheld, so that the producers' wait for that stage runs out)
             if (!(test_drop_release && me == 0 && my_items == 0)) ummaCommit(&a_empty[s]);
             ++my_items;
           }
           ++items;
-          if (++s == S) {
-            s = 0;
-            a_parity ^= 1u;
-          }
+          if (++s == S) s = 0;
         }
         // the tile's output_grad rows are free once both issuers' MMAs issued so far are done
         if (ok) ummaCommit(&g_empty[g]);

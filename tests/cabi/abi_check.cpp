@@ -69,6 +69,24 @@ int main() {
                                              0) != MLUOP_STATUS_SUCCESS);
   EXPECT(mluOpGetIndicePairs(handle, conv, nullptr, p, p, 64, pairs, p, out, p, features, p) == MLUOP_STATUS_BAD_PARAM);
 
+  // the neighbour-table extensions: declared for C callers too, same conventions
+  size_t table_size = 0;
+  EXPECT(mluOpGetIndiceNeighbourTableSize(handle, pairs, 9, &table_size) == MLUOP_STATUS_SUCCESS && table_size > 0);
+  EXPECT(mluOpGetIndiceInputNeighbourTableSize(handle, pairs, &table_size) == MLUOP_STATUS_SUCCESS && table_size > 0);
+  EXPECT(mluOpBuildIndiceNeighbourTable(nullptr, pairs, p, indice_num, 9, p, table_size) == MLUOP_STATUS_BAD_PARAM);
+  EXPECT(mluOpBuildIndiceInputNeighbourTable(nullptr, pairs, p, indice_num, 9, p, table_size) == MLUOP_STATUS_BAD_PARAM);
+  EXPECT(mluOpIndiceConvolutionForwardFromTable(nullptr, features, p, filters, p, pairs, p, table_size, indice_num, 9, 0,
+                                                0, p, 64, out, p) == MLUOP_STATUS_BAD_PARAM);
+  EXPECT(mluOpIndiceConvolutionBackwardDataFromTable(nullptr, out, p, filters, p, pairs, p, table_size, indice_num, 0, 0,
+                                                     p, 64, features, p) == MLUOP_STATUS_BAD_PARAM);
+  EXPECT(mluOpIndiceConvolutionBackwardDataFromForwardTable(nullptr, out, p, filters, p, pairs, p, table_size,
+                                                            indice_num, 0, 1, p, 64, features, p) ==
+         MLUOP_STATUS_BAD_PARAM);
+  EXPECT(mluOpIndiceConvolutionBackwardFilterFromTable(nullptr, features, p, out, p, pairs, p, table_size, indice_num,
+                                                       0, 0, p, 64, filters, p) == MLUOP_STATUS_BAD_PARAM);
+  EXPECT(mluOpGetIndicePairsWithNeighbourTable(handle, conv, nullptr, p, p, 64, pairs, p, out, p, features, p, p,
+                                               table_size) == MLUOP_STATUS_BAD_PARAM);
+
   EXPECT(mluOpDestroySparseConvolutionDescriptor(conv) == MLUOP_STATUS_SUCCESS);
   EXPECT(mluOpDestroyTensorDescriptor(features) == MLUOP_STATUS_SUCCESS);
   EXPECT(mluOpDestroyTensorDescriptor(filters) == MLUOP_STATUS_SUCCESS);
